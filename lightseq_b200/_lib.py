@@ -1,0 +1,93 @@
+"""ctypes binding of ``libls100.so`` (the C ABI declared in ``include/ls100.h``).
+
+The library is required: importing this module raises if it has not been built
+(``python -m lightseq_b200.build``); there is no CPU or PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libls100.so"
+
+if not LIB_PATH.exists():
+    raise ImportError(
+        f"{LIB_PATH} is missing: build the CUDA library first with `python -m lightseq_b200.build` "
+        "(lightseq_b200 has no fallback path)"
+    )
+
+lib = C.CDLL(str(LIB_PATH), mode=C.RTLD_GLOBAL)
+
+OK = 0
+ERR_BAD_ARG, ERR_ALIGN, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_NO_DRIVER = -1, -2, -3, -4, -5, -6
+
+OUT_OUTQ_I8, OUT_F32, OUT_REQ_S8, OUT_REQ_U8, OUT_F16, OUT_I32 = range(6)
+ACT_NONE, ACT_RELU, ACT_GELU = range(3)
+
+
+class Ls100Error(RuntimeError):
+    def __init__(self, code: int, where: str):
+        self.code = code
+        msg = lib.ls100_strerror(code)
+        super().__init__(f"{where}: {msg.decode() if msg else code} ({code})")
+
+
+def check(code: int, where: str) -> None:
+    if code != 0:
+        raise Ls100Error(code, where)
+
+
+class GemmI8Args(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("lda", C.c_int64),
+        ("w", C.c_void_p), ("ldw", C.c_int64),
+        ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+        ("s_acc", C.c_float),
+        ("w_off", C.c_void_p),
+        ("s_outq", C.c_float),
+        ("bias", C.c_void_p),
+        ("act", C.c_int32),
+        ("resid", C.c_void_p), ("ldr", C.c_int64),
+        ("out_kind", C.c_int32),
+        ("s_req", C.c_float),
+        ("out", C.c_void_p), ("ldo", C.c_int64),
+    ]
+
+
+lib.ls100_strerror.restype = C.c_char_p
+lib.ls100_strerror.argtypes = [C.c_int]
+lib.ls100_ctx_create.restype = C.c_int
+lib.ls100_ctx_create.argtypes = [C.POINTER(C.c_void_p), C.c_int]
+lib.ls100_ctx_destroy.restype = None
+lib.ls100_ctx_destroy.argtypes = [C.c_void_p]
+lib.ls100_ctx_poll_error.restype = C.c_int
+lib.ls100_ctx_poll_error.argtypes = [C.c_void_p, C.c_void_p]
+lib.ls100_sm_count.restype = C.c_int
+lib.ls100_sm_count.argtypes = [C.c_void_p]
+lib.ls100_gemm_i8.restype = C.c_int
+lib.ls100_gemm_i8.argtypes = [C.c_void_p, C.POINTER(GemmI8Args), C.c_void_p]
+
+
+class Context:
+    """Owns one ``ls100_ctx`` for a device."""
+
+    def __init__(self, device: int = 0):
+        h = C.c_void_p()
+        check(lib.ls100_ctx_create(C.byref(h), device), "ls100_ctx_create")
+        self.handle = h
+        self.device = device
+
+    def poll_error(self, stream: int = 0) -> int:
+        return lib.ls100_ctx_poll_error(self.handle, C.c_void_p(stream))
+
+    def close(self):
+        if self.handle:
+            lib.ls100_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

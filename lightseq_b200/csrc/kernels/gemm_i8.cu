@@ -1,0 +1,370 @@
+// int8 x int8 -> int32 GEMM on the 5th-generation tensor cores (tcgen05.mma
+// kind::i8), operands staged by TMA into 128-byte-swizzled shared memory,
+// accumulators in TMEM, fused QuantLinear epilogue.
+//
+// out[M,N] = epilogue(A[M,K] . W[N,K]^T): both operands are K-major, which is
+// the torch Linear weight layout, so no load-time transpose is needed.
+//
+// CTA = one 128 x BN output tile, 6 warps:
+//   warp 0     TMA producer (one elected lane)
+//   warp 1     TMEM allocator + MMA issuer (one elected lane)
+//   warps 2-5  epilogue; warp w reads TMEM lanes 32*(w%4)..+31 (one row per thread)
+// Shared-memory ring of STAGES x (A 128x128 B + W BNx128 B); full/empty
+// mbarriers; tcgen05.commit releases a stage when the MMAs that read it retire.
+// Epilogue overlap comes from two co-resident CTAs per SM for BN <= 128.
+//
+// Every wait is bounded: on expiry the thread records LS100_ERR_TIMEOUT in the
+// context's device error word and falls through to the common exit, where the
+// allocating warp frees TMEM.
+//
+// Epilogue arithmetic restates QuantLinear.forward
+// (lightseq/training/ops/pytorch/quantization.py:50-61) on exact int32
+// accumulators; see include/ls100.h for the per-element recipe.
+#include "common.cuh"
+#include "ctx.h"
+
+namespace ls100 {
+
+struct GemmEpi {
+  int m, n, k;
+  float s_acc, s_outq, s_req;
+  const int32_t* w_off;
+  const float* bias;
+  const float* resid;
+  long long ldr;
+  int act, out_kind;
+  void* out;
+  long long ldo;
+  int* err;
+};
+
+constexpr int BM = 128;
+constexpr int BK = 128;  // bytes == int8 elements per k-block (one 128B swizzle row)
+constexpr int UMMA_K = 32;
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int A_BYTES = BM * BK;
+  static constexpr int B_BYTES = BN * BK;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
+};
+
+// Shared-memory matrix descriptor, K-major, SWIZZLE_128B, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);  // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                   // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                   // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
+  return d;
+}
+
+template <int BN>
+__device__ __forceinline__ constexpr uint32_t make_idesc_i8() {
+  return (2u << 4)      // D format: s32
+         | (1u << 7)    // A: signed 8-bit
+         | (1u << 10)   // B: signed 8-bit
+         | (0u << 15)   // A K-major
+         | (0u << 16)   // B K-major
+         | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void record_timeout(int* err) {
+  if (err) atomicExch(err, (int)LS100_ERR_TIMEOUT);
+}
+
+template <int BN>
+__device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t (&r)[32], int row, int col0) {
+  // 32 consecutive columns of one output row
+  const bool row_ok = row < p.m;
+  const bool full = (col0 + 32 <= p.n);
+  float v[32];
+  float q8[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const int n = col0 + j;
+    int a = (int)r[j];
+    if (p.w_off != nullptr && n < p.n) a += __ldg(p.w_off + n);
+    if (p.out_kind == LS100_OUT_I32) {
+      q8[j] = __int_as_float(a);
+      continue;
+    }
+    float x = __fmul_rn(__int2float_rn(a), p.s_acc);
+    if (p.s_outq > 0.f) {
+      const float q = quant_s(x, p.s_outq);
+      q8[j] = q;
+      x = __fmul_rn(q, p.s_outq);
+    }
+    if (p.bias != nullptr && n < p.n) x = __fadd_rn(x, __ldg(p.bias + n));
+    if (p.act == LS100_ACT_RELU) x = fmaxf(x, 0.f);
+    else if (p.act == LS100_ACT_GELU) x = gelu_erf(x);
+    v[j] = x;
+  }
+  if (!row_ok) return;
+  if (p.resid != nullptr && p.out_kind != LS100_OUT_I32) {
+    const float* rp = p.resid + (long long)row * p.ldr + col0;
+    if (full && ((p.ldr & 3) == 0) && ((((uintptr_t)p.resid) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(rp + j);
+        v[j] = __fadd_rn(v[j], t.x);
+        v[j + 1] = __fadd_rn(v[j + 1], t.y);
+        v[j + 2] = __fadd_rn(v[j + 2], t.z);
+        v[j + 3] = __fadd_rn(v[j + 3], t.w);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.n) v[j] = __fadd_rn(v[j], rp[j]);
+    }
+  }
+  switch (p.out_kind) {
+    case LS100_OUT_F32: {
+      float* op = reinterpret_cast<float*>(p.out) + (long long)row * p.ldo + col0;
+      if (full && ((p.ldo & 3) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(op + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.n) op[j] = v[j];
+      }
+      break;
+    }
+    case LS100_OUT_I32: {
+      int* op = reinterpret_cast<int*>(p.out) + (long long)row * p.ldo + col0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.n) op[j] = __float_as_int(q8[j]);
+      break;
+    }
+    case LS100_OUT_F16: {
+      __half* op = reinterpret_cast<__half*>(p.out) + (long long)row * p.ldo + col0;
+      if (full && ((p.ldo & 7) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          __half2 h0 = __floats2half2_rn(v[j], v[j + 1]), h1 = __floats2half2_rn(v[j + 2], v[j + 3]);
+          __half2 h2 = __floats2half2_rn(v[j + 4], v[j + 5]), h3 = __floats2half2_rn(v[j + 6], v[j + 7]);
+          uint4 u;
+          u.x = *reinterpret_cast<uint32_t*>(&h0);
+          u.y = *reinterpret_cast<uint32_t*>(&h1);
+          u.z = *reinterpret_cast<uint32_t*>(&h2);
+          u.w = *reinterpret_cast<uint32_t*>(&h3);
+          *reinterpret_cast<uint4*>(op + j) = u;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.n) op[j] = __float2half_rn(v[j]);
+      }
+      break;
+    }
+    default: {  // int8 outputs
+      if (p.out_kind == LS100_OUT_REQ_S8) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) q8[j] = quant_s(v[j], p.s_req);
+      } else if (p.out_kind == LS100_OUT_REQ_U8) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) q8[j] = quant_u(v[j], p.s_req);
+      }
+      int8_t* op = reinterpret_cast<int8_t*>(p.out) + (long long)row * p.ldo + col0;
+      if (full && ((p.ldo & 15) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 16) {
+          uint4 u;
+          u.x = pack_i8x4(q8[j], q8[j + 1], q8[j + 2], q8[j + 3]);
+          u.y = pack_i8x4(q8[j + 4], q8[j + 5], q8[j + 6], q8[j + 7]);
+          u.z = pack_i8x4(q8[j + 8], q8[j + 9], q8[j + 10], q8[j + 11]);
+          u.w = pack_i8x4(q8[j + 12], q8[j + 13], q8[j + 14], q8[j + 15]);
+          *reinterpret_cast<uint4*>(op + j) = u;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.n) op[j] = (int8_t)(int)q8[j];
+      }
+      break;
+    }
+  }
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tma_a,
+                                                         const __grid_constant__ CUtensorMap tma_b,
+                                                         const GemmEpi p) {
+  using SM = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full_bar = empty_bar + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.y * BM;
+  const int num_kb = (p.k + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tmem_full_bar, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      uint32_t phase = 0;
+      int s = 0;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
+          record_timeout(p.err);
+          break;
+        }
+        uint8_t* sa = smem + s * SM::STAGE_BYTES;
+        uint8_t* sb = sa + SM::A_BYTES;
+        mbar_expect_tx(&full_bar[s], SM::STAGE_BYTES);
+        tma_load_2d(sa, &tma_a, &full_bar[s], kb * BK, m0);
+        tma_load_2d(sb, &tma_b, &full_bar[s], kb * BK, n0);
+        if (++s == STAGES) {
+          s = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_i8<BN>();
+      uint32_t phase = 0;
+      int s = 0;
+      bool ok = true;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(&full_bar[s], phase)) {
+          record_timeout(p.err);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + s * SM::STAGE_BYTES);
+        const uint64_t adesc = make_smem_desc(sa);
+        const uint64_t bdesc = make_smem_desc(sa + SM::A_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+          // advance 32 bytes along K inside the 128-byte swizzle row: +2 in 16-byte units
+          tc_mma_i8(tmem_base, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
+                    (kb > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&empty_bar[s]);
+        if (++s == STAGES) {
+          s = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok) tc_commit(tmem_full_bar);
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    bool ok = mbar_wait(tmem_full_bar, 0);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) {
+      if (lane == 0) record_timeout(p.err);
+    } else {
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= p.n) break;
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+        tmem_ld_wait();
+        epilogue_chunk<BN>(p, r, row, n0 + c0);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cudaStream_t stream) {
+  using SM = GemmSmem<BN, STAGES>;
+  static bool attr_set[16] = {false};
+  auto kern = gemm_i8_tc_kernel<BN, STAGES>;
+  if (ctx->device < 16 && !attr_set[ctx->device]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL) != cudaSuccess)
+      return LS100_ERR_CUDA;
+    attr_set[ctx->device] = true;
+  }
+  CUtensorMap ta, tb;
+  int rc = ls100_get_tmap_u8(ctx, a->a, (uint64_t)a->m, (uint64_t)a->k, (uint64_t)a->lda, BM, BK, &ta);
+  if (rc) return rc;
+  rc = ls100_get_tmap_u8(ctx, a->w, (uint64_t)a->n, (uint64_t)a->k, (uint64_t)a->ldw, BN, BK, &tb);
+  if (rc) return rc;
+  GemmEpi p;
+  p.m = a->m;
+  p.n = a->n;
+  p.k = a->k;
+  p.s_acc = a->s_acc;
+  p.s_outq = a->s_outq;
+  p.s_req = a->s_req;
+  p.w_off = a->w_off;
+  p.bias = a->bias;
+  p.resid = a->resid;
+  p.ldr = a->ldr;
+  p.act = a->act;
+  p.out_kind = a->out_kind;
+  p.out = a->out;
+  p.ldo = a->ldo;
+  p.err = ctx->d_err;
+  dim3 grid((a->n + BN - 1) / BN, (a->m + BM - 1) / BM);
+  kern<<<grid, 192, SM::TOTAL, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+}
+
+}  // namespace ls100
+
+extern "C" int ls100_gemm_i8(ls100_ctx* ctx, const ls100_gemm_i8_args* a, ls100_stream_t stream_) {
+  using namespace ls100;
+  if (!ctx || !a || !a->a || !a->w || !a->out) return LS100_ERR_BAD_ARG;
+  if (a->m <= 0 || a->n <= 0 || a->k <= 0) return LS100_ERR_BAD_ARG;
+  if ((((uintptr_t)a->a) & 15) || (((uintptr_t)a->w) & 15) || (a->lda & 15) || (a->ldw & 15)) return LS100_ERR_ALIGN;
+  if (a->lda < a->k || a->ldw < a->k) return LS100_ERR_BAD_ARG;
+  if (a->out_kind < LS100_OUT_OUTQ_I8 || a->out_kind > LS100_OUT_I32) return LS100_ERR_BAD_ARG;
+  if (a->out_kind == LS100_OUT_OUTQ_I8 && !(a->s_outq > 0.f)) return LS100_ERR_BAD_ARG;
+  if ((a->out_kind == LS100_OUT_REQ_S8 || a->out_kind == LS100_OUT_REQ_U8) && !(a->s_req > 0.f))
+    return LS100_ERR_BAD_ARG;
+  if (a->resid && a->ldr < a->n) return LS100_ERR_BAD_ARG;
+  if (a->ldo < a->n) return LS100_ERR_BAD_ARG;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const long long mt = (a->m + BM - 1) / BM;
+  auto ctas = [&](int bn) { return mt * ((a->n + bn - 1) / bn); };
+  const long long sms = ctx->sm_count;
+  // Largest tile that still fills the machine; small problems fall to BN=32.
+  if (ctas(256) >= 2 * sms) return launch_gemm<256, 4>(ctx, a, stream);
+  if (ctas(128) >= sms) return launch_gemm<128, 3>(ctx, a, stream);
+  if (ctas(64) >= sms) return launch_gemm<64, 4>(ctx, a, stream);
+  return launch_gemm<32, 4>(ctx, a, stream);
+}

@@ -1,0 +1,235 @@
+"""Seeded synthetic int8 models for benchmarking and testing.
+
+There are no pretrained checkpoints or datasets in the build environment, so the
+benchmark configurations are stated as *shapes plus distributions*: weights
+N(0, 0.02^2), biases 0, LayerNorm gamma 1 / beta 0, sinusoidal positions, and every
+clip-max = 4 x std of the tensor it clips. The std of a weight comes from the weight
+itself; the std of an activation is measured here by one un-quantised fp32
+calibration pass over (a sample of) the seeded inputs — the role the reference gives
+to its calibrators (lightseq/training/pytorch_quantization/calib/). That pass is plain
+fp32 numpy and cannot produce the quantised model's outputs.
+
+Tensor names (shared with the engine's loader):
+  emb [V,H];  enc.{l}.{qkv,out,fc1,fc2}.{w,b};  enc.{l}.ln{1,2}.{g,b};  enc.ln.{g,b}
+  dec.{l}.{qkv,out,xq,xk,xv,xout,fc1,fc2}.{w,b};  dec.{l}.ln{1,2,3}.{g,b};  dec.ln.{g,b}
+Clip-max names: ``<linear>.in`` / ``<linear>.w`` / ``<linear>.out``, ``dec.{l}.kv`` (int8
+self-attention cache), ``emb``, ``logits.in`` / ``logits.out``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+
+F32 = np.float32
+
+
+class _Stats:
+    def __init__(self):
+        self.s: Dict[str, list] = {}
+
+    def see(self, name: str, x: np.ndarray):
+        x = np.asarray(x, dtype=np.float64)
+        a = self.s.setdefault(name, [0.0, 0.0, 0])
+        a[0] += float(x.sum())
+        a[1] += float((x * x).sum())
+        a[2] += x.size
+
+    def amax(self, k: float = 4.0) -> Dict[str, float]:
+        out = {}
+        for name, (s, q, n) in self.s.items():
+            m = s / n
+            out[name] = float(F32(k * math.sqrt(max(q / n - m * m, 1e-12))))
+        return out
+
+
+def sinusoid_table(n: int, dim: int) -> np.ndarray:
+    """Sinusoidal positions as SinusoidalPositionalEmbedding.get_embedding
+    (lightseq/training/ops/pytorch/torch_transformer_layers.py:1086-1106)."""
+    half = dim // 2
+    e = F32(math.log(10000) / (half - 1))
+    freq = np.exp(np.arange(half, dtype=F32) * -e).astype(F32)
+    ang = (np.arange(n, dtype=F32)[:, None] * freq[None, :]).astype(F32)
+    tab = np.concatenate([np.sin(ang), np.cos(ang)], axis=1).astype(F32)
+    if dim % 2 == 1:
+        tab = np.concatenate([tab, np.zeros((n, 1), F32)], axis=1)
+    return tab
+
+
+def _ln(x, g, b):
+    m = x.mean(-1, keepdims=True)
+    v = ((x - m) ** 2).mean(-1, keepdims=True)
+    return ((x - m) / np.sqrt(v + 1e-5) * g + b).astype(F32)
+
+
+def _softmax(s):
+    s = s - s.max(-1, keepdims=True)
+    e = np.exp(s)
+    return e / e.sum(-1, keepdims=True)
+
+
+def _attn(q, k, v, heads, mask):
+    """q [B,Lq,H], k,v [B,Lk,H]; mask broadcastable to [B,heads,Lq,Lk], True = masked."""
+    B, Lq, H = q.shape
+    Lk = k.shape[1]
+    dh = H // heads
+    qh = (q * F32(dh ** -0.5)).reshape(B, Lq, heads, dh).transpose(0, 2, 1, 3)
+    kh = k.reshape(B, Lk, heads, dh).transpose(0, 2, 3, 1)
+    vh = v.reshape(B, Lk, heads, dh).transpose(0, 2, 1, 3)
+    s = np.matmul(qh, kh)
+    if mask is not None:
+        s = np.where(mask, F32(-1e30), s)
+    return np.matmul(_softmax(s), vh).transpose(0, 2, 1, 3).reshape(B, Lq, H).astype(F32)
+
+
+def _act(x, act):
+    if act == "relu":
+        return np.maximum(x, 0)
+    from scipy.special import erf
+
+    return (0.5 * x * (1.0 + erf(x / math.sqrt(2.0)))).astype(F32)
+
+
+def transformer_weights(hidden=512, heads=8, ffn=2048, n_enc=6, n_dec=6, vocab=32000, pad_id=1, seed=1234,
+                        std=0.02) -> Dict[str, np.ndarray]:
+    rng = np.random.default_rng(seed)
+
+    def nrm(*shape):
+        return (rng.standard_normal(shape, dtype=F32) * F32(std)).astype(F32)
+
+    w: Dict[str, np.ndarray] = {}
+    w["emb"] = nrm(vocab, hidden)
+    w["emb"][pad_id] = 0
+    H = hidden
+
+    def lin(name, n_out, n_in):
+        w[name + ".w"] = nrm(n_out, n_in)
+        w[name + ".b"] = np.zeros(n_out, F32)
+
+    def ln(name):
+        w[name + ".g"] = np.ones(H, F32)
+        w[name + ".b"] = np.zeros(H, F32)
+
+    for l in range(n_enc):
+        p = f"enc.{l}"
+        lin(p + ".qkv", 3 * H, H)
+        lin(p + ".out", H, H)
+        lin(p + ".fc1", ffn, H)
+        lin(p + ".fc2", H, ffn)
+        ln(p + ".ln1")
+        ln(p + ".ln2")
+    ln("enc.ln")
+    for l in range(n_dec):
+        p = f"dec.{l}"
+        lin(p + ".qkv", 3 * H, H)
+        lin(p + ".out", H, H)
+        lin(p + ".xq", H, H)
+        lin(p + ".xk", H, H)
+        lin(p + ".xv", H, H)
+        lin(p + ".xout", H, H)
+        lin(p + ".fc1", ffn, H)
+        lin(p + ".fc2", H, ffn)
+        ln(p + ".ln1")
+        ln(p + ".ln2")
+        ln(p + ".ln3")
+    ln("dec.ln")
+    return w
+
+
+def transformer_inputs(batch=128, min_len=20, max_len=60, vocab=32000, pad_id=1, seed=4321) -> np.ndarray:
+    """Source ids [B, max(len)] int32, uniform over [4, vocab), right-padded with ``pad_id``."""
+    rng = np.random.default_rng(seed)
+    lens = rng.integers(min_len, max_len + 1, size=batch)
+    S = int(lens.max())
+    ids = np.full((batch, S), pad_id, dtype=np.int32)
+    for i, n in enumerate(lens):
+        ids[i, :n] = rng.integers(4, vocab, size=n)
+    return ids
+
+
+def calibrate_transformer(w: Dict[str, np.ndarray], src: np.ndarray, *, heads: int, n_enc: int, n_dec: int,
+                          act: str = "relu", pad_id: int = 1, seed: int = 99, k: float = 4.0) -> Dict[str, float]:
+    """Clip-max table = k x std, from one fp32 pass: encoder on ``src``; decoder teacher-forced
+    on random target ids of the source lengths (causal self-attention)."""
+    st = _Stats()
+    H = w["emb"].shape[1]
+    V = w["emb"].shape[0]
+    B, S = src.shape
+    pos = sinusoid_table(max(1024, S + 64), H)
+    rng = np.random.default_rng(seed)
+
+    def lin(name, x, see_in=True, see_out=True):
+        if see_in:
+            st.see(name + ".in", x)
+        y = x @ w[name + ".w"].T
+        if see_out:
+            st.see(name + ".out", y)
+        return (y + w[name + ".b"]).astype(F32)
+
+    def emb(ids):
+        mask = ids != pad_id
+        p = (np.cumsum(mask, 1) - 1) * mask
+        return (F32(math.sqrt(H)) * w["emb"][ids] + pos[p] * mask[..., None]).astype(F32)
+
+    pad = src == pad_id
+    x = emb(src)
+    for l in range(n_enc):
+        p = f"enc.{l}"
+        qkv = lin(p + ".qkv", _ln(x, w[p + ".ln1.g"], w[p + ".ln1.b"]))
+        a = _attn(qkv[..., :H], qkv[..., H:2 * H], qkv[..., 2 * H:], heads, pad[:, None, None, :])
+        x = x + lin(p + ".out", a)
+        h = _act(lin(p + ".fc1", _ln(x, w[p + ".ln2.g"], w[p + ".ln2.b"])), act)
+        x = x + lin(p + ".fc2", h)
+    enc = _ln(x, w["enc.ln.g"], w["enc.ln.b"])
+
+    lens = (~pad).sum(1)
+    tgt = np.full((B, S), pad_id, dtype=np.int64)
+    for i, n in enumerate(lens):
+        tgt[i, :n] = rng.integers(4, V, size=n)
+    tpad = tgt == pad_id
+    causal = ~np.tril(np.ones((S, S), dtype=bool))
+    x = emb(tgt)
+    for l in range(n_dec):
+        p = f"dec.{l}"
+        qkv = lin(p + ".qkv", _ln(x, w[p + ".ln1.g"], w[p + ".ln1.b"]))
+        st.see(p + ".kv", qkv)
+        a = _attn(qkv[..., :H], qkv[..., H:2 * H], qkv[..., 2 * H:], heads,
+                  causal[None, None] | tpad[:, None, None, :])
+        x = x + lin(p + ".out", a)
+        q = lin(p + ".xq", _ln(x, w[p + ".ln2.g"], w[p + ".ln2.b"]))
+        kx = lin(p + ".xk", enc, False, False)
+        vx = lin(p + ".xv", enc, False, False)
+        a = _attn(q, kx, vx, heads, pad[:, None, None, :])
+        x = x + lin(p + ".xout", a)
+        h = _act(lin(p + ".fc1", _ln(x, w[p + ".ln3.g"], w[p + ".ln3.b"])), act)
+        x = x + lin(p + ".fc2", h)
+    x = _ln(x, w["dec.ln.g"], w["dec.ln.b"])
+    st.see("logits.in", x)
+    st.see("logits.out", x[:, : min(S, 8)] @ w["emb"].T)
+    amax = st.amax(k)
+    for name, t in w.items():
+        if name.endswith(".w") and t.ndim == 2:
+            amax[name] = float(F32(k * t.std()))
+    amax["emb"] = float(F32(k * w["emb"].std()))
+    return amax
+
+
+def make_transformer(path: Optional[str] = None, *, hidden=512, heads=8, ffn=2048, n_enc=6, n_dec=6, vocab=32000,
+                     act="relu", beam=4, length_penalty=0.6, extra_decode_length=50, max_step=256, pad_id=1,
+                     start_id=2, end_id=2, seed=1234, calib_src: Optional[np.ndarray] = None
+                     ) -> Tuple[Dict[str, float], Dict[str, float], Dict[str, np.ndarray]]:
+    """Builds (conf, amax, tensors) of a seeded synthetic QuantTransformer and optionally writes ``path``."""
+    w = transformer_weights(hidden, heads, ffn, n_enc, n_dec, vocab, pad_id, seed)
+    if calib_src is None:
+        calib_src = transformer_inputs(batch=8, min_len=8, max_len=24, vocab=vocab, pad_id=pad_id, seed=seed + 1)
+    amax = calibrate_transformer(w, calib_src, heads=heads, n_enc=n_enc, n_dec=n_dec, act=act, pad_id=pad_id)
+    conf = dict(hidden=hidden, heads=heads, ffn=ffn, n_enc=n_enc, n_dec=n_dec, vocab=vocab,
+                act_gelu=float(act == "gelu"), pre_ln=1.0, beam=beam, length_penalty=length_penalty,
+                extra_decode_length=extra_decode_length, max_step=max_step, pad_id=pad_id, start_id=start_id,
+                end_id=end_id)
+    if path is not None:
+        from . import weights
+
+        weights.save(path, "QuantTransformer", conf, amax, w)
+    return conf, amax, w

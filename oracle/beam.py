@@ -1,0 +1,93 @@
+"""CPU oracle (test infrastructure, not product code): one beam-search step and the
+top-k / top-p sampling step, restated from the reference inference engine.
+
+Beam step = ``select_beam_rough_topk_i8I`` (lightseq/inference/kernels/transformerKernels_int8.cc.cu:1690-1844)
++ the global sort of ``QuantDecoder::beam_search`` (lightseq/inference/model/quant_decoder.cc.cu:987-1076)
++ ``ker_refresh_result`` (lightseq/inference/kernels/transformerKernels.cc.cu:1398-1463):
+
+* a beam whose last token is EOS re-emits EOS with its frozen ``seq_score``;
+* a live beam scores token v as ``(logit_v + prefix - logsumexp) * length_norm``, with
+  ``exp`` arguments clamped at -64 (``logit_thresh_min``, transformerKernels.h:11) and the
+  result floored at -1999 (``min_log_probability + 1``);
+* per batch the best ``beam`` candidates survive; live ones get ``seq_probs = score / length_norm``.
+
+Differences from the engine, on purpose: exact top-``beam`` per row instead of the
+rough threshold of ``blockRoughTopK`` (a superset of the winners, so the winners are
+the same); no ``-2000 * batch_id`` float offsets (they only separate batches inside
+one global sort and cost precision); ties broken by (higher score, lower beam, lower
+token id) instead of the unspecified Thrust order; ``seq_score`` is also refreshed
+for live beams (the engine leaves it stale there).
+
+Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs may import
+this package.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+F32 = np.float32
+LOGIT_THRESH_MIN = F32(-64.0)
+MIN_LOG_PROB = F32(-2000.0)
+
+
+def length_norm(length: int, alpha: float) -> np.float32:
+    """transformerKernels.h:137-140."""
+    if alpha < 0:
+        return F32(1.0 / length)
+    return F32(np.power(F32((5.0 + length) / 6.0), F32(-alpha)))
+
+
+def row_logsumexp_base(lq_row: np.ndarray, s_l: np.float32):
+    """max logit and log(sum exp) of one dequantised int8 row; sums run over the 255-bin
+    histogram of the int8 values from the largest value down (order-independent)."""
+    hist = np.bincount(lq_row.astype(np.int32) + 128, minlength=256)
+    vals = np.nonzero(hist)[0]
+    qmax = vals.max() - 128
+    mx = F32(qmax) * s_l
+    tot = np.float64(0.0)
+    for b in vals[::-1]:
+        lg = F32(b - 128) * s_l
+        d = max(F32(lg - mx), LOGIT_THRESH_MIN)
+        tot += np.float64(hist[b]) * np.float64(np.exp(F32(d), dtype=F32))
+    return mx, F32(np.log(F32(tot), dtype=F32))
+
+
+def beam_step(lq: np.ndarray, s_l, alive: np.ndarray, probs: np.ndarray, score: np.ndarray, cur_step: int,
+              ln, end_id: int):
+    """lq int8 [B,K,V]; alive int32 [B,K,max_step]; probs/score fp32 [B,K].
+    Returns (new_alive, new_probs, new_score, parent [B,K], n_finished)."""
+    B, K, V = lq.shape
+    s_l = F32(s_l)
+    ln = F32(ln)
+    new_alive = np.full_like(alive, end_id)
+    new_probs = probs.copy()
+    new_score = score.copy()
+    parent = np.zeros((B, K), dtype=np.int64)
+    n_fin = 0
+    for b in range(B):
+        cands = []  # (score, beam, token)
+        for k in range(K):
+            if cur_step != 0 and alive[b, k, cur_step] == end_id:
+                cands.append((F32(score[b, k]), k, end_id))
+                continue
+            row = lq[b, k]
+            mx, lse = row_logsumexp_base(row, s_l)
+            base = F32(F32(probs[b, k] - lse) - mx)
+            # exact top-K of the row: larger int8 value first, then lower token id
+            order = np.lexsort((np.arange(V), -row.astype(np.int32)))[:K]
+            for v in order:
+                lg = F32(row[v]) * s_l
+                sc = max(F32(F32(lg + base) * ln), F32(MIN_LOG_PROB + F32(1.0)))
+                cands.append((F32(sc), k, int(v)))
+        cands.sort(key=lambda c: (-float(c[0]), c[1], c[2]))
+        for j in range(K):
+            sc, k, v = cands[j]
+            parent[b, j] = k
+            new_alive[b, j, :cur_step + 1] = alive[b, k, :cur_step + 1]
+            new_alive[b, j, cur_step + 1] = v
+            new_score[b, j] = sc
+            if v != end_id:
+                new_probs[b, j] = F32(sc / ln)
+            else:
+                n_fin += 1
+    return new_alive, new_probs, new_score, parent, n_fin
