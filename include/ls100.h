@@ -94,6 +94,196 @@ typedef struct {
 
 int ls100_gemm_i8(ls100_ctx* ctx, const ls100_gemm_i8_args* args, ls100_stream_t stream);
 
+
+/* ------------------------------------------------------- LayerNorm + quantise ---
+ * y = LayerNorm(x) over the last dim (eps 1e-5, float64 statistics), optionally
+ * written as fp32 and/or quantised to int8 with the consumer's input clip-max.
+ * Replaces ker_norm_layer_resual_i8O (lightseq/inference/kernels/transformerKernels_int8.cc.cu:149-316);
+ * restates the LayerNorm -> QuantLinear.input_quant edge of
+ * lightseq/training/ops/pytorch/torch_transformer_layers.py:642-661.
+ * hidden % 4 == 0, hidden <= 4096. */
+typedef struct {
+  const float* x;
+  int64_t ldx; /* elements */
+  const float* gamma;
+  const float* beta;
+  int32_t rows, hidden;
+  float amax;   /* clip-max of the int8 output (used when out_q != NULL) */
+  int8_t* out_q; /* optional [rows, hidden] */
+  int64_t ldq;
+  float* out_f; /* optional fp32 LayerNorm output */
+  int64_t ldf;
+} ls100_ln_quant_args;
+int ls100_ln_quant(ls100_ctx* ctx, const ls100_ln_quant_args* args, ls100_stream_t stream);
+
+/* ----------------------------------------------------------------- embedding ---
+ * x[r, :] = sqrt_h * (table_q[id] * s_emb) + pos[p] * (id != pad_id), p = (#non-pad ids
+ * up to and including this one) - 1 + pos_offset. Replaces launch_enc_emb_i8I /
+ * launch_dec_emb_i8I (lightseq/inference/kernels/embKernels_int8.cc.cu:99-212); restates
+ * TransformerEmbeddingLayer.forward (torch_transformer_layers.py:1027-1036).
+ * Encoder form: ids [batch, seq] (ld_ids = seq), step_ptr NULL.
+ * Decoder form: seq = 1, the id of row r is ids[r*ld_ids + *step_ptr] and pos_offset = *step_ptr
+ * (step read on the device so a captured CUDA graph can be replayed every step). */
+typedef struct {
+  const int32_t* ids;
+  int64_t ld_ids;
+  int32_t batch, seq, hidden;
+  const int32_t* step_ptr; /* optional device int */
+  const int8_t* table_q;   /* [vocab, hidden] int8 */
+  float s_emb;             /* amax_emb / 127 */
+  float sqrt_h;            /* embed_scale */
+  const float* pos;        /* [n_pos, hidden] fp32 */
+  int32_t n_pos, pad_id, vocab;
+  float* out;        /* [batch*seq, hidden] fp32 */
+  uint8_t* pad_mask; /* optional [batch, seq], 1 = pad */
+} ls100_embed_args;
+int ls100_embed(ls100_ctx* ctx, const ls100_embed_args* args, ls100_stream_t stream);
+
+/* ------------------------------------------------- encoder-style self attention ---
+ * softmax((q*dh^-0.5) k^T + mask) v per (batch, head) over a full sequence, output
+ * quantised with the out-projection's input clip-max. q,k,v are read from the QKV
+ * GEMM's int8 output [batch*seq, 3*hidden] as x*s_qkv (+ bias[c]). Key-padding mask
+ * excludes keys; `causal` also excludes keys after the query (GPT prefill).
+ * Replaces ker_arrange_encself_qkv_i8I + cublasGemmStridedBatchedEx x2 +
+ * ker_correlation_softmax_encself + ker_arrange_atten_output_i8O
+ * (lightseq/inference/model/quant_encoder.cc.cu:306-342); restates
+ * MultiheadAttention.forward (torch_transformer_layers.py:201-376). head_dim == 64. */
+typedef struct {
+  const int8_t* qkv;
+  int64_t ld_qkv;
+  float s_qkv;
+  const float* bias; /* optional [3*hidden] */
+  const uint8_t* pad_mask; /* optional [batch, seq] */
+  int32_t batch, seq, heads, causal;
+  float amax_out;
+  int8_t* out; /* [batch*seq, hidden] */
+  int64_t ld_out;
+  /* optional: also store k,v of every position into an int8 cache laid out
+   * [batch, heads, max_step, 64] (GPT prefill); requires bias == NULL */
+  int8_t* k_cache;
+  int8_t* v_cache;
+  int32_t max_step;
+} ls100_attn_self_args;
+int ls100_attn_self(ls100_ctx* ctx, const ls100_attn_self_args* args, ls100_stream_t stream);
+
+/* --------------------------------------- decoder self attention over int8 KV cache ---
+ * One new token per row. qkv [rows, 3*hidden] int8 holds attention_quant(q,k,v) (scale
+ * s_kv). The new k,v are appended at position *step_ptr of the row's own cache slot;
+ * history position p of row r lives in slot anc[r*max_step + p] (beam ancestry, written
+ * by ls100_beam_update; pass NULL for "own slot"). Caches: [rows, heads, max_step, 64].
+ * Replaces ker_arrange_decself_qkv_i8I_i8O + int8 cublasGemmStridedBatchedEx +
+ * ker_fuse_softmax_new_value_i32I_i8O and the per-step ker_refresh_cache
+ * (lightseq/inference/model/quant_decoder.cc.cu:662-700,1060-1074); restates the
+ * incremental branch of MultiheadAttention.forward (torch_transformer_layers.py:262-300). */
+typedef struct {
+  const int8_t* qkv;
+  int64_t ld_qkv;
+  float s_kv;
+  int8_t* k_cache;
+  int8_t* v_cache;
+  const int32_t* anc; /* optional [rows, max_step] */
+  const int32_t* step_ptr;
+  int32_t rows, heads, max_step;
+  float amax_out;
+  int8_t* out;
+  int64_t ld_out;
+} ls100_attn_dec_args;
+int ls100_attn_dec(ls100_ctx* ctx, const ls100_attn_dec_args* args, ls100_stream_t stream);
+
+/* ------------------------------------------------------------- cross attention ---
+ * rows = batch*beam queries (q int8 * s_q + bias) against the fp16 encoder keys/values
+ * [batch*src_len, hidden] of one decoder layer, source key-padding mask, output int8.
+ * Replaces ker_arrange_encdec_q_i8I + cublasGemmStridedBatchedEx x2 +
+ * ker_correlation_softmax_encdec + ker_arrange_atten_output_i8O
+ * (lightseq/inference/model/quant_decoder.cc.cu:767-814). */
+typedef struct {
+  const int8_t* q;
+  int64_t ld_q;
+  float s_q;
+  const float* bias; /* [hidden] */
+  const void* k;     /* fp16 [batch*src_len, hidden] */
+  const void* v;
+  int64_t ld_kv; /* elements */
+  const uint8_t* pad_mask; /* [batch, src_len] */
+  int32_t batch, beam, src_len, heads;
+  float amax_out;
+  int8_t* out;
+  int64_t ld_out;
+} ls100_attn_cross_args;
+int ls100_attn_cross(ls100_ctx* ctx, const ls100_attn_cross_args* args, ls100_stream_t stream);
+
+/* -------------------------------------------- fp32 x fake-quant weight projection ---
+ * out_f16[M,N] = (x[M,K] . Wq[N,K]^T) * s_w + bias : the weight-only-quantised k_proj /
+ * v_proj of the decoder's cross attention, run once per request. Replaces the fp16
+ * cublasGemmEx + ker_arrange_encdec_kv of QuantDecoder::project_encoder_output
+ * (lightseq/inference/model/quant_decoder.cc.cu:489-520); restates QuantLinear with
+ * pre_activation="encoder_out" (quantization.py:41-46). */
+typedef struct {
+  const float* x;
+  int64_t ldx;
+  const int8_t* w;
+  int64_t ldw;
+  float s_w;
+  const float* bias;
+  int32_t m, n, k;
+  void* out; /* fp16 */
+  int64_t ldo;
+} ls100_proj_f32_args;
+int ls100_proj_f32(ls100_ctx* ctx, const ls100_proj_f32_args* args, ls100_stream_t stream);
+
+/* ------------------------------------------------------------------ beam search ---
+ * Step 1 (ls100_beam_topk): per (batch, beam) row of int8 logits, log-softmax base from
+ * the 255-bin histogram (exp arguments clamped at -64), exact top-`beam` by (logit desc,
+ * token asc), candidate score = max((logit + prefix - logsumexp) * length_norm, -1999);
+ * a finished row (last token == end_id, step > 0) emits only (seq_score, EOS).
+ * Step 2 (ls100_beam_update): per batch, best `beam` of the beam*beam candidates by
+ * (score desc, beam asc, token asc); rebuilds alive_seq and the KV ancestry table in
+ * place, updates seq_probs / seq_score, counts finished beams, advances *step_ptr and
+ * records the first step at which every beam is finished in *stop_step (init -1).
+ * Replaces select_beam_rough_topk_i8I (transformerKernels_int8.cc.cu:1690-1906), the
+ * thrust scan/sort + two host syncs of QuantDecoder::beam_search
+ * (quant_decoder.cc.cu:987-1076), ker_refresh_result (transformerKernels.cc.cu:1398-1463)
+ * and ker_refresh_cache (:1578-1681). beam <= 8. */
+typedef struct {
+  const int8_t* logits; /* [batch*beam, ld_logits] */
+  int64_t ld_logits;
+  float s_logits;
+  int32_t batch, beam, vocab, max_step, end_id;
+  const int32_t* step_ptr;
+  const float* length_norm; /* [max_step] device table, entry s = norm of length s+1 */
+  const int32_t* alive;     /* [batch, beam, max_step] */
+  const float* seq_probs;   /* [batch, beam] */
+  const float* seq_score;   /* [batch, beam] */
+  float* cand_score;        /* out [batch*beam, beam] */
+  int32_t* cand_token;      /* out [batch*beam, beam] */
+} ls100_beam_topk_args;
+int ls100_beam_topk(ls100_ctx* ctx, const ls100_beam_topk_args* args, ls100_stream_t stream);
+
+typedef struct {
+  const float* cand_score;
+  const int32_t* cand_token;
+  int32_t batch, beam, max_step, end_id;
+  int32_t* step_ptr;   /* advanced by one */
+  const float* length_norm;
+  int32_t* alive;      /* in place */
+  int32_t* anc;        /* in place, optional */
+  float* seq_probs;
+  float* seq_score;
+  int32_t* fin_count;  /* [max_step] zeroed by the caller before the first step */
+  int32_t* ticket;     /* [max_step] zeroed by the caller before the first step */
+  int32_t* stop_step;  /* device int, -1 until every beam is finished */
+  int32_t* stop_host;  /* optional mapped host int mirroring *stop_step */
+} ls100_beam_update_args;
+int ls100_beam_update(ls100_ctx* ctx, const ls100_beam_update_args* args, ls100_stream_t stream);
+
+/* ------------------------------------------------------------- load-time prep ---
+ * fp32 -> int8 with the tensor's clip-max (quantize_weight, lightseq/inference/model/
+ * cublas_helper.cc:553-593) and, optionally, off[n] = 127 * sum_k q[n,k]: the exact
+ * integer form of the ReLU "colsum" correction (launch_scaled_colsum,
+ * lightseq/inference/kernels/transformerKernels.cc.cu:18-80). */
+int ls100_quantize_weight(ls100_ctx* ctx, const float* w, int64_t rows, int64_t cols, float amax, int8_t* out_q,
+                          int32_t* row_off /* optional [rows] */, ls100_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

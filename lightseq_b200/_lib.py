@@ -55,6 +55,63 @@ class GemmI8Args(C.Structure):
     ]
 
 
+
+class LnQuantArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("ldx", C.c_int64), ("gamma", C.c_void_p), ("beta", C.c_void_p),
+                ("rows", C.c_int32), ("hidden", C.c_int32), ("amax", C.c_float),
+                ("out_q", C.c_void_p), ("ldq", C.c_int64), ("out_f", C.c_void_p), ("ldf", C.c_int64)]
+
+
+class EmbedArgs(C.Structure):
+    _fields_ = [("ids", C.c_void_p), ("ld_ids", C.c_int64), ("batch", C.c_int32), ("seq", C.c_int32),
+                ("hidden", C.c_int32), ("step_ptr", C.c_void_p), ("table_q", C.c_void_p), ("s_emb", C.c_float),
+                ("sqrt_h", C.c_float), ("pos", C.c_void_p), ("n_pos", C.c_int32), ("pad_id", C.c_int32),
+                ("vocab", C.c_int32), ("out", C.c_void_p), ("pad_mask", C.c_void_p)]
+
+
+class AttnSelfArgs(C.Structure):
+    _fields_ = [("qkv", C.c_void_p), ("ld_qkv", C.c_int64), ("s_qkv", C.c_float), ("bias", C.c_void_p),
+                ("pad_mask", C.c_void_p), ("batch", C.c_int32), ("seq", C.c_int32), ("heads", C.c_int32),
+                ("causal", C.c_int32), ("amax_out", C.c_float), ("out", C.c_void_p), ("ld_out", C.c_int64),
+                ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("max_step", C.c_int32)]
+
+
+class AttnDecArgs(C.Structure):
+    _fields_ = [("qkv", C.c_void_p), ("ld_qkv", C.c_int64), ("s_kv", C.c_float), ("k_cache", C.c_void_p),
+                ("v_cache", C.c_void_p), ("anc", C.c_void_p), ("step_ptr", C.c_void_p), ("rows", C.c_int32),
+                ("heads", C.c_int32), ("max_step", C.c_int32), ("amax_out", C.c_float), ("out", C.c_void_p),
+                ("ld_out", C.c_int64)]
+
+
+class AttnCrossArgs(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("ld_q", C.c_int64), ("s_q", C.c_float), ("bias", C.c_void_p),
+                ("k", C.c_void_p), ("v", C.c_void_p), ("ld_kv", C.c_int64), ("pad_mask", C.c_void_p),
+                ("batch", C.c_int32), ("beam", C.c_int32), ("src_len", C.c_int32), ("heads", C.c_int32),
+                ("amax_out", C.c_float), ("out", C.c_void_p), ("ld_out", C.c_int64)]
+
+
+class ProjF32Args(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("ldx", C.c_int64), ("w", C.c_void_p), ("ldw", C.c_int64), ("s_w", C.c_float),
+                ("bias", C.c_void_p), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("out", C.c_void_p),
+                ("ldo", C.c_int64)]
+
+
+class BeamTopkArgs(C.Structure):
+    _fields_ = [("logits", C.c_void_p), ("ld_logits", C.c_int64), ("s_logits", C.c_float), ("batch", C.c_int32),
+                ("beam", C.c_int32), ("vocab", C.c_int32), ("max_step", C.c_int32), ("end_id", C.c_int32),
+                ("step_ptr", C.c_void_p), ("length_norm", C.c_void_p), ("alive", C.c_void_p),
+                ("seq_probs", C.c_void_p), ("seq_score", C.c_void_p), ("cand_score", C.c_void_p),
+                ("cand_token", C.c_void_p)]
+
+
+class BeamUpdateArgs(C.Structure):
+    _fields_ = [("cand_score", C.c_void_p), ("cand_token", C.c_void_p), ("batch", C.c_int32), ("beam", C.c_int32),
+                ("max_step", C.c_int32), ("end_id", C.c_int32), ("step_ptr", C.c_void_p),
+                ("length_norm", C.c_void_p), ("alive", C.c_void_p), ("anc", C.c_void_p), ("seq_probs", C.c_void_p),
+                ("seq_score", C.c_void_p), ("fin_count", C.c_void_p), ("ticket", C.c_void_p),
+                ("stop_step", C.c_void_p), ("stop_host", C.c_void_p)]
+
+
 lib.ls100_strerror.restype = C.c_char_p
 lib.ls100_strerror.argtypes = [C.c_int]
 lib.ls100_ctx_create.restype = C.c_int
@@ -67,6 +124,23 @@ lib.ls100_sm_count.restype = C.c_int
 lib.ls100_sm_count.argtypes = [C.c_void_p]
 lib.ls100_gemm_i8.restype = C.c_int
 lib.ls100_gemm_i8.argtypes = [C.c_void_p, C.POINTER(GemmI8Args), C.c_void_p]
+
+
+for _name, _cls in (("ls100_ln_quant", LnQuantArgs), ("ls100_embed", EmbedArgs), ("ls100_attn_self", AttnSelfArgs),
+                    ("ls100_attn_dec", AttnDecArgs), ("ls100_attn_cross", AttnCrossArgs),
+                    ("ls100_proj_f32", ProjF32Args), ("ls100_beam_topk", BeamTopkArgs),
+                    ("ls100_beam_update", BeamUpdateArgs)):
+    _fn = getattr(lib, _name)
+    _fn.restype = C.c_int
+    _fn.argtypes = [C.c_void_p, C.POINTER(_cls), C.c_void_p]
+lib.ls100_quantize_weight.restype = C.c_int
+lib.ls100_quantize_weight.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_void_p,
+                                      C.c_void_p, C.c_void_p]
+
+
+def call(name: str, ctx: "Context", args, stream: int = 0) -> None:
+    """Launches ``name`` and raises on a non-zero status."""
+    check(getattr(lib, name)(ctx.handle, C.byref(args), C.c_void_p(stream)), name)
 
 
 class Context:

@@ -1,0 +1,180 @@
+// Bandwidth-bound row kernels: LayerNorm (+ int8 quantise), embedding lookup and the
+// load-time weight quantiser. One warp per row, 16-byte vector accesses, shuffle
+// reductions; LayerNorm statistics are accumulated in float64 so the result does not
+// depend on the reduction order.
+#include "common.cuh"
+#include "ctx.h"
+
+namespace ls100 {
+
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ------------------------------------------------------------------ LayerNorm
+constexpr int LN_MAXV = 32;  // float4 per lane -> hidden <= 32*32*4 = 4096
+
+template <int NV>
+__global__ void __launch_bounds__(256) ln_quant_kernel(const ls100_ln_quant_args a, const float scale) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= a.rows) return;
+  const float* xr = a.x + (long long)warp * a.ldx;
+  float4 v[NV];
+  double s = 0.0;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * 32 + lane) * 4;
+    if (c < a.hidden) {
+      v[i] = *reinterpret_cast<const float4*>(xr + c);
+      s += (double)v[i].x + (double)v[i].y + (double)v[i].z + (double)v[i].w;
+    }
+  }
+  s = warp_sum_d(s);
+  const double mean = s / (double)a.hidden;
+  double sq = 0.0;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * 32 + lane) * 4;
+    if (c < a.hidden) {
+      const double d0 = (double)v[i].x - mean, d1 = (double)v[i].y - mean;
+      const double d2 = (double)v[i].z - mean, d3 = (double)v[i].w - mean;
+      sq += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+    }
+  }
+  sq = warp_sum_d(sq);
+  const double rstd = 1.0 / sqrt(sq / (double)a.hidden + 1e-5);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * 32 + lane) * 4;
+    if (c < a.hidden) {
+      const float4 g = *reinterpret_cast<const float4*>(a.gamma + c);
+      const float4 b = *reinterpret_cast<const float4*>(a.beta + c);
+      float4 y;
+      y.x = __fadd_rn(__fmul_rn((float)(((double)v[i].x - mean) * rstd), g.x), b.x);
+      y.y = __fadd_rn(__fmul_rn((float)(((double)v[i].y - mean) * rstd), g.y), b.y);
+      y.z = __fadd_rn(__fmul_rn((float)(((double)v[i].z - mean) * rstd), g.z), b.z);
+      y.w = __fadd_rn(__fmul_rn((float)(((double)v[i].w - mean) * rstd), g.w), b.w);
+      if (a.out_f) *reinterpret_cast<float4*>(a.out_f + (long long)warp * a.ldf + c) = y;
+      if (a.out_q) {
+        const uint32_t p = pack_i8x4(quant_s(clipf(y.x, a.amax), scale), quant_s(clipf(y.y, a.amax), scale),
+                                     quant_s(clipf(y.z, a.amax), scale), quant_s(clipf(y.w, a.amax), scale));
+        *reinterpret_cast<uint32_t*>(a.out_q + (long long)warp * a.ldq + c) = p;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ embedding
+__global__ void __launch_bounds__(256) embed_kernel(const ls100_embed_args a) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int rows = a.batch * a.seq;
+  if (warp >= rows) return;
+  const int b = warp / a.seq, s = warp % a.seq;
+  int id, pos;
+  if (a.step_ptr) {
+    const int step = *a.step_ptr;
+    id = a.ids[(long long)b * a.ld_ids + step];
+    pos = (id != a.pad_id) ? step : 0;
+  } else {
+    const int32_t* row = a.ids + (long long)b * a.ld_ids;
+    id = row[s];
+    // position = (#non-pad ids in row[0..s]) - 1, zero for pads
+    int cnt = 0;
+    for (int j = lane; j <= s; j += 32) cnt += (row[j] != a.pad_id) ? 1 : 0;
+    cnt = warp_sum_i(cnt);
+    pos = (id != a.pad_id) ? cnt - 1 : 0;
+  }
+  const bool is_pad = (id == a.pad_id);
+  if (a.pad_mask && lane == 0) a.pad_mask[warp] = is_pad ? 1 : 0;
+  if (id < 0 || id >= a.vocab) id = a.pad_id;  // out-of-range ids read the pad row instead of faulting
+  if (pos >= a.n_pos) pos = a.n_pos - 1;
+  const int8_t* er = a.table_q + (long long)id * a.hidden;
+  const float* pr = a.pos + (long long)pos * a.hidden;
+  float* orow = a.out + (long long)warp * a.hidden;
+  const float m = is_pad ? 0.f : 1.f;
+  for (int c = lane * 4; c < a.hidden; c += 128) {
+    const char4 q = *reinterpret_cast<const char4*>(er + c);
+    const float4 p = *reinterpret_cast<const float4*>(pr + c);
+    float4 y;
+    y.x = __fadd_rn(__fmul_rn(a.sqrt_h, __fmul_rn((float)q.x, a.s_emb)), __fmul_rn(p.x, m));
+    y.y = __fadd_rn(__fmul_rn(a.sqrt_h, __fmul_rn((float)q.y, a.s_emb)), __fmul_rn(p.y, m));
+    y.z = __fadd_rn(__fmul_rn(a.sqrt_h, __fmul_rn((float)q.z, a.s_emb)), __fmul_rn(p.z, m));
+    y.w = __fadd_rn(__fmul_rn(a.sqrt_h, __fmul_rn((float)q.w, a.s_emb)), __fmul_rn(p.w, m));
+    *reinterpret_cast<float4*>(orow + c) = y;
+  }
+}
+
+// ------------------------------------------------------------------ weight quantiser
+__global__ void __launch_bounds__(256) quantize_weight_kernel(const float* __restrict__ w, long long rows,
+                                                               long long cols, float amax, float scale,
+                                                               int8_t* __restrict__ out, int32_t* __restrict__ off) {
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const float* wr = w + warp * cols;
+  int8_t* orow = out + warp * cols;
+  int sum = 0;
+  for (long long c = lane * 4; c < cols; c += 128) {
+    const float4 x = *reinterpret_cast<const float4*>(wr + c);
+    const float q0 = quant_s(clipf(x.x, amax), scale), q1 = quant_s(clipf(x.y, amax), scale);
+    const float q2 = quant_s(clipf(x.z, amax), scale), q3 = quant_s(clipf(x.w, amax), scale);
+    sum += (int)q0 + (int)q1 + (int)q2 + (int)q3;
+    *reinterpret_cast<uint32_t*>(orow + c) = pack_i8x4(q0, q1, q2, q3);
+  }
+  if (off) {
+    sum = warp_sum_i(sum);
+    if (lane == 0) off[warp] = 127 * sum;
+  }
+}
+
+}  // namespace ls100
+
+using namespace ls100;
+
+extern "C" int ls100_ln_quant(ls100_ctx* ctx, const ls100_ln_quant_args* a, ls100_stream_t stream_) {
+  if (!ctx || !a || !a->x || !a->gamma || !a->beta || (!a->out_q && !a->out_f)) return LS100_ERR_BAD_ARG;
+  if (a->rows <= 0 || a->hidden <= 0) return LS100_ERR_BAD_ARG;
+  if ((a->hidden & 3) || a->hidden > LN_MAXV * 128) return LS100_ERR_UNSUPPORTED;
+  if (a->out_q && !(a->amax > 0.f)) return LS100_ERR_BAD_ARG;
+  if ((((uintptr_t)a->x) & 15) || (a->ldx & 3) || (((uintptr_t)a->gamma) & 15) || (((uintptr_t)a->beta) & 15))
+    return LS100_ERR_ALIGN;
+  if (a->out_q && ((((uintptr_t)a->out_q) & 3) || (a->ldq & 3))) return LS100_ERR_ALIGN;
+  if (a->out_f && ((((uintptr_t)a->out_f) & 15) || (a->ldf & 3))) return LS100_ERR_ALIGN;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const float scale = a->amax / 127.0f;
+  const int warps_per_block = 8;
+  const int blocks = (a->rows + warps_per_block - 1) / warps_per_block;
+  const int nv = (a->hidden + 127) / 128;
+  if (nv <= 4) ln_quant_kernel<4><<<blocks, 256, 0, stream>>>(*a, scale);
+  else if (nv <= 8) ln_quant_kernel<8><<<blocks, 256, 0, stream>>>(*a, scale);
+  else if (nv <= 16) ln_quant_kernel<16><<<blocks, 256, 0, stream>>>(*a, scale);
+  else ln_quant_kernel<32><<<blocks, 256, 0, stream>>>(*a, scale);
+  return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+}
+
+extern "C" int ls100_embed(ls100_ctx* ctx, const ls100_embed_args* a, ls100_stream_t stream_) {
+  if (!ctx || !a || !a->ids || !a->table_q || !a->pos || !a->out) return LS100_ERR_BAD_ARG;
+  if (a->batch <= 0 || a->seq <= 0 || a->hidden <= 0 || a->n_pos <= 0 || a->vocab <= 0) return LS100_ERR_BAD_ARG;
+  if (a->step_ptr && a->seq != 1) return LS100_ERR_BAD_ARG;
+  if (a->hidden & 3) return LS100_ERR_UNSUPPORTED;
+  if ((((uintptr_t)a->table_q) & 3) || (((uintptr_t)a->pos) & 15) || (((uintptr_t)a->out) & 15)) return LS100_ERR_ALIGN;
+  const int rows = a->batch * a->seq;
+  embed_kernel<<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream_>>>(*a);
+  return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+}
+
+extern "C" int ls100_quantize_weight(ls100_ctx* ctx, const float* w, int64_t rows, int64_t cols, float amax,
+                                     int8_t* out_q, int32_t* row_off, ls100_stream_t stream_) {
+  if (!ctx || !w || !out_q || rows <= 0 || cols <= 0 || !(amax > 0.f)) return LS100_ERR_BAD_ARG;
+  if (cols & 3) return LS100_ERR_UNSUPPORTED;
+  if ((((uintptr_t)w) & 15) || (((uintptr_t)out_q) & 3)) return LS100_ERR_ALIGN;
+  const float scale = amax / 127.0f;
+  const long long blocks = (rows + 7) / 8;
+  quantize_weight_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream_>>>(w, rows, cols, amax, scale, out_q,
+                                                                               row_off);
+  return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+}

@@ -1,0 +1,49 @@
+"""Helpers shared by the GPU parity tests: device buffers via torch, calls via the C ABI."""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from lightseq_b200 import _lib as L
+
+_ctx = None
+
+
+def ctx():
+    global _ctx
+    if _ctx is None:
+        _ctx = L.Context(0)
+    return _ctx
+
+
+def dev(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(a)).to("cuda:0")
+
+
+def empty(shape, dtype) -> torch.Tensor:
+    return torch.empty(shape, dtype=dtype, device="cuda:0")
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def sync_check():
+    torch.cuda.synchronize()
+    assert ctx().poll_error() == 0, "device-side bounded wait reported a timeout"
+
+
+def gemm(a_q, w_q, *, s_acc, out_kind, s_outq=0.0, bias=None, act=L.ACT_NONE, resid=None, s_req=0.0, w_off=None,
+         out_dtype=None):
+    """a_q [M,K] int8 device, w_q [N,K] int8 device -> device tensor."""
+    m, k = a_q.shape
+    n = w_q.shape[0]
+    dt = {L.OUT_OUTQ_I8: torch.int8, L.OUT_F32: torch.float32, L.OUT_REQ_S8: torch.int8, L.OUT_REQ_U8: torch.int8,
+          L.OUT_F16: torch.float16, L.OUT_I32: torch.int32}[out_kind]
+    out = torch.full((m, n), 0, dtype=dt, device="cuda:0")
+    args = L.GemmI8Args(a=ptr(a_q), lda=a_q.stride(0), w=ptr(w_q), ldw=w_q.stride(0), m=m, n=n, k=k, s_acc=s_acc,
+                        w_off=ptr(w_off), s_outq=s_outq, bias=ptr(bias), act=act, resid=ptr(resid),
+                        ldr=(resid.stride(0) if resid is not None else 0), out_kind=out_kind, s_req=s_req,
+                        out=ptr(out), ldo=n)
+    L.call("ls100_gemm_i8", ctx(), args)
+    return out

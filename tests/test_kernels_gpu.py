@@ -1,0 +1,392 @@
+"""Stage-wise parity of every CUDA kernel family against the numpy oracle, called through
+the C ABI (ctypes). Integer stages (quantised weights, int32 accumulators, requantised
+GEMM outputs, embedding, LayerNorm->int8) must be bit-exact; attention outputs go through
+fp32 softmax in a different summation order, so their int8 result may differ by one
+quantisation step on a small fraction of elements (bound stated per test)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+from lightseq_b200 import _lib as L  # noqa: E402
+from oracle import beam as ob  # noqa: E402
+from oracle import model as om  # noqa: E402
+from oracle import quant as oq  # noqa: E402
+from tests.gpu_util import ctx, dev, empty, gemm, ptr, sync_check  # noqa: E402
+
+F32 = np.float32
+
+
+def rng(seed):
+    return np.random.default_rng(seed)
+
+
+# ----------------------------------------------------------------------------- weights
+@pytest.mark.parametrize("rows,cols", [(512, 512), (96, 64), (2048, 512), (37, 128)])
+def test_quantize_weight_bit_exact(rows, cols):
+    w = (rng(1).standard_normal((rows, cols)) * 0.02).astype(F32)
+    amax = float(F32(4 * w.std()))
+    q_ref, _ = oq.quantize(w, amax)
+    dw = dev(w)
+    out = empty((rows, cols), torch.int8)
+    off = empty((rows,), torch.int32)
+    L.check(L.lib.ls100_quantize_weight(ctx().handle, ptr(dw), rows, cols, amax, ptr(out), ptr(off), None), "quantize")
+    sync_check()
+    assert np.array_equal(out.cpu().numpy(), q_ref)
+    assert np.array_equal(off.cpu().numpy(), 127 * q_ref.astype(np.int64).sum(1))
+
+
+# ----------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("m,n,k", [(512, 1536, 512), (200, 80, 256), (7680, 512, 512), (64, 1024, 1024),
+                                   (1, 64, 64), (129, 48, 144), (512, 512, 2048)])
+def test_gemm_int32_accumulators_bit_exact(m, n, k):
+    r = rng(m + n + k)
+    a = r.integers(-127, 128, size=(m, k), dtype=np.int8)
+    w = r.integers(-127, 128, size=(n, k), dtype=np.int8)
+    out = gemm(dev(a), dev(w), s_acc=1.0, out_kind=L.OUT_I32)
+    sync_check()
+    assert np.array_equal(out.cpu().numpy().astype(np.int64), oq.int_matmul(a, w))
+
+
+def _qlinear_case(seed, m, n, k, unsigned_in=False):
+    r = rng(seed)
+    w = (r.standard_normal((n, k)) * 0.02).astype(F32)
+    x = r.standard_normal((m, k)).astype(F32)
+    if unsigned_in:
+        x = np.maximum(x, 0)
+    b = (r.standard_normal(n) * 0.1).astype(F32)
+    st = om.State(w={"l.w": w, "l.b": b}, amax={"l.w": float(F32(4 * w.std())), "l.in": float(F32(4 * x.std())),
+                                                  "l.out": float(F32(4 * (x @ w.T).std()))})
+    return st, x, w, b
+
+
+def test_gemm_outq_int8_and_bias_residual_bit_exact():
+    """QKV-style (int8 of the output quantiser) and out-proj-style (fake-quant + bias + residual, fp32)."""
+    m, n, k = 300, 512, 512
+    st, x, w, b = _qlinear_case(5, m, n, k)
+    st.trace = {}
+    y = om.qlinear(st, x, "l")
+    xq, s_x = oq.quantize(x, st.amax["l.in"])
+    wq, s_w = oq.quantize(w, st.amax["l.w"])
+    s_o = oq.scale_of(st.amax["l.out"])
+    out = gemm(dev(xq), dev(wq), s_acc=float(F32(s_x * s_w)), out_kind=L.OUT_OUTQ_I8, s_outq=float(s_o))
+    sync_check()
+    assert np.array_equal(out.cpu().numpy(), st.trace["l.out_q"])
+    resid = rng(6).standard_normal((m, n)).astype(F32)
+    out = gemm(dev(xq), dev(wq), s_acc=float(F32(s_x * s_w)), out_kind=L.OUT_F32, s_outq=float(s_o), bias=dev(b),
+               resid=dev(resid))
+    sync_check()
+    assert np.array_equal(out.cpu().numpy(), resid + y)
+
+
+def test_gemm_ffn_relu_unsigned_chain_bit_exact():
+    """fc1 (+bias, ReLU, unsigned requantise) then fc2 with the 127*rowsum offset."""
+    m, h, f = 260, 512, 2048
+    r = rng(9)
+    w1 = (r.standard_normal((f, h)) * 0.02).astype(F32)
+    w2 = (r.standard_normal((h, f)) * 0.02).astype(F32)
+    b1 = (r.standard_normal(f) * 0.05).astype(F32)
+    b2 = (r.standard_normal(h) * 0.05).astype(F32)
+    x = r.standard_normal((m, h)).astype(F32)
+    h1 = np.maximum(x @ w1.T + b1, 0)
+    st = om.State(w={"p.fc1.w": w1, "p.fc1.b": b1, "p.fc2.w": w2, "p.fc2.b": b2},
+                  amax={"p.fc1.w": float(F32(4 * w1.std())), "p.fc2.w": float(F32(4 * w2.std())),
+                        "p.fc1.in": float(F32(4 * x.std())), "p.fc1.out": float(F32(4 * (x @ w1.T).std())),
+                        "p.fc2.in": float(F32(4 * h1.std())), "p.fc2.out": float(F32(4 * (h1 @ w2.T).std()))})
+    st.trace = {}
+    y = om.ffn(st, x, "p", om.Config(hidden=h, ffn=f))
+    xq, s_x = oq.quantize(x, st.amax["p.fc1.in"])
+    w1q, s_w1 = oq.quantize(w1, st.amax["p.fc1.w"])
+    w2q, s_w2 = oq.quantize(w2, st.amax["p.fc2.w"])
+    s_h = oq.scale_of(st.amax["p.fc2.in"], unsigned=True)
+    hq = gemm(dev(xq), dev(w1q), s_acc=float(F32(s_x * s_w1)), out_kind=L.OUT_REQ_U8,
+              s_outq=float(oq.scale_of(st.amax["p.fc1.out"])), bias=dev(b1), act=L.ACT_RELU, s_req=float(s_h))
+    sync_check()
+    assert np.array_equal(hq.cpu().numpy(), st.trace["p.fc2.in_q"])
+    off = dev((127 * w2q.astype(np.int64).sum(1)).astype(np.int32))
+    out = gemm(hq, dev(w2q), s_acc=float(F32(s_h * s_w2)), out_kind=L.OUT_F32,
+               s_outq=float(oq.scale_of(st.amax["p.fc2.out"])), bias=dev(b2), w_off=off)
+    sync_check()
+    assert np.array_equal(out.cpu().numpy(), y)
+
+
+def test_gemm_gelu_requant_close():
+    """GELU uses erff on the device and scipy erf in the oracle: allow one int8 step on <0.1% of elements."""
+    m, n, k = 256, 768, 768
+    st, x, w, b = _qlinear_case(11, m, n, k)
+    pre = om.qlinear(st, x, "l")
+    act = oq.gelu(pre)
+    amax2 = float(F32(4 * act.std()))
+    ref, s2 = oq.quantize(act, amax2)
+    xq, s_x = oq.quantize(x, st.amax["l.in"])
+    wq, s_w = oq.quantize(w, st.amax["l.w"])
+    out = gemm(dev(xq), dev(wq), s_acc=float(F32(s_x * s_w)), out_kind=L.OUT_REQ_S8,
+               s_outq=float(oq.scale_of(st.amax["l.out"])), bias=dev(b), act=L.ACT_GELU, s_req=float(s2))
+    sync_check()
+    d = np.abs(out.cpu().numpy().astype(np.int32) - ref.astype(np.int32))
+    assert d.max() <= 1 and (d > 0).mean() < 1e-3
+
+
+def test_gemm_rejects_bad_arguments():
+    a = dev(np.zeros((16, 64), np.int8))
+    out = empty((16, 16), torch.int32)
+    args = L.GemmI8Args(a=ptr(a), lda=60, w=ptr(a), ldw=64, m=16, n=16, k=64, s_acc=1.0, out_kind=L.OUT_I32,
+                        out=ptr(out), ldo=16)
+    assert L.lib.ls100_gemm_i8(ctx().handle, C.byref(args), None) == L.ERR_ALIGN
+    args.lda = 64
+    args.m = 0
+    assert L.lib.ls100_gemm_i8(ctx().handle, C.byref(args), None) == L.ERR_BAD_ARG
+    args.m = 16
+    args.out_kind = L.OUT_OUTQ_I8  # needs s_outq > 0
+    assert L.lib.ls100_gemm_i8(ctx().handle, C.byref(args), None) == L.ERR_BAD_ARG
+
+
+# ----------------------------------------------------------------------------- LayerNorm, embedding
+@pytest.mark.parametrize("rows,hidden", [(512, 512), (33, 64), (1000, 768), (7, 1024), (3, 2048)])
+def test_ln_quant_bit_exact(rows, hidden):
+    r = rng(rows)
+    x = (r.standard_normal((rows, hidden)) * 1.7 + 0.3).astype(F32)
+    g = (1 + 0.1 * r.standard_normal(hidden)).astype(F32)
+    b = (0.1 * r.standard_normal(hidden)).astype(F32)
+    y = om.layer_norm(x, g, b)
+    amax = float(F32(4 * y.std()))
+    q_ref, _ = oq.quantize(y, amax)
+    oq_t, of_t = empty((rows, hidden), torch.int8), empty((rows, hidden), torch.float32)
+    dx, dg, db = dev(x), dev(g), dev(b)
+    args = L.LnQuantArgs(x=ptr(dx), ldx=hidden, gamma=ptr(dg), beta=ptr(db), rows=rows, hidden=hidden, amax=amax,
+                         out_q=ptr(oq_t), ldq=hidden, out_f=ptr(of_t), ldf=hidden)
+    L.call("ls100_ln_quant", ctx(), args)
+    sync_check()
+    assert np.array_equal(of_t.cpu().numpy(), y)
+    assert np.array_equal(oq_t.cpu().numpy(), q_ref)
+
+
+def test_embed_encoder_and_decoder_forms_bit_exact():
+    V, H, pad = 500, 128, 1
+    r = rng(2)
+    tab = (r.standard_normal((V, H)) * 0.02).astype(F32)
+    tab[pad] = 0
+    amax = float(F32(4 * tab.std()))
+    st = om.State(w={"emb": tab}, amax={"emb": amax})
+    cfg = om.Config(hidden=H, vocab=V, pad_id=pad)
+    pos = om.sinusoid_table(64, H)
+    ids = r.integers(4, V, size=(5, 19)).astype(np.int32)
+    for i, n in enumerate([19, 3, 11, 1, 8]):
+        ids[i, n:] = pad
+    ref = om.embed(st, ids, 0, cfg, pos)
+    tq, s = oq.quantize(tab, amax)
+    dt, dp, di = dev(tq), dev(pos), dev(ids)
+    out = empty((5 * 19, H), torch.float32)
+    mask = empty((5, 19), torch.uint8)
+    args = L.EmbedArgs(ids=ptr(di), ld_ids=19, batch=5, seq=19, hidden=H, step_ptr=None, table_q=ptr(dt), s_emb=float(s),
+                       sqrt_h=float(F32(np.sqrt(H))), pos=ptr(dp), n_pos=64, pad_id=pad, vocab=V, out=ptr(out),
+                       pad_mask=ptr(mask))
+    L.call("ls100_embed", ctx(), args)
+    sync_check()
+    assert np.array_equal(out.cpu().numpy().reshape(5, 19, H), ref)
+    assert np.array_equal(mask.cpu().numpy().astype(bool), ids == pad)
+    # decoder form: token of row r at column *step of a [rows, max_step] history, position = step
+    hist = r.integers(4, V, size=(6, 32)).astype(np.int32)
+    step = 7
+    dstep = dev(np.array([step], np.int32))
+    dh = dev(hist)
+    out = empty((6, H), torch.float32)
+    args = L.EmbedArgs(ids=ptr(dh), ld_ids=32, batch=6, seq=1, hidden=H, step_ptr=ptr(dstep), table_q=ptr(dt),
+                       s_emb=float(s), sqrt_h=float(F32(np.sqrt(H))), pos=ptr(dp), n_pos=64, pad_id=pad, vocab=V,
+                       out=ptr(out), pad_mask=None)
+    L.call("ls100_embed", ctx(), args)
+    sync_check()
+    ref = om.embed(st, hist[:, step:step + 1], step, cfg, pos)[:, 0]
+    assert np.array_equal(out.cpu().numpy(), ref)
+
+
+# ----------------------------------------------------------------------------- attention
+def _int8_close(got, ref, max_rate):
+    d = np.abs(got.astype(np.int32) - ref.astype(np.int32))
+    assert d.max() <= 1, f"int8 outputs differ by {d.max()} steps"
+    rate = float((d > 0).mean())
+    assert rate < max_rate, f"one-step mismatch rate {rate}"
+    return rate
+
+
+@pytest.mark.parametrize("B,S,heads,causal,with_bias", [(3, 60, 8, 0, 1), (2, 150, 4, 0, 1), (2, 100, 4, 1, 0),
+                                                       (1, 1, 2, 0, 1), (4, 64, 2, 0, 1)])
+def test_attn_self_matches_oracle(B, S, heads, causal, with_bias):
+    H = heads * 64
+    r = rng(B * S)
+    qkv_q = r.integers(-127, 128, size=(B, S, 3 * H), dtype=np.int8)
+    s_qkv = F32(0.021)
+    bias = (r.standard_normal(3 * H) * 0.2).astype(F32) if with_bias else None
+    lens = r.integers(max(1, S // 3), S + 1, size=B)
+    pad = np.arange(S)[None, :] >= lens[:, None]
+    qkv = qkv_q.astype(F32) * s_qkv
+    if bias is not None:
+        qkv = qkv + bias
+    a = om.attention_core(qkv[..., :H], qkv[..., H:2 * H], qkv[..., 2 * H:], heads, pad, 64 ** -0.5, bool(causal))
+    amax = float(F32(4 * a.std()))
+    ref, _ = oq.quantize(a, amax)
+    dq, dpad = dev(qkv_q.reshape(B * S, 3 * H)), dev(pad.astype(np.uint8))
+    db = dev(bias) if bias is not None else None
+    out = empty((B * S, H), torch.int8)
+    args = L.AttnSelfArgs(qkv=ptr(dq), ld_qkv=3 * H, s_qkv=float(s_qkv), bias=ptr(db), pad_mask=ptr(dpad), batch=B,
+                          seq=S, heads=heads, causal=causal, amax_out=amax, out=ptr(out), ld_out=H, k_cache=None,
+                          v_cache=None, max_step=0)
+    L.call("ls100_attn_self", ctx(), args)
+    sync_check()
+    got = out.cpu().numpy().reshape(B, S, H)
+    valid = ~pad
+    _int8_close(got[valid], ref[valid], 5e-3)
+
+
+def test_attn_dec_int8_cache_with_beam_ancestry():
+    """Five decode steps with a random beam reshuffle after each; the oracle permutes its
+    cache physically, the kernel only follows the ancestry table."""
+    B, K, heads, ms = 3, 4, 4, 16
+    H, T = heads * 64, 3 * 4
+    r = rng(17)
+    s_kv = F32(0.03)
+    kc, vc = empty((T, heads, ms, 64), torch.int8), empty((T, heads, ms, 64), torch.int8)
+    kc.zero_()
+    vc.zero_()
+    anc = np.zeros((T, ms), np.int32)
+    danc = dev(anc)
+    dstep = dev(np.zeros(1, np.int32))
+    ok_k = np.zeros((T, 0, H), np.int8)
+    ok_v = np.zeros((T, 0, H), np.int8)
+    worst = 0.0
+    for step in range(5):
+        qkv = r.integers(-127, 128, size=(T, 3 * H), dtype=np.int8)
+        ok_k = np.concatenate([ok_k, qkv[:, None, H:2 * H]], 1)
+        ok_v = np.concatenate([ok_v, qkv[:, None, 2 * H:]], 1)
+        q = qkv[:, :H].astype(F32) * s_kv
+        a = om.attention_core(q[:, None], ok_k.astype(F32) * s_kv, ok_v.astype(F32) * s_kv, heads, None, 64 ** -0.5)[:, 0]
+        amax = float(F32(4 * a.std()))
+        ref, _ = oq.quantize(a, amax)
+        dq = dev(qkv)
+        dstep.copy_(torch.tensor([step], dtype=torch.int32))
+        danc.copy_(torch.from_numpy(anc))
+        out = empty((T, H), torch.int8)
+        args = L.AttnDecArgs(qkv=ptr(dq), ld_qkv=3 * H, s_kv=float(s_kv), k_cache=ptr(kc), v_cache=ptr(vc), anc=ptr(danc),
+                             step_ptr=ptr(dstep), rows=T, heads=heads, max_step=ms, amax_out=amax, out=ptr(out), ld_out=H)
+        L.call("ls100_attn_dec", ctx(), args)
+        sync_check()
+        worst = max(worst, _int8_close(out.cpu().numpy(), ref, 5e-3))
+        # beam reshuffle: new beam j of batch b continues old beam parent[b, j]
+        parent = r.integers(0, K, size=(B, K))
+        flat = (parent + np.arange(B)[:, None] * K).reshape(-1)
+        ok_k, ok_v = ok_k[flat], ok_v[flat]
+        new_anc = anc.copy()
+        for t in range(T):
+            new_anc[t, :step] = anc[flat[t], :step]
+            new_anc[t, step] = flat[t]
+        anc = new_anc
+    print("attn_dec worst one-step rate", worst)
+
+
+def test_attn_cross_matches_oracle():
+    B, K, S, heads = 5, 4, 37, 8
+    H = heads * 64
+    r = rng(23)
+    q_q = r.integers(-127, 128, size=(B * K, H), dtype=np.int8)
+    s_q = F32(0.017)
+    bias = (r.standard_normal(H) * 0.1).astype(F32)
+    k = (r.standard_normal((B, S, H)) * 0.5).astype(np.float16)
+    v = (r.standard_normal((B, S, H)) * 0.5).astype(np.float16)
+    lens = r.integers(1, S + 1, size=B)
+    pad = np.arange(S)[None, :] >= lens[:, None]
+    q = q_q.astype(F32) * s_q + bias
+    a = om.attention_core(q[:, None], np.repeat(k.astype(F32), K, 0), np.repeat(v.astype(F32), K, 0), heads,
+                          np.repeat(pad, K, 0), 64 ** -0.5)[:, 0]
+    amax = float(F32(4 * a.std()))
+    ref, _ = oq.quantize(a, amax)
+    dq, db, dk, dv, dp = dev(q_q), dev(bias), dev(k.reshape(B * S, H)), dev(v.reshape(B * S, H)), dev(pad.astype(np.uint8))
+    out = empty((B * K, H), torch.int8)
+    args = L.AttnCrossArgs(q=ptr(dq), ld_q=H, s_q=float(s_q), bias=ptr(db), k=ptr(dk), v=ptr(dv), ld_kv=H,
+                           pad_mask=ptr(dp), batch=B, beam=K, src_len=S, heads=heads, amax_out=amax, out=ptr(out), ld_out=H)
+    L.call("ls100_attn_cross", ctx(), args)
+    sync_check()
+    _int8_close(out.cpu().numpy(), ref, 5e-3)
+
+
+def test_proj_f32_weight_only_quant():
+    m, n, k = 333, 192, 512
+    r = rng(31)
+    x = r.standard_normal((m, k)).astype(F32)
+    w = (r.standard_normal((n, k)) * 0.02).astype(F32)
+    b = (r.standard_normal(n) * 0.1).astype(F32)
+    st = om.State(w={"l.w": w, "l.b": b}, amax={"l.w": float(F32(4 * w.std()))})
+    ref = om.qlinear(st, x, "l", quant_in=False, quant_out=False)
+    wq, s_w = oq.quantize(w, st.amax["l.w"])
+    dx, dw, db = dev(x), dev(wq), dev(b)
+    out = empty((m, n), torch.float16)
+    args = L.ProjF32Args(x=ptr(dx), ldx=k, w=ptr(dw), ldw=k, s_w=float(s_w), bias=ptr(db), m=m, n=n, k=k, out=ptr(out), ldo=n)
+    L.call("ls100_proj_f32", ctx(), args)
+    sync_check()
+    d = np.abs(out.cpu().numpy().astype(F32) - ref)
+    # fp16 storage: half an ulp of the largest magnitude
+    assert d.max() <= np.abs(ref).max() * 2.0 ** -10
+
+
+# ----------------------------------------------------------------------------- beam search
+@pytest.mark.parametrize("V,ties", [(32000, False), (1000, True), (37, True), (40000, False)])
+def test_beam_step_matches_oracle(V, ties):
+    """Several steps of topk+update vs oracle.beam.beam_step, incl. EOS finishing, heavy logit ties and
+    the in-place history / ancestry rewrite."""
+    B, K, ms, end_id = 6, 4, 24, 2
+    r = rng(V)
+    ldv = (V + 15) // 16 * 16
+    s_l = F32(0.08)
+    alive = np.full((B, K, ms), end_id, np.int32)
+    probs = np.full((B, K), -1000.0, F32)
+    probs[:, 0] = 0
+    score = np.zeros((B, K), F32)
+    anc = np.zeros((B * K, ms), np.int32)
+    ln_tab = np.array([ob.length_norm(i + 1, 0.6) for i in range(ms)], F32)
+    d_alive, d_probs, d_score, d_anc = dev(alive), dev(probs), dev(score), dev(anc)
+    d_ln = dev(ln_tab)
+    d_step = dev(np.zeros(1, np.int32))
+    d_fin, d_ticket = dev(np.zeros(ms, np.int32)), dev(np.zeros(ms, np.int32))
+    d_stop = dev(np.full(1, -1, np.int32))
+    cs, ct = empty((B * K, K), torch.float32), empty((B * K, K), torch.int32)
+    for step in range(8):
+        if ties:
+            lq = r.integers(-3, 4, size=(B, K, V)).astype(np.int8)
+        else:
+            lq = np.clip(np.rint(r.standard_normal((B, K, V)) * 32), -127, 127).astype(np.int8)
+        if step >= 2:  # push EOS so that beams finish
+            lq[:, :, end_id] = 127 if ties else 120
+        pad = np.full((B * K, ldv), 55, np.int8)
+        pad[:, :V] = lq.reshape(B * K, V)
+        d_l = dev(pad)
+        a1 = L.BeamTopkArgs(logits=ptr(d_l), ld_logits=ldv, s_logits=float(s_l), batch=B, beam=K, vocab=V, max_step=ms,
+                            end_id=end_id, step_ptr=ptr(d_step), length_norm=ptr(d_ln), alive=ptr(d_alive),
+                            seq_probs=ptr(d_probs), seq_score=ptr(d_score), cand_score=ptr(cs), cand_token=ptr(ct))
+        L.call("ls100_beam_topk", ctx(), a1)
+        a2 = L.BeamUpdateArgs(cand_score=ptr(cs), cand_token=ptr(ct), batch=B, beam=K, max_step=ms, end_id=end_id,
+                              step_ptr=ptr(d_step), length_norm=ptr(d_ln), alive=ptr(d_alive), anc=ptr(d_anc),
+                              seq_probs=ptr(d_probs), seq_score=ptr(d_score), fin_count=ptr(d_fin), ticket=ptr(d_ticket),
+                              stop_step=ptr(d_stop), stop_host=None)
+        L.call("ls100_beam_update", ctx(), a2)
+        sync_check()
+        alive, probs, score, parent, n_fin = ob.beam_step(lq, s_l, alive, probs, score, step, ln_tab[step], end_id)
+        flat = (parent + np.arange(B)[:, None] * K).reshape(-1)
+        new_anc = anc.copy()
+        for t in range(B * K):
+            new_anc[t, :step] = anc[flat[t], :step]
+            new_anc[t, step] = flat[t]
+        anc = new_anc
+        assert int(d_step.cpu()[0]) == step + 1
+        assert np.array_equal(d_alive.cpu().numpy(), alive), f"step {step}: token histories differ"
+        assert np.array_equal(d_anc.cpu().numpy()[:, :step + 1], anc[:, :step + 1])
+        np.testing.assert_allclose(d_score.cpu().numpy(), score, rtol=2e-6, atol=2e-5)
+        live = alive[:, :, step + 1] != end_id
+        np.testing.assert_allclose(d_probs.cpu().numpy()[live], probs[live], rtol=2e-6, atol=2e-5)
+        assert int(d_fin.cpu()[step]) == n_fin
+        if n_fin == B * K:
+            assert int(d_stop.cpu()[0]) >= 0
+            break
+    assert int(d_stop.cpu()[0]) == step if n_fin == B * K else int(d_stop.cpu()[0]) == -1
