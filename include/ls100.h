@@ -284,6 +284,33 @@ int ls100_beam_update(ls100_ctx* ctx, const ls100_beam_update_args* args, ls100_
 int ls100_quantize_weight(ls100_ctx* ctx, const float* w, int64_t rows, int64_t cols, float amax, int8_t* out_q,
                           int32_t* row_off /* optional [rows] */, ls100_stream_t stream);
 
+/* ------------------------------------------------------------- model level ---
+ * The LSModel interface of lightseq/inference/pywrapper/model_base.h:59-148 as plain C:
+ * create by name ("QuantTransformer", "QuantBert", "QuantGpt") from a weight file and
+ * max batch size, hand over caller-owned DEVICE pointers, run, read shapes back.
+ * Every function returns 0 or a negative code; ls100_model_last_error() gives the
+ * message of the last failure on the calling thread (what the C++ API throws as
+ * std::runtime_error). A model uses the device that is current at creation. */
+typedef struct ls100_model ls100_model;
+int ls100_model_create(const char* model_name, const char* weight_path, int max_batch_size, ls100_model** out);
+void ls100_model_destroy(ls100_model* m);
+const char* ls100_model_last_error(void);
+int ls100_model_set_input_ptr(ls100_model* m, int index, void* device_ptr);
+int ls100_model_set_input_shape(ls100_model* m, int index, const int32_t* dims, int ndim);
+int ls100_model_set_output_ptr(ls100_model* m, int index, void* device_ptr);
+int ls100_model_infer(ls100_model* m);
+int ls100_model_get_output_shape(ls100_model* m, int index, int32_t* dims /* >= 4 */, int* ndim);
+int ls100_model_get_output_max_shape(ls100_model* m, int index, int32_t* dims /* >= 4 */, int* ndim);
+int ls100_model_benchmark_mode(ls100_model* m, int on);
+
+/* Host-buffer convenience = what PyQuantTransformer::infer does
+ * (lightseq/inference/pywrapper/wrapper.cc:121-155): H2D copy of ids [batch, seq_len],
+ * Infer(), D2H copy of tokens [batch, 1, *out_len] (written densely into out_tokens, which
+ * must hold batch*max_step ints) and scores [batch]. Device staging buffers are owned by
+ * the model and allocated at creation. */
+int ls100_transformer_infer_host(ls100_model* m, const int32_t* ids, int batch, int seq_len, int32_t* out_tokens,
+                                 float* out_scores, int* out_len);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,291 @@
+// Layers of the int8 Transformer, with the constructor / operator() / before_forward /
+// forward shape of the reference's new-arch layers
+// (lightseq/csrc/layers_new/includes/transformer_encoder_layer.h:17-36,
+//  transformer_decoder_layer.h:33-61, generator_layer.cpp:5-110); the dataflow and the
+// clip-max placement follow the PyTorch fake-quant layers
+// (lightseq/training/ops/pytorch/torch_transformer_layers.py:630-679, 844-965).
+#pragma once
+#include "ops.h"
+
+namespace ls100 {
+
+struct LayerNormParams {
+  float* g = nullptr;
+  float* b = nullptr;
+  void load(Context& ctx, const WeightsFile& wf, const std::string& name, int hidden) {
+    g = upload_vec(ctx, wf, name + ".g", hidden);
+    b = upload_vec(ctx, wf, name + ".b", hidden);
+  }
+};
+
+// Buffers shared by every layer of a stack (sized for the maxima at construction).
+struct StackBuffers {
+  Variable* x = nullptr;       // fp32 residual stream [rows, H]
+  Variable* a_q = nullptr;     // int8 LayerNorm output [rows, H]
+  Variable* qkv_q = nullptr;   // int8 [rows, 3H]
+  Variable* attn_q = nullptr;  // int8 [rows, H]
+  Variable* h_q = nullptr;     // int8 [rows, F]
+  Variable* q_q = nullptr;     // int8 [rows, H] (cross-attention query)
+};
+
+// ---------------------------------------------------------------------------------------
+// Encoder layer (pre- or post-LN, ReLU or GELU). Also serves BERT (post-LN, GELU).
+class QuantTransformerEncoderLayer : public Layer {
+ public:
+  QuantTransformerEncoderLayer(ContextPtr ctx, const WeightsFile& wf, const std::string& prefix, int layer_id,
+                               int max_batch_tokens, int max_seq_len, int hidden, int heads, int ffn, bool is_pre_ln,
+                               const std::string& activation_fn, bool mask_future = false)
+      : Layer(prefix, ctx), hidden_(hidden), heads_(heads), ffn_(ffn), pre_ln_(is_pre_ln), causal_(mask_future),
+        act_(activation_fn == "gelu" ? Act::Gelu : Act::Relu), max_tokens_(max_batch_tokens) {
+    (void)layer_id;
+    (void)max_seq_len;
+    const bool relu = act_ == Act::Relu;
+    qkv_.load(*ctx, wf, prefix + ".qkv", false);
+    out_.load(*ctx, wf, prefix + ".out", false);
+    fc1_.load(*ctx, wf, prefix + ".fc1", false);
+    fc2_.load(*ctx, wf, prefix + ".fc2", relu);
+    ln1_.load(*ctx, wf, prefix + ".ln1", hidden);
+    ln2_.load(*ctx, wf, prefix + ".ln2", hidden);
+  }
+  // (inp, pad_mask) -> out, in place on the residual stream
+  Variable* operator()(StackBuffers* bufs, Variable* pad_mask) {
+    b_ = bufs;
+    pad_mask_ = pad_mask;
+    return bufs->x;
+  }
+  void before_forward(int batch, int seq) {
+    batch_ = batch;
+    seq_ = seq;
+    if ((long long)batch * seq > max_tokens_) throw std::runtime_error("batch tokens exceed max_batch_tokens");
+  }
+  const QLinearParams& qkv() const { return qkv_; }
+  const QLinearParams& fc1() const { return fc1_; }
+  const LayerNormParams& ln1() const { return ln1_; }
+
+  void forward() override {
+    if (!pre_ln_) throw std::runtime_error("post-LN encoder layers run through forward_post_ln");
+    const int rows = batch_ * seq_;
+    ls100_ctx* k = ctx_->kernels();
+    cudaStream_t s = ctx_->get_stream();
+    ln_quant(rows, ln1_, qkv_.amax_in);
+    gemm(b_->a_q, qkv_, rows, LS100_OUT_OUTQ_I8, b_->qkv_q, true, false, Act::None, nullptr, 0.f);
+    attention(rows);
+    gemm(b_->attn_q, out_, rows, LS100_OUT_F32, b_->x, true, true, Act::None, b_->x, 0.f);
+    ln_quant(rows, ln2_, fc1_.amax_in);
+    gemm(b_->a_q, fc1_, rows, act_ == Act::Relu ? LS100_OUT_REQ_U8 : LS100_OUT_REQ_S8, b_->h_q, true, true, act_,
+         nullptr, fc2_.s_in);
+    gemm(b_->h_q, fc2_, rows, LS100_OUT_F32, b_->x, true, true, Act::None, b_->x, 0.f);
+    (void)k;
+    (void)s;
+  }
+
+ protected:
+  void ln_quant(int rows, const LayerNormParams& ln, float amax) {
+    ls100_ln_quant_args a;
+    memset(&a, 0, sizeof(a));
+    a.x = b_->x->value<float>();
+    a.ldx = hidden_;
+    a.gamma = ln.g;
+    a.beta = ln.b;
+    a.rows = rows;
+    a.hidden = hidden_;
+    a.amax = amax;
+    a.out_q = b_->a_q->value<int8_t>();
+    a.ldq = hidden_;
+    LS_RC(ls100_ln_quant(ctx_->kernels(), &a, ctx_->get_stream()));
+  }
+  void gemm(Variable* in, const QLinearParams& p, int rows, int out_kind, Variable* out, bool out_quant, bool add_bias,
+            Act act, Variable* resid, float s_req) {
+    QuantLinearOp op(ctx_, name_ + ".gemm", &p, out_kind, act, out_quant, add_bias, s_req);
+    op(in, out, resid);
+    op.before_forward(rows);
+    op.forward();
+  }
+  void attention(int rows) {
+    (void)rows;
+    ls100_attn_self_args a;
+    memset(&a, 0, sizeof(a));
+    a.qkv = b_->qkv_q->value<int8_t>();
+    a.ld_qkv = 3 * hidden_;
+    a.s_qkv = qkv_.s_out;
+    a.bias = qkv_.bias;
+    a.pad_mask = pad_mask_ ? pad_mask_->value<uint8_t>() : nullptr;
+    a.batch = batch_;
+    a.seq = seq_;
+    a.heads = heads_;
+    a.causal = causal_ ? 1 : 0;
+    a.amax_out = out_.amax_in;
+    a.out = b_->attn_q->value<int8_t>();
+    a.ld_out = hidden_;
+    LS_RC(ls100_attn_self(ctx_->kernels(), &a, ctx_->get_stream()));
+  }
+
+  int hidden_, heads_, ffn_;
+  bool pre_ln_, causal_;
+  Act act_;
+  int max_tokens_;
+  QLinearParams qkv_, out_, fc1_, fc2_;
+  LayerNormParams ln1_, ln2_;
+  StackBuffers* b_ = nullptr;
+  Variable* pad_mask_ = nullptr;
+  int batch_ = 0, seq_ = 0;
+};
+
+// ---------------------------------------------------------------------------------------
+// Decoder layer, one token per row per call (incremental decoding with an int8 self-attention
+// cache and fp16 cross-attention keys/values computed once per request).
+class QuantTransformerDecoderLayer : public Layer {
+ public:
+  QuantTransformerDecoderLayer(ContextPtr ctx, const WeightsFile& wf, const std::string& prefix, int layer_id,
+                               int max_batch_tokens, int max_seq_len, int hidden, int heads, int ffn, bool is_pre_ln,
+                               const std::string& activation_fn, int max_batch_size, int beam_size, int max_step)
+      : Layer(prefix, ctx), hidden_(hidden), heads_(heads), ffn_(ffn), act_(activation_fn == "gelu" ? Act::Gelu : Act::Relu),
+        max_rows_(max_batch_size * beam_size), max_step_(max_step), max_enc_tokens_(max_batch_tokens) {
+    (void)layer_id;
+    (void)max_seq_len;
+    if (!is_pre_ln) throw std::runtime_error("post-LN decoder layers are not supported");
+    const bool relu = act_ == Act::Relu;
+    qkv_.load(*ctx, wf, prefix + ".qkv", false);
+    out_.load(*ctx, wf, prefix + ".out", false);
+    xq_.load(*ctx, wf, prefix + ".xq", false);
+    xk_.load(*ctx, wf, prefix + ".xk", false, false, false);
+    xv_.load(*ctx, wf, prefix + ".xv", false, false, false);
+    xout_.load(*ctx, wf, prefix + ".xout", false);
+    fc1_.load(*ctx, wf, prefix + ".fc1", false);
+    fc2_.load(*ctx, wf, prefix + ".fc2", relu);
+    ln1_.load(*ctx, wf, prefix + ".ln1", hidden);
+    ln2_.load(*ctx, wf, prefix + ".ln2", hidden);
+    ln3_.load(*ctx, wf, prefix + ".ln3", hidden);
+    amax_kv_ = wf.amax(prefix + ".kv");
+    s_kv_ = amax_kv_ / 127.0f;
+    const size_t cache = (size_t)max_rows_ * max_step * hidden;
+    k_cache_ = ctx->alloc_n<int8_t>(cache);
+    v_cache_ = ctx->alloc_n<int8_t>(cache);
+    LS_CUDA(cudaMemset(k_cache_, 0, cache));
+    LS_CUDA(cudaMemset(v_cache_, 0, cache));
+    enc_k_ = ctx->alloc_n<uint16_t>((size_t)max_batch_tokens * hidden);
+    enc_v_ = ctx->alloc_n<uint16_t>((size_t)max_batch_tokens * hidden);
+  }
+  void operator()(StackBuffers* bufs, Variable* src_pad_mask, const int32_t* anc, const int32_t* step_ptr) {
+    b_ = bufs;
+    pad_mask_ = src_pad_mask;
+    anc_ = anc;
+    step_ptr_ = step_ptr;
+  }
+  void before_forward(int batch, int beam, int src_len) {
+    batch_ = batch;
+    beam_ = beam;
+    src_len_ = src_len;
+    if (batch * beam > max_rows_) throw std::runtime_error("decoder rows exceed max_batch_size * beam_size");
+    if ((long long)batch * src_len > max_enc_tokens_) throw std::runtime_error("encoder tokens exceed max_batch_tokens");
+  }
+  // cross-attention keys / values of this layer from the encoder output (once per request)
+  void project_encoder_output(const float* enc_out) {
+    for (int which = 0; which < 2; ++which) {
+      const QLinearParams& p = which == 0 ? xk_ : xv_;
+      ls100_proj_f32_args a;
+      memset(&a, 0, sizeof(a));
+      a.x = enc_out;
+      a.ldx = hidden_;
+      a.w = p.w;
+      a.ldw = p.k;
+      a.s_w = p.s_w;
+      a.bias = p.bias;
+      a.m = batch_ * src_len_;
+      a.n = hidden_;
+      a.k = hidden_;
+      a.out = which == 0 ? enc_k_ : enc_v_;
+      a.ldo = hidden_;
+      LS_RC(ls100_proj_f32(ctx_->kernels(), &a, ctx_->get_stream()));
+    }
+  }
+  void forward() override {
+    const int rows = batch_ * beam_;
+    ln_quant(rows, ln1_, qkv_.amax_in);
+    // qkv = attention_quant(fq_out(acc) + bias): int8 with the KV-cache clip-max
+    gemm(b_->a_q, qkv_, rows, LS100_OUT_REQ_S8, b_->qkv_q, Act::None, nullptr, s_kv_);
+    {
+      ls100_attn_dec_args a;
+      memset(&a, 0, sizeof(a));
+      a.qkv = b_->qkv_q->value<int8_t>();
+      a.ld_qkv = 3 * hidden_;
+      a.s_kv = s_kv_;
+      a.k_cache = k_cache_;
+      a.v_cache = v_cache_;
+      a.anc = anc_;
+      a.step_ptr = step_ptr_;
+      a.rows = rows;
+      a.heads = heads_;
+      a.max_step = max_step_;
+      a.amax_out = out_.amax_in;
+      a.out = b_->attn_q->value<int8_t>();
+      a.ld_out = hidden_;
+      LS_RC(ls100_attn_dec(ctx_->kernels(), &a, ctx_->get_stream()));
+    }
+    gemm(b_->attn_q, out_, rows, LS100_OUT_F32, b_->x, Act::None, b_->x, 0.f);
+    ln_quant(rows, ln2_, xq_.amax_in);
+    gemm(b_->a_q, xq_, rows, LS100_OUT_OUTQ_I8, b_->q_q, Act::None, nullptr, 0.f, false);
+    {
+      ls100_attn_cross_args a;
+      memset(&a, 0, sizeof(a));
+      a.q = b_->q_q->value<int8_t>();
+      a.ld_q = hidden_;
+      a.s_q = xq_.s_out;
+      a.bias = xq_.bias;
+      a.k = enc_k_;
+      a.v = enc_v_;
+      a.ld_kv = hidden_;
+      a.pad_mask = pad_mask_->value<uint8_t>();
+      a.batch = batch_;
+      a.beam = beam_;
+      a.src_len = src_len_;
+      a.heads = heads_;
+      a.amax_out = xout_.amax_in;
+      a.out = b_->attn_q->value<int8_t>();
+      a.ld_out = hidden_;
+      LS_RC(ls100_attn_cross(ctx_->kernels(), &a, ctx_->get_stream()));
+    }
+    gemm(b_->attn_q, xout_, rows, LS100_OUT_F32, b_->x, Act::None, b_->x, 0.f);
+    ln_quant(rows, ln3_, fc1_.amax_in);
+    gemm(b_->a_q, fc1_, rows, act_ == Act::Relu ? LS100_OUT_REQ_U8 : LS100_OUT_REQ_S8, b_->h_q, act_, nullptr, fc2_.s_in);
+    gemm(b_->h_q, fc2_, rows, LS100_OUT_F32, b_->x, Act::None, b_->x, 0.f);
+  }
+
+ private:
+  void ln_quant(int rows, const LayerNormParams& ln, float amax) {
+    ls100_ln_quant_args a;
+    memset(&a, 0, sizeof(a));
+    a.x = b_->x->value<float>();
+    a.ldx = hidden_;
+    a.gamma = ln.g;
+    a.beta = ln.b;
+    a.rows = rows;
+    a.hidden = hidden_;
+    a.amax = amax;
+    a.out_q = b_->a_q->value<int8_t>();
+    a.ldq = hidden_;
+    LS_RC(ls100_ln_quant(ctx_->kernels(), &a, ctx_->get_stream()));
+  }
+  void gemm(Variable* in, const QLinearParams& p, int rows, int out_kind, Variable* out, Act act, Variable* resid,
+            float s_req, bool add_bias = true) {
+    QuantLinearOp op(ctx_, name_ + ".gemm", &p, out_kind, act, true, add_bias, s_req);
+    op(in, out, resid);
+    op.before_forward(rows);
+    op.forward();
+  }
+  int hidden_, heads_, ffn_;
+  Act act_;
+  int max_rows_, max_step_, max_enc_tokens_;
+  QLinearParams qkv_, out_, xq_, xk_, xv_, xout_, fc1_, fc2_;
+  LayerNormParams ln1_, ln2_, ln3_;
+  float amax_kv_ = 0, s_kv_ = 0;
+  int8_t *k_cache_ = nullptr, *v_cache_ = nullptr;
+  uint16_t *enc_k_ = nullptr, *enc_v_ = nullptr;
+  StackBuffers* b_ = nullptr;
+  Variable* pad_mask_ = nullptr;
+  const int32_t* anc_ = nullptr;
+  const int32_t* step_ptr_ = nullptr;
+  int batch_ = 0, beam_ = 0, src_len_ = 0;
+};
+
+}  // namespace ls100

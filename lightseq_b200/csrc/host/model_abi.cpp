@@ -1,0 +1,151 @@
+// C ABI over LSModel / LSModelFactory (see include/ls100.h, "model level").
+#include <cuda_runtime.h>
+#include <string.h>
+
+#include <memory>
+#include <string>
+
+#include "../../../include/ls100.h"
+#include "lsflow.h"
+#include "model_base.h"
+
+namespace ls100 {
+const float* quant_transformer_encoder_output(LSModel* m);
+const int8_t* quant_transformer_last_logits(LSModel* m, int* ld);
+int quant_transformer_steps_run(LSModel* m);
+}  // namespace ls100
+
+struct ls100_model {
+  std::unique_ptr<ls100::LSModel> model;
+  // staging buffers of the *_host entry points
+  void* d_in = nullptr;
+  void* d_out0 = nullptr;
+  void* d_out1 = nullptr;
+  size_t in_bytes = 0, out0_bytes = 0, out1_bytes = 0;
+  int device = 0;
+};
+
+static thread_local std::string g_last_error;
+
+template <typename F>
+static int guarded(F&& f) {
+  try {
+    f();
+    return LS100_OK;
+  } catch (const std::exception& e) {
+    g_last_error = e.what();
+    return LS100_ERR_BAD_ARG;
+  } catch (...) {
+    g_last_error = "unknown error";
+    return LS100_ERR_BAD_ARG;
+  }
+}
+
+static size_t prod(const std::vector<int>& v) {
+  size_t n = 1;
+  for (int d : v) n *= (size_t)d;
+  return n;
+}
+
+extern "C" const char* ls100_model_last_error(void) { return g_last_error.c_str(); }
+
+extern "C" int ls100_model_create(const char* name, const char* path, int max_bs, ls100_model** out) {
+  if (!name || !path || !out) return LS100_ERR_BAD_ARG;
+  *out = nullptr;
+  return guarded([&] {
+    std::unique_ptr<ls100_model> h(new ls100_model());
+    LS_CUDA(cudaGetDevice(&h->device));
+    h->model.reset(ls100::LSModelFactory::GetInstance().CreateModel(name, path, max_bs));
+    ls100::LSModel& m = *h->model;
+    h->in_bytes = prod(m.get_input_max_shape(0)) * 4;
+    LS_CUDA(cudaMalloc(&h->d_in, h->in_bytes));
+    h->out0_bytes = prod(m.get_output_max_shape(0)) * 4;
+    LS_CUDA(cudaMalloc(&h->d_out0, h->out0_bytes));
+    if (m.get_output_size() > 1) {
+      h->out1_bytes = prod(m.get_output_max_shape(1)) * 4;
+      LS_CUDA(cudaMalloc(&h->d_out1, h->out1_bytes));
+    }
+    *out = h.release();
+  });
+}
+
+extern "C" void ls100_model_destroy(ls100_model* m) {
+  if (!m) return;
+  cudaSetDevice(m->device);
+  m->model.reset();
+  cudaFree(m->d_in);
+  cudaFree(m->d_out0);
+  cudaFree(m->d_out1);
+  delete m;
+}
+
+extern "C" int ls100_model_set_input_ptr(ls100_model* m, int index, void* p) {
+  if (!m) return LS100_ERR_BAD_ARG;
+  return guarded([&] { m->model->set_input_ptr(index, p); });
+}
+extern "C" int ls100_model_set_input_shape(ls100_model* m, int index, const int32_t* dims, int nd) {
+  if (!m || !dims || nd < 0) return LS100_ERR_BAD_ARG;
+  return guarded([&] { m->model->set_input_shape(index, std::vector<int>(dims, dims + nd)); });
+}
+extern "C" int ls100_model_set_output_ptr(ls100_model* m, int index, void* p) {
+  if (!m) return LS100_ERR_BAD_ARG;
+  return guarded([&] { m->model->set_output_ptr(index, p); });
+}
+extern "C" int ls100_model_infer(ls100_model* m) {
+  if (!m) return LS100_ERR_BAD_ARG;
+  return guarded([&] { m->model->Infer(); });
+}
+static int copy_shape(const std::vector<int>& s, int32_t* dims, int* nd) {
+  if (s.size() > 4) return LS100_ERR_UNSUPPORTED;
+  for (size_t i = 0; i < s.size(); ++i) dims[i] = s[i];
+  *nd = (int)s.size();
+  return LS100_OK;
+}
+extern "C" int ls100_model_get_output_shape(ls100_model* m, int index, int32_t* dims, int* nd) {
+  if (!m || !dims || !nd) return LS100_ERR_BAD_ARG;
+  int rc = LS100_OK;
+  int g = guarded([&] { rc = copy_shape(m->model->get_output_shape(index), dims, nd); });
+  return g ? g : rc;
+}
+extern "C" int ls100_model_get_output_max_shape(ls100_model* m, int index, int32_t* dims, int* nd) {
+  if (!m || !dims || !nd) return LS100_ERR_BAD_ARG;
+  int rc = LS100_OK;
+  int g = guarded([&] { rc = copy_shape(m->model->get_output_max_shape(index), dims, nd); });
+  return g ? g : rc;
+}
+extern "C" int ls100_model_benchmark_mode(ls100_model* m, int on) {
+  if (!m) return LS100_ERR_BAD_ARG;
+  return guarded([&] { m->model->benchmark_mode(on != 0); });
+}
+
+extern "C" int ls100_transformer_infer_host(ls100_model* m, const int32_t* ids, int batch, int seq_len,
+                                            int32_t* out_tokens, float* out_scores, int* out_len) {
+  if (!m || !ids || !out_tokens || !out_scores || !out_len || batch < 1 || seq_len < 1) return LS100_ERR_BAD_ARG;
+  return guarded([&] {
+    const size_t nb = (size_t)batch * seq_len * 4;
+    if (nb > m->in_bytes) throw std::runtime_error("input larger than max_batch_size x max_step");
+    LS_CUDA(cudaSetDevice(m->device));
+    LS_CUDA(cudaMemcpy(m->d_in, ids, nb, cudaMemcpyHostToDevice));
+    m->model->set_input_ptr(0, m->d_in);
+    m->model->set_input_shape(0, {batch, seq_len});
+    m->model->set_output_ptr(0, m->d_out0);
+    m->model->set_output_ptr(1, m->d_out1);
+    m->model->Infer();
+    const std::vector<int> shp = m->model->get_output_shape(0);
+    const int n = shp.at(2);
+    LS_CUDA(cudaMemcpy(out_tokens, m->d_out0, (size_t)batch * n * 4, cudaMemcpyDeviceToHost));
+    LS_CUDA(cudaMemcpy(out_scores, m->d_out1, (size_t)batch * 4, cudaMemcpyDeviceToHost));
+    *out_len = n;
+  });
+}
+
+// ---- test-only taps (not declared in include/ls100.h): device pointers valid until the next Infer()
+extern "C" const float* ls100_debug_encoder_output(ls100_model* m) {
+  return m ? ls100::quant_transformer_encoder_output(m->model.get()) : nullptr;
+}
+extern "C" const int8_t* ls100_debug_last_logits(ls100_model* m, int* ld) {
+  return m ? ls100::quant_transformer_last_logits(m->model.get(), ld) : nullptr;
+}
+extern "C" int ls100_debug_steps_run(ls100_model* m) {
+  return m ? ls100::quant_transformer_steps_run(m->model.get()) : -1;
+}

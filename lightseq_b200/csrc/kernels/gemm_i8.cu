@@ -311,13 +311,7 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
 template <int BN, int STAGES>
 static int launch_gemm(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cudaStream_t stream) {
   using SM = GemmSmem<BN, STAGES>;
-  static bool attr_set[16] = {false};
   auto kern = gemm_i8_tc_kernel<BN, STAGES>;
-  if (ctx->device < 16 && !attr_set[ctx->device]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL) != cudaSuccess)
-      return LS100_ERR_CUDA;
-    attr_set[ctx->device] = true;
-  }
   CUtensorMap ta, tb;
   int rc = ls100_get_tmap_u8(ctx, a->a, (uint64_t)a->m, (uint64_t)a->k, (uint64_t)a->lda, BM, BK, &ta);
   if (rc) return rc;
@@ -344,7 +338,26 @@ static int launch_gemm(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cudaStream_t
   return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
 
+template <int BN, int STAGES>
+static int set_smem_attr() {
+  return cudaFuncSetAttribute(gemm_i8_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              GemmSmem<BN, STAGES>::TOTAL) == cudaSuccess
+             ? LS100_OK
+             : LS100_ERR_CUDA;
+}
+
 }  // namespace ls100
+
+// Opts every tile variant into its dynamic shared-memory size on the current device.
+// Called once from ls100_ctx_create so that no attribute call happens inside a stream capture.
+int ls100_gemm_i8_init_device() {
+  using namespace ls100;
+  int rc = set_smem_attr<256, 4>();
+  if (!rc) rc = set_smem_attr<128, 3>();
+  if (!rc) rc = set_smem_attr<64, 4>();
+  if (!rc) rc = set_smem_attr<32, 4>();
+  return rc;
+}
 
 extern "C" int ls100_gemm_i8(ls100_ctx* ctx, const ls100_gemm_i8_args* a, ls100_stream_t stream_) {
   using namespace ls100;

@@ -1,0 +1,73 @@
+// pybind11 module with the class surface of the reference's `lightseq.inference`
+// (lightseq/inference/pywrapper/wrapper.cc:85-156 PyQuantTransformer, :919-996 module
+// definition): QuantTransformer(weight_path, max_batch_size).infer(int32[B,S]) ->
+// (int32[B,1,L], float32[B,1]). Each call copies the ids host->device, runs the model and
+// copies the results back, like the reference wrapper. The classes sit on the C ABI of
+// libls100.so (include/ls100.h, "model level").
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "ls100.h"
+
+namespace py = pybind11;
+
+namespace {
+
+void check(int rc, const char* what) {
+  if (rc != LS100_OK) {
+    const char* msg = ls100_model_last_error();
+    throw std::runtime_error(std::string(what) + ": " + ((msg && *msg) ? msg : ls100_strerror(rc)));
+  }
+}
+
+class PyQuantTransformer {
+ public:
+  PyQuantTransformer(const std::string& weight_path, int max_batch_size) {
+    check(ls100_model_create("QuantTransformer", weight_path.c_str(), max_batch_size, &m_), "QuantTransformer");
+    int32_t dims[4];
+    int nd = 0;
+    check(ls100_model_get_output_max_shape(m_, 0, dims, &nd), "get_output_max_shape");
+    max_step_ = dims[2];
+  }
+  ~PyQuantTransformer() { ls100_model_destroy(m_); }
+  PyQuantTransformer(const PyQuantTransformer&) = delete;
+  PyQuantTransformer& operator=(const PyQuantTransformer&) = delete;
+
+  std::tuple<py::array_t<int>, py::array_t<float>> infer(
+      py::array_t<int, py::array::c_style | py::array::forcecast> input_seq) {
+    if (input_seq.ndim() != 2) throw std::runtime_error("input_seq must be a 2-D int32 array [batch, seq_len]");
+    const int batch = (int)input_seq.shape(0), seq = (int)input_seq.shape(1);
+    std::vector<int32_t> toks((size_t)batch * max_step_);
+    py::array_t<float> scores({batch, 1});
+    int n = 0;
+    {
+      py::gil_scoped_release nogil;
+      check(ls100_transformer_infer_host(m_, input_seq.data(), batch, seq, toks.data(), scores.mutable_data(), &n),
+            "infer");
+    }
+    py::array_t<int> tokens({batch, 1, n});
+    std::copy(toks.begin(), toks.begin() + (size_t)batch * n, tokens.mutable_data());
+    return std::make_tuple(tokens, scores);
+  }
+  void benchmark_mode(bool on) { check(ls100_model_benchmark_mode(m_, on ? 1 : 0), "benchmark_mode"); }
+  std::uintptr_t handle() const { return reinterpret_cast<std::uintptr_t>(m_); }
+
+ private:
+  ls100_model* m_ = nullptr;
+  int max_step_ = 0;
+};
+
+}  // namespace
+
+PYBIND11_MODULE(_ls100_py, m) {
+  m.doc() = "B200 int8 inference engine with the lightseq.inference class surface";
+  py::class_<PyQuantTransformer>(m, "QuantTransformer")
+      .def(py::init<const std::string&, int>(), py::arg("weight_path"), py::arg("max_batch_size"))
+      .def("infer", &PyQuantTransformer::infer, py::arg("input_seq"))
+      .def("benchmark_mode", &PyQuantTransformer::benchmark_mode)
+      .def_property_readonly("_handle", &PyQuantTransformer::handle);
+}

@@ -228,6 +228,7 @@ def make_transformer(path: Optional[str] = None, *, hidden=512, heads=8, ffn=204
                 act_gelu=float(act == "gelu"), pre_ln=1.0, beam=beam, length_penalty=length_penalty,
                 extra_decode_length=extra_decode_length, max_step=max_step, pad_id=pad_id, start_id=start_id,
                 end_id=end_id)
+    w["pos"] = sinusoid_table(max_step, hidden)
     if path is not None:
         from . import weights
 
