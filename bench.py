@@ -1,0 +1,406 @@
+#!/usr/bin/env python
+"""Benchmark of the int8 Transformer-base beam-4 generation path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" = one whole generation (encoder + beam-search decode loop) of one batch of the
+benchmark workload: 128 source sentences, lengths U{20..60}, ids U[4, 32000), beam 4, up to
+source length + 50 output tokens, on a seeded synthetic Transformer-base (6+6 layers, hidden
+512, 8 heads, FFN 2048, ReLU, pre-LN, shared 32000 vocabulary, clip-max = 4 x std).
+
+Prints ONE JSON line (rank 0). ``value`` = generated tokens/s over all ranks with the source
+ids already in HBM (model-level C ABI, device pointers); ``e2e`` = the same through the
+pybind ``QuantTransformer.infer(numpy ids)`` call a user makes, host->device and
+device->host copies inside the timed region. ``roofline`` is the dominant decode kernel timed
+alone with CUDA events on the shapes of this workload; ``cpu_baseline`` is the numpy oracle of
+the same path on the host cores, on a bounded sample.
+
+``--impl reference`` times the reference path's CPU restatement (oracle/) on the host cores;
+the reference's own implementation is a Python/PyTorch module tree that cannot travel to the
+GPU box, so the oracle port pinned to it (tests/golden) stands in.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "int8 Transformer-base generated tokens/sec (beam 4)"
+WORKLOAD = dict(batch=128, min_len=20, max_len=60, vocab=32000, beam=4, extra_decode_length=50, max_step=128)
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_model_file(tmpdir: str):
+    from lightseq_b200 import synth
+
+    path = os.path.join(tmpdir, "transformer_base_int8.ls100")
+    calib = synth.transformer_inputs(batch=8, min_len=WORKLOAD["min_len"], max_len=WORKLOAD["max_len"],
+                                     vocab=WORKLOAD["vocab"], seed=4321)
+    conf, amax, w = synth.make_transformer(path, beam=WORKLOAD["beam"], extra_decode_length=WORKLOAD["extra_decode_length"],
+                                           max_step=WORKLOAD["max_step"], vocab=WORKLOAD["vocab"], seed=1234,
+                                           calib_src=calib)
+    return path, conf, amax, w
+
+
+def batch_for_rank(rank: int) -> np.ndarray:
+    from lightseq_b200 import synth
+
+    return synth.transformer_inputs(batch=WORKLOAD["batch"], min_len=WORKLOAD["min_len"], max_len=WORKLOAD["max_len"],
+                                    vocab=WORKLOAD["vocab"], seed=4321 + 1000 * rank)
+
+
+def count_tokens(tok: np.ndarray, end_id: int) -> int:
+    """Tokens of the best beam up to and including the first EOS (all of them if none)."""
+    t = tok.reshape(tok.shape[0], -1)
+    is_eos = t == end_id
+    first = np.where(is_eos.any(1), is_eos.argmax(1) + 1, t.shape[1])
+    return int(first.sum())
+
+
+# ------------------------------------------------------------------------------ CPU arm
+def cpu_generate_sample(conf, amax, w, src, n_sent: int):
+    from oracle import model as om
+
+    cfg = om.Config(hidden=int(conf["hidden"]), heads=int(conf["heads"]), ffn=int(conf["ffn"]), n_enc=int(conf["n_enc"]),
+                    n_dec=int(conf["n_dec"]), vocab=int(conf["vocab"]), max_step=int(conf["max_step"]),
+                    beam=int(conf["beam"]), length_penalty=float(conf["length_penalty"]),
+                    extra_decode_length=int(conf["extra_decode_length"]), pad_id=int(conf["pad_id"]),
+                    start_id=int(conf["start_id"]), end_id=int(conf["end_id"]))
+    st = om.State(w=w, amax=amax)
+    m = om.Seq2Seq(cfg, st)
+    sub = src[:n_sent]
+    m.generate(sub[:1, :4], max_len=3)  # quantise the weights outside the timed region
+    t0 = time.perf_counter()
+    tok, score, n = m.generate(sub)
+    dt = time.perf_counter() - t0
+    return count_tokens(tok, cfg.end_id), dt, tok
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    with tempfile.TemporaryDirectory() as td:
+        _, conf, amax, w = build_model_file(td)
+    src = batch_for_rank(0)
+    n_sent = 4
+    for _ in range(min(args.warmup, 1)):
+        cpu_generate_sample(conf, amax, w, src, 1)
+    toks, secs = 0, 0.0
+    for _ in range(args.steps):
+        n, dt, _ = cpu_generate_sample(conf, amax, w, src, n_sent)
+        toks += n
+        secs += dt
+    val = toks / secs
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * secs / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "transformer-base int8 beam-4 generation, batch 128 x src 20..60 (+50)",
+                   "sample": f"first {n_sent} sentences of the batch per step"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+                         "sample": f"first {n_sent} of 128 sentences, full beam-4 generation, numpy oracle"},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ------------------------------------------------------------------------------ GPU arm
+def time_attn_dec_kernel(torch, L, ctx, heads: int, rows: int, max_step: int, step: int, iters: int = 30):
+    """Average duration of the decoder self-attention kernel at decode position ``step`` (the dominant
+    HBM-bound kernel of a decode step), timed alone with CUDA events on the default stream. A rotating
+    set of caches larger than L2 keeps every launch reading from HBM."""
+    H = heads * 64
+    n_sets = max(2, int(200e6 // (2 * rows * max_step * H)) + 1)
+    kcs = [torch.randint(-127, 128, (rows, heads, max_step, 64), dtype=torch.int8, device="cuda") for _ in range(n_sets)]
+    vcs = [torch.randint(-127, 128, (rows, heads, max_step, 64), dtype=torch.int8, device="cuda") for _ in range(n_sets)]
+    qkv = torch.randint(-127, 128, (rows, 3 * H), dtype=torch.int8, device="cuda")
+    out = torch.empty((rows, H), dtype=torch.int8, device="cuda")
+    dstep = torch.tensor([step], dtype=torch.int32, device="cuda")
+
+    def launch(i):
+        a = L.AttnDecArgs(qkv=qkv.data_ptr(), ld_qkv=3 * H, s_kv=0.03, k_cache=kcs[i % n_sets].data_ptr(),
+                          v_cache=vcs[i % n_sets].data_ptr(), anc=None, step_ptr=dstep.data_ptr(), rows=rows, heads=heads,
+                          max_step=max_step, amax_out=1.0, out=out.data_ptr(), ld_out=H)
+        L.call("ls100_attn_dec", ctx, a, torch.cuda.current_stream().cuda_stream)
+
+    for i in range(3):
+        launch(i)
+    torch.cuda.synchronize()
+    evs = []
+    for i in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        launch(i)
+        e1.record()
+        evs.append((e0, e1))
+    torch.cuda.synchronize()
+    ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    algo_bytes = rows * heads * 64 * (2 * (step + 1) + 3)  # K and V read once, q read, k/v appended, out written
+    return ms, algo_bytes
+
+
+def run_ours(args):
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    from lightseq_b200 import _lib as L
+    import lightseq_b200.inference as lsi
+
+    td = tempfile.mkdtemp(prefix=f"ls100_bench_r{rank}_")
+    path, conf, amax, w = build_model_file(td)
+    src = batch_for_rank(rank)
+    B, S = src.shape
+    end_id = int(conf["end_id"])
+    model = lsi.QuantTransformer(path, B)
+    handle = C.c_void_p(model._handle)
+    lib = L.lib
+    lib.ls100_model_get_stream.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+    lib.ls100_model_set_input_ptr.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+    lib.ls100_model_set_output_ptr.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+    lib.ls100_model_set_input_shape.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_int32), C.c_int]
+    lib.ls100_model_infer.argtypes = [C.c_void_p]
+    lib.ls100_model_get_output_shape.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int)]
+    lib.ls100_debug_steps_run.argtypes = [C.c_void_p]
+    sptr = C.c_void_p()
+    L.check(lib.ls100_model_get_stream(handle, C.byref(sptr)), "get_stream")
+    mstream = torch.cuda.ExternalStream(sptr.value)
+
+    d_src = torch.from_numpy(src).cuda()
+    max_step = int(conf["max_step"])
+    d_tok = torch.empty((B, int(conf["beam"]), max_step), dtype=torch.int32, device="cuda")
+    d_score = torch.empty((B, int(conf["beam"])), dtype=torch.float32, device="cuda")
+    L.check(lib.ls100_model_set_input_ptr(handle, 0, d_src.data_ptr()), "set_input_ptr")
+    L.check(lib.ls100_model_set_output_ptr(handle, 0, d_tok.data_ptr()), "set_output_ptr")
+    L.check(lib.ls100_model_set_output_ptr(handle, 1, d_score.data_ptr()), "set_output_ptr")
+    dims = (C.c_int32 * 2)(B, S)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")  # > 126 MB L2
+
+    def infer_device():
+        L.check(lib.ls100_model_set_input_shape(handle, 0, dims, 2), "set_input_shape")
+        rc = lib.ls100_model_infer(handle)
+        if rc != 0:
+            raise RuntimeError(lib.ls100_model_last_error())
+        od = (C.c_int32 * 4)()
+        nd = C.c_int()
+        lib.ls100_model_get_output_shape(handle, 0, od, C.byref(nd))
+        return int(od[2])
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident arm
+    n_warm = args.warmup if args.quick else max(args.warmup, 3)
+    for _ in range(n_warm):
+        n_out = infer_device()
+    steps_per_infer = lib.ls100_debug_steps_run(handle)
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    total_ms, tokens = 0.0, 0
+    for _ in range(args.steps):
+        flush.fill_(1)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(mstream)
+        n_out = infer_device()
+        e1.record(mstream)
+        e1.synchronize()
+        total_ms += e0.elapsed_time(e1)
+        tok = d_tok.view(-1)[: B * n_out].view(B, n_out).cpu().numpy()
+        tokens += count_tokens(tok, end_id)
+    barrier()
+    clocks = sampler.stop()
+    t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
+    tk = torch.tensor([float(tokens)], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tk, op=dist.ReduceOp.SUM)
+    max_ms, all_tokens = float(t.item()), float(tk.item())
+    value = all_tokens / (max_ms / 1e3)
+
+    if args.quick:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": "tokens/s", "ms_per_step": max_ms / args.steps,
+                              "quick": True, "decode_steps": steps_per_infer}), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return 0
+
+    # ---- end-to-end arm: numpy ids in, numpy tokens out, through the pybind call
+    for _ in range(2):
+        model.infer(src)
+    barrier()
+    e2e_tokens, t0 = 0, time.perf_counter()
+    e2e_ms = 0.0
+    d2h = 0
+    for _ in range(args.steps):
+        flush.fill_(1)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        tok, score = model.infer(src)
+        e2e_ms += (time.perf_counter() - t0) * 1e3
+        e2e_tokens += count_tokens(tok, end_id)
+        d2h = tok.nbytes + score.nbytes
+    barrier()
+    t = torch.tensor([e2e_ms], dtype=torch.float64, device="cuda")
+    tk = torch.tensor([float(e2e_tokens)], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tk, op=dist.ReduceOp.SUM)
+    e2e_value = float(tk.item()) / (float(t.item()) / 1e3)
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return 0
+
+    # ---- roofline of the dominant decode kernel, and the CPU baseline (rank 0, N = 1 only for the latter)
+    hbm_peak, peak_src = peaks()
+    ctx = L.Context(local)
+    mid_step = max(steps_per_infer // 2, 1)
+    ms_k, algo = time_attn_dec_kernel(torch, L, ctx, int(conf["heads"]), B * int(conf["beam"]), max_step, mid_step)
+    achieved = algo / (ms_k / 1e3) / 1e9
+    traffic = None
+    prof = ROOT / "profiles" / "attn_dec_traffic.json"
+    if prof.exists():
+        try:
+            pj = json.loads(prof.read_text())
+            traffic = pj["dram_bytes_per_position_row"] * (mid_step + 1) * B * int(conf["beam"])
+        except Exception:
+            traffic = None
+    roofline = {"kernel": "attn_dec_kernel (decoder self-attention over the int8 KV cache)", "bound": "hbm",
+                "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "traffic": traffic,
+                "peak_source": peak_src, "launch_us": ms_k * 1e3,
+                "how": f"kernel timed alone with CUDA events at decode position {mid_step} (mid-sequence), rows "
+                       f"{B * int(conf['beam'])}, rotating caches larger than L2; algorithmic bytes = rows*H*(2*L+3)"}
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        n_sent = 4
+        n, dt, _ = cpu_generate_sample(conf, amax, w, src, n_sent)
+        cpu = {"value": n / dt, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+               "sample": f"first {n_sent} of {B} sentences, full beam-4 generation with the numpy oracle ({dt:.1f} s)"}
+    # kernels of this library launched in the timed region (per generation: encoder + cross-KV + decode steps)
+    n_enc, n_dec = int(conf["n_enc"]), int(conf["n_dec"])
+    per_infer = (1 + 7 * n_enc + 1) + 2 * n_dec + steps_per_infer * (1 + 11 * n_dec + 2 + 2)
+    line = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": n_warm,
+        "ms_per_step": max_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "transformer-base int8 (6+6 layers, H512, 8 heads, FFN2048, V32000) beam-4 generation, "
+                               "batch 128 per GPU, src len U{20..60}, max out = src+50",
+                   "global_batch": B * world, "src_len_padded": S, "decode_steps": steps_per_infer,
+                   "tokens_per_sentence": n_out, "parallelism": f"replicas x{world} (batch sharding, no collective)",
+                   "l2": "256 MB buffer written between timed iterations; per-step working set (KV caches, logits) > L2"},
+        "clocks": clocks, "gpu_launches": per_infer * args.steps,
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": int(src.nbytes), "d2h_bytes_per_step": int(d2h)},
+        "roofline": roofline, "cpu_baseline": cpu,
+    }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--quick", action="store_true",
+                    help="device-resident arm only, warm-up exactly as given (for profiler launch lists)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

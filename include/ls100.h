@@ -191,7 +191,7 @@ typedef struct {
 int ls100_attn_dec(ls100_ctx* ctx, const ls100_attn_dec_args* args, ls100_stream_t stream);
 
 /* ------------------------------------------------------------- cross attention ---
- * rows = batch*beam queries (q int8 * s_q + bias) against the fp16 encoder keys/values
+ * rows = batch*beam queries (q int8 * s_q + bias) against the fp32 encoder keys/values
  * [batch*src_len, hidden] of one decoder layer, source key-padding mask, output int8.
  * Replaces ker_arrange_encdec_q_i8I + cublasGemmStridedBatchedEx x2 +
  * ker_correlation_softmax_encdec + ker_arrange_atten_output_i8O
@@ -201,7 +201,7 @@ typedef struct {
   int64_t ld_q;
   float s_q;
   const float* bias; /* [hidden] */
-  const void* k;     /* fp16 [batch*src_len, hidden] */
+  const void* k;     /* fp32 [batch*src_len, hidden] */
   const void* v;
   int64_t ld_kv; /* elements */
   const uint8_t* pad_mask; /* [batch, src_len] */
@@ -213,7 +213,7 @@ typedef struct {
 int ls100_attn_cross(ls100_ctx* ctx, const ls100_attn_cross_args* args, ls100_stream_t stream);
 
 /* -------------------------------------------- fp32 x fake-quant weight projection ---
- * out_f16[M,N] = (x[M,K] . Wq[N,K]^T) * s_w + bias : the weight-only-quantised k_proj /
+ * out_f32[M,N] = (x[M,K] . Wq[N,K]^T) * s_w + bias : the weight-only-quantised k_proj /
  * v_proj of the decoder's cross attention, run once per request. Replaces the fp16
  * cublasGemmEx + ker_arrange_encdec_kv of QuantDecoder::project_encoder_output
  * (lightseq/inference/model/quant_decoder.cc.cu:489-520); restates QuantLinear with
@@ -226,7 +226,7 @@ typedef struct {
   float s_w;
   const float* bias;
   int32_t m, n, k;
-  void* out; /* fp16 */
+  void* out; /* fp32 */
   int64_t ldo;
 } ls100_proj_f32_args;
 int ls100_proj_f32(ls100_ctx* ctx, const ls100_proj_f32_args* args, ls100_stream_t stream);
@@ -302,6 +302,8 @@ int ls100_model_infer(ls100_model* m);
 int ls100_model_get_output_shape(ls100_model* m, int index, int32_t* dims /* >= 4 */, int* ndim);
 int ls100_model_get_output_max_shape(ls100_model* m, int index, int32_t* dims /* >= 4 */, int* ndim);
 int ls100_model_benchmark_mode(ls100_model* m, int on);
+/* The cudaStream_t every kernel of this model is launched on (for event timing by the caller). */
+int ls100_model_get_stream(ls100_model* m, ls100_stream_t* stream);
 
 /* Host-buffer convenience = what PyQuantTransformer::infer does
  * (lightseq/inference/pywrapper/wrapper.cc:121-155): H2D copy of ids [batch, seq_len],

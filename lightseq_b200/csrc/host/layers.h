@@ -133,7 +133,7 @@ class QuantTransformerEncoderLayer : public Layer {
 
 // ---------------------------------------------------------------------------------------
 // Decoder layer, one token per row per call (incremental decoding with an int8 self-attention
-// cache and fp16 cross-attention keys/values computed once per request).
+// cache and fp32 cross-attention keys/values computed once per request).
 class QuantTransformerDecoderLayer : public Layer {
  public:
   QuantTransformerDecoderLayer(ContextPtr ctx, const WeightsFile& wf, const std::string& prefix, int layer_id,
@@ -163,8 +163,8 @@ class QuantTransformerDecoderLayer : public Layer {
     v_cache_ = ctx->alloc_n<int8_t>(cache);
     LS_CUDA(cudaMemset(k_cache_, 0, cache));
     LS_CUDA(cudaMemset(v_cache_, 0, cache));
-    enc_k_ = ctx->alloc_n<uint16_t>((size_t)max_batch_tokens * hidden);
-    enc_v_ = ctx->alloc_n<uint16_t>((size_t)max_batch_tokens * hidden);
+    enc_k_ = ctx->alloc_n<float>((size_t)max_batch_tokens * hidden);
+    enc_v_ = ctx->alloc_n<float>((size_t)max_batch_tokens * hidden);
   }
   void operator()(StackBuffers* bufs, Variable* src_pad_mask, const int32_t* anc, const int32_t* step_ptr) {
     b_ = bufs;
@@ -280,7 +280,7 @@ class QuantTransformerDecoderLayer : public Layer {
   LayerNormParams ln1_, ln2_, ln3_;
   float amax_kv_ = 0, s_kv_ = 0;
   int8_t *k_cache_ = nullptr, *v_cache_ = nullptr;
-  uint16_t *enc_k_ = nullptr, *enc_v_ = nullptr;
+  float *enc_k_ = nullptr, *enc_v_ = nullptr;
   StackBuffers* b_ = nullptr;
   Variable* pad_mask_ = nullptr;
   const int32_t* anc_ = nullptr;

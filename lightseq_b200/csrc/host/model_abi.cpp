@@ -10,9 +10,13 @@
 #include "model_base.h"
 
 namespace ls100 {
+cudaStream_t model_stream(LSModel* m);
 const float* quant_transformer_encoder_output(LSModel* m);
 const int8_t* quant_transformer_last_logits(LSModel* m, int* ld);
 int quant_transformer_steps_run(LSModel* m);
+int quant_transformer_set_step_limit(LSModel* m, int n);
+int quant_transformer_beam_state(LSModel* m, const int32_t** alive, const int32_t** anc, const float** probs,
+                                 const float** score, int* max_step, int* beam);
 }  // namespace ls100
 
 struct ls100_model {
@@ -118,6 +122,13 @@ extern "C" int ls100_model_benchmark_mode(ls100_model* m, int on) {
   return guarded([&] { m->model->benchmark_mode(on != 0); });
 }
 
+extern "C" int ls100_model_get_stream(ls100_model* m, ls100_stream_t* stream) {
+  if (!m || !stream) return LS100_ERR_BAD_ARG;
+  cudaStream_t s = ls100::model_stream(m->model.get());
+  *stream = (ls100_stream_t)s;
+  return LS100_OK;
+}
+
 extern "C" int ls100_transformer_infer_host(ls100_model* m, const int32_t* ids, int batch, int seq_len,
                                             int32_t* out_tokens, float* out_scores, int* out_len) {
   if (!m || !ids || !out_tokens || !out_scores || !out_len || batch < 1 || seq_len < 1) return LS100_ERR_BAD_ARG;
@@ -148,4 +159,11 @@ extern "C" const int8_t* ls100_debug_last_logits(ls100_model* m, int* ld) {
 }
 extern "C" int ls100_debug_steps_run(ls100_model* m) {
   return m ? ls100::quant_transformer_steps_run(m->model.get()) : -1;
+}
+extern "C" int ls100_debug_set_step_limit(ls100_model* m, int n) {
+  return m ? ls100::quant_transformer_set_step_limit(m->model.get(), n) : -1;
+}
+extern "C" int ls100_debug_beam_state(ls100_model* m, const int32_t** alive, const int32_t** anc, const float** probs,
+                                      const float** score, int* max_step, int* beam) {
+  return m ? ls100::quant_transformer_beam_state(m->model.get(), alive, anc, probs, score, max_step, beam) : -1;
 }

@@ -154,7 +154,8 @@ class QuantTransformer : public LSModel {
 
     // _batch_max_decode_length of the reference (quant_decoder.cc.cu:428-430)
     const int max_decode = std::min(max_step_, S + extra_len_) - 1;
-    const int n_steps = std::max(max_decode - 1, 0);
+    int n_steps = std::max(max_decode - 1, 0);
+    if (debug_step_limit_ >= 0) n_steps = std::min(n_steps, debug_step_limit_);
     cudaGraphExec_t exec = use_graph_ ? decode_graph(B, S) : nullptr;
     int launched = 0;
     for (int s = 0; s < n_steps; ++s) {
@@ -225,6 +226,17 @@ class QuantTransformer : public LSModel {
   const int8_t* last_logits() const { return logits_q_->value<int8_t>(); }
   int logits_ld() const { return ldv_; }
   int steps_run() const { return steps_run_; }
+  void set_debug_step_limit(int n) { debug_step_limit_ = n; }
+  // beam state after the last Infer(): alive [rows, max_step], anc [rows, max_step], probs/score [rows]
+  void beam_state(const int32_t** alive, const int32_t** anc, const float** probs, const float** score, int* max_step,
+                  int* beam) const {
+    *alive = alive_;
+    *anc = anc_;
+    *probs = seq_probs_;
+    *score = seq_score_;
+    *max_step = max_step_;
+    *beam = beam_;
+  }
   ContextPtr context() const { return ctx_; }
 
  private:
@@ -398,9 +410,15 @@ class QuantTransformer : public LSModel {
   int32_t* d_out_ids_ = nullptr;
   float* d_out_scores_ = nullptr;
   int steps_run_ = 0;
+  int debug_step_limit_ = -1;
 };
 
 LSMODEL_REGISTER(QuantTransformer)
+
+cudaStream_t model_stream(LSModel* m) {
+  if (auto* t = dynamic_cast<QuantTransformer*>(m)) return t->context()->get_stream();
+  return nullptr;
+}
 
 // Accessors for the test-only debug taps declared in model_abi.cpp.
 const float* quant_transformer_encoder_output(LSModel* m) {
@@ -412,6 +430,19 @@ const int8_t* quant_transformer_last_logits(LSModel* m, int* ld) {
   if (!t) return nullptr;
   if (ld) *ld = t->logits_ld();
   return t->last_logits();
+}
+int quant_transformer_set_step_limit(LSModel* m, int n) {
+  auto* t = dynamic_cast<QuantTransformer*>(m);
+  if (!t) return -1;
+  t->set_debug_step_limit(n);
+  return 0;
+}
+int quant_transformer_beam_state(LSModel* m, const int32_t** alive, const int32_t** anc, const float** probs,
+                                 const float** score, int* max_step, int* beam) {
+  auto* t = dynamic_cast<QuantTransformer*>(m);
+  if (!t) return -1;
+  t->beam_state(alive, anc, probs, score, max_step, beam);
+  return 0;
 }
 int quant_transformer_steps_run(LSModel* m) {
   auto* t = dynamic_cast<QuantTransformer*>(m);

@@ -3,7 +3,7 @@
 //                output (encoder, BERT, GPT prefill); online softmax, fp32 math.
 //   attn_dec   — one-token decoder self-attention over the int8 KV cache with beam
 //                ancestry indirection (no per-step cache permutation), dp4a scores.
-//   attn_cross — decoder cross-attention over fp16 encoder keys/values.
+//   attn_cross — decoder cross-attention over fp32 encoder keys/values.
 // All three quantise their output with the out-projection's input clip-max, so the
 // next GEMM consumes int8 directly.
 //
@@ -32,7 +32,7 @@ __device__ __forceinline__ void unpack16(const int4 v, float (&f)[16]) {
 }
 
 // ------------------------------------------------------------------ attn_self
-__global__ void __launch_bounds__(64) attn_self_kernel(const ls100_attn_self_args a, const float s_out) {
+__global__ void __launch_bounds__(64) attn_self_kernel(const ls100_attn_self_args a, const float s_out, const float rs_out) {
   __shared__ __align__(16) float Ks[64][DH];
   __shared__ __align__(16) float Vs[64][DH];
   __shared__ uint8_t msk[64];
@@ -54,11 +54,19 @@ __global__ void __launch_bounds__(64) attn_self_kernel(const ls100_attn_self_arg
       float f[16];
       unpack16(*reinterpret_cast<const int4*>(qp + c * 16), f);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        float x = __fmul_rn(f[j], a.s_qkv);
-        if (a.bias) x = __fadd_rn(x, __ldg(a.bias + h * DH + c * 16 + j));
-        qf[c * 16 + j] = __fmul_rn(x, scaling);
+      for (int j = 0; j < 16; ++j) f[j] = __fmul_rn(f[j], a.s_qkv);
+      if (a.bias) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          const float4 bb = __ldg(reinterpret_cast<const float4*>(a.bias + h * DH + c * 16 + j));
+          f[j] = __fadd_rn(f[j], bb.x);
+          f[j + 1] = __fadd_rn(f[j + 1], bb.y);
+          f[j + 2] = __fadd_rn(f[j + 2], bb.z);
+          f[j + 3] = __fadd_rn(f[j + 3], bb.w);
+        }
       }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) qf[c * 16 + j] = __fmul_rn(f[j], scaling);
     }
   }
   if (a.k_cache && valid) {  // GPT prefill: keep this row's int8 k,v for the decode steps
@@ -89,9 +97,16 @@ __global__ void __launch_bounds__(64) attn_self_kernel(const ls100_attn_self_arg
         const int col = (1 + mat) * hidden + h * DH + part * 16;
         unpack16(*reinterpret_cast<const int4*>(base + (long long)key * a.ld_qkv + col), f);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          f[j] = __fmul_rn(f[j], a.s_qkv);
-          if (a.bias) f[j] = __fadd_rn(f[j], __ldg(a.bias + col + j));
+        for (int j = 0; j < 16; ++j) f[j] = __fmul_rn(f[j], a.s_qkv);
+        if (a.bias) {
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) {
+            const float4 bb = __ldg(reinterpret_cast<const float4*>(a.bias + col + j));
+            f[j] = __fadd_rn(f[j], bb.x);
+            f[j + 1] = __fadd_rn(f[j + 1], bb.y);
+            f[j + 2] = __fadd_rn(f[j + 2], bb.z);
+            f[j + 3] = __fadd_rn(f[j + 3], bb.w);
+          }
         }
       } else {
 #pragma unroll
@@ -166,9 +181,9 @@ __global__ void __launch_bounds__(64) attn_self_kernel(const ls100_attn_self_arg
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int d = c * 16 + j * 4;
-      w[j] = pack_i8x4(quant_s(clipf(acc[d] * inv, a.amax_out), s_out), quant_s(clipf(acc[d + 1] * inv, a.amax_out), s_out),
-                       quant_s(clipf(acc[d + 2] * inv, a.amax_out), s_out),
-                       quant_s(clipf(acc[d + 3] * inv, a.amax_out), s_out));
+      w[j] = pack_i8x4(quant_s(clipf(acc[d] * inv, a.amax_out), s_out, rs_out), quant_s(clipf(acc[d + 1] * inv, a.amax_out), s_out, rs_out),
+                       quant_s(clipf(acc[d + 2] * inv, a.amax_out), s_out, rs_out),
+                       quant_s(clipf(acc[d + 3] * inv, a.amax_out), s_out, rs_out));
     }
     u.x = w[0];
     u.y = w[1];
@@ -180,7 +195,7 @@ __global__ void __launch_bounds__(64) attn_self_kernel(const ls100_attn_self_arg
 
 // ------------------------------------------------------------------ attn_dec
 __global__ void __launch_bounds__(128) attn_dec_kernel(const ls100_attn_dec_args a, const float s_out,
-                                                        const float score_scale) {
+                                                        const float rs_out, const float score_scale) {
   extern __shared__ float sc_all[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wid = blockIdx.x * 4 + warp;
@@ -262,9 +277,9 @@ __global__ void __launch_bounds__(128) attn_dec_kernel(const ls100_attn_dec_args
     uint32_t w[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j)
-      w[j] = pack_i8x4(quant_s(clipf(acc[j * 4] * f, a.amax_out), s_out), quant_s(clipf(acc[j * 4 + 1] * f, a.amax_out), s_out),
-                       quant_s(clipf(acc[j * 4 + 2] * f, a.amax_out), s_out),
-                       quant_s(clipf(acc[j * 4 + 3] * f, a.amax_out), s_out));
+      w[j] = pack_i8x4(quant_s(clipf(acc[j * 4] * f, a.amax_out), s_out, rs_out), quant_s(clipf(acc[j * 4 + 1] * f, a.amax_out), s_out, rs_out),
+                       quant_s(clipf(acc[j * 4 + 2] * f, a.amax_out), s_out, rs_out),
+                       quant_s(clipf(acc[j * 4 + 3] * f, a.amax_out), s_out, rs_out));
     uint4 u;
     u.x = w[0];
     u.y = w[1];
@@ -275,7 +290,9 @@ __global__ void __launch_bounds__(128) attn_dec_kernel(const ls100_attn_dec_args
 }
 
 // ------------------------------------------------------------------ attn_cross
-__global__ void __launch_bounds__(256) attn_cross_kernel(const ls100_attn_cross_args a, const float s_out) {
+// One CTA per (batch, head), one warp per beam; encoder keys/values are fp32 rows of 64
+// floats: 16 lanes x 16 bytes cover a row, two rows per pass.
+__global__ void __launch_bounds__(256) attn_cross_kernel(const ls100_attn_cross_args a, const float s_out, const float rs_out) {
   extern __shared__ float sc_all[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (warp >= a.beam) return;
@@ -283,39 +300,41 @@ __global__ void __launch_bounds__(256) attn_cross_kernel(const ls100_attn_cross_
   const int r = b * a.beam + warp;
   const int S = a.src_len;
   float* sc = sc_all + warp * S;
-  const int g = lane >> 3, c = lane & 7;
-  float qf[8];
+  const int g = lane >> 4, c = lane & 15;
+  float qf[4];
   {
-    const int8_t* qp = a.q + (long long)r * a.ld_q + h * DH + c * 8;
-    const int2 q2 = *reinterpret_cast<const int2*>(qp);
-    const int w[2] = {q2.x, q2.y};
+    const int8_t* qp = a.q + (long long)r * a.ld_q + h * DH + c * 4;
+    const int w = *reinterpret_cast<const int*>(qp);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float x = __fmul_rn((float)(int8_t)((w[j >> 2] >> ((j & 3) * 8)) & 0xff), a.s_q);
-      if (a.bias) x = __fadd_rn(x, __ldg(a.bias + h * DH + c * 8 + j));
-      qf[j] = __fmul_rn(x, 0.125f);
+    for (int j = 0; j < 4; ++j) qf[j] = __fmul_rn((float)(int8_t)((w >> (j * 8)) & 0xff), a.s_q);
+    if (a.bias) {
+      const float4 bb = __ldg(reinterpret_cast<const float4*>(a.bias + h * DH + c * 4));
+      qf[0] = __fadd_rn(qf[0], bb.x);
+      qf[1] = __fadd_rn(qf[1], bb.y);
+      qf[2] = __fadd_rn(qf[2], bb.z);
+      qf[3] = __fadd_rn(qf[3], bb.w);
     }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) qf[j] = __fmul_rn(qf[j], 0.125f);
   }
-  const __half* kb = reinterpret_cast<const __half*>(a.k) + (long long)b * S * a.ld_kv + h * DH + c * 8;
-  const __half* vb = reinterpret_cast<const __half*>(a.v) + (long long)b * S * a.ld_kv + h * DH + c * 8;
+  const float* kb = reinterpret_cast<const float*>(a.k) + (long long)b * S * a.ld_kv + h * DH + c * 4;
+  const float* vb = reinterpret_cast<const float*>(a.v) + (long long)b * S * a.ld_kv + h * DH + c * 4;
   const uint8_t* pm = a.pad_mask ? a.pad_mask + (long long)b * S : nullptr;
-  for (int j0 = 0; j0 < S; j0 += 4) {
+  for (int j0 = 0; j0 < S; j0 += 2) {
     const int j = j0 + g;
     float s = 0.f;
     const bool ok = (j < S) && !(pm && pm[j]);
     if (ok) {
-      const uint4 u = *reinterpret_cast<const uint4*>(kb + (long long)j * a.ld_kv);
-      const __half2* h2 = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const float2 f = __half22float2(h2[t]);
-        s = fmaf(qf[2 * t], f.x, s);
-        s = fmaf(qf[2 * t + 1], f.y, s);
-      }
+      const float4 k4 = *reinterpret_cast<const float4*>(kb + (long long)j * a.ld_kv);
+      s = fmaf(qf[0], k4.x, s);
+      s = fmaf(qf[1], k4.y, s);
+      s = fmaf(qf[2], k4.z, s);
+      s = fmaf(qf[3], k4.w, s);
     }
     s += __shfl_xor_sync(0xffffffffu, s, 1);
     s += __shfl_xor_sync(0xffffffffu, s, 2);
     s += __shfl_xor_sync(0xffffffffu, s, 4);
+    s += __shfl_xor_sync(0xffffffffu, s, 8);
     if (j < S && c == 0) sc[j] = ok ? s : -INFINITY;
   }
   __syncwarp();
@@ -330,38 +349,29 @@ __global__ void __launch_bounds__(256) attn_cross_kernel(const ls100_attn_cross_
   }
   sum = warp_sum(sum);
   __syncwarp();
-  float acc[8];
-#pragma unroll
-  for (int t = 0; t < 8; ++t) acc[t] = 0.f;
-  for (int j0 = 0; j0 < S; j0 += 4) {
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int j0 = 0; j0 < S; j0 += 2) {
     const int j = j0 + g;
     if (j < S) {
       const float w = sc[j];
       if (w != 0.f) {
-        const uint4 u = *reinterpret_cast<const uint4*>(vb + (long long)j * a.ld_kv);
-        const __half2* h2 = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float2 f = __half22float2(h2[t]);
-          acc[2 * t] = fmaf(w, f.x, acc[2 * t]);
-          acc[2 * t + 1] = fmaf(w, f.y, acc[2 * t + 1]);
-        }
+        const float4 v4 = *reinterpret_cast<const float4*>(vb + (long long)j * a.ld_kv);
+        acc[0] = fmaf(w, v4.x, acc[0]);
+        acc[1] = fmaf(w, v4.y, acc[1]);
+        acc[2] = fmaf(w, v4.z, acc[2]);
+        acc[3] = fmaf(w, v4.w, acc[3]);
       }
     }
   }
 #pragma unroll
-  for (int t = 0; t < 8; ++t) {
-    acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], 8);
-    acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], 16);
-  }
+  for (int t = 0; t < 4; ++t) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], 16);
   if (g == 0) {
     const float inv = sum > 0.f ? 1.f / sum : 0.f;
-    uint2 u;
-    u.x = pack_i8x4(quant_s(clipf(acc[0] * inv, a.amax_out), s_out), quant_s(clipf(acc[1] * inv, a.amax_out), s_out),
-                    quant_s(clipf(acc[2] * inv, a.amax_out), s_out), quant_s(clipf(acc[3] * inv, a.amax_out), s_out));
-    u.y = pack_i8x4(quant_s(clipf(acc[4] * inv, a.amax_out), s_out), quant_s(clipf(acc[5] * inv, a.amax_out), s_out),
-                    quant_s(clipf(acc[6] * inv, a.amax_out), s_out), quant_s(clipf(acc[7] * inv, a.amax_out), s_out));
-    *reinterpret_cast<uint2*>(a.out + (long long)r * a.ld_out + h * DH + c * 8) = u;
+    const uint32_t u = pack_i8x4(quant_s(clipf(acc[0] * inv, a.amax_out), s_out, rs_out),
+                                 quant_s(clipf(acc[1] * inv, a.amax_out), s_out, rs_out),
+                                 quant_s(clipf(acc[2] * inv, a.amax_out), s_out, rs_out),
+                                 quant_s(clipf(acc[3] * inv, a.amax_out), s_out, rs_out));
+    *reinterpret_cast<uint32_t*>(a.out + (long long)r * a.ld_out + h * DH + c * 4) = u;
   }
 }
 
@@ -379,7 +389,7 @@ extern "C" int ls100_attn_self(ls100_ctx* ctx, const ls100_attn_self_args* a, ls
     return LS100_ERR_BAD_ARG;
   if (a->heads > 65535 || a->batch > 65535) return LS100_ERR_UNSUPPORTED;
   dim3 grid((a->seq + 63) / 64, a->heads, a->batch);
-  attn_self_kernel<<<grid, 64, 0, (cudaStream_t)stream_>>>(*a, a->amax_out / 127.0f);
+  attn_self_kernel<<<grid, 64, 0, (cudaStream_t)stream_>>>(*a, a->amax_out / 127.0f, 1.0f / (a->amax_out / 127.0f));
   return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
 
@@ -393,7 +403,7 @@ extern "C" int ls100_attn_dec(ls100_ctx* ctx, const ls100_attn_dec_args* a, ls10
   const long long warps = (long long)a->rows * a->heads;
   const float score_scale = (a->s_kv * a->s_kv) * 0.125f;
   attn_dec_kernel<<<(unsigned)((warps + 3) / 4), 128, 4 * a->max_step * sizeof(float), (cudaStream_t)stream_>>>(
-      *a, a->amax_out / 127.0f, score_scale);
+      *a, a->amax_out / 127.0f, 1.0f / (a->amax_out / 127.0f), score_scale);
   return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
 
@@ -401,11 +411,11 @@ extern "C" int ls100_attn_cross(ls100_ctx* ctx, const ls100_attn_cross_args* a, 
   if (!ctx || !a || !a->q || !a->k || !a->v || !a->out) return LS100_ERR_BAD_ARG;
   if (a->batch <= 0 || a->beam <= 0 || a->src_len <= 0 || a->heads <= 0 || !(a->amax_out > 0.f)) return LS100_ERR_BAD_ARG;
   if (a->beam > 8 || a->src_len > 4096 || a->heads > 65535) return LS100_ERR_UNSUPPORTED;
-  if ((((uintptr_t)a->q) & 7) || (a->ld_q & 7) || (((uintptr_t)a->k) & 15) || (((uintptr_t)a->v) & 15) || (a->ld_kv & 7) ||
-      (((uintptr_t)a->out) & 7) || (a->ld_out & 7))
+  if ((((uintptr_t)a->q) & 3) || (a->ld_q & 3) || (((uintptr_t)a->k) & 15) || (((uintptr_t)a->v) & 15) || (a->ld_kv & 3) ||
+      (((uintptr_t)a->out) & 3) || (a->ld_out & 3))
     return LS100_ERR_ALIGN;
   dim3 grid(a->batch, a->heads);
   attn_cross_kernel<<<grid, 32 * a->beam, (size_t)a->beam * a->src_len * sizeof(float), (cudaStream_t)stream_>>>(
-      *a, a->amax_out / 127.0f);
+      *a, a->amax_out / 127.0f, 1.0f / (a->amax_out / 127.0f));
   return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }

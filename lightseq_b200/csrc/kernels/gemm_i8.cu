@@ -23,11 +23,15 @@
 #include "common.cuh"
 #include "ctx.h"
 
+#ifndef LS100_TRACE
+#define LS100_TRACE(slot)
+#endif
+
 namespace ls100 {
 
 struct GemmEpi {
   int m, n, k;
-  float s_acc, s_outq, s_req;
+  float s_acc, s_outq, s_req, rs_outq, rs_req;
   const int32_t* w_off;
   const float* bias;
   const float* resid;
@@ -76,118 +80,151 @@ __device__ __forceinline__ void record_timeout(int* err) {
   if (err) atomicExch(err, (int)LS100_ERR_TIMEOUT);
 }
 
+// 32 consecutive columns of one output row. Written as a sequence of branch-free passes
+// over the 32 registers, with the (warp-uniform) mode tests between the passes: a taken
+// branch per element costs more than the arithmetic it guards.
 template <int BN>
 __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t (&r)[32], int row, int col0) {
-  // 32 consecutive columns of one output row
   const bool row_ok = row < p.m;
   const bool full = (col0 + 32 <= p.n);
-  float v[32];
-  float q8[32];
+  const int nmax = p.n - 1;
+  int acc[32];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    const int n = col0 + j;
-    int a = (int)r[j];
-    if (p.w_off != nullptr && n < p.n) a += __ldg(p.w_off + n);
-    if (p.out_kind == LS100_OUT_I32) {
-      q8[j] = __int_as_float(a);
-      continue;
-    }
-    float x = __fmul_rn(__int2float_rn(a), p.s_acc);
-    if (p.s_outq > 0.f) {
-      const float q = quant_s(x, p.s_outq);
-      q8[j] = q;
-      x = __fmul_rn(q, p.s_outq);
-    }
-    if (p.bias != nullptr && n < p.n) x = __fadd_rn(x, __ldg(p.bias + n));
-    if (p.act == LS100_ACT_RELU) x = fmaxf(x, 0.f);
-    else if (p.act == LS100_ACT_GELU) x = gelu_erf(x);
-    v[j] = x;
-  }
-  if (!row_ok) return;
-  if (p.resid != nullptr && p.out_kind != LS100_OUT_I32) {
-    const float* rp = p.resid + (long long)row * p.ldr + col0;
-    if (full && ((p.ldr & 3) == 0) && ((((uintptr_t)p.resid) & 15) == 0)) {
+  for (int j = 0; j < 32; ++j) acc[j] = (int)r[j];
+  if (p.w_off != nullptr) {
+    if (full) {
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
-        const float4 t = *reinterpret_cast<const float4*>(rp + j);
-        v[j] = __fadd_rn(v[j], t.x);
-        v[j + 1] = __fadd_rn(v[j + 1], t.y);
-        v[j + 2] = __fadd_rn(v[j + 2], t.z);
-        v[j + 3] = __fadd_rn(v[j + 3], t.w);
+        const int4 o = __ldg(reinterpret_cast<const int4*>(p.w_off + col0 + j));
+        acc[j] += o.x;
+        acc[j + 1] += o.y;
+        acc[j + 2] += o.z;
+        acc[j + 3] += o.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[j] += __ldg(p.w_off + min(col0 + j, nmax));
+    }
+  }
+  if (p.out_kind == LS100_OUT_I32) {
+    if (!row_ok) return;
+    int* op = reinterpret_cast<int*>(p.out) + (long long)row * p.ldo + col0;
+    if (full && ((p.ldo & 3) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<int4*>(op + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.n) op[j] = acc[j];
+    }
+    return;
+  }
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(__int2float_rn(acc[j]), p.s_acc);
+  if (p.s_outq > 0.f) {
+    if (p.out_kind == LS100_OUT_OUTQ_I8) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = quant_s(v[j], p.s_outq, p.rs_outq);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(quant_s(v[j], p.s_outq, p.rs_outq), p.s_outq);
+    }
+  }
+  if (p.out_kind != LS100_OUT_OUTQ_I8) {
+    if (p.bias != nullptr) {
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + j));
+          v[j] = __fadd_rn(v[j], b.x);
+          v[j + 1] = __fadd_rn(v[j + 1], b.y);
+          v[j + 2] = __fadd_rn(v[j + 2], b.z);
+          v[j + 3] = __fadd_rn(v[j + 3], b.w);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], __ldg(p.bias + min(col0 + j, nmax)));
+      }
+    }
+    if (p.act == LS100_ACT_RELU) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+    } else if (p.act == LS100_ACT_GELU) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+    }
+    if (p.resid != nullptr && row_ok) {
+      const float* rp = p.resid + (long long)row * p.ldr + col0;
+      if (full && ((p.ldr & 3) == 0) && ((((uintptr_t)p.resid) & 15) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 t = *reinterpret_cast<const float4*>(rp + j);
+          v[j] = __fadd_rn(v[j], t.x);
+          v[j + 1] = __fadd_rn(v[j + 1], t.y);
+          v[j + 2] = __fadd_rn(v[j + 2], t.z);
+          v[j + 3] = __fadd_rn(v[j + 3], t.w);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.n) v[j] = __fadd_rn(v[j], rp[j]);
+      }
+    }
+    if (p.out_kind == LS100_OUT_REQ_S8) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = quant_s(v[j], p.s_req, p.rs_req);
+    } else if (p.out_kind == LS100_OUT_REQ_U8) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = quant_u(v[j], p.s_req, p.rs_req);
+    }
+  }
+  if (!row_ok) return;
+  if (p.out_kind == LS100_OUT_F32) {
+    float* op = reinterpret_cast<float*>(p.out) + (long long)row * p.ldo + col0;
+    if (full && ((p.ldo & 3) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(op + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.n) op[j] = v[j];
+    }
+  } else if (p.out_kind == LS100_OUT_F16) {
+    __half* op = reinterpret_cast<__half*>(p.out) + (long long)row * p.ldo + col0;
+    if (full && ((p.ldo & 7) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        __half2 h0 = __floats2half2_rn(v[j], v[j + 1]), h1 = __floats2half2_rn(v[j + 2], v[j + 3]);
+        __half2 h2 = __floats2half2_rn(v[j + 4], v[j + 5]), h3 = __floats2half2_rn(v[j + 6], v[j + 7]);
+        uint4 u;
+        u.x = *reinterpret_cast<uint32_t*>(&h0);
+        u.y = *reinterpret_cast<uint32_t*>(&h1);
+        u.z = *reinterpret_cast<uint32_t*>(&h2);
+        u.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(op + j) = u;
       }
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (col0 + j < p.n) v[j] = __fadd_rn(v[j], rp[j]);
+        if (col0 + j < p.n) op[j] = __float2half_rn(v[j]);
     }
-  }
-  switch (p.out_kind) {
-    case LS100_OUT_F32: {
-      float* op = reinterpret_cast<float*>(p.out) + (long long)row * p.ldo + col0;
-      if (full && ((p.ldo & 3) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
+  } else {  // int8 outputs: v[] holds the quantised integers
+    int8_t* op = reinterpret_cast<int8_t*>(p.out) + (long long)row * p.ldo + col0;
+    if (full && ((p.ldo & 15) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(op + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (col0 + j < p.n) op[j] = v[j];
+      for (int j = 0; j < 32; j += 16) {
+        uint4 u;
+        u.x = pack_i8x4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        u.y = pack_i8x4(v[j + 4], v[j + 5], v[j + 6], v[j + 7]);
+        u.z = pack_i8x4(v[j + 8], v[j + 9], v[j + 10], v[j + 11]);
+        u.w = pack_i8x4(v[j + 12], v[j + 13], v[j + 14], v[j + 15]);
+        *reinterpret_cast<uint4*>(op + j) = u;
       }
-      break;
-    }
-    case LS100_OUT_I32: {
-      int* op = reinterpret_cast<int*>(p.out) + (long long)row * p.ldo + col0;
+    } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (col0 + j < p.n) op[j] = __float_as_int(q8[j]);
-      break;
-    }
-    case LS100_OUT_F16: {
-      __half* op = reinterpret_cast<__half*>(p.out) + (long long)row * p.ldo + col0;
-      if (full && ((p.ldo & 7) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-          __half2 h0 = __floats2half2_rn(v[j], v[j + 1]), h1 = __floats2half2_rn(v[j + 2], v[j + 3]);
-          __half2 h2 = __floats2half2_rn(v[j + 4], v[j + 5]), h3 = __floats2half2_rn(v[j + 6], v[j + 7]);
-          uint4 u;
-          u.x = *reinterpret_cast<uint32_t*>(&h0);
-          u.y = *reinterpret_cast<uint32_t*>(&h1);
-          u.z = *reinterpret_cast<uint32_t*>(&h2);
-          u.w = *reinterpret_cast<uint32_t*>(&h3);
-          *reinterpret_cast<uint4*>(op + j) = u;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (col0 + j < p.n) op[j] = __float2half_rn(v[j]);
-      }
-      break;
-    }
-    default: {  // int8 outputs
-      if (p.out_kind == LS100_OUT_REQ_S8) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) q8[j] = quant_s(v[j], p.s_req);
-      } else if (p.out_kind == LS100_OUT_REQ_U8) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) q8[j] = quant_u(v[j], p.s_req);
-      }
-      int8_t* op = reinterpret_cast<int8_t*>(p.out) + (long long)row * p.ldo + col0;
-      if (full && ((p.ldo & 15) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 16) {
-          uint4 u;
-          u.x = pack_i8x4(q8[j], q8[j + 1], q8[j + 2], q8[j + 3]);
-          u.y = pack_i8x4(q8[j + 4], q8[j + 5], q8[j + 6], q8[j + 7]);
-          u.z = pack_i8x4(q8[j + 8], q8[j + 9], q8[j + 10], q8[j + 11]);
-          u.w = pack_i8x4(q8[j + 12], q8[j + 13], q8[j + 14], q8[j + 15]);
-          *reinterpret_cast<uint4*>(op + j) = u;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (col0 + j < p.n) op[j] = (int8_t)(int)q8[j];
-      }
-      break;
+        if (col0 + j < p.n) op[j] = (int8_t)(int)v[j];
     }
   }
 }
@@ -211,6 +248,7 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
   const int m0 = blockIdx.y * BM;
   const int num_kb = (p.k + BK - 1) / BK;
 
+  LS100_TRACE(0);
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
@@ -230,6 +268,7 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  LS100_TRACE(1);
 
   if (warp == 0) {
     if (elect_one()) {
@@ -264,6 +303,7 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
           break;
         }
         tc_fence_after();
+        if (kb == 0) { LS100_TRACE(2); }
         const uint32_t sa = smem_u32(smem + s * SM::STAGE_BYTES);
         const uint64_t adesc = make_smem_desc(sa);
         const uint64_t bdesc = make_smem_desc(sa + SM::A_BYTES);
@@ -280,6 +320,7 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
         }
       }
       if (ok) tc_commit(tmem_full_bar);
+      LS100_TRACE(3);
     }
   } else {
     const int quarter = warp & 3;
@@ -290,22 +331,27 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
       if (lane == 0) record_timeout(p.err);
     } else {
       tc_fence_after();
+      LS100_TRACE(4);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         if (n0 + c0 >= p.n) break;
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
         tmem_ld_wait();
+        if (c0 == 0) { LS100_TRACE(7); }
         epilogue_chunk<BN>(p, r, row, n0 + c0);
+        LS100_TRACE(8 + c0 / 32);
       }
     }
   }
+  LS100_TRACE(5);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  LS100_TRACE(6);
 }
 
 template <int BN, int STAGES>
@@ -324,6 +370,8 @@ static int launch_gemm(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cudaStream_t
   p.s_acc = a->s_acc;
   p.s_outq = a->s_outq;
   p.s_req = a->s_req;
+  p.rs_outq = a->s_outq > 0.f ? 1.0f / a->s_outq : 0.f;
+  p.rs_req = a->s_req > 0.f ? 1.0f / a->s_req : 0.f;
   p.w_off = a->w_off;
   p.bias = a->bias;
   p.resid = a->resid;

@@ -17,7 +17,7 @@ __device__ __forceinline__ double warp_sum_d(double v) {
 constexpr int LN_MAXV = 32;  // float4 per lane -> hidden <= 32*32*4 = 4096
 
 template <int NV>
-__global__ void __launch_bounds__(256) ln_quant_kernel(const ls100_ln_quant_args a, const float scale) {
+__global__ void __launch_bounds__(256) ln_quant_kernel(const ls100_ln_quant_args a, const float scale, const float rs) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= a.rows) return;
@@ -59,8 +59,8 @@ __global__ void __launch_bounds__(256) ln_quant_kernel(const ls100_ln_quant_args
       y.w = __fadd_rn(__fmul_rn((float)(((double)v[i].w - mean) * rstd), g.w), b.w);
       if (a.out_f) *reinterpret_cast<float4*>(a.out_f + (long long)warp * a.ldf + c) = y;
       if (a.out_q) {
-        const uint32_t p = pack_i8x4(quant_s(clipf(y.x, a.amax), scale), quant_s(clipf(y.y, a.amax), scale),
-                                     quant_s(clipf(y.z, a.amax), scale), quant_s(clipf(y.w, a.amax), scale));
+        const uint32_t p = pack_i8x4(quant_s(clipf(y.x, a.amax), scale, rs), quant_s(clipf(y.y, a.amax), scale, rs),
+                                     quant_s(clipf(y.z, a.amax), scale, rs), quant_s(clipf(y.w, a.amax), scale, rs));
         *reinterpret_cast<uint32_t*>(a.out_q + (long long)warp * a.ldq + c) = p;
       }
     }
@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(256) embed_kernel(const ls100_embed_args a) {
 
 // ------------------------------------------------------------------ weight quantiser
 __global__ void __launch_bounds__(256) quantize_weight_kernel(const float* __restrict__ w, long long rows,
-                                                               long long cols, float amax, float scale,
+                                                               long long cols, float amax, float scale, float rs,
                                                                int8_t* __restrict__ out, int32_t* __restrict__ off) {
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -120,8 +120,8 @@ __global__ void __launch_bounds__(256) quantize_weight_kernel(const float* __res
   int sum = 0;
   for (long long c = lane * 4; c < cols; c += 128) {
     const float4 x = *reinterpret_cast<const float4*>(wr + c);
-    const float q0 = quant_s(clipf(x.x, amax), scale), q1 = quant_s(clipf(x.y, amax), scale);
-    const float q2 = quant_s(clipf(x.z, amax), scale), q3 = quant_s(clipf(x.w, amax), scale);
+    const float q0 = quant_s(clipf(x.x, amax), scale, rs), q1 = quant_s(clipf(x.y, amax), scale, rs);
+    const float q2 = quant_s(clipf(x.z, amax), scale, rs), q3 = quant_s(clipf(x.w, amax), scale, rs);
     sum += (int)q0 + (int)q1 + (int)q2 + (int)q3;
     *reinterpret_cast<uint32_t*>(orow + c) = pack_i8x4(q0, q1, q2, q3);
   }
@@ -149,10 +149,10 @@ extern "C" int ls100_ln_quant(ls100_ctx* ctx, const ls100_ln_quant_args* a, ls10
   const int warps_per_block = 8;
   const int blocks = (a->rows + warps_per_block - 1) / warps_per_block;
   const int nv = (a->hidden + 127) / 128;
-  if (nv <= 4) ln_quant_kernel<4><<<blocks, 256, 0, stream>>>(*a, scale);
-  else if (nv <= 8) ln_quant_kernel<8><<<blocks, 256, 0, stream>>>(*a, scale);
-  else if (nv <= 16) ln_quant_kernel<16><<<blocks, 256, 0, stream>>>(*a, scale);
-  else ln_quant_kernel<32><<<blocks, 256, 0, stream>>>(*a, scale);
+  if (nv <= 4) ln_quant_kernel<4><<<blocks, 256, 0, stream>>>(*a, scale, 1.0f / scale);
+  else if (nv <= 8) ln_quant_kernel<8><<<blocks, 256, 0, stream>>>(*a, scale, 1.0f / scale);
+  else if (nv <= 16) ln_quant_kernel<16><<<blocks, 256, 0, stream>>>(*a, scale, 1.0f / scale);
+  else ln_quant_kernel<32><<<blocks, 256, 0, stream>>>(*a, scale, 1.0f / scale);
   return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
 
@@ -174,7 +174,7 @@ extern "C" int ls100_quantize_weight(ls100_ctx* ctx, const float* w, int64_t row
   if ((((uintptr_t)w) & 15) || (((uintptr_t)out_q) & 3)) return LS100_ERR_ALIGN;
   const float scale = amax / 127.0f;
   const long long blocks = (rows + 7) / 8;
-  quantize_weight_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream_>>>(w, rows, cols, amax, scale, out_q,
+  quantize_weight_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream_>>>(w, rows, cols, amax, scale, 1.0f / scale, out_q,
                                                                                row_off);
   return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }

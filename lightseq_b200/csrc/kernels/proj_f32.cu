@@ -1,4 +1,4 @@
-// out_f16[M,N] = (x_f32[M,K] . Wq_i8[N,K]^T) * s_w + bias
+// out_f32[M,N] = (x_f32[M,K] . Wq_i8[N,K]^T) * s_w + bias
 // The decoder's cross-attention k_proj / v_proj: activations stay fp32, only the weight
 // is fake-quantised (QuantLinear with pre_activation="encoder_out",
 // lightseq/training/ops/pytorch/quantization.py:41-46). Runs once per request
@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(256) proj_f32_kernel(const ls100_proj_f32_args
     }
     __syncthreads();
   }
-  __half* out = reinterpret_cast<__half*>(a.out);
+  float* out = reinterpret_cast<float*>(a.out);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int m = m0 + ty * 4 + i;
@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(256) proj_f32_kernel(const ls100_proj_f32_args
       if (n >= a.n) continue;
       float v = __fmul_rn(acc[i][j], a.s_w);
       if (a.bias) v = __fadd_rn(v, __ldg(a.bias + n));
-      out[(long long)m * a.ldo + n] = __float2half_rn(v);
+      out[(long long)m * a.ldo + n] = v;
     }
   }
 }

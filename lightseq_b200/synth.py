@@ -217,7 +217,7 @@ def calibrate_transformer(w: Dict[str, np.ndarray], src: np.ndarray, *, heads: i
 
 def make_transformer(path: Optional[str] = None, *, hidden=512, heads=8, ffn=2048, n_enc=6, n_dec=6, vocab=32000,
                      act="relu", beam=4, length_penalty=0.6, extra_decode_length=50, max_step=256, pad_id=1,
-                     start_id=2, end_id=2, seed=1234, calib_src: Optional[np.ndarray] = None
+                     start_id=3, end_id=2, seed=1234, calib_src: Optional[np.ndarray] = None
                      ) -> Tuple[Dict[str, float], Dict[str, float], Dict[str, np.ndarray]]:
     """Builds (conf, amax, tensors) of a seeded synthetic QuantTransformer and optionally writes ``path``."""
     w = transformer_weights(hidden, heads, ffn, n_enc, n_dec, vocab, pad_id, seed)

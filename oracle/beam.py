@@ -52,6 +52,15 @@ def row_logsumexp_base(lq_row: np.ndarray, s_l: np.float32):
     return mx, F32(np.log(F32(tot), dtype=F32))
 
 
+def candidate_score(lq_row: np.ndarray, s_l, prob, ln, token: int) -> np.float32:
+    """Score the engine/oracle assigns to extending a live beam (prefix log-prob ``prob``) with ``token``."""
+    s_l = F32(s_l)
+    mx, lse = row_logsumexp_base(lq_row, s_l)
+    base = F32(F32(F32(prob) - lse) - mx)
+    lg = F32(lq_row[token]) * s_l
+    return max(F32(F32(lg + base) * F32(ln)), F32(MIN_LOG_PROB + F32(1.0)))
+
+
 def beam_step(lq: np.ndarray, s_l, alive: np.ndarray, probs: np.ndarray, score: np.ndarray, cur_step: int,
               ln, end_id: int):
     """lq int8 [B,K,V]; alive int32 [B,K,max_step]; probs/score fp32 [B,K].

@@ -294,8 +294,8 @@ def test_attn_cross_matches_oracle():
     q_q = r.integers(-127, 128, size=(B * K, H), dtype=np.int8)
     s_q = F32(0.017)
     bias = (r.standard_normal(H) * 0.1).astype(F32)
-    k = (r.standard_normal((B, S, H)) * 0.5).astype(np.float16)
-    v = (r.standard_normal((B, S, H)) * 0.5).astype(np.float16)
+    k = (r.standard_normal((B, S, H)) * 0.5).astype(F32)
+    v = (r.standard_normal((B, S, H)) * 0.5).astype(F32)
     lens = r.integers(1, S + 1, size=B)
     pad = np.arange(S)[None, :] >= lens[:, None]
     q = q_q.astype(F32) * s_q + bias
@@ -322,13 +322,13 @@ def test_proj_f32_weight_only_quant():
     ref = om.qlinear(st, x, "l", quant_in=False, quant_out=False)
     wq, s_w = oq.quantize(w, st.amax["l.w"])
     dx, dw, db = dev(x), dev(wq), dev(b)
-    out = empty((m, n), torch.float16)
+    out = empty((m, n), torch.float32)
     args = L.ProjF32Args(x=ptr(dx), ldx=k, w=ptr(dw), ldw=k, s_w=float(s_w), bias=ptr(db), m=m, n=n, k=k, out=ptr(out), ldo=n)
     L.call("ls100_proj_f32", ctx(), args)
     sync_check()
-    d = np.abs(out.cpu().numpy().astype(F32) - ref)
-    # fp16 storage: half an ulp of the largest magnitude
-    assert d.max() <= np.abs(ref).max() * 2.0 ** -10
+    d = np.abs(out.cpu().numpy() - ref)
+    # fp32 accumulation in a different order than the oracle's float64 sum
+    assert d.max() <= np.abs(ref).max() * 1e-5
 
 
 # ----------------------------------------------------------------------------- beam search
