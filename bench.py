@@ -244,6 +244,9 @@ def run_ours(args):
     lib.ls100_model_infer.argtypes = [C.c_void_p]
     lib.ls100_model_get_output_shape.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int)]
     lib.ls100_debug_steps_run.argtypes = [C.c_void_p]
+    if args.decode_steps >= 0:
+        lib.ls100_debug_set_step_limit.argtypes = [C.c_void_p, C.c_int]
+        lib.ls100_debug_set_step_limit(handle, args.decode_steps)
     sptr = C.c_void_p()
     L.check(lib.ls100_model_get_stream(handle, C.byref(sptr)), "get_stream")
     mstream = torch.cuda.ExternalStream(sptr.value)
@@ -394,6 +397,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--decode-steps", type=int, default=-1,
+                    help="cap the number of decode steps per generation (profiling aid; the result is not a bench value)")
     ap.add_argument("--quick", action="store_true",
                     help="device-resident arm only, warm-up exactly as given (for profiler launch lists)")
     args = ap.parse_args()

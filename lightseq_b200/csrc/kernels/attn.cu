@@ -194,9 +194,15 @@ __global__ void __launch_bounds__(64) attn_self_kernel(const ls100_attn_self_arg
 }
 
 // ------------------------------------------------------------------ attn_dec
+// One warp per (row, head). 4 lanes x 16 bytes cover one cached position, so one warp-wide
+// load instruction fetches 8 positions (512 B). Keys AND values of 32 positions are requested
+// together (8 x 16-byte loads per lane in flight) and folded in with an online softmax, so a
+// 100-token history costs 4 memory round trips instead of a key pass plus a value pass. The
+// beam-ancestry slots of all positions are fetched into shared memory first so that the cache
+// loads do not wait on them.
 __global__ void __launch_bounds__(128) attn_dec_kernel(const ls100_attn_dec_args a, const float s_out,
                                                         const float rs_out, const float score_scale) {
-  extern __shared__ float sc_all[];
+  extern __shared__ int slot_all[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wid = blockIdx.x * 4 + warp;
   if (wid >= a.rows * a.heads) return;
@@ -204,8 +210,12 @@ __global__ void __launch_bounds__(128) attn_dec_kernel(const ls100_attn_dec_args
   const int hidden = a.heads * DH;
   const int step = *a.step_ptr;
   const int L = step + 1;
-  float* sc = sc_all + warp * a.max_step;
+  int* slot_s = slot_all + warp * a.max_step;
   const int g = lane >> 2, c = lane & 3;
+  {
+    const int32_t* anc = a.anc ? a.anc + (long long)r * a.max_step : nullptr;
+    for (int p = lane; p < L; p += 32) slot_s[p] = (anc && p < step) ? anc[p] : r;
+  }
   const int8_t* row = a.qkv + (long long)r * a.ld_qkv + h * DH + c * 16;
   const int4 q4 = *reinterpret_cast<const int4*>(row);
   const int4 knew = *reinterpret_cast<const int4*>(row + hidden);
@@ -213,59 +223,62 @@ __global__ void __launch_bounds__(128) attn_dec_kernel(const ls100_attn_dec_args
   const long long own = (((long long)r * a.heads + h) * a.max_step + step) * DH + c * 16;
   if (g == 0) *reinterpret_cast<int4*>(a.k_cache + own) = knew;
   if (g == 1) *reinterpret_cast<int4*>(a.v_cache + own) = vnew;
-  const int32_t* anc = a.anc ? a.anc + (long long)r * a.max_step : nullptr;
+  __syncwarp();
+  const long long head_off = (long long)h * a.max_step * DH + c * 16;
+  const long long slot_stride = (long long)a.heads * a.max_step * DH;
 
-  // scores: 8 positions per pass, 4 lanes per position
-  for (int p0 = 0; p0 < L; p0 += 8) {
-    const int p = p0 + g;
-    int dot = 0;
-    if (p < L) {
-      int4 k4;
-      if (p == step) k4 = knew;
-      else {
-        const int slot = anc ? anc[p] : r;
-        k4 = *reinterpret_cast<const int4*>(a.k_cache + (((long long)slot * a.heads + h) * a.max_step + p) * DH + c * 16);
-      }
-      dot = __dp4a(q4.x, k4.x, dot);
-      dot = __dp4a(q4.y, k4.y, dot);
-      dot = __dp4a(q4.z, k4.z, dot);
-      dot = __dp4a(q4.w, k4.w, dot);
-    }
-    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-    if (p < L && c == 0) sc[p] = (float)dot * score_scale;
-  }
-  __syncwarp();
-  float mx = -INFINITY;
-  for (int p = lane; p < L; p += 32) mx = fmaxf(mx, sc[p]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int p = lane; p < L; p += 32) {
-    const float e = expf(sc[p] - mx);
-    sc[p] = e;
-    sum += e;
-  }
-  sum = warp_sum(sum);
-  __syncwarp();
+  float m = -INFINITY, l = 0.f;
   float acc[16];
 #pragma unroll
   for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-  for (int p0 = 0; p0 < L; p0 += 8) {
-    const int p = p0 + g;
-    if (p < L) {
-      int4 v4;
-      if (p == step) v4 = vnew;
-      else {
-        const int slot = anc ? anc[p] : r;
-        v4 = *reinterpret_cast<const int4*>(a.v_cache + (((long long)slot * a.heads + h) * a.max_step + p) * DH + c * 16);
+  for (int p0 = 0; p0 < L; p0 += 32) {
+    int4 k4[4], v4[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int p = p0 + u * 8 + g;
+      k4[u] = make_int4(0, 0, 0, 0);
+      v4[u] = make_int4(0, 0, 0, 0);
+      if (p < step) {
+        const long long o = slot_s[p] * slot_stride + head_off + (long long)p * DH;
+        k4[u] = *reinterpret_cast<const int4*>(a.k_cache + o);
+        v4[u] = *reinterpret_cast<const int4*>(a.v_cache + o);
+      } else if (p == step) {
+        k4[u] = knew;
+        v4[u] = vnew;
       }
+    }
+    float sv[4];
+    float bm = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int p = p0 + u * 8 + g;
+      int dot = __dp4a(q4.x, k4[u].x, 0);
+      dot = __dp4a(q4.y, k4[u].y, dot);
+      dot = __dp4a(q4.z, k4[u].z, dot);
+      dot = __dp4a(q4.w, k4[u].w, dot);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+      sv[u] = (p < L) ? (float)dot * score_scale : -INFINITY;
+      bm = fmaxf(bm, sv[u]);
+    }
+    bm = warp_max(bm);  // p0 < L, so at least one position of the block is valid
+    const float m_new = fmaxf(m, bm);
+    const float resc = __expf(m - m_new);  // 0 when m = -inf
+    l *= resc;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] *= resc;
+    m = m_new;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float w = (sv[u] == -INFINITY) ? 0.f : expf(sv[u] - m);
+      if (c == 0) l += w;  // each position is seen by the 4 lanes of its group
       float f[16];
-      unpack16(v4, f);
-      const float w = sc[p];
+      unpack16(v4[u], f);
 #pragma unroll
       for (int j = 0; j < 16; ++j) acc[j] = fmaf(w, f[j], acc[j]);
     }
   }
+  const float sum = warp_sum(l);
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
     acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 4);
@@ -290,94 +303,138 @@ __global__ void __launch_bounds__(128) attn_dec_kernel(const ls100_attn_dec_args
 }
 
 // ------------------------------------------------------------------ attn_cross
-// One CTA per (batch, head), one warp per beam; encoder keys/values are fp32 rows of 64
-// floats: 16 lanes x 16 bytes cover a row, two rows per pass.
-__global__ void __launch_bounds__(256) attn_cross_kernel(const ls100_attn_cross_args a, const float s_out, const float rs_out) {
-  extern __shared__ float sc_all[];
+// One CTA per (batch, head), one warp per beam. The head's fp32 keys and values are staged in
+// shared memory once per 128-key tile with coalesced 16-byte loads (all loads in flight
+// together, then shared by the beams), scores use one key per lane, the PV product two head
+// dims per lane; tiles are merged with an online softmax.
+constexpr int XT = 128;      // keys per tile
+constexpr int XKS = DH + 1;  // padded key row (conflict-free when lanes read different rows)
+
+__global__ void __launch_bounds__(256) attn_cross_kernel(const ls100_attn_cross_args a, const float s_out, const float rs_out,
+                                                          const int tr /* tile rows held in shared memory, <= XT */) {
+  extern __shared__ float xs[];
+  float* Ks = xs;                    // [tr][XKS]
+  float* Vs = Ks + tr * XKS;         // [tr][DH]
+  float* qs = Vs + tr * DH;          // [beam][DH]
+  float* ps = qs + a.beam * DH;      // [beam][tr]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (warp >= a.beam) return;
   const int b = blockIdx.x, h = blockIdx.y;
   const int r = b * a.beam + warp;
   const int S = a.src_len;
-  float* sc = sc_all + warp * S;
-  const int g = lane >> 4, c = lane & 15;
-  float qf[4];
-  {
-    const int8_t* qp = a.q + (long long)r * a.ld_q + h * DH + c * 4;
-    const int w = *reinterpret_cast<const int*>(qp);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) qf[j] = __fmul_rn((float)(int8_t)((w >> (j * 8)) & 0xff), a.s_q);
+  {  // q of this beam -> shared memory, dequantised, biased, scaled
+    const int8_t* qp = a.q + (long long)r * a.ld_q + h * DH + lane * 2;
+    const short w = *reinterpret_cast<const short*>(qp);
+    float q0 = __fmul_rn((float)(int8_t)(w & 0xff), a.s_q), q1 = __fmul_rn((float)(int8_t)((w >> 8) & 0xff), a.s_q);
     if (a.bias) {
-      const float4 bb = __ldg(reinterpret_cast<const float4*>(a.bias + h * DH + c * 4));
-      qf[0] = __fadd_rn(qf[0], bb.x);
-      qf[1] = __fadd_rn(qf[1], bb.y);
-      qf[2] = __fadd_rn(qf[2], bb.z);
-      qf[3] = __fadd_rn(qf[3], bb.w);
+      const float2 bb = __ldg(reinterpret_cast<const float2*>(a.bias + h * DH + lane * 2));
+      q0 = __fadd_rn(q0, bb.x);
+      q1 = __fadd_rn(q1, bb.y);
     }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) qf[j] = __fmul_rn(qf[j], 0.125f);
+    qs[warp * DH + lane * 2] = __fmul_rn(q0, 0.125f);
+    qs[warp * DH + lane * 2 + 1] = __fmul_rn(q1, 0.125f);
   }
-  const float* kb = reinterpret_cast<const float*>(a.k) + (long long)b * S * a.ld_kv + h * DH + c * 4;
-  const float* vb = reinterpret_cast<const float*>(a.v) + (long long)b * S * a.ld_kv + h * DH + c * 4;
+  const float* kb = reinterpret_cast<const float*>(a.k) + (long long)b * S * a.ld_kv + h * DH;
+  const float* vb = reinterpret_cast<const float*>(a.v) + (long long)b * S * a.ld_kv + h * DH;
   const uint8_t* pm = a.pad_mask ? a.pad_mask + (long long)b * S : nullptr;
-  for (int j0 = 0; j0 < S; j0 += 2) {
-    const int j = j0 + g;
-    float s = 0.f;
-    const bool ok = (j < S) && !(pm && pm[j]);
-    if (ok) {
-      const float4 k4 = *reinterpret_cast<const float4*>(kb + (long long)j * a.ld_kv);
-      s = fmaf(qf[0], k4.x, s);
-      s = fmaf(qf[1], k4.y, s);
-      s = fmaf(qf[2], k4.z, s);
-      s = fmaf(qf[3], k4.w, s);
-    }
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
-    s += __shfl_xor_sync(0xffffffffu, s, 8);
-    if (j < S && c == 0) sc[j] = ok ? s : -INFINITY;
-  }
-  __syncwarp();
-  float mx = -INFINITY;
-  for (int j = lane; j < S; j += 32) mx = fmaxf(mx, sc[j]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int j = lane; j < S; j += 32) {
-    const float e = (sc[j] == -INFINITY) ? 0.f : expf(sc[j] - mx);
-    sc[j] = e;
-    sum += e;
-  }
-  sum = warp_sum(sum);
-  __syncwarp();
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int j0 = 0; j0 < S; j0 += 2) {
-    const int j = j0 + g;
-    if (j < S) {
-      const float w = sc[j];
-      if (w != 0.f) {
-        const float4 v4 = *reinterpret_cast<const float4*>(vb + (long long)j * a.ld_kv);
-        acc[0] = fmaf(w, v4.x, acc[0]);
-        acc[1] = fmaf(w, v4.y, acc[1]);
-        acc[2] = fmaf(w, v4.z, acc[2]);
-        acc[3] = fmaf(w, v4.w, acc[3]);
+  float m = -INFINITY, l = 0.f, acc0 = 0.f, acc1 = 0.f;
+  for (int t0 = 0; t0 < S; t0 += tr) {
+    const int ns = min(tr, S - t0);
+    __syncthreads();
+    for (int i0 = threadIdx.x; i0 < ns * 16; i0 += 4 * blockDim.x) {
+      float4 k4[4], v4[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {  // 8 x 16-byte loads in flight per thread before any store
+        const int i = i0 + u * blockDim.x;
+        if (i < ns * 16) {
+          const int row = i >> 4, c4 = (i & 15) * 4;
+          k4[u] = *reinterpret_cast<const float4*>(kb + (long long)(t0 + row) * a.ld_kv + c4);
+          v4[u] = *reinterpret_cast<const float4*>(vb + (long long)(t0 + row) * a.ld_kv + c4);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < ns * 16) {
+          const int row = i >> 4, c4 = (i & 15) * 4;
+          float* kd = Ks + row * XKS + c4;
+          kd[0] = k4[u].x;
+          kd[1] = k4[u].y;
+          kd[2] = k4[u].z;
+          kd[3] = k4[u].w;
+          *reinterpret_cast<float4*>(Vs + row * DH + c4) = v4[u];
+        }
       }
     }
-  }
+    __syncthreads();
+    // scores: lane handles keys lane, lane+32, ...
+    float sc[XT / 32];
+    float tmax = -INFINITY;
 #pragma unroll
-  for (int t = 0; t < 4; ++t) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], 16);
-  if (g == 0) {
-    const float inv = sum > 0.f ? 1.f / sum : 0.f;
-    const uint32_t u = pack_i8x4(quant_s(clipf(acc[0] * inv, a.amax_out), s_out, rs_out),
-                                 quant_s(clipf(acc[1] * inv, a.amax_out), s_out, rs_out),
-                                 quant_s(clipf(acc[2] * inv, a.amax_out), s_out, rs_out),
-                                 quant_s(clipf(acc[3] * inv, a.amax_out), s_out, rs_out));
-    *reinterpret_cast<uint32_t*>(a.out + (long long)r * a.ld_out + h * DH + c * 4) = u;
+    for (int u = 0; u < XT / 32; ++u) {
+      const int j = u * 32 + lane;
+      float sv = -INFINITY;
+      if (j < ns && !(pm && pm[t0 + j])) {
+        sv = 0.f;
+        const float* kr = Ks + j * XKS;
+        const float* qr = qs + warp * DH;
+#pragma unroll
+        for (int d = 0; d < DH; d += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qr + d);
+          sv = fmaf(q4.x, kr[d], sv);
+          sv = fmaf(q4.y, kr[d + 1], sv);
+          sv = fmaf(q4.z, kr[d + 2], sv);
+          sv = fmaf(q4.w, kr[d + 3], sv);
+        }
+      }
+      sc[u] = sv;
+      tmax = fmaxf(tmax, sv);
+    }
+    tmax = warp_max(tmax);
+    if (tmax == -INFINITY) continue;  // whole tile masked (uniform across the warp)
+    const float m_new = fmaxf(m, tmax);
+    const float resc = __expf(m - m_new);  // 0 when m = -inf
+    l *= resc;
+    acc0 *= resc;
+    acc1 *= resc;
+    m = m_new;
+    float lsum = 0.f;
+#pragma unroll
+    for (int u = 0; u < XT / 32; ++u) {
+      const int j = u * 32 + lane;
+      const float e = (sc[u] == -INFINITY) ? 0.f : expf(sc[u] - m);
+      if (j < tr) ps[warp * tr + j] = e;
+      lsum += e;
+    }
+    l += warp_sum(lsum);
+    __syncwarp();
+    const float* pr = ps + warp * tr;
+    for (int j = 0; j < ns; ++j) {
+      const float w = pr[j];
+      const float2 v2 = *reinterpret_cast<const float2*>(Vs + j * DH + lane * 2);
+      acc0 = fmaf(w, v2.x, acc0);
+      acc1 = fmaf(w, v2.y, acc1);
+    }
+    __syncwarp();
   }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  const float o0 = quant_s(clipf(acc0 * inv, a.amax_out), s_out, rs_out);
+  const float o1 = quant_s(clipf(acc1 * inv, a.amax_out), s_out, rs_out);
+  const uint32_t pk = pack_i8x4(o0, o1, 0.f, 0.f);
+  *reinterpret_cast<unsigned short*>(a.out + (long long)r * a.ld_out + h * DH + lane * 2) = (unsigned short)(pk & 0xffff);
 }
 
 }  // namespace ls100
 
 using namespace ls100;
+
+// Opts the cross-attention kernel into its largest shared-memory tile on the current device
+// (called once from ls100_ctx_create, never inside a stream capture).
+int ls100_attn_init_device() {
+  const size_t smem = (size_t)(XT * XKS + XT * DH + 8 * DH + 8 * XT) * sizeof(float);
+  return cudaFuncSetAttribute(attn_cross_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess
+             ? LS100_OK
+             : LS100_ERR_CUDA;
+}
 
 extern "C" int ls100_attn_self(ls100_ctx* ctx, const ls100_attn_self_args* a, ls100_stream_t stream_) {
   if (!ctx || !a || !a->qkv || !a->out) return LS100_ERR_BAD_ARG;
@@ -399,10 +456,10 @@ extern "C" int ls100_attn_dec(ls100_ctx* ctx, const ls100_attn_dec_args* a, ls10
   if ((((uintptr_t)a->qkv) & 15) || (a->ld_qkv & 15) || (((uintptr_t)a->out) & 15) || (a->ld_out & 15) ||
       (((uintptr_t)a->k_cache) & 15) || (((uintptr_t)a->v_cache) & 15))
     return LS100_ERR_ALIGN;
-  if (a->max_step > 2048) return LS100_ERR_UNSUPPORTED;
+  if (a->max_step > 2048) return LS100_ERR_UNSUPPORTED;  // 4 * max_step * 4 bytes of shared memory per CTA
   const long long warps = (long long)a->rows * a->heads;
   const float score_scale = (a->s_kv * a->s_kv) * 0.125f;
-  attn_dec_kernel<<<(unsigned)((warps + 3) / 4), 128, 4 * a->max_step * sizeof(float), (cudaStream_t)stream_>>>(
+  attn_dec_kernel<<<(unsigned)((warps + 3) / 4), 128, 4 * a->max_step * sizeof(int), (cudaStream_t)stream_>>>(
       *a, a->amax_out / 127.0f, 1.0f / (a->amax_out / 127.0f), score_scale);
   return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
@@ -411,11 +468,13 @@ extern "C" int ls100_attn_cross(ls100_ctx* ctx, const ls100_attn_cross_args* a, 
   if (!ctx || !a || !a->q || !a->k || !a->v || !a->out) return LS100_ERR_BAD_ARG;
   if (a->batch <= 0 || a->beam <= 0 || a->src_len <= 0 || a->heads <= 0 || !(a->amax_out > 0.f)) return LS100_ERR_BAD_ARG;
   if (a->beam > 8 || a->src_len > 4096 || a->heads > 65535) return LS100_ERR_UNSUPPORTED;
-  if ((((uintptr_t)a->q) & 3) || (a->ld_q & 3) || (((uintptr_t)a->k) & 15) || (((uintptr_t)a->v) & 15) || (a->ld_kv & 3) ||
-      (((uintptr_t)a->out) & 3) || (a->ld_out & 3))
+  if ((((uintptr_t)a->q) & 1) || (a->ld_q & 1) || (((uintptr_t)a->k) & 15) || (((uintptr_t)a->v) & 15) || (a->ld_kv & 3) ||
+      (((uintptr_t)a->out) & 1) || (a->ld_out & 1) || (a->bias && (((uintptr_t)a->bias) & 7)))
     return LS100_ERR_ALIGN;
   dim3 grid(a->batch, a->heads);
-  attn_cross_kernel<<<grid, 32 * a->beam, (size_t)a->beam * a->src_len * sizeof(float), (cudaStream_t)stream_>>>(
-      *a, a->amax_out / 127.0f, 1.0f / (a->amax_out / 127.0f));
+  const int tr = a->src_len >= XT ? XT : (a->src_len + 31) / 32 * 32;
+  const size_t smem = (size_t)(tr * XKS + tr * DH + a->beam * DH + a->beam * tr) * sizeof(float);
+  attn_cross_kernel<<<grid, 32 * a->beam, smem, (cudaStream_t)stream_>>>(*a, a->amax_out / 127.0f,
+                                                                        1.0f / (a->amax_out / 127.0f), tr);
   return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }

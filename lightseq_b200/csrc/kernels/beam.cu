@@ -1,8 +1,8 @@
 // Beam-search step on the device, no host round trip:
-//   beam_topk   one CTA per (batch, beam) row: the row of int8 logits is read ONCE into
-//               registers (16-byte loads), a 256-bin histogram gives max / log-sum-exp and
-//               the value of the k-th largest logit, and the exact top-k by (logit desc,
-//               token asc) is emitted with length-normalised scores.
+//   beam_topk   one warp per (batch, beam) row: the row of int8 logits is streamed ONCE with
+//               16-byte loads; a 256-entry exp table + float64 per-lane sums give the
+//               log-sum-exp, per-lane register lists + a warp merge give the exact top-k by
+//               (logit desc, token asc), emitted with length-normalised scores.
 //   beam_update one CTA per batch element: merges beam*beam candidates, rewrites the
 //               token history and the KV-cache ancestry table in place (staged through
 //               shared memory), updates probabilities/scores, counts finished beams and
@@ -23,166 +23,167 @@ constexpr float LOGIT_THRESH_MIN = -64.f;   // lightseq/inference/kernels/transf
 constexpr float MIN_LOG_PROB = -2000.f;     // transformerKernels.h:12
 constexpr int MAX_BEAM = 8;
 
-template <int NCH>
-__global__ void __launch_bounds__(256) beam_topk_kernel(const ls100_beam_topk_args a) {
-  __shared__ int whist[8][256];
-  __shared__ int hist[256];
-  __shared__ double red[256];
-  __shared__ int s_qmax, s_thr, s_need, s_nabove, s_best;
-  __shared__ int l_val[MAX_BEAM], l_idx[MAX_BEAM];
-  const int t = threadIdx.x, warp = t >> 5;
-  const int row = blockIdx.x;
+// One warp per row, four rows per CTA, ONE pass over the row with 16-byte loads:
+//  * sum of exp: every byte indexes a 256-entry table exp((q - 127) * s) in shared memory;
+//    four independent fp32 partial sums per lane, combined in float64 at the end;
+//  * top-k: the warp keeps ONE threshold (the k-th best value seen so far by the whole
+//    warp). A 16-byte chunk is rejected with four SIMD byte compares; the rare bytes above
+//    the threshold are appended (ballot-prefix, no atomics) to a shared-memory candidate
+//    buffer of packed keys (value, then lower token id first), and when the buffer passes 32
+//    entries the warp re-selects its k best with k arg-max rounds and raises the threshold.
+//    Because the threshold reflects everything the warp has seen, only ~k*ln(V/k) bytes ever
+//    take the slow path.
+// log-sum-exp is taken relative to the largest representable logit (127 * s) instead of the
+// row maximum; the reference's clamp of exp arguments at -64 can then never trigger, which
+// the launcher enforces by requiring 254 * s <= 64.
+constexpr int TOPK_WARPS = 4;
+constexpr int TOPK_BUF = 512 + 64;  // one chunk can add 512 candidates while the threshold is still open
+
+__device__ __forceinline__ int4 load_row16(const int8_t* lp, int off, int vocab) {
+  if (off + 16 <= vocab) return *reinterpret_cast<const int4*>(lp + off);
+  int w[4] = {(int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080};  // -128 = "no token"
+  for (int j = 0; j < vocab - off; ++j) {
+    const int byte = (int)(uint8_t)lp[off + j];
+    w[j >> 2] = (w[j >> 2] & ~(0xff << ((j & 3) * 8))) | (byte << ((j & 3) * 8));
+  }
+  return make_int4(w[0], w[1], w[2], w[3]);
+}
+
+__device__ __forceinline__ unsigned topk_key(int val, int idx) {
+  return ((unsigned)(val + 128) << 22) | (unsigned)(0x3fffff - idx);  // larger key = better candidate
+}
+
+// Re-selects the K best keys of buf[0 .. n) into buf[0 .. min(K, n)), best first. Returns the new
+// threshold: the value of the K-th best, or -128 while fewer than K candidates exist.
+__device__ __forceinline__ int topk_flush(unsigned* buf, int n, int K, int lane, int* n_kept) {
+  constexpr int PER = (TOPK_BUF + 31) / 32;
+  unsigned keys[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = lane + 32 * i;
+    keys[i] = (e < n) ? buf[e] : 0u;
+  }
+  __syncwarp();
+  unsigned winner = 0;
+  int thr = -128;
+  for (int rnd = 0; rnd < K; ++rnd) {
+    unsigned loc = 0;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) loc = max(loc, keys[i]);
+    unsigned best = loc;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    if (best != 0u && loc == best) {  // keys are unique (token ids are), so exactly one lane owns it
+#pragma unroll
+      for (int i = 0; i < PER; ++i)
+        if (keys[i] == best) keys[i] = 0u;
+    }
+    if (lane == rnd) winner = best;
+    if (rnd == K - 1 && best != 0u) thr = (int)(best >> 22) - 128;
+  }
+  if (lane < K) buf[lane] = winner;
+  __syncwarp();
+  *n_kept = min(n, K);
+  return thr;
+}
+
+__global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_beam_topk_args a) {
+  __shared__ float s_lut[256];  // index = byte pattern (two's complement), value = exp((q - 127) * s); 0 for -128
+  __shared__ unsigned s_buf[TOPK_WARPS][TOPK_BUF];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+    const int q = (int)(int8_t)i;
+    s_lut[i] = (q == -128) ? 0.f : expf(__fmul_rn((float)(q - 127), a.s_logits));
+  }
+  __syncthreads();
+  const int row = blockIdx.x * TOPK_WARPS + warp;
+  if (row >= a.batch * a.beam) return;
   const int step = *a.step_ptr;
   const int K = a.beam;
   float* cs = a.cand_score + (long long)row * K;
   int32_t* ct = a.cand_token + (long long)row * K;
   if (step != 0 && a.alive[(long long)row * a.max_step + step] == a.end_id) {
-    if (t < K) {
-      cs[t] = (t == 0) ? a.seq_score[row] : -FLT_MAX;
-      ct[t] = a.end_id;
+    if (lane < K) {
+      cs[lane] = (lane == 0) ? a.seq_score[row] : -FLT_MAX;
+      ct[lane] = a.end_id;
     }
     return;
   }
-  for (int i = t; i < 8 * 256; i += 256) (&whist[0][0])[i] = 0;
-  if (t == 0) {
-    s_qmax = 0;
-    s_nabove = 0;
-  }
-  __syncthreads();
-  // ---- the row, once: 16 bytes per load, invalid tail bytes become -128
   const int8_t* lp = a.logits + (long long)row * a.ld_logits;
-  int4 reg[NCH];
+  unsigned* buf = s_buf[warp];
+  int n_buf = 0;   // entries in buf (the first ones are the current best list)
+  int thr = -128;  // bytes strictly above thr are candidates
+  unsigned thr4 = 0x80808080u;
+  float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
+  const int n_chunks = (a.vocab + 511) / 512;
+  int4 vnext = make_int4((int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080);
+  if (lane * 16 < a.vocab) vnext = load_row16(lp, lane * 16, a.vocab);
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    const int off = ch * 512 + lane * 16;
+    const int4 v = vnext;
+    vnext = make_int4((int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080);
+    if (off + 512 < a.vocab) vnext = load_row16(lp, off + 512, a.vocab);  // next chunk in flight
+    const unsigned w4[4] = {(unsigned)v.x, (unsigned)v.y, (unsigned)v.z, (unsigned)v.w};
+    unsigned hit = 0;
 #pragma unroll
-  for (int i = 0; i < NCH; ++i) {
-    const int off = (t + 256 * i) * 16;
-    int4 v = make_int4((int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080);
-    if (off + 16 <= a.vocab) v = *reinterpret_cast<const int4*>(lp + off);
-    else if (off < a.vocab) {
-      int w[4] = {(int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080};
-      for (int j = 0; j < a.vocab - off; ++j) {
-        const int byte = (int)(uint8_t)lp[off + j];
-        w[j >> 2] = (w[j >> 2] & ~(0xff << ((j & 3) * 8))) | (byte << ((j & 3) * 8));
+    for (int w = 0; w < 4; ++w) {
+      ps0 += s_lut[w4[w] & 0xff];
+      ps1 += s_lut[(w4[w] >> 8) & 0xff];
+      ps2 += s_lut[(w4[w] >> 16) & 0xff];
+      ps3 += s_lut[w4[w] >> 24];
+      hit |= __vcmpgts4(w4[w], thr4);
+    }
+    if (__ballot_sync(0xffffffffu, hit != 0u) != 0u) {  // rare, warp-uniform
+      unsigned qbits = 0;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const unsigned g = __vcmpgts4(w4[w], thr4);
+        qbits |= (((g >> 7) & 1u) | ((g >> 14) & 2u) | ((g >> 21) & 4u) | ((g >> 28) & 8u)) << (w * 4);
       }
-      v = make_int4(w[0], w[1], w[2], w[3]);
-    }
-    reg[i] = v;
-    const int w4[4] = {v.x, v.y, v.z, v.w};
+      const int mine = __popc(qbits);
+      int pre = mine;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const int q = (int)(int8_t)((w4[j >> 2] >> ((j & 3) * 8)) & 0xff);
-      if (q != -128) atomicAdd(&whist[warp][q + 128], 1);
-    }
-  }
-  __syncthreads();
-  int cnt = 0;
-#pragma unroll
-  for (int w = 0; w < 8; ++w) cnt += whist[w][t];
-  hist[t] = cnt;
-  if (cnt > 0) atomicMax(&s_qmax, t);
-  __syncthreads();
-  const int qmax = s_qmax - 128;
-  const float mx = __fmul_rn((float)qmax, a.s_logits);
-  {
-    const float lg = __fmul_rn((float)(t - 128), a.s_logits);
-    const float d = fmaxf(__fsub_rn(lg, mx), LOGIT_THRESH_MIN);
-    red[t] = cnt > 0 ? (double)cnt * (double)expf(d) : 0.0;
-  }
-  __syncthreads();
-  for (int s = 128; s > 0; s >>= 1) {
-    if (t < s) red[t] += red[t + s];
-    __syncthreads();
-  }
-  if (t == 0) {
-    int acc = 0, b = s_qmax;
-    for (; b > 0; --b) {
-      if (acc + hist[b] >= K) break;
-      acc += hist[b];
-    }
-    s_thr = b - 128;
-    s_nabove = 0;
-    s_need = K - acc;  // how many tokens of value == thr are taken (lowest ids first)
-    s_best = 0x7fffffff;
-  }
-  __syncthreads();
-  const int thr = s_thr;
-  // ---- tokens above the threshold value, and a bitmap of tokens equal to it
-  uint32_t eq[(NCH * 16 + 31) / 32];
-#pragma unroll
-  for (int i = 0; i < (NCH * 16 + 31) / 32; ++i) eq[i] = 0;
-#pragma unroll
-  for (int i = 0; i < NCH; ++i) {
-    const int w4[4] = {reg[i].x, reg[i].y, reg[i].z, reg[i].w};
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const int q = (int)(int8_t)((w4[j >> 2] >> ((j & 3) * 8)) & 0xff);
-      if (q == -128) continue;
-      if (q > thr) {
-        const int slot = atomicAdd(&s_nabove, 1);
-        if (slot < MAX_BEAM) {
-          l_val[slot] = q;
-          l_idx[slot] = (t + 256 * i) * 16 + j;
-        }
-      } else if (q == thr) {
-        eq[(i * 16 + j) >> 5] |= 1u << ((i * 16 + j) & 31);
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, pre, o);
+        if (lane >= o) pre += t;
       }
-    }
-  }
-  __syncthreads();
-  const int nabove = s_nabove;
-  const int need = s_need;
-  int last = -1;
-  for (int rnd = 0; rnd < need; ++rnd) {
-    // this thread's smallest token id with value == thr and id > last
-    int mine = 0x7fffffff;
-#pragma unroll
-    for (int wv = 0; wv < (NCH * 16 + 31) / 32; ++wv) {
-      uint32_t bits = eq[wv];
-      while (bits && mine == 0x7fffffff) {
+      const int total = __shfl_sync(0xffffffffu, pre, 31);
+      int pos = n_buf + pre - mine;
+      unsigned bits = qbits;
+      while (bits) {
         const int bpos = __ffs(bits) - 1;
         bits &= bits - 1;
-        const int pos = wv * 32 + bpos;
-        const int idx = (t + 256 * (pos >> 4)) * 16 + (pos & 15);
-        if (idx > last) mine = idx;
-        else eq[wv] &= ~(1u << bpos);
+        const int q = (int)(int8_t)((w4[bpos >> 2] >> ((bpos & 3) * 8)) & 0xff);
+        buf[pos++] = topk_key(q, off + bpos);
+      }
+      n_buf += total;
+      __syncwarp();
+      if (n_buf > 32) {
+        thr = topk_flush(buf, n_buf, K, lane, &n_buf);
+        thr4 = (unsigned)(thr & 0xff) * 0x01010101u;
       }
     }
-    if (mine != 0x7fffffff) atomicMin(&s_best, mine);
-    __syncthreads();
-    last = s_best;
-    if (t == 0) {
-      l_val[nabove + rnd] = thr;
-      l_idx[nabove + rnd] = last;
-    }
-    __syncthreads();
-    if (t == 0) s_best = 0x7fffffff;
-    __syncthreads();
   }
-  if (t == 0) {
-    // order the "above" part by (value desc, token asc); the "equal" part is already in token order
-    for (int i = 1; i < nabove; ++i) {
-      const int v = l_val[i], x = l_idx[i];
-      int j = i - 1;
-      while (j >= 0 && (l_val[j] < v || (l_val[j] == v && l_idx[j] > x))) {
-        l_val[j + 1] = l_val[j];
-        l_idx[j + 1] = l_idx[j];
-        --j;
-      }
-      l_val[j + 1] = v;
-      l_idx[j + 1] = x;
-    }
-    const float lse = logf((float)red[0]);
-    const float base = __fsub_rn(__fsub_rn(a.seq_probs[row], lse), mx);
+  __syncwarp();
+  topk_flush(buf, n_buf, K, lane, &n_buf);
+  double sum = ((double)ps0 + (double)ps1) + ((double)ps2 + (double)ps3);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane < K) {
+    // log-sum-exp relative to 127*s:  lse = log(sum) + 127*s;  base = prefix - lse
+    const float ref = __fmul_rn(127.f, a.s_logits);
+    const float lse = __fadd_rn(logf((float)sum), ref);
+    const float base = __fsub_rn(a.seq_probs[row], lse);
     const float ln = a.length_norm[step];
-    const int n = min(K, nabove + need);
-    for (int j = 0; j < K; ++j) {
-      if (j < n) {
-        const float lg = __fmul_rn((float)l_val[j], a.s_logits);
-        cs[j] = fmaxf(__fmul_rn(__fadd_rn(lg, base), ln), MIN_LOG_PROB + 1.f);
-        ct[j] = l_idx[j];
-      } else {
-        cs[j] = -FLT_MAX;
-        ct[j] = a.end_id;
-      }
+    if (lane >= n_buf) {
+      cs[lane] = -FLT_MAX;
+      ct[lane] = a.end_id;
+    } else {
+      const unsigned key = buf[lane];
+      const int val = (int)(key >> 22) - 128;
+      const float lg = __fmul_rn((float)val, a.s_logits);
+      cs[lane] = fmaxf(__fmul_rn(__fadd_rn(lg, base), ln), MIN_LOG_PROB + 1.f);
+      ct[lane] = 0x3fffff - (int)(key & 0x3fffff);
     }
   }
 }
@@ -270,12 +271,11 @@ extern "C" int ls100_beam_topk(ls100_ctx* ctx, const ls100_beam_topk_args* a, ls
       !a->cand_score || !a->cand_token)
     return LS100_ERR_BAD_ARG;
   if (a->batch <= 0 || a->beam <= 0 || a->vocab <= 0 || a->max_step <= 0 || !(a->s_logits > 0.f)) return LS100_ERR_BAD_ARG;
-  if (a->beam > MAX_BEAM || a->vocab > 65536 || a->vocab < a->beam) return LS100_ERR_UNSUPPORTED;
+  if (a->beam > MAX_BEAM || a->vocab < a->beam || a->vocab > (1 << 22)) return LS100_ERR_UNSUPPORTED;
+  if (254.f * a->s_logits > 64.f) return LS100_ERR_UNSUPPORTED;  // the -64 clamp of the reference would matter
   if ((((uintptr_t)a->logits) & 15) || (a->ld_logits & 15)) return LS100_ERR_ALIGN;
   const int rows = a->batch * a->beam;
-  cudaStream_t stream = (cudaStream_t)stream_;
-  if (a->vocab <= 32768) beam_topk_kernel<8><<<rows, 256, 0, stream>>>(*a);
-  else beam_topk_kernel<16><<<rows, 256, 0, stream>>>(*a);
+  beam_topk_kernel<<<(rows + TOPK_WARPS - 1) / TOPK_WARPS, 32 * TOPK_WARPS, 0, (cudaStream_t)stream_>>>(*a);
   return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
 

@@ -4,6 +4,7 @@
 #include <stdio.h>
 
 int ls100_gemm_i8_init_device();
+int ls100_attn_init_device();
 
 extern "C" int ls100_ctx_create(ls100_ctx** out, int device) {
   if (!out) return LS100_ERR_BAD_ARG;
@@ -32,7 +33,7 @@ extern "C" int ls100_ctx_create(ls100_ctx** out, int device) {
     return LS100_ERR_NO_DRIVER;
   }
   c->encode = (ls100_encode_tiled_fn)fn;
-  if (ls100_gemm_i8_init_device() != LS100_OK) {
+  if (ls100_gemm_i8_init_device() != LS100_OK || ls100_attn_init_device() != LS100_OK) {
     cudaFree(c->d_err);
     delete c;
     return LS100_ERR_CUDA;

@@ -52,7 +52,8 @@ struct GemmSmem {
   static constexpr int B_BYTES = BN * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
+  static constexpr int VEC_OFFSET = BAR_OFFSET + 256;          // per-tile bias (fp32) and w_off (int32)
+  static constexpr int TOTAL = VEC_OFFSET + BN * 8 + 1024;     // + alignment slack
 };
 
 // Shared-memory matrix descriptor, K-major, SWIZZLE_128B, 8-row groups 1024 B apart.
@@ -84,7 +85,9 @@ __device__ __forceinline__ void record_timeout(int* err) {
 // over the 32 registers, with the (warp-uniform) mode tests between the passes: a taken
 // branch per element costs more than the arithmetic it guards.
 template <int BN>
-__device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t (&r)[32], int row, int col0) {
+__device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t (&r)[32], int row, int col0,
+                                               const float* s_bias, const int* s_off, const float (&rr)[32],
+                                               bool rr_valid) {
   const bool row_ok = row < p.m;
   const bool full = (col0 + 32 <= p.n);
   const int nmax = p.n - 1;
@@ -92,18 +95,13 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
 #pragma unroll
   for (int j = 0; j < 32; ++j) acc[j] = (int)r[j];
   if (p.w_off != nullptr) {
-    if (full) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        const int4 o = __ldg(reinterpret_cast<const int4*>(p.w_off + col0 + j));
-        acc[j] += o.x;
-        acc[j + 1] += o.y;
-        acc[j + 2] += o.z;
-        acc[j + 3] += o.w;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) acc[j] += __ldg(p.w_off + min(col0 + j, nmax));
+    for (int j = 0; j < 32; j += 4) {
+      const int4 o = *reinterpret_cast<const int4*>(s_off + j);  // staged in shared memory, zero beyond N
+      acc[j] += o.x;
+      acc[j + 1] += o.y;
+      acc[j + 2] += o.z;
+      acc[j + 3] += o.w;
     }
   }
   if (p.out_kind == LS100_OUT_I32) {
@@ -133,18 +131,13 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
   }
   if (p.out_kind != LS100_OUT_OUTQ_I8) {
     if (p.bias != nullptr) {
-      if (full) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + j));
-          v[j] = __fadd_rn(v[j], b.x);
-          v[j + 1] = __fadd_rn(v[j + 1], b.y);
-          v[j + 2] = __fadd_rn(v[j + 2], b.z);
-          v[j + 3] = __fadd_rn(v[j + 3], b.w);
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], __ldg(p.bias + min(col0 + j, nmax)));
+      for (int j = 0; j < 32; j += 4) {
+        const float4 b = *reinterpret_cast<const float4*>(s_bias + j);
+        v[j] = __fadd_rn(v[j], b.x);
+        v[j + 1] = __fadd_rn(v[j + 1], b.y);
+        v[j + 2] = __fadd_rn(v[j + 2], b.z);
+        v[j + 3] = __fadd_rn(v[j + 3], b.w);
       }
     }
     if (p.act == LS100_ACT_RELU) {
@@ -155,20 +148,25 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
       for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
     }
     if (p.resid != nullptr && row_ok) {
-      const float* rp = p.resid + (long long)row * p.ldr + col0;
-      if (full && ((p.ldr & 3) == 0) && ((((uintptr_t)p.resid) & 15) == 0)) {
+      if (rr_valid) {  // prefetched before the accumulator was ready
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float4 t = *reinterpret_cast<const float4*>(rp + j);
-          v[j] = __fadd_rn(v[j], t.x);
-          v[j + 1] = __fadd_rn(v[j + 1], t.y);
-          v[j + 2] = __fadd_rn(v[j + 2], t.z);
-          v[j + 3] = __fadd_rn(v[j + 3], t.w);
-        }
+        for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], rr[j]);
       } else {
+        const float* rp = p.resid + (long long)row * p.ldr + col0;
+        if (full && ((p.ldr & 3) == 0) && ((((uintptr_t)p.resid) & 15) == 0)) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (col0 + j < p.n) v[j] = __fadd_rn(v[j], rp[j]);
+          for (int j = 0; j < 32; j += 4) {
+            const float4 t = *reinterpret_cast<const float4*>(rp + j);
+            v[j] = __fadd_rn(v[j], t.x);
+            v[j + 1] = __fadd_rn(v[j + 1], t.y);
+            v[j + 2] = __fadd_rn(v[j + 2], t.z);
+            v[j + 3] = __fadd_rn(v[j + 3], t.w);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.n) v[j] = __fadd_rn(v[j], rp[j]);
+        }
       }
     }
     if (p.out_kind == LS100_OUT_REQ_S8) {
@@ -240,6 +238,8 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tmem_full_bar = empty_bar + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+  float* s_bias = reinterpret_cast<float*>(smem + SM::VEC_OFFSET);
+  int* s_off = reinterpret_cast<int*>(smem + SM::VEC_OFFSET + BN * 4);
 
   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
   const int warp = threadIdx.x >> 5;
@@ -325,6 +325,35 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
   } else {
     const int quarter = warp & 3;
     const int row = m0 + quarter * 32 + lane;
+    // While the main loop runs: stage this tile's bias / weight offsets in shared memory and
+    // prefetch the first 32 residual values of this thread's row, so that no global-load latency
+    // is left between "accumulator ready" and the stores.
+    {
+      const int te = threadIdx.x - 64;
+      for (int i = te; i < BN; i += 128) {
+        const int n = n0 + i;
+        s_bias[i] = (p.bias != nullptr && n < p.n) ? __ldg(p.bias + n) : 0.f;
+        s_off[i] = (p.w_off != nullptr && n < p.n) ? __ldg(p.w_off + n) : 0;
+      }
+    }
+    float rr[32];
+    const bool rr_ok = p.resid != nullptr && row < p.m && (n0 + 32 <= p.n) && ((p.ldr & 3) == 0) &&
+                       ((((uintptr_t)p.resid) & 15) == 0) && p.out_kind != LS100_OUT_I32 && p.out_kind != LS100_OUT_OUTQ_I8;
+    if (rr_ok) {
+      const float* rp = p.resid + (long long)row * p.ldr + n0;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(rp + j);
+        rr[j] = t.x;
+        rr[j + 1] = t.y;
+        rr[j + 2] = t.z;
+        rr[j + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) rr[j] = 0.f;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
     bool ok = mbar_wait(tmem_full_bar, 0);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) {
@@ -339,7 +368,7 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
         tmem_ld_wait();
         if (c0 == 0) { LS100_TRACE(7); }
-        epilogue_chunk<BN>(p, r, row, n0 + c0);
+        epilogue_chunk<BN>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, rr_ok && c0 == 0);
         LS100_TRACE(8 + c0 / 32);
       }
     }
