@@ -177,38 +177,136 @@ def run_reference_arm(args):
 
 
 # ------------------------------------------------------------------------------ GPU arm
-def time_attn_dec_kernel(torch, L, ctx, heads: int, rows: int, max_step: int, step: int, iters: int = 30):
-    """Average duration of the decoder self-attention kernel at decode position ``step`` (the dominant
-    HBM-bound kernel of a decode step), timed alone with CUDA events on the default stream. A rotating
-    set of caches larger than L2 keeps every launch reading from HBM."""
-    H = heads * 64
-    n_sets = max(2, int(200e6 // (2 * rows * max_step * H)) + 1)
-    kcs = [torch.randint(-127, 128, (rows, heads, max_step, 64), dtype=torch.int8, device="cuda") for _ in range(n_sets)]
-    vcs = [torch.randint(-127, 128, (rows, heads, max_step, 64), dtype=torch.int8, device="cuda") for _ in range(n_sets)]
-    qkv = torch.randint(-127, 128, (rows, 3 * H), dtype=torch.int8, device="cuda")
-    out = torch.empty((rows, H), dtype=torch.int8, device="cuda")
-    dstep = torch.tensor([step], dtype=torch.int32, device="cuda")
+def kernel_cases(torch, L, conf, B, S, step):
+    """The kernels of one decode step at this workload's shapes, each as (launch(i, stream), algorithmic bytes,
+    bound, note). Operands rotate through more than 126 MB of device memory so that every launch misses L2."""
+    H, F, V = int(conf["hidden"]), int(conf["ffn"]), int(conf["vocab"])
+    heads, K, ms = int(conf["heads"]), int(conf["beam"]), int(conf["max_step"])
+    T = B * K
+    dev = "cuda"
 
-    def launch(i):
-        a = L.AttnDecArgs(qkv=qkv.data_ptr(), ld_qkv=3 * H, s_kv=0.03, k_cache=kcs[i % n_sets].data_ptr(),
-                          v_cache=vcs[i % n_sets].data_ptr(), anc=None, step_ptr=dstep.data_ptr(), rows=rows, heads=heads,
-                          max_step=max_step, amax_out=1.0, out=out.data_ptr(), ld_out=H)
-        L.call("ls100_attn_dec", ctx, a, torch.cuda.current_stream().cuda_stream)
+    def i8(*shape):
+        return torch.randint(-127, 128, shape, dtype=torch.int8, device=dev)
 
-    for i in range(3):
-        launch(i)
-    torch.cuda.synchronize()
-    evs = []
-    for i in range(iters):
+    cases = {}
+    # out-projection-shaped GEMM: int8 [T,H] x [H,H] -> fake-quant + bias + residual -> fp32 (most frequent launch)
+    n_sets = 100
+    a_s, w_s = [i8(T, H) for _ in range(n_sets)], [i8(H, H) for _ in range(n_sets)]
+    x_s = [torch.randn(T, H, device=dev) for _ in range(n_sets)]
+    bias = torch.zeros(H, device=dev)
+
+    def gemm_dec(i, st):
+        j = i % n_sets
+        a = L.GemmI8Args(a=a_s[j].data_ptr(), lda=H, w=w_s[j].data_ptr(), ldw=H, m=T, n=H, k=H, s_acc=1e-4, s_outq=0.02,
+                         bias=bias.data_ptr(), resid=x_s[j].data_ptr(), ldr=H, out_kind=L.OUT_F32, out=x_s[j].data_ptr(), ldo=H)
+        L.call("ls100_gemm_i8", CTX[0], a, st)
+
+    cases["gemm_dec"] = (gemm_dec, T * H + H * H + 2 * T * H * 4 + H * 4, "hbm",
+                         f"gemm_i8_tc_kernel<32,4>, {T}x{H}x{H}, fused fake-quant+bias+residual, fp32 out")
+    # logits GEMM
+    wl = [i8(V, H) for _ in range(8)]
+    ldv = (V + 15) // 16 * 16
+    lo = [torch.empty(T, ldv, dtype=torch.int8, device=dev) for _ in range(8)]
+
+    def gemm_logits(i, st):
+        j = i % 8
+        a = L.GemmI8Args(a=a_s[j].data_ptr(), lda=H, w=wl[j].data_ptr(), ldw=H, m=T, n=V, k=H, s_acc=1e-4, s_outq=0.02,
+                         out_kind=L.OUT_OUTQ_I8, out=lo[j].data_ptr(), ldo=ldv)
+        L.call("ls100_gemm_i8", CTX[0], a, st)
+
+    cases["gemm_logits"] = (gemm_logits, T * H + V * H + T * V, "hbm", f"gemm_i8_tc_kernel<256,4>, {T}x{V}x{H}, int8 out")
+    # decoder self-attention at decode position `step`
+    nk = max(2, int(200e6 // (2 * T * ms * H)) + 1)
+    kcs, vcs = [i8(T, heads, ms, 64) for _ in range(nk)], [i8(T, heads, ms, 64) for _ in range(nk)]
+    qkv, o8 = i8(T, 3 * H), torch.empty(T, H, dtype=torch.int8, device=dev)
+    dstep = torch.tensor([step], dtype=torch.int32, device=dev)
+
+    def attn_dec(i, st):
+        a = L.AttnDecArgs(qkv=qkv.data_ptr(), ld_qkv=3 * H, s_kv=0.03, k_cache=kcs[i % nk].data_ptr(),
+                          v_cache=vcs[i % nk].data_ptr(), anc=None, step_ptr=dstep.data_ptr(), rows=T, heads=heads,
+                          max_step=ms, amax_out=1.0, out=o8.data_ptr(), ld_out=H)
+        L.call("ls100_attn_dec", CTX[0], a, st)
+
+    cases["attn_dec"] = (attn_dec, T * H * (2 * (step + 1) + 3), "hbm", f"attn_dec_kernel, rows {T}, history {step + 1}")
+    # cross attention
+    nx = 6
+    kx, vx = [torch.randn(B * S, H, device=dev) for _ in range(nx)], [torch.randn(B * S, H, device=dev) for _ in range(nx)]
+    pm = torch.zeros(B, S, dtype=torch.uint8, device=dev)
+
+    def attn_cross(i, st):
+        a = L.AttnCrossArgs(q=o8.data_ptr(), ld_q=H, s_q=0.02, bias=bias.data_ptr(), k=kx[i % nx].data_ptr(),
+                            v=vx[i % nx].data_ptr(), ld_kv=H, pad_mask=pm.data_ptr(), batch=B, beam=K, src_len=S, heads=heads,
+                            amax_out=1.0, out=o8.data_ptr(), ld_out=H)
+        L.call("ls100_attn_cross", CTX[0], a, st)
+
+    cases["attn_cross"] = (attn_cross, 2 * B * S * H * 4 + 2 * T * H, "hbm", f"attn_cross_kernel, batch {B} beam {K} src {S}")
+    # beam top-k over the int8 logits
+    lg = [torch.clamp(torch.randn(T, ldv, device=dev) * 32, -127, 127).to(torch.int8) for _ in range(10)]
+    alive = torch.full((T, ms), 5, dtype=torch.int32, device=dev)
+    pr, sc, lnt = torch.zeros(T, device=dev), torch.zeros(T, device=dev), torch.ones(ms, device=dev)
+    cs, ct = torch.empty(T, K, device=dev), torch.empty(T, K, dtype=torch.int32, device=dev)
+
+    def beam_topk(i, st):
+        a = L.BeamTopkArgs(logits=lg[i % 10].data_ptr(), ld_logits=ldv, s_logits=0.014, batch=B, beam=K, vocab=V, max_step=ms,
+                           end_id=2, step_ptr=dstep.data_ptr(), length_norm=lnt.data_ptr(), alive=alive.data_ptr(),
+                           seq_probs=pr.data_ptr(), seq_score=sc.data_ptr(), cand_score=cs.data_ptr(), cand_token=ct.data_ptr())
+        L.call("ls100_beam_topk", CTX[0], a, st)
+
+    cases["beam_topk"] = (beam_topk, T * V, "hbm", f"beam_topk_kernel, {T} rows x {V}")
+    g1, b1 = torch.ones(H, device=dev), torch.zeros(H, device=dev)
+
+    def ln_quant(i, st):
+        j = i % n_sets
+        a = L.LnQuantArgs(x=x_s[j].data_ptr(), ldx=H, gamma=g1.data_ptr(), beta=b1.data_ptr(), rows=T, hidden=H, amax=4.0,
+                          out_q=a_s[j].data_ptr(), ldq=H, out_f=None, ldf=0)
+        L.call("ls100_ln_quant", CTX[0], a, st)
+
+    cases["ln_quant"] = (ln_quant, T * H * 5, "hbm", f"ln_quant_kernel, {T}x{H}")
+    return cases
+
+
+CTX = [None]
+
+
+def time_kernel(torch, launch, iters: int = 40, reps: int = 5):
+    """Mean duration of one launch. ``iters`` launches with rotating operands are captured into one CUDA graph
+    (so that the host's launch cost is not what is measured) and the graph is replayed ``reps`` times between two
+    CUDA events recorded on the launching stream."""
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for i in range(3):
+            launch(i, side.cuda_stream)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for i in range(iters):
+                launch(i, side.cuda_stream)
+        g.replay()
+        torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        launch(i)
-        e1.record()
-        evs.append((e0, e1))
-    torch.cuda.synchronize()
-    ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
-    algo_bytes = rows * heads * 64 * (2 * (step + 1) + 3)  # K and V read once, q read, k/v appended, out written
-    return ms, algo_bytes
+        e0.record(side)
+        for _ in range(reps):
+            g.replay()
+        e1.record(side)
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (iters * reps)
+
+
+def run_single_kernel(args):
+    """``--kernel NAME``: launches one kernel family alone (what the ncu captures under profiles/ ran)."""
+    import torch
+
+    from lightseq_b200 import _lib as L
+
+    torch.cuda.set_device(0)
+    CTX[0] = L.Context(0)
+    conf = dict(hidden=512, ffn=2048, vocab=WORKLOAD["vocab"], heads=8, beam=WORKLOAD["beam"], max_step=WORKLOAD["max_step"])
+    cases = kernel_cases(torch, L, conf, WORKLOAD["batch"], WORKLOAD["max_len"], 54)
+    launch, algo, bound, note = cases[args.kernel]
+    ms = time_kernel(torch, launch)
+    print(json.dumps({"kernel": args.kernel, "note": note, "launch_us": ms * 1e3, "algorithmic_bytes": algo,
+                      "achieved_gbs": algo / (ms / 1e3) / 1e9}), flush=True)
+    return 0
 
 
 def run_ours(args):
@@ -345,23 +443,30 @@ def run_ours(args):
 
     # ---- roofline of the dominant decode kernel, and the CPU baseline (rank 0, N = 1 only for the latter)
     hbm_peak, peak_src = peaks()
-    ctx = L.Context(local)
+    CTX[0] = L.Context(local)
     mid_step = max(steps_per_infer // 2, 1)
-    ms_k, algo = time_attn_dec_kernel(torch, L, ctx, int(conf["heads"]), B * int(conf["beam"]), max_step, mid_step)
-    achieved = algo / (ms_k / 1e3) / 1e9
-    traffic = None
-    prof = ROOT / "profiles" / "attn_dec_traffic.json"
+    cases = kernel_cases(torch, L, conf, B, S, mid_step)
+    traffic_tab = {}
+    prof = ROOT / "profiles" / "dram_traffic.json"
     if prof.exists():
         try:
-            pj = json.loads(prof.read_text())
-            traffic = pj["dram_bytes_per_position_row"] * (mid_step + 1) * B * int(conf["beam"])
+            traffic_tab = json.loads(prof.read_text())
         except Exception:
-            traffic = None
-    roofline = {"kernel": "attn_dec_kernel (decoder self-attention over the int8 KV cache)", "bound": "hbm",
-                "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "traffic": traffic,
-                "peak_source": peak_src, "launch_us": ms_k * 1e3,
-                "how": f"kernel timed alone with CUDA events at decode position {mid_step} (mid-sequence), rows "
-                       f"{B * int(conf['beam'])}, rotating caches larger than L2; algorithmic bytes = rows*H*(2*L+3)"}
+            traffic_tab = {}
+    per_kernel = {}
+    for name, (launch, algo, bound, note) in cases.items():
+        ms_k = time_kernel(torch, launch)
+        ach = algo / (ms_k / 1e3) / 1e9
+        per_kernel[name] = {"kernel": note, "bound": bound, "achieved": ach, "peak": hbm_peak, "unit": "GB/s",
+                            "frac": ach / hbm_peak, "traffic": traffic_tab.get(name), "launch_us": ms_k * 1e3,
+                            "algorithmic_bytes": algo}
+    # Dominant kernel of the timed region by total time (profiles/launch_list_transformer_base.md): the small
+    # decode GEMM family, ~36 launches per decode step.
+    roofline = dict(per_kernel["gemm_dec"])
+    roofline.update({"peak_source": peak_src,
+                     "how": "each kernel timed alone: 40 launches with operands rotating through >126 MB (no launch served "
+                            "from L2) captured in one CUDA graph, replayed between two CUDA events on the launching "
+                            "stream; achieved = algorithmic bytes / mean launch time"})
     cpu = None
     if world == 1 and not args.no_cpu:
         n_sent = 4
@@ -382,7 +487,8 @@ def run_ours(args):
                    "l2": "256 MB buffer written between timed iterations; per-step working set (KV caches, logits) > L2"},
         "clocks": clocks, "gpu_launches": per_infer * args.steps,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": int(src.nbytes), "d2h_bytes_per_step": int(d2h)},
-        "roofline": roofline, "cpu_baseline": cpu,
+        "roofline": roofline, "roofline_other_kernels": {k: v for k, v in per_kernel.items() if k != "gemm_dec"},
+        "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)
     if dist is not None:
@@ -399,11 +505,15 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--decode-steps", type=int, default=-1,
                     help="cap the number of decode steps per generation (profiling aid; the result is not a bench value)")
+    ap.add_argument("--kernel", default=None,
+                    help="run one kernel family alone (gemm_dec, gemm_logits, attn_dec, attn_cross, beam_topk, ln_quant)")
     ap.add_argument("--quick", action="store_true",
                     help="device-resident arm only, warm-up exactly as given (for profiler launch lists)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.kernel:
+        return run_single_kernel(args)
     return run_ours(args)
 
 
