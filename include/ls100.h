@@ -276,6 +276,23 @@ typedef struct {
 } ls100_beam_update_args;
 int ls100_beam_update(ls100_ctx* ctx, const ls100_beam_update_args* args, ls100_stream_t stream);
 
+/* Allocation-free form of ls100_beam_update. It has no counterpart in the reference.
+ * For callers that cannot provide the two scratch arrays because they cannot allocate device memory at all:
+ * a serving process that handed every byte of the GPU to its own arena at start-up, or a latency-critical
+ * thread that must never reach cudaMalloc/cudaFree (both synchronise the device). The `fin_count` and `ticket`
+ * fields of `args` are ignored; the counters live in an 8 KB array inside the library image (held by every GPU
+ * that loads the library until the process exits), which bounds max_step to
+ * LS100_BEAM_UPDATE_NOALLOC_MAX_STEP - larger values return LS100_ERR_UNSUPPORTED and launch nothing.
+ * Everything else (inputs, outputs, results) is exactly ls100_beam_update's.
+ *  - The FIRST call on each device looks up the array's device address (the context's device must be
+ *    current). Make that first call outside any stream capture.
+ *  - Every call clears the array on `stream` before launching, so it does not matter what the previous call
+ *    left behind; but all calls share the one array: two calls that can overlap on the GPU (different streams,
+ *    or different contexts on the same device) race on it. Serialise them on one stream.
+ *  - No cudaMalloc, cudaFree or allocating library routine is called. */
+#define LS100_BEAM_UPDATE_NOALLOC_MAX_STEP 1024
+int ls100_beam_update_noalloc(ls100_ctx* ctx, const ls100_beam_update_args* args, ls100_stream_t stream);
+
 /* ------------------------------------------------------------- load-time prep ---
  * fp32 -> int8 with the tensor's clip-max (quantize_weight, lightseq/inference/model/
  * cublas_helper.cc:553-593) and, optionally, off[n] = 127 * sum_k q[n,k]: the exact

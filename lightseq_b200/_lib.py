@@ -129,7 +129,7 @@ lib.ls100_gemm_i8.argtypes = [C.c_void_p, C.POINTER(GemmI8Args), C.c_void_p]
 for _name, _cls in (("ls100_ln_quant", LnQuantArgs), ("ls100_embed", EmbedArgs), ("ls100_attn_self", AttnSelfArgs),
                     ("ls100_attn_dec", AttnDecArgs), ("ls100_attn_cross", AttnCrossArgs),
                     ("ls100_proj_f32", ProjF32Args), ("ls100_beam_topk", BeamTopkArgs),
-                    ("ls100_beam_update", BeamUpdateArgs)):
+                    ("ls100_beam_update", BeamUpdateArgs), ("ls100_beam_update_noalloc", BeamUpdateArgs)):
     _fn = getattr(lib, _name)
     _fn.restype = C.c_int
     _fn.argtypes = [C.c_void_p, C.POINTER(_cls), C.c_void_p]

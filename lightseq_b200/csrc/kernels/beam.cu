@@ -13,6 +13,9 @@
 // the rough threshold + global Thrust sort are replaced by an exact selection with a
 // fixed tie-break (higher score, lower beam, lower token id).
 #include <float.h>
+#include <stdio.h>
+
+#include <mutex>
 
 #include "common.cuh"
 #include "ctx.h"
@@ -290,3 +293,47 @@ extern "C" int ls100_beam_update(ls100_ctx* ctx, const ls100_beam_update_args* a
   beam_update_kernel<<<a->batch, 128, smem, (cudaStream_t)stream_>>>(*a);
   return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
+
+// ------------------------------------------------------------------ allocation-free variant
+// Scratch of ls100_beam_update_noalloc: the per-step finished counters and CTA tickets that
+// ls100_beam_update takes from the caller. Lives in the library image: every GPU that loads
+// libls100.so holds these 8 KB until the process exits.
+static __device__ __align__(256) int32_t g_noalloc_scratch[2 * LS100_BEAM_UPDATE_NOALLOC_MAX_STEP];
+
+namespace {
+std::mutex g_noalloc_mu;
+int32_t* g_noalloc_ptr[64] = {nullptr};  // device address of g_noalloc_scratch, per device ordinal
+}  // namespace
+
+extern "C" int ls100_beam_update_noalloc(ls100_ctx* ctx, const ls100_beam_update_args* a, ls100_stream_t stream_) {
+  if (!ctx || !a) return LS100_ERR_BAD_ARG;
+  if (a->max_step > LS100_BEAM_UPDATE_NOALLOC_MAX_STEP) {
+    fprintf(stderr, "ls100_beam_update_noalloc: max_step %d exceeds the built-in scratch (limit %d); use ls100_beam_update "
+                    "with caller-provided fin_count/ticket arrays\n", a->max_step, LS100_BEAM_UPDATE_NOALLOC_MAX_STEP);
+    return LS100_ERR_UNSUPPORTED;
+  }
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return LS100_ERR_CUDA;
+  if (dev != ctx->device || dev < 0 || dev >= 64) return LS100_ERR_BAD_ARG;  // the context's device must be current
+  int32_t* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+      // In host code the array's name is only a handle for the runtime, not a device address:
+      // ask the runtime for the address on the current device, once per device.
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) return LS100_ERR_CUDA;
+      g_noalloc_ptr[dev] = static_cast<int32_t*>(p);
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  cudaStream_t stream = (cudaStream_t)stream_;
+  // The array keeps whatever the previous call left in it; the counters must start at zero.
+  if (cudaMemsetAsync(scratch, 0, sizeof(int32_t) * 2 * LS100_BEAM_UPDATE_NOALLOC_MAX_STEP, stream) != cudaSuccess)
+    return LS100_ERR_CUDA;
+  ls100_beam_update_args b = *a;
+  b.fin_count = scratch;
+  b.ticket = scratch + LS100_BEAM_UPDATE_NOALLOC_MAX_STEP;
+  return ls100_beam_update(ctx, &b, stream_);
+}
+
