@@ -36,6 +36,8 @@ __global__ void __launch_bounds__(64) attn_self_kernel(const ls100_attn_self_arg
   __shared__ __align__(16) float Ks[64][DH];
   __shared__ __align__(16) float Vs[64][DH];
   __shared__ uint8_t msk[64];
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int q0 = blockIdx.x * 64;
   const int h = blockIdx.y;
@@ -203,6 +205,8 @@ __global__ void __launch_bounds__(64) attn_self_kernel(const ls100_attn_self_arg
 __global__ void __launch_bounds__(128) attn_dec_kernel(const ls100_attn_dec_args a, const float s_out,
                                                         const float rs_out, const float score_scale) {
   extern __shared__ int slot_all[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wid = blockIdx.x * 4 + warp;
   if (wid >= a.rows * a.heads) return;
@@ -313,6 +317,8 @@ constexpr int XKS = DH + 1;  // padded key row (conflict-free when lanes read di
 __global__ void __launch_bounds__(256) attn_cross_kernel(const ls100_attn_cross_args a, const float s_out, const float rs_out,
                                                           const int tr /* tile rows held in shared memory, <= XT */) {
   extern __shared__ float xs[];
+  pdl_launch_dependents();
+  pdl_wait();
   float* Ks = xs;                    // [tr][XKS]
   float* Vs = Ks + tr * XKS;         // [tr][DH]
   float* qs = Vs + tr * DH;          // [beam][DH]
@@ -446,8 +452,10 @@ extern "C" int ls100_attn_self(ls100_ctx* ctx, const ls100_attn_self_args* a, ls
     return LS100_ERR_BAD_ARG;
   if (a->heads > 65535 || a->batch > 65535) return LS100_ERR_UNSUPPORTED;
   dim3 grid((a->seq + 63) / 64, a->heads, a->batch);
-  attn_self_kernel<<<grid, 64, 0, (cudaStream_t)stream_>>>(*a, a->amax_out / 127.0f, 1.0f / (a->amax_out / 127.0f));
-  return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+  const float so = a->amax_out / 127.0f;
+  return ls100_launch(attn_self_kernel, grid, dim3(64), 0, (cudaStream_t)stream_, *a, so, 1.0f / so) == cudaSuccess
+             ? LS100_OK
+             : LS100_ERR_CUDA;
 }
 
 extern "C" int ls100_attn_dec(ls100_ctx* ctx, const ls100_attn_dec_args* a, ls100_stream_t stream_) {
@@ -459,9 +467,11 @@ extern "C" int ls100_attn_dec(ls100_ctx* ctx, const ls100_attn_dec_args* a, ls10
   if (a->max_step > 2048) return LS100_ERR_UNSUPPORTED;  // 4 * max_step * 4 bytes of shared memory per CTA
   const long long warps = (long long)a->rows * a->heads;
   const float score_scale = (a->s_kv * a->s_kv) * 0.125f;
-  attn_dec_kernel<<<(unsigned)((warps + 3) / 4), 128, 4 * a->max_step * sizeof(int), (cudaStream_t)stream_>>>(
-      *a, a->amax_out / 127.0f, 1.0f / (a->amax_out / 127.0f), score_scale);
-  return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+  const float so = a->amax_out / 127.0f;
+  return ls100_launch(attn_dec_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 4 * a->max_step * sizeof(int),
+                      (cudaStream_t)stream_, *a, so, 1.0f / so, score_scale) == cudaSuccess
+             ? LS100_OK
+             : LS100_ERR_CUDA;
 }
 
 extern "C" int ls100_attn_cross(ls100_ctx* ctx, const ls100_attn_cross_args* a, ls100_stream_t stream_) {
@@ -474,7 +484,9 @@ extern "C" int ls100_attn_cross(ls100_ctx* ctx, const ls100_attn_cross_args* a, 
   dim3 grid(a->batch, a->heads);
   const int tr = a->src_len >= XT ? XT : (a->src_len + 31) / 32 * 32;
   const size_t smem = (size_t)(tr * XKS + tr * DH + a->beam * DH + a->beam * tr) * sizeof(float);
-  attn_cross_kernel<<<grid, 32 * a->beam, smem, (cudaStream_t)stream_>>>(*a, a->amax_out / 127.0f,
-                                                                        1.0f / (a->amax_out / 127.0f), tr);
-  return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+  const float so = a->amax_out / 127.0f;
+  return ls100_launch(attn_cross_kernel, grid, dim3(32 * a->beam), smem, (cudaStream_t)stream_, *a, so, 1.0f / so, tr) ==
+                 cudaSuccess
+             ? LS100_OK
+             : LS100_ERR_CUDA;
 }

@@ -94,10 +94,12 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
   __shared__ float s_lut[256];  // index = byte pattern (two's complement), value = exp((q - 127) * s); 0 for -128
   __shared__ unsigned s_buf[TOPK_WARPS][TOPK_BUF];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+  pdl_launch_dependents();
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) {  // the table depends on the scale only: built before the wait
     const int q = (int)(int8_t)i;
     s_lut[i] = (q == -128) ? 0.f : expf(__fmul_rn((float)(q - 127), a.s_logits));
   }
+  pdl_wait();
   __syncthreads();
   const int row = blockIdx.x * TOPK_WARPS + warp;
   if (row >= a.batch * a.beam) return;
@@ -195,33 +197,49 @@ __global__ void __launch_bounds__(128) beam_update_kernel(const ls100_beam_updat
   extern __shared__ int stage[];  // [2][K][max_step]
   __shared__ int s_parent[MAX_BEAM], s_token[MAX_BEAM];
   __shared__ float s_score[MAX_BEAM];
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x, t = threadIdx.x;
   const int K = a.beam;
   const int step = *a.step_ptr;
   const int ms = a.max_step;
   int* st_alive = stage;
   int* st_anc = stage + K * ms;
-  if (t == 0) {
-    // best K of K*K candidates by (score desc, beam asc, token asc)
+  if (t < 32) {
+    // best K of K*K candidates by (score desc, beam asc, token asc). Candidate c = beam * K + rank is already in
+    // (beam asc, then logit desc / token asc) order, so "lower c" is the tie-break. Lane t holds c = t and t + 32.
     const float* cs = a.cand_score + (long long)b * K * K;
     const int32_t* ct = a.cand_token + (long long)b * K * K;
-    unsigned long long used = 0ull;
+    const int n = K * K;
+    float sc0 = (t < n) ? cs[t] : -INFINITY, sc1 = (t + 32 < n) ? cs[t + 32] : -INFINITY;
+    const int tk0 = (t < n) ? ct[t] : 0, tk1 = (t + 32 < n) ? ct[t + 32] : 0;
+    bool used0 = !(t < n), used1 = !(t + 32 < n);
     for (int j = 0; j < K; ++j) {
-      int best = -1;
-      for (int c = 0; c < K * K; ++c) {
-        if (used >> c & 1ull) continue;
-        if (best < 0) {
-          best = c;
-          continue;
-        }
-        const float sc = cs[c], sb = cs[best];
-        if (sc > sb) best = c;  // equal scores keep the earlier (lower beam, then lower-token-first) candidate
-        else if (sc == sb && (c / K == best / K) && ct[c] < ct[best]) best = c;
+      float my = -INFINITY;
+      int myc = 0x7fffffff;
+      if (!used0) {
+        my = sc0;
+        myc = t;
       }
-      used |= 1ull << best;
-      s_parent[j] = best / K;
-      s_token[j] = ct[best];
-      s_score[j] = cs[best];
+      if (!used1 && (sc1 > my || myc == 0x7fffffff)) {
+        my = sc1;
+        myc = t + 32;
+      }
+      float best = my;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
+      int bc = (myc != 0x7fffffff && my == best) ? myc : 0x7fffffff;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) bc = min(bc, __shfl_xor_sync(0xffffffffu, bc, o));
+      if (bc == t) used0 = true;
+      if (bc == t + 32) used1 = true;
+      const int owner = bc & 31;
+      const int tok = __shfl_sync(0xffffffffu, bc < 32 ? tk0 : tk1, owner);
+      if (t == 0) {
+        s_parent[j] = bc / K;
+        s_token[j] = tok;
+        s_score[j] = best;
+      }
     }
   }
   int* alive_b = a.alive + (long long)b * K * ms;
@@ -278,8 +296,10 @@ extern "C" int ls100_beam_topk(ls100_ctx* ctx, const ls100_beam_topk_args* a, ls
   if (254.f * a->s_logits > 64.f) return LS100_ERR_UNSUPPORTED;  // the -64 clamp of the reference would matter
   if ((((uintptr_t)a->logits) & 15) || (a->ld_logits & 15)) return LS100_ERR_ALIGN;
   const int rows = a->batch * a->beam;
-  beam_topk_kernel<<<(rows + TOPK_WARPS - 1) / TOPK_WARPS, 32 * TOPK_WARPS, 0, (cudaStream_t)stream_>>>(*a);
-  return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+  return ls100_launch(beam_topk_kernel, dim3((rows + TOPK_WARPS - 1) / TOPK_WARPS), dim3(32 * TOPK_WARPS), 0,
+                      (cudaStream_t)stream_, *a) == cudaSuccess
+             ? LS100_OK
+             : LS100_ERR_CUDA;
 }
 
 extern "C" int ls100_beam_update(ls100_ctx* ctx, const ls100_beam_update_args* a, ls100_stream_t stream_) {
@@ -290,8 +310,9 @@ extern "C" int ls100_beam_update(ls100_ctx* ctx, const ls100_beam_update_args* a
   if (a->beam > MAX_BEAM) return LS100_ERR_UNSUPPORTED;
   const size_t smem = (size_t)2 * a->beam * a->max_step * sizeof(int);
   if (smem > 48 * 1024) return LS100_ERR_UNSUPPORTED;
-  beam_update_kernel<<<a->batch, 128, smem, (cudaStream_t)stream_>>>(*a);
-  return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+  return ls100_launch(beam_update_kernel, dim3(a->batch), dim3(128), smem, (cudaStream_t)stream_, *a) == cudaSuccess
+             ? LS100_OK
+             : LS100_ERR_CUDA;
 }
 
 // ------------------------------------------------------------------ allocation-free variant

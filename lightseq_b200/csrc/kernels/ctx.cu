@@ -2,9 +2,18 @@
 #include "ctx.h"
 
 #include <stdio.h>
+#include <stdlib.h>
 
 int ls100_gemm_i8_init_device();
 int ls100_attn_init_device();
+
+bool ls100_pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("LS100_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 
 extern "C" int ls100_ctx_create(ls100_ctx** out, int device) {
   if (!out) return LS100_ERR_BAD_ARG;

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <mutex>
+#include <utility>
 #include <unordered_map>
 
 #include "../../../include/ls100.h"
@@ -41,6 +42,28 @@ struct ls100_ctx {
   std::mutex mu;
   std::unordered_map<ls100_tmap_key, CUtensorMap, ls100_tmap_hash> tmaps;
 };
+
+// True unless the environment sets LS100_PDL=0: kernels are then launched with the programmatic
+// stream-serialisation attribute so that each kernel's prologue overlaps its predecessor's tail.
+bool ls100_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t ls100_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  if (ls100_pdl_enabled()) {
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
 
 // 2-D uint8 tensor map, 128-byte swizzle, box = box_cols (bytes, <=128) x box_rows.
 int ls100_get_tmap_u8(ls100_ctx* ctx, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld_bytes,

@@ -249,6 +249,7 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
   const int num_kb = (p.k + BK - 1) / BK;
 
   LS100_TRACE(0);
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
@@ -272,9 +273,19 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
 
   if (warp == 0) {
     if (elect_one()) {
-      uint32_t phase = 0;
-      int s = 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      // First ring fill: the weight tiles do not depend on the previous kernel, so they are requested
+      // before the grid-dependency wait; the activation tiles follow it.
+      const int n_pre = num_kb < STAGES ? num_kb : STAGES;
+      for (int kb = 0; kb < n_pre; ++kb) {
+        uint8_t* sb = smem + kb * SM::STAGE_BYTES + SM::A_BYTES;
+        mbar_expect_tx(&full_bar[kb], SM::STAGE_BYTES);
+        tma_load_2d(sb, &tma_b, &full_bar[kb], kb * BK, n0);
+      }
+      pdl_wait();
+      for (int kb = 0; kb < n_pre; ++kb) tma_load_2d(smem + kb * SM::STAGE_BYTES, &tma_a, &full_bar[kb], kb * BK, m0);
+      uint32_t phase = (n_pre == STAGES) ? 1 : 0;
+      int s = (n_pre == STAGES) ? 0 : n_pre;
+      for (int kb = n_pre; kb < num_kb; ++kb) {
         if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
           record_timeout(p.err);
           break;
@@ -336,6 +347,7 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
         s_off[i] = (p.w_off != nullptr && n < p.n) ? __ldg(p.w_off + n) : 0;
       }
     }
+    pdl_wait();  // the residual (and everything written below) belongs to the chain of kernels before this one
     float rr[32];
     const bool rr_ok = p.resid != nullptr && row < p.m && (n0 + 32 <= p.n) && ((p.ldr & 3) == 0) &&
                        ((((uintptr_t)p.resid) & 15) == 0) && p.out_kind != LS100_OUT_I32 && p.out_kind != LS100_OUT_OUTQ_I8;
@@ -411,8 +423,7 @@ static int launch_gemm(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cudaStream_t
   p.ldo = a->ldo;
   p.err = ctx->d_err;
   dim3 grid((a->n + BN - 1) / BN, (a->m + BM - 1) / BM);
-  kern<<<grid, 192, SM::TOTAL, stream>>>(ta, tb, p);
-  return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+  return ls100_launch(kern, grid, dim3(192), SM::TOTAL, stream, ta, tb, p) == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
 
 template <int BN, int STAGES>

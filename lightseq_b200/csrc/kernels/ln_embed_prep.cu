@@ -18,6 +18,8 @@ constexpr int LN_MAXV = 32;  // float4 per lane -> hidden <= 32*32*4 = 4096
 
 template <int NV>
 __global__ void __launch_bounds__(256) ln_quant_kernel(const ls100_ln_quant_args a, const float scale, const float rs) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= a.rows) return;
@@ -69,6 +71,8 @@ __global__ void __launch_bounds__(256) ln_quant_kernel(const ls100_ln_quant_args
 
 // ------------------------------------------------------------------ embedding
 __global__ void __launch_bounds__(256) embed_kernel(const ls100_embed_args a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int rows = a.batch * a.seq;
@@ -149,11 +153,13 @@ extern "C" int ls100_ln_quant(ls100_ctx* ctx, const ls100_ln_quant_args* a, ls10
   const int warps_per_block = 8;
   const int blocks = (a->rows + warps_per_block - 1) / warps_per_block;
   const int nv = (a->hidden + 127) / 128;
-  if (nv <= 4) ln_quant_kernel<4><<<blocks, 256, 0, stream>>>(*a, scale, 1.0f / scale);
-  else if (nv <= 8) ln_quant_kernel<8><<<blocks, 256, 0, stream>>>(*a, scale, 1.0f / scale);
-  else if (nv <= 16) ln_quant_kernel<16><<<blocks, 256, 0, stream>>>(*a, scale, 1.0f / scale);
-  else ln_quant_kernel<32><<<blocks, 256, 0, stream>>>(*a, scale, 1.0f / scale);
-  return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+  const float rs = 1.0f / scale;
+  cudaError_t e;
+  if (nv <= 4) e = ls100_launch(ln_quant_kernel<4>, dim3(blocks), dim3(256), 0, stream, *a, scale, rs);
+  else if (nv <= 8) e = ls100_launch(ln_quant_kernel<8>, dim3(blocks), dim3(256), 0, stream, *a, scale, rs);
+  else if (nv <= 16) e = ls100_launch(ln_quant_kernel<16>, dim3(blocks), dim3(256), 0, stream, *a, scale, rs);
+  else e = ls100_launch(ln_quant_kernel<32>, dim3(blocks), dim3(256), 0, stream, *a, scale, rs);
+  return e == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
 
 extern "C" int ls100_embed(ls100_ctx* ctx, const ls100_embed_args* a, ls100_stream_t stream_) {
@@ -163,8 +169,9 @@ extern "C" int ls100_embed(ls100_ctx* ctx, const ls100_embed_args* a, ls100_stre
   if (a->hidden & 3) return LS100_ERR_UNSUPPORTED;
   if ((((uintptr_t)a->table_q) & 3) || (((uintptr_t)a->pos) & 15) || (((uintptr_t)a->out) & 15)) return LS100_ERR_ALIGN;
   const int rows = a->batch * a->seq;
-  embed_kernel<<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream_>>>(*a);
-  return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+  return ls100_launch(embed_kernel, dim3((rows + 7) / 8), dim3(256), 0, (cudaStream_t)stream_, *a) == cudaSuccess
+             ? LS100_OK
+             : LS100_ERR_CUDA;
 }
 
 extern "C" int ls100_quantize_weight(ls100_ctx* ctx, const float* w, int64_t rows, int64_t cols, float amax,

@@ -12,6 +12,8 @@ namespace ls100 {
 __global__ void __launch_bounds__(256) proj_f32_kernel(const ls100_proj_f32_args a) {
   __shared__ float As[16][64 + 4];
   __shared__ float Ws[16][64 + 4];
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = threadIdx.x;
   const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
   const int tx = t & 15, ty = t >> 4;  // 16 x 16 threads, each 4 x 4 outputs
@@ -84,6 +86,7 @@ extern "C" int ls100_proj_f32(ls100_ctx* ctx, const ls100_proj_f32_args* a, ls10
   if (a->m <= 0 || a->n <= 0 || a->k <= 0 || !(a->s_w > 0.f)) return LS100_ERR_BAD_ARG;
   if ((((uintptr_t)a->x) & 15) || (a->ldx & 3)) return LS100_ERR_ALIGN;
   dim3 grid((a->n + 63) / 64, (a->m + 63) / 64);
-  ls100::proj_f32_kernel<<<grid, 256, 0, (cudaStream_t)stream_>>>(*a);
-  return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+  return ls100_launch(ls100::proj_f32_kernel, grid, dim3(256), 0, (cudaStream_t)stream_, *a) == cudaSuccess
+             ? LS100_OK
+             : LS100_ERR_CUDA;
 }
