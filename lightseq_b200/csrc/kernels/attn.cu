@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(64) attn_self_kernel(const ls100_attn_self_arg
 // 100-token history costs 4 memory round trips instead of a key pass plus a value pass. The
 // beam-ancestry slots of all positions are fetched into shared memory first so that the cache
 // loads do not wait on them.
-__global__ void __launch_bounds__(128) attn_dec_kernel(const ls100_attn_dec_args a, const float s_out,
+__global__ void __launch_bounds__(128, 7) attn_dec_kernel(const ls100_attn_dec_args a, const float s_out,
                                                         const float rs_out, const float score_scale) {
   extern __shared__ int slot_all[];
   pdl_launch_dependents();
@@ -482,7 +482,9 @@ extern "C" int ls100_attn_cross(ls100_ctx* ctx, const ls100_attn_cross_args* a, 
       (((uintptr_t)a->out) & 1) || (a->ld_out & 1) || (a->bias && (((uintptr_t)a->bias) & 7)))
     return LS100_ERR_ALIGN;
   dim3 grid(a->batch, a->heads);
-  const int tr = a->src_len >= XT ? XT : (a->src_len + 31) / 32 * 32;
+  // 32-key tiles keep a CTA at ~17 KB of shared memory, so that every (sentence, head) CTA of a large batch is
+  // resident at once and the tile loads of one CTA overlap the arithmetic of the others
+  const int tr = 32;
   const size_t smem = (size_t)(tr * XKS + tr * DH + a->beam * DH + a->beam * tr) * sizeof(float);
   const float so = a->amax_out / 127.0f;
   return ls100_launch(attn_cross_kernel, grid, dim3(32 * a->beam), smem, (cudaStream_t)stream_, *a, so, 1.0f / so, tr) ==
