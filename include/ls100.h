@@ -136,6 +136,8 @@ typedef struct {
   int32_t n_pos, pad_id, vocab;
   float* out;        /* [batch*seq, hidden] fp32 */
   uint8_t* pad_mask; /* optional [batch, seq], 1 = pad */
+  int32_t pos_mode;  /* 0: positions count non-pad tokens and pads get none (fairseq / Transformer);
+                        1: position = column index (+ *step_ptr), added to every token (BERT, GPT-2 learned tables) */
 } ls100_embed_args;
 int ls100_embed(ls100_ctx* ctx, const ls100_embed_args* args, ls100_stream_t stream);
 
@@ -329,6 +331,9 @@ int ls100_model_get_stream(ls100_model* m, ls100_stream_t* stream);
  * the model and allocated at creation. */
 int ls100_transformer_infer_host(ls100_model* m, const int32_t* ids, int batch, int seq_len, int32_t* out_tokens,
                                  float* out_scores, int* out_len);
+/* QuantBert: ids [batch, seq_len] -> fp32 encoder output [batch, seq_len, hidden] (PyQuantBert::infer,
+ * lightseq/inference/pywrapper/wrapper.cc:276-321). */
+int ls100_bert_infer_host(ls100_model* m, const int32_t* ids, int batch, int seq_len, float* out);
 
 #ifdef __cplusplus
 }

@@ -66,7 +66,7 @@ class EmbedArgs(C.Structure):
     _fields_ = [("ids", C.c_void_p), ("ld_ids", C.c_int64), ("batch", C.c_int32), ("seq", C.c_int32),
                 ("hidden", C.c_int32), ("step_ptr", C.c_void_p), ("table_q", C.c_void_p), ("s_emb", C.c_float),
                 ("sqrt_h", C.c_float), ("pos", C.c_void_p), ("n_pos", C.c_int32), ("pad_id", C.c_int32),
-                ("vocab", C.c_int32), ("out", C.c_void_p), ("pad_mask", C.c_void_p)]
+                ("vocab", C.c_int32), ("out", C.c_void_p), ("pad_mask", C.c_void_p), ("pos_mode", C.c_int32)]
 
 
 class AttnSelfArgs(C.Structure):

@@ -62,9 +62,24 @@ class QuantTransformerEncoderLayer : public Layer {
   const QLinearParams& fc1() const { return fc1_; }
   const LayerNormParams& ln1() const { return ln1_; }
 
+  // Post-LN layers hand their output to the next layer already quantised with that layer's QKV input
+  // clip-max (0 = last layer: no int8 copy is written).
+  void set_next_input_amax(float amax) { next_amax_ = amax; }
+
   void forward() override {
-    if (!pre_ln_) throw std::runtime_error("post-LN encoder layers run through forward_post_ln");
     const int rows = batch_ * seq_;
+    if (!pre_ln_) {
+      // x is the post-LN output of the previous block and a_q = quant(x) with this layer's QKV clip-max
+      gemm(b_->a_q, qkv_, rows, LS100_OUT_OUTQ_I8, b_->qkv_q, true, false, Act::None, nullptr, 0.f);
+      attention(rows);
+      gemm(b_->attn_q, out_, rows, LS100_OUT_F32, b_->x, true, true, Act::None, b_->x, 0.f);
+      ln_quant(rows, ln1_, fc1_.amax_in, true, true);
+      gemm(b_->a_q, fc1_, rows, act_ == Act::Relu ? LS100_OUT_REQ_U8 : LS100_OUT_REQ_S8, b_->h_q, true, true, act_,
+           nullptr, fc2_.s_in);
+      gemm(b_->h_q, fc2_, rows, LS100_OUT_F32, b_->x, true, true, Act::None, b_->x, 0.f);
+      ln_quant(rows, ln2_, next_amax_, true, next_amax_ > 0.f);
+      return;
+    }
     ls100_ctx* k = ctx_->kernels();
     cudaStream_t s = ctx_->get_stream();
     ln_quant(rows, ln1_, qkv_.amax_in);
@@ -80,7 +95,7 @@ class QuantTransformerEncoderLayer : public Layer {
   }
 
  protected:
-  void ln_quant(int rows, const LayerNormParams& ln, float amax) {
+  void ln_quant(int rows, const LayerNormParams& ln, float amax, bool write_f = false, bool write_q = true) {
     ls100_ln_quant_args a;
     memset(&a, 0, sizeof(a));
     a.x = b_->x->value<float>();
@@ -90,8 +105,10 @@ class QuantTransformerEncoderLayer : public Layer {
     a.rows = rows;
     a.hidden = hidden_;
     a.amax = amax;
-    a.out_q = b_->a_q->value<int8_t>();
+    a.out_q = write_q ? b_->a_q->value<int8_t>() : nullptr;
     a.ldq = hidden_;
+    a.out_f = write_f ? b_->x->value<float>() : nullptr;  // in place: a row is read completely before it is written
+    a.ldf = hidden_;
     LS_RC(ls100_ln_quant(ctx_->kernels(), &a, ctx_->get_stream()));
   }
   void gemm(Variable* in, const QLinearParams& p, int rows, int out_kind, Variable* out, bool out_quant, bool add_bias,
@@ -129,6 +146,7 @@ class QuantTransformerEncoderLayer : public Layer {
   StackBuffers* b_ = nullptr;
   Variable* pad_mask_ = nullptr;
   int batch_ = 0, seq_ = 0;
+  float next_amax_ = 0.f;
 };
 
 // ---------------------------------------------------------------------------------------

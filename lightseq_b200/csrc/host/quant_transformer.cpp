@@ -15,15 +15,15 @@
 #include <map>
 #include <memory>
 
+#include "engine_model.h"
 #include "layers.h"
-#include "model_base.h"
 
 namespace ls100 {
 
-class QuantTransformer : public LSModel {
+class QuantTransformer : public EngineModel {
  public:
   QuantTransformer(const std::string& weight_path, int max_batch_size)
-      : LSModel({"source_ids"}, {"target_ids", "target_scores"}), max_bs_(max_batch_size) {
+      : EngineModel({"source_ids"}, {"target_ids", "target_scores"}), max_bs_(max_batch_size) {
     WeightsFile wf(weight_path);
     H_ = (int)wf.conf("hidden");
     heads_ = (int)wf.conf("heads");
@@ -237,7 +237,7 @@ class QuantTransformer : public LSModel {
     *max_step = max_step_;
     *beam = beam_;
   }
-  ContextPtr context() const { return ctx_; }
+  ContextPtr context() const override { return ctx_; }
 
  private:
   static constexpr int kRing = 4;
@@ -416,7 +416,7 @@ class QuantTransformer : public LSModel {
 LSMODEL_REGISTER(QuantTransformer)
 
 cudaStream_t model_stream(LSModel* m) {
-  if (auto* t = dynamic_cast<QuantTransformer*>(m)) return t->context()->get_stream();
+  if (auto* t = dynamic_cast<EngineModel*>(m)) return t->context()->get_stream();
   return nullptr;
 }
 

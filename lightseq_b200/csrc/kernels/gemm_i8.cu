@@ -144,8 +144,25 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
     } else if (p.act == LS100_ACT_GELU) {
+      const bool requant = (p.out_kind == LS100_OUT_REQ_S8 || p.out_kind == LS100_OUT_REQ_U8) && p.resid == nullptr;
+      if (requant) {
+        // fp32 erff is within a few ulp of the float64 erf the oracle uses; that can only change the int8
+        // result when gelu(x)/s_req + 0.5 lands within ~1e-4 of an integer. Those rare elements are redone
+        // with the float64 erf, everything else keeps the cheap path.
+        const float shift = (p.out_kind == LS100_OUT_REQ_U8) ? -126.5f : 0.5f;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+        for (int j = 0; j < 32; ++j) {
+          const float x = v[j];
+          float g = gelu_erf(x);
+          const float u = __fadd_rn(div_rn(g, p.s_req, p.rs_req), shift);
+          const float r = __fsub_rn(__fadd_rn(u, 12582912.f), 12582912.f);  // nearest integer
+          if (fabsf(u) < 200.f && fabsf(__fsub_rn(u, r)) < 2e-4f * fmaxf(1.f, fabsf(u))) g = gelu_erf_exact(x);
+          v[j] = g;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = gelu_erf_exact(v[j]);
+      }
     }
     if (p.resid != nullptr && row_ok) {
       if (rr_valid) {  // prefetched before the accumulator was ready

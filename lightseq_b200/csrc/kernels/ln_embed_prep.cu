@@ -82,15 +82,19 @@ __global__ void __launch_bounds__(256) embed_kernel(const ls100_embed_args a) {
   if (a.step_ptr) {
     const int step = *a.step_ptr;
     id = a.ids[(long long)b * a.ld_ids + step];
-    pos = (id != a.pad_id) ? step : 0;
+    pos = (a.pos_mode == 1 || id != a.pad_id) ? step : 0;
   } else {
     const int32_t* row = a.ids + (long long)b * a.ld_ids;
     id = row[s];
-    // position = (#non-pad ids in row[0..s]) - 1, zero for pads
-    int cnt = 0;
-    for (int j = lane; j <= s; j += 32) cnt += (row[j] != a.pad_id) ? 1 : 0;
-    cnt = warp_sum_i(cnt);
-    pos = (id != a.pad_id) ? cnt - 1 : 0;
+    if (a.pos_mode == 1) {
+      pos = s;
+    } else {
+      // position = (#non-pad ids in row[0..s]) - 1, zero for pads
+      int cnt = 0;
+      for (int j = lane; j <= s; j += 32) cnt += (row[j] != a.pad_id) ? 1 : 0;
+      cnt = warp_sum_i(cnt);
+      pos = (id != a.pad_id) ? cnt - 1 : 0;
+    }
   }
   const bool is_pad = (id == a.pad_id);
   if (a.pad_mask && lane == 0) a.pad_mask[warp] = is_pad ? 1 : 0;
@@ -99,7 +103,7 @@ __global__ void __launch_bounds__(256) embed_kernel(const ls100_embed_args a) {
   const int8_t* er = a.table_q + (long long)id * a.hidden;
   const float* pr = a.pos + (long long)pos * a.hidden;
   float* orow = a.out + (long long)warp * a.hidden;
-  const float m = is_pad ? 0.f : 1.f;
+  const float m = (is_pad && a.pos_mode == 0) ? 0.f : 1.f;
   for (int c = lane * 4; c < a.hidden; c += 128) {
     const char4 q = *reinterpret_cast<const char4*>(er + c);
     const float4 p = *reinterpret_cast<const float4*>(pr + c);

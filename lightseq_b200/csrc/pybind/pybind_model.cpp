@@ -61,6 +61,37 @@ class PyQuantTransformer {
   int max_step_ = 0;
 };
 
+// QuantBert(weight_path, max_batch_size).infer(int32[B,S]) -> float32[B,S,H]
+// (PyQuantBert, lightseq/inference/pywrapper/wrapper.cc:240-321)
+class PyQuantBert {
+ public:
+  PyQuantBert(const std::string& weight_path, int max_batch_size) {
+    check(ls100_model_create("QuantBert", weight_path.c_str(), max_batch_size, &m_), "QuantBert");
+    int32_t dims[4];
+    int nd = 0;
+    check(ls100_model_get_output_max_shape(m_, 0, dims, &nd), "get_output_max_shape");
+    hidden_ = dims[2];
+  }
+  ~PyQuantBert() { ls100_model_destroy(m_); }
+  PyQuantBert(const PyQuantBert&) = delete;
+  PyQuantBert& operator=(const PyQuantBert&) = delete;
+  py::array_t<float> infer(py::array_t<int, py::array::c_style | py::array::forcecast> input_seq) {
+    if (input_seq.ndim() != 2) throw std::runtime_error("input_seq must be a 2-D int32 array [batch, seq_len]");
+    const int batch = (int)input_seq.shape(0), seq = (int)input_seq.shape(1);
+    py::array_t<float> out({batch, seq, hidden_});
+    {
+      py::gil_scoped_release nogil;
+      check(ls100_bert_infer_host(m_, input_seq.data(), batch, seq, out.mutable_data()), "infer");
+    }
+    return out;
+  }
+  std::uintptr_t handle() const { return reinterpret_cast<std::uintptr_t>(m_); }
+
+ private:
+  ls100_model* m_ = nullptr;
+  int hidden_ = 0;
+};
+
 }  // namespace
 
 PYBIND11_MODULE(_ls100_py, m) {
@@ -70,4 +101,8 @@ PYBIND11_MODULE(_ls100_py, m) {
       .def("infer", &PyQuantTransformer::infer, py::arg("input_seq"))
       .def("benchmark_mode", &PyQuantTransformer::benchmark_mode)
       .def_property_readonly("_handle", &PyQuantTransformer::handle);
+  py::class_<PyQuantBert>(m, "QuantBert")
+      .def(py::init<const std::string&, int>(), py::arg("weight_path"), py::arg("max_batch_size"))
+      .def("infer", &PyQuantBert::infer, py::arg("input_seq"))
+      .def_property_readonly("_handle", &PyQuantBert::handle);
 }

@@ -234,3 +234,79 @@ def make_transformer(path: Optional[str] = None, *, hidden=512, heads=8, ffn=204
 
         weights.save(path, "QuantTransformer", conf, amax, w)
     return conf, amax, w
+
+
+# ------------------------------------------------------------------------------------------- BERT
+def bert_weights(hidden=768, heads=12, ffn=3072, n_layer=12, vocab=30522, max_pos=512, seed=1234, std=0.02):
+    rng = np.random.default_rng(seed)
+
+    def nrm(*shape):
+        return (rng.standard_normal(shape, dtype=F32) * F32(std)).astype(F32)
+
+    w: Dict[str, np.ndarray] = {"emb": nrm(vocab, hidden), "type_emb": nrm(2, hidden), "pos": nrm(max_pos, hidden),
+                                "emb.ln.g": np.ones(hidden, F32), "emb.ln.b": np.zeros(hidden, F32)}
+    for l in range(n_layer):
+        p = f"enc.{l}"
+        for name, (no, ni) in (("qkv", (3 * hidden, hidden)), ("out", (hidden, hidden)), ("fc1", (ffn, hidden)),
+                               ("fc2", (hidden, ffn))):
+            w[f"{p}.{name}.w"] = nrm(no, ni)
+            w[f"{p}.{name}.b"] = np.zeros(no, F32)
+        for ln in ("ln1", "ln2"):
+            w[f"{p}.{ln}.g"] = np.ones(hidden, F32)
+            w[f"{p}.{ln}.b"] = np.zeros(hidden, F32)
+    return w
+
+
+def bert_inputs(batch=128, seq=128, vocab=30522, pad_id=0, seed=4321) -> np.ndarray:
+    """ids [batch, seq]: valid lengths U{seq/4..seq}, ids U[1000, vocab), right-padded with ``pad_id``."""
+    rng = np.random.default_rng(seed)
+    lens = rng.integers(max(seq // 4, 1), seq + 1, size=batch)
+    ids = np.full((batch, seq), pad_id, dtype=np.int32)
+    for i, n in enumerate(lens):
+        ids[i, :n] = rng.integers(min(1000, vocab - 1), vocab, size=n)
+    return ids
+
+
+def calibrate_bert(w, ids, *, heads: int, n_layer: int, pad_id: int = 0, k: float = 4.0) -> Dict[str, float]:
+    st = _Stats()
+    H = w["emb"].shape[1]
+    B, S = ids.shape
+
+    def lin(name, x):
+        st.see(name + ".in", x)
+        y = x @ w[name + ".w"].T
+        st.see(name + ".out", y)
+        return (y + w[name + ".b"]).astype(F32)
+
+    pad = ids == pad_id
+    e = w["emb"][ids] + w["type_emb"][0]
+    st.see("emb", w["emb"] + w["type_emb"][0])
+    x = _ln(e + w["pos"][np.arange(S)], w["emb.ln.g"], w["emb.ln.b"])
+    for l in range(n_layer):
+        p = f"enc.{l}"
+        qkv = lin(p + ".qkv", x)
+        a = _attn(qkv[..., :H], qkv[..., H:2 * H], qkv[..., 2 * H:], heads, pad[:, None, None, :])
+        x = _ln(x + lin(p + ".out", a), w[p + ".ln1.g"], w[p + ".ln1.b"])
+        h = _act(lin(p + ".fc1", x), "gelu")
+        x = _ln(x + lin(p + ".fc2", h), w[p + ".ln2.g"], w[p + ".ln2.b"])
+    amax = st.amax(k)
+    for name, t in w.items():
+        if name.endswith(".w") and t.ndim == 2:
+            amax[name] = float(F32(k * t.std()))
+    return amax
+
+
+def make_bert(path: Optional[str] = None, *, hidden=768, heads=12, ffn=3072, n_layer=12, vocab=30522, max_step=512,
+              pad_id=0, seed=1234, calib_ids: Optional[np.ndarray] = None):
+    """Builds (conf, amax, tensors) of a seeded synthetic QuantBert (post-LN, GELU, learned positions)."""
+    w = bert_weights(hidden, heads, ffn, n_layer, vocab, max_step, seed)
+    if calib_ids is None:
+        calib_ids = bert_inputs(batch=4, seq=min(32, max_step), vocab=vocab, pad_id=pad_id, seed=seed + 1)
+    amax = calibrate_bert(w, calib_ids, heads=heads, n_layer=n_layer, pad_id=pad_id)
+    conf = dict(hidden=hidden, heads=heads, ffn=ffn, n_enc=n_layer, vocab=vocab, act_gelu=1.0, pre_ln=0.0,
+                max_step=max_step, pad_id=pad_id)
+    if path is not None:
+        from . import weights
+
+        weights.save(path, "QuantBert", conf, amax, w)
+    return conf, amax, w

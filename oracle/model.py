@@ -395,3 +395,31 @@ class Seq2Seq:
             cur = max(max_decode - 1, 0)
         n = cur + 1
         return alive[:, 0, 1:n + 1].copy(), score[:, 0].copy(), n
+
+
+# --------------------------------------------------------------------------- BERT
+class Bert:
+    """BertEmbeddingLayer (torch_transformer_layers.py:1177-1207: word + token-type(0) -> emb_quant -> + learned
+    position -> LayerNorm) followed by post-LN GELU encoder layers (:630-679); output [B,S,H] fp32, as
+    QuantBertEncoder::run_one_infer returns it (lightseq/inference/model/quant_bert_encoder.cc.cu:214-265)."""
+
+    def __init__(self, cfg: Config, st: State):
+        self.cfg = cfg
+        self.st = st
+
+    def embed(self, ids: np.ndarray) -> np.ndarray:
+        st = self.st
+        e = st.w["emb"][ids] + st.w["type_emb"][0]
+        eq, s = Q.quantize(e, st.amax["emb"])
+        x = eq.astype(F32) * s + st.w["pos"][np.arange(ids.shape[1])]
+        return layer_norm(x, st.w["emb.ln.g"], st.w["emb.ln.b"])
+
+    def forward(self, ids: np.ndarray) -> np.ndarray:
+        cfg, st = self.cfg, self.st
+        pad = ids == cfg.pad_id
+        x = self.embed(ids)
+        st.rec("emb.out", x)
+        for l in range(cfg.n_enc):
+            x = encoder_layer(st, x, pad, f"enc.{l}", cfg)
+            st.rec(f"enc.{l}.y", x)
+        return x

@@ -235,8 +235,41 @@ def golden_quantizer():
     print("quantizer vectors", x.size)
 
 
+@torch.no_grad()
+def golden_small_bert():
+    """BertEmbeddingLayer + two post-LN GELU encoder layers (H 64, 1 head... here 2 heads of 32 are not
+    supported by the engine, so H 128 / 2 heads), vocab 120, batch 3 x seq 12 with padding."""
+    H, heads, F, V, n_layer, pad_id, S = 128, 2, 256, 120, 2, 0, 12
+    conf, amax, w = synth.make_bert(None, hidden=H, heads=heads, ffn=F, n_layer=n_layer, vocab=V, max_step=16, seed=21)
+    ids = synth.bert_inputs(batch=3, seq=S, vocab=V, pad_id=pad_id, seed=8)
+    cfg = tl.BertEmbeddingLayer.get_config(
+        vocab_size=V, embedding_dim=H, max_batch_tokens=4096, max_seq_len=16, padding_idx=pad_id, dropout=0.0,
+        fp16=False, local_rank=-1)
+    cfg.type_vocab_size = 2
+    cfg.layer_norm_eps = 1e-5
+    emb = tl.BertEmbeddingLayer(cfg)
+    emb.word_embeddings.weight.data.copy_(torch.from_numpy(w["emb"]))
+    emb.position_embeddings.weight.data.copy_(torch.from_numpy(w["pos"]))
+    emb.token_type_embeddings.weight.data.copy_(torch.from_numpy(w["type_emb"]))
+    load_ln(emb.LayerNorm, w, "emb.ln")
+    emb.emb_quant.clip.clip_value_max.data.fill_(amax["emb"])
+    emb.eval()
+    emb.apply(qz.enable_quant)
+    layers = [build_encoder_layer(w, amax, f"enc.{l}", H, heads, F, act="gelu", pre_ln=False) for l in range(n_layer)]
+    t = torch.from_numpy(ids.astype(np.int64))
+    x = emb(t)
+    out = {"ids": ids, "emb_out": x.numpy().copy()}
+    pad = t.eq(pad_id)
+    for l, lyr in enumerate(layers):
+        x = lyr(x, pad)
+        out[f"y{l}"] = x.numpy().copy()
+    np.savez_compressed(HERE / "small_bert.npz", **out)
+    print("small bert:", out["y1"].shape)
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     golden_quantizer()
     golden_c0()
     golden_small_seq2seq()
+    golden_small_bert()

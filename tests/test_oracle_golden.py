@@ -81,3 +81,20 @@ def test_small_seq2seq_matches_reference(golden_dir):
         assert dq.max() <= 3, f"step {s}: int8 logits differ by {dq.max()} steps"
     print("logit int8 mismatch rate", flips / total)
     assert flips / total < 0.15
+
+
+def test_small_bert_matches_reference(golden_dir):
+    """BertEmbeddingLayer + two post-LN GELU layers of the reference vs the oracle's Bert."""
+    g = np.load(golden_dir / "small_bert.npz")
+    H, heads, F, V = 128, 2, 256, 120
+    conf, amax, w = synth.make_bert(None, hidden=H, heads=heads, ffn=F, n_layer=2, vocab=V, max_step=16, seed=21)
+    cfg = om.Config(hidden=H, heads=heads, ffn=F, n_enc=2, n_dec=0, vocab=V, act="gelu", pre_ln=False, pad_id=0)
+    st = om.State(w=w, amax=amax, trace={})
+    ids = g["ids"]
+    assert np.array_equal(ids, synth.bert_inputs(batch=3, seq=12, vocab=V, pad_id=0, seed=8))
+    y = om.Bert(cfg, st).forward(ids)
+    assert np.abs(st.trace["emb.out"] - g["emb_out"]).max() < 2e-6
+    valid = ids != 0
+    d = np.abs(y - g["y1"])[valid]
+    print("bert y1 max", d.max(), "mean", d.mean())
+    assert d.mean() < 1e-3 and d.max() < 5e-2
