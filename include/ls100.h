@@ -295,6 +295,32 @@ int ls100_beam_update(ls100_ctx* ctx, const ls100_beam_update_args* args, ls100_
 #define LS100_BEAM_UPDATE_NOALLOC_MAX_STEP 1024
 int ls100_beam_update_noalloc(ls100_ctx* ctx, const ls100_beam_update_args* args, ls100_stream_t stream);
 
+/* ------------------------------------------------------------- top-k sampling ---
+ * One new token per row from the int8 logits of its newest position: exact top-k by (logit desc, token asc),
+ * softmax over those k (p_i = exp(l_i - l_0) / sum), cumulative in that order, pick the first i with
+ * u <= cum_i where u in (0,1] comes from Philox4x32-10 with key (seed_lo, seed_hi) and counter
+ * (position, row, 0, 0): u = ((x0 >> 8) + 1) * 2^-24. A row whose newest token is `end_id` appends `end_id`.
+ * The token is written to seq[row, *cur + 1]; the last CTA advances *cur and, when every row has ended,
+ * records the position in *stop (init -1). Replaces ker_topk_sample_i8I + the per-token host sync of
+ * QuantGptEncoder::sample_one_token_with_cache (lightseq/inference/kernels/gptKernels_int8.cc.cu:252-430,
+ * lightseq/inference/model/quant_gpt_encoder.cc.cu:441-481); the rough threshold, CUB scan and clock()-seeded
+ * cuRAND state of the reference become an exact selection and a counter-based generator, so a run is
+ * reproducible. k <= 8. */
+typedef struct {
+  const int8_t* logits; /* [rows, ld_logits] */
+  int64_t ld_logits;
+  float s_logits;
+  int32_t rows, vocab, k, max_step, end_id;
+  uint32_t seed_lo, seed_hi;
+  int32_t* seq;     /* [rows, max_step], in place */
+  int32_t* cur;     /* device int: index of the newest token of every row; advanced by one */
+  int32_t* ticket;  /* device int, zero before the call sequence starts; reset by the kernel */
+  int32_t* n_ended; /* device int, zero before the call sequence starts; reset by the kernel */
+  int32_t* stop;    /* device int, -1 until every row has produced end_id */
+  int32_t* stop_host; /* optional mapped host mirror of *stop */
+} ls100_sample_topk_args;
+int ls100_sample_topk(ls100_ctx* ctx, const ls100_sample_topk_args* args, ls100_stream_t stream);
+
 /* ------------------------------------------------------------- load-time prep ---
  * fp32 -> int8 with the tensor's clip-max (quantize_weight, lightseq/inference/model/
  * cublas_helper.cc:553-593) and, optionally, off[n] = 127 * sum_k q[n,k]: the exact

@@ -100,3 +100,39 @@ def beam_step(lq: np.ndarray, s_l, alive: np.ndarray, probs: np.ndarray, score: 
             else:
                 n_fin += 1
     return new_alive, new_probs, new_score, parent, n_fin
+
+
+# --------------------------------------------------------------------------- top-k sampling
+def philox4x32_10_first(c0: int, c1: int, c2: int, c3: int, k0: int, k1: int) -> int:
+    """First output word of Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11)."""
+    M0, M1, W0, W1, MASK = 0xD2511F53, 0xCD9E8D57, 0x9E3779B9, 0xBB67AE85, 0xFFFFFFFF
+    for _ in range(10):
+        p0, p1 = M0 * c0, M1 * c2
+        hi0, lo0, hi1, lo1 = p0 >> 32, p0 & MASK, p1 >> 32, p1 & MASK
+        c0, c1, c2, c3 = (hi1 ^ c1 ^ k0) & MASK, lo1, (hi0 ^ c3 ^ k1) & MASK, lo0
+        k0, k1 = (k0 + W0) & MASK, (k1 + W1) & MASK
+    return c0
+
+
+def sample_topk_row(lq_row: np.ndarray, s_l, k: int, position: int, row: int, seed_lo: int, seed_hi: int) -> int:
+    """Top-k sampling of one row of int8 logits, restating ker_topk_sample_i8I
+    (lightseq/inference/kernels/gptKernels_int8.cc.cu:252-430) with an exact top-k (logit desc, token asc),
+    softmax over the kept logits, cumulative in that order, and a counter-based uniform
+    u = ((philox(position, row; seed) >> 8) + 1) * 2^-24 instead of the engine's clock()-seeded cuRAND state."""
+    s_l = F32(s_l)
+    V = lq_row.shape[0]
+    order = np.lexsort((np.arange(V), -lq_row.astype(np.int32)))[:k]
+    v0 = int(lq_row[order[0]])
+    e = [np.exp(F32(F32(int(lq_row[i]) - v0) * s_l), dtype=F32) for i in order]
+    tot = F32(0)
+    for x in e:
+        tot = F32(tot + x)
+    u = F32(F32((philox4x32_10_first(position, row, 0, 0, seed_lo, seed_hi) >> 8) + 1) * F32(2.0 ** -24))
+    cum = F32(0)
+    pick = len(order) - 1
+    for i, x in enumerate(e):
+        cum = F32(cum + F32(x / tot))
+        if u <= cum:
+            pick = i
+            break
+    return int(order[pick])

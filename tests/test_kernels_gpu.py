@@ -413,3 +413,46 @@ def test_beam_step_matches_oracle(V, ties):
             assert int(d_stop.cpu()[0]) >= 0
             break
     assert int(d_stop.cpu()[0]) == step if n_fin == B * K else int(d_stop.cpu()[0]) == -1
+
+
+# ----------------------------------------------------------------------------- top-k sampling
+@pytest.mark.parametrize("V,k", [(50257, 8), (1000, 4), (50, 1)])
+def test_sample_topk_matches_oracle(V, k):
+    """Several sampling steps: tokens equal the oracle's (same Philox counter stream), ended rows keep emitting
+    EOS, the position advances on the device and the all-ended position is recorded."""
+    rows, ms, end_id = 10, 16, 3
+    r = rng(V + k)
+    ldv = (V + 15) // 16 * 16
+    s_l = F32(0.06)
+    seq = np.full((rows, ms), end_id, np.int32)
+    seq[:, :2] = r.integers(4, V, size=(rows, 2))
+    d_seq = dev(seq)
+    d_cur = dev(np.array([1], np.int32))
+    d_ticket, d_ended, d_stop = dev(np.zeros(1, np.int32)), dev(np.zeros(1, np.int32)), dev(np.full(1, -1, np.int32))
+    seed_lo, seed_hi = 2024, 7
+    stop_ref = -1
+    for step in range(6):
+        cur = 1 + step
+        lq = np.clip(np.rint(r.standard_normal((rows, ldv)) * 30), -127, 127).astype(np.int8)
+        if step >= 2:
+            lq[step % rows::3, end_id] = 127  # make some rows end
+        if step == 5:
+            lq[:, :] = -100
+            lq[:, end_id] = 127          # everything ends
+        d_l = dev(lq)
+        a = L.SampleTopkArgs(logits=ptr(d_l), ld_logits=ldv, s_logits=float(s_l), rows=rows, vocab=V, k=k, max_step=ms,
+                             end_id=end_id, seed_lo=seed_lo, seed_hi=seed_hi, seq=ptr(d_seq), cur=ptr(d_cur),
+                             ticket=ptr(d_ticket), n_ended=ptr(d_ended), stop=ptr(d_stop), stop_host=None)
+        L.call("ls100_sample_topk", ctx(), a)
+        sync_check()
+        for row in range(rows):
+            if seq[row, cur] == end_id:
+                seq[row, cur + 1] = end_id
+            else:
+                seq[row, cur + 1] = ob.sample_topk_row(lq[row, :V], s_l, k, cur + 1, row, seed_lo, seed_hi)
+        if stop_ref < 0 and (seq[:, cur + 1] == end_id).all():
+            stop_ref = cur + 1
+        assert int(d_cur.cpu()[0]) == cur + 1
+        assert np.array_equal(d_seq.cpu().numpy(), seq), f"step {step}: sampled tokens differ"
+        assert int(d_stop.cpu()[0]) == stop_ref
+    assert stop_ref > 0
