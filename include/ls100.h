@@ -360,6 +360,9 @@ int ls100_transformer_infer_host(ls100_model* m, const int32_t* ids, int batch, 
 /* QuantBert: ids [batch, seq_len] -> fp32 encoder output [batch, seq_len, hidden] (PyQuantBert::infer,
  * lightseq/inference/pywrapper/wrapper.cc:276-321). */
 int ls100_bert_infer_host(ls100_model* m, const int32_t* ids, int batch, int seq_len, float* out);
+/* QuantGpt: prompt ids [batch, prompt_len] -> prompt + sampled tokens [batch, *out_len], written densely into
+ * out_tokens (batch*max_step ints) (PyQuantGpt::sample, lightseq/inference/pywrapper/wrapper.cc:463-495). */
+int ls100_gpt_sample_host(ls100_model* m, const int32_t* ids, int batch, int prompt_len, int32_t* out_tokens, int* out_len);
 
 #ifdef __cplusplus
 }

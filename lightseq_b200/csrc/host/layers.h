@@ -306,4 +306,116 @@ class QuantTransformerDecoderLayer : public Layer {
   int batch_ = 0, beam_ = 0, src_len_ = 0;
 };
 
+// ---------------------------------------------------------------------------------------
+// Decoder-only layer (GPT-2 layout: pre-LN, causal self-attention on attention_quant(qkv), GELU FFN), with the
+// prefill form (all prompt positions at once, filling the int8 KV cache) and the one-token decode form.
+// Counterpart of GptLayer / GptAttentionLayer (lightseq/csrc/layers_new/includes/gpt_layer.h) and of
+// QuantGptEncoder::self_attention / self_attention_with_cache (lightseq/inference/model/quant_gpt_encoder.cc.cu:485-658).
+class QuantGptLayer : public Layer {
+ public:
+  QuantGptLayer(ContextPtr ctx, const WeightsFile& wf, const std::string& prefix, int layer_id, int max_batch_tokens,
+                int max_seq_len, int hidden, int heads, int ffn, int max_batch_size)
+      : Layer(prefix, ctx), hidden_(hidden), heads_(heads), ffn_(ffn), max_tokens_(max_batch_tokens),
+        max_bs_(max_batch_size), max_step_(max_seq_len) {
+    (void)layer_id;
+    qkv_.load(*ctx, wf, prefix + ".qkv", false);
+    out_.load(*ctx, wf, prefix + ".out", false);
+    fc1_.load(*ctx, wf, prefix + ".fc1", false);
+    fc2_.load(*ctx, wf, prefix + ".fc2", false);
+    ln1_.load(*ctx, wf, prefix + ".ln1", hidden);
+    ln2_.load(*ctx, wf, prefix + ".ln2", hidden);
+    s_kv_ = wf.amax(prefix + ".kv") / 127.0f;
+    const size_t cache = (size_t)max_batch_size * max_seq_len * hidden;
+    k_cache_ = ctx->alloc_n<int8_t>(cache);
+    v_cache_ = ctx->alloc_n<int8_t>(cache);
+    LS_CUDA(cudaMemset(k_cache_, 0, cache));
+    LS_CUDA(cudaMemset(v_cache_, 0, cache));
+  }
+  void operator()(StackBuffers* bufs, const int32_t* step_ptr) {
+    b_ = bufs;
+    step_ptr_ = step_ptr;
+  }
+  // prompt_len > 0: prefill of batch x prompt_len rows; prompt_len == 0: one token per sequence at *step_ptr
+  void before_forward(int batch, int prompt_len) {
+    batch_ = batch;
+    prompt_ = prompt_len;
+    if (batch > max_bs_) throw std::runtime_error("batch exceeds max_batch_size");
+    if ((long long)batch * std::max(prompt_len, 1) > max_tokens_) throw std::runtime_error("tokens exceed max_batch_tokens");
+    if (prompt_len > max_step_) throw std::runtime_error("prompt longer than max_step");
+  }
+  void forward() override {
+    const int rows = prompt_ > 0 ? batch_ * prompt_ : batch_;
+    ln_quant(rows, ln1_, qkv_.amax_in);
+    gemm(b_->a_q, qkv_, rows, LS100_OUT_REQ_S8, b_->qkv_q, Act::None, nullptr, s_kv_);
+    if (prompt_ > 0) {
+      ls100_attn_self_args a;
+      memset(&a, 0, sizeof(a));
+      a.qkv = b_->qkv_q->value<int8_t>();
+      a.ld_qkv = 3 * hidden_;
+      a.s_qkv = s_kv_;
+      a.batch = batch_;
+      a.seq = prompt_;
+      a.heads = heads_;
+      a.causal = 1;
+      a.amax_out = out_.amax_in;
+      a.out = b_->attn_q->value<int8_t>();
+      a.ld_out = hidden_;
+      a.k_cache = k_cache_;
+      a.v_cache = v_cache_;
+      a.max_step = max_step_;
+      LS_RC(ls100_attn_self(ctx_->kernels(), &a, ctx_->get_stream()));
+    } else {
+      ls100_attn_dec_args a;
+      memset(&a, 0, sizeof(a));
+      a.qkv = b_->qkv_q->value<int8_t>();
+      a.ld_qkv = 3 * hidden_;
+      a.s_kv = s_kv_;
+      a.k_cache = k_cache_;
+      a.v_cache = v_cache_;
+      a.step_ptr = step_ptr_;
+      a.rows = rows;
+      a.heads = heads_;
+      a.max_step = max_step_;
+      a.amax_out = out_.amax_in;
+      a.out = b_->attn_q->value<int8_t>();
+      a.ld_out = hidden_;
+      LS_RC(ls100_attn_dec(ctx_->kernels(), &a, ctx_->get_stream()));
+    }
+    gemm(b_->attn_q, out_, rows, LS100_OUT_F32, b_->x, Act::None, b_->x, 0.f);
+    ln_quant(rows, ln2_, fc1_.amax_in);
+    gemm(b_->a_q, fc1_, rows, LS100_OUT_REQ_S8, b_->h_q, Act::Gelu, nullptr, fc2_.s_in);
+    gemm(b_->h_q, fc2_, rows, LS100_OUT_F32, b_->x, Act::None, b_->x, 0.f);
+  }
+
+ private:
+  void ln_quant(int rows, const LayerNormParams& ln, float amax) {
+    ls100_ln_quant_args a;
+    memset(&a, 0, sizeof(a));
+    a.x = b_->x->value<float>();
+    a.ldx = hidden_;
+    a.gamma = ln.g;
+    a.beta = ln.b;
+    a.rows = rows;
+    a.hidden = hidden_;
+    a.amax = amax;
+    a.out_q = b_->a_q->value<int8_t>();
+    a.ldq = hidden_;
+    LS_RC(ls100_ln_quant(ctx_->kernels(), &a, ctx_->get_stream()));
+  }
+  void gemm(Variable* in, const QLinearParams& p, int rows, int out_kind, Variable* out, Act act, Variable* resid, float s_req) {
+    QuantLinearOp op(ctx_, name_ + ".gemm", &p, out_kind, act, true, true, s_req);
+    op(in, out, resid);
+    op.before_forward(rows);
+    op.forward();
+  }
+  int hidden_, heads_, ffn_, max_tokens_, max_bs_, max_step_;
+  QLinearParams qkv_, out_, fc1_, fc2_;
+  LayerNormParams ln1_, ln2_;
+  float s_kv_ = 0.f;
+  int8_t *k_cache_ = nullptr, *v_cache_ = nullptr;
+  StackBuffers* b_ = nullptr;
+  const int32_t* step_ptr_ = nullptr;
+  int batch_ = 0, prompt_ = 0;
+};
+
 }  // namespace ls100

@@ -166,6 +166,24 @@ extern "C" int ls100_bert_infer_host(ls100_model* m, const int32_t* ids, int bat
   });
 }
 
+extern "C" int ls100_gpt_sample_host(ls100_model* m, const int32_t* ids, int batch, int prompt_len, int32_t* out_tokens,
+                                     int* out_len) {
+  if (!m || !ids || !out_tokens || !out_len || batch < 1 || prompt_len < 1) return LS100_ERR_BAD_ARG;
+  return guarded([&] {
+    const size_t nb = (size_t)batch * prompt_len * 4;
+    if (nb > m->in_bytes) throw std::runtime_error("input larger than max_batch_size x max_step");
+    LS_CUDA(cudaSetDevice(m->device));
+    LS_CUDA(cudaMemcpy(m->d_in, ids, nb, cudaMemcpyHostToDevice));
+    m->model->set_input_ptr(0, m->d_in);
+    m->model->set_input_shape(0, {batch, prompt_len});
+    m->model->set_output_ptr(0, m->d_out0);
+    m->model->Infer();
+    const std::vector<int> shp = m->model->get_output_shape(0);
+    LS_CUDA(cudaMemcpy(out_tokens, m->d_out0, prod(shp) * 4, cudaMemcpyDeviceToHost));
+    *out_len = shp.at(1);
+  });
+}
+
 // ---- test-only taps (not declared in include/ls100.h): device pointers valid until the next Infer()
 extern "C" const float* ls100_debug_encoder_output(ls100_model* m) {
   return m ? ls100::quant_transformer_encoder_output(m->model.get()) : nullptr;

@@ -98,7 +98,8 @@ __global__ void __launch_bounds__(256) embed_kernel(const ls100_embed_args a) {
   }
   const bool is_pad = (id == a.pad_id);
   if (a.pad_mask && lane == 0) a.pad_mask[warp] = is_pad ? 1 : 0;
-  if (id < 0 || id >= a.vocab) id = a.pad_id;  // out-of-range ids read the pad row instead of faulting
+  // out-of-range ids read the pad row (row 0 when there is no pad id) instead of faulting
+  if (id < 0 || id >= a.vocab) id = (a.pad_id >= 0 && a.pad_id < a.vocab) ? a.pad_id : 0;
   if (pos >= a.n_pos) pos = a.n_pos - 1;
   const int8_t* er = a.table_q + (long long)id * a.hidden;
   const float* pr = a.pos + (long long)pos * a.hidden;

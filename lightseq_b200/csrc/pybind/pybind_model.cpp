@@ -92,6 +92,41 @@ class PyQuantBert {
   int hidden_ = 0;
 };
 
+// QuantGpt(weight_path, max_batch_size).sample(int32[B,P]) -> int32[B,L]
+// (PyQuantGpt::sample, lightseq/inference/pywrapper/wrapper.cc:427-495)
+class PyQuantGpt {
+ public:
+  PyQuantGpt(const std::string& weight_path, int max_batch_size) {
+    check(ls100_model_create("QuantGpt", weight_path.c_str(), max_batch_size, &m_), "QuantGpt");
+    int32_t dims[4];
+    int nd = 0;
+    check(ls100_model_get_output_max_shape(m_, 0, dims, &nd), "get_output_max_shape");
+    max_step_ = dims[1];
+  }
+  ~PyQuantGpt() { ls100_model_destroy(m_); }
+  PyQuantGpt(const PyQuantGpt&) = delete;
+  PyQuantGpt& operator=(const PyQuantGpt&) = delete;
+  py::array_t<int> sample(py::array_t<int, py::array::c_style | py::array::forcecast> input_seq) {
+    if (input_seq.ndim() != 2) throw std::runtime_error("input_seq must be a 2-D int32 array [batch, seq_len]");
+    const int batch = (int)input_seq.shape(0), seq = (int)input_seq.shape(1);
+    std::vector<int32_t> toks((size_t)batch * max_step_);
+    int n = 0;
+    {
+      py::gil_scoped_release nogil;
+      check(ls100_gpt_sample_host(m_, input_seq.data(), batch, seq, toks.data(), &n), "sample");
+    }
+    py::array_t<int> out({batch, n});
+    std::copy(toks.begin(), toks.begin() + (size_t)batch * n, out.mutable_data());
+    return out;
+  }
+  void benchmark_mode(bool on) { check(ls100_model_benchmark_mode(m_, on ? 1 : 0), "benchmark_mode"); }
+  std::uintptr_t handle() const { return reinterpret_cast<std::uintptr_t>(m_); }
+
+ private:
+  ls100_model* m_ = nullptr;
+  int max_step_ = 0;
+};
+
 }  // namespace
 
 PYBIND11_MODULE(_ls100_py, m) {
@@ -101,6 +136,11 @@ PYBIND11_MODULE(_ls100_py, m) {
       .def("infer", &PyQuantTransformer::infer, py::arg("input_seq"))
       .def("benchmark_mode", &PyQuantTransformer::benchmark_mode)
       .def_property_readonly("_handle", &PyQuantTransformer::handle);
+  py::class_<PyQuantGpt>(m, "QuantGpt")
+      .def(py::init<const std::string&, int>(), py::arg("weight_path"), py::arg("max_batch_size"))
+      .def("sample", &PyQuantGpt::sample, py::arg("input_seq"))
+      .def("benchmark_mode", &PyQuantGpt::benchmark_mode)
+      .def_property_readonly("_handle", &PyQuantGpt::handle);
   py::class_<PyQuantBert>(m, "QuantBert")
       .def(py::init<const std::string&, int>(), py::arg("weight_path"), py::arg("max_batch_size"))
       .def("infer", &PyQuantBert::infer, py::arg("input_seq"))

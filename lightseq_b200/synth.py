@@ -310,3 +310,75 @@ def make_bert(path: Optional[str] = None, *, hidden=768, heads=12, ffn=3072, n_l
 
         weights.save(path, "QuantBert", conf, amax, w)
     return conf, amax, w
+
+
+# ------------------------------------------------------------------------------------------- GPT-2
+def gpt_weights(hidden=1024, heads=16, ffn=4096, n_layer=24, vocab=50257, max_pos=1024, seed=1234, std=0.02):
+    rng = np.random.default_rng(seed)
+
+    def nrm(*shape):
+        return (rng.standard_normal(shape, dtype=F32) * F32(std)).astype(F32)
+
+    w: Dict[str, np.ndarray] = {"emb": nrm(vocab, hidden), "pos": nrm(max_pos, hidden),
+                                "dec.ln.g": np.ones(hidden, F32), "dec.ln.b": np.zeros(hidden, F32)}
+    for l in range(n_layer):
+        p = f"dec.{l}"
+        for name, (no, ni) in (("qkv", (3 * hidden, hidden)), ("out", (hidden, hidden)), ("fc1", (ffn, hidden)),
+                               ("fc2", (hidden, ffn))):
+            w[f"{p}.{name}.w"] = nrm(no, ni)
+            w[f"{p}.{name}.b"] = np.zeros(no, F32)
+        for ln in ("ln1", "ln2"):
+            w[f"{p}.{ln}.g"] = np.ones(hidden, F32)
+            w[f"{p}.{ln}.b"] = np.zeros(hidden, F32)
+    return w
+
+
+def gpt_inputs(batch=64, prompt=64, vocab=50257, seed=4321) -> np.ndarray:
+    return np.random.default_rng(seed).integers(0, vocab, size=(batch, prompt)).astype(np.int32)
+
+
+def calibrate_gpt(w, ids, *, heads: int, n_layer: int, k: float = 4.0) -> Dict[str, float]:
+    st = _Stats()
+    H = w["emb"].shape[1]
+    B, S = ids.shape
+
+    def lin(name, x):
+        st.see(name + ".in", x)
+        y = x @ w[name + ".w"].T
+        st.see(name + ".out", y)
+        return (y + w[name + ".b"]).astype(F32)
+
+    causal = ~np.tril(np.ones((S, S), dtype=bool))
+    x = (w["emb"][ids] + w["pos"][np.arange(S)]).astype(F32)
+    for l in range(n_layer):
+        p = f"dec.{l}"
+        qkv = lin(p + ".qkv", _ln(x, w[p + ".ln1.g"], w[p + ".ln1.b"]))
+        st.see(p + ".kv", qkv)
+        a = _attn(qkv[..., :H], qkv[..., H:2 * H], qkv[..., 2 * H:], heads, causal[None, None])
+        x = x + lin(p + ".out", a)
+        x = x + lin(p + ".fc2", _act(lin(p + ".fc1", _ln(x, w[p + ".ln2.g"], w[p + ".ln2.b"])), "gelu"))
+    x = _ln(x, w["dec.ln.g"], w["dec.ln.b"])
+    st.see("logits.in", x)
+    st.see("logits.out", x[:, -4:] @ w["emb"].T)
+    amax = st.amax(k)
+    for name, t in w.items():
+        if name.endswith(".w") and t.ndim == 2:
+            amax[name] = float(F32(k * t.std()))
+    amax["emb"] = float(F32(k * w["emb"].std()))
+    return amax
+
+
+def make_gpt(path: Optional[str] = None, *, hidden=1024, heads=16, ffn=4096, n_layer=24, vocab=50257, max_step=256,
+             end_id=50256, topk=8, max_new_tokens=192, seed=1234, rng_seed=2024, calib_ids: Optional[np.ndarray] = None):
+    """Builds (conf, amax, tensors) of a seeded synthetic QuantGpt (GPT-2 layout: pre-LN, GELU, learned positions)."""
+    w = gpt_weights(hidden, heads, ffn, n_layer, vocab, max_step, seed)
+    if calib_ids is None:
+        calib_ids = gpt_inputs(batch=4, prompt=min(24, max_step), vocab=vocab, seed=seed + 1)
+    amax = calibrate_gpt(w, calib_ids, heads=heads, n_layer=n_layer)
+    conf = dict(hidden=hidden, heads=heads, ffn=ffn, n_dec=n_layer, vocab=vocab, act_gelu=1.0, pre_ln=1.0,
+                max_step=max_step, end_id=end_id, topk=topk, max_new_tokens=max_new_tokens, rng_seed=rng_seed)
+    if path is not None:
+        from . import weights
+
+        weights.save(path, "QuantGpt", conf, amax, w)
+    return conf, amax, w

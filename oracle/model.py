@@ -423,3 +423,76 @@ class Bert:
             x = encoder_layer(st, x, pad, f"enc.{l}", cfg)
             st.rec(f"enc.{l}.y", x)
         return x
+
+
+# --------------------------------------------------------------------------- GPT-2 style decoder-only model
+def gpt_layer(st: State, x: np.ndarray, p: str, cfg: Config, cache: dict) -> np.ndarray:
+    """Decoder-only layer (TransformerDecoderLayer with has_cross_attn=False, pre-LN, causal;
+    torch_transformer_layers.py:682-965 wired as in examples/training/huggingface/gpt/ls_hf_gpt_layer.py:44-83).
+    x [B,L,H] holds the L newest positions; ``cache`` keeps the int8 keys/values of all earlier positions
+    (attention_quant is applied to the whole biased qkv, :95-97,203-204)."""
+    B, L, H = x.shape
+    res = x
+    h = layer_norm(x, st.w[p + ".ln1.g"], st.w[p + ".ln1.b"])
+    qkv = qlinear(st, h.reshape(B * L, H), p + ".qkv").reshape(B, L, 3 * H)
+    qq, s_kv = Q.quantize(qkv, st.amax[p + ".kv"], clip=False)
+    st.rec(p + ".qkv_q", qq)
+    kq, vq = qq[..., H:2 * H], qq[..., 2 * H:]
+    cache["k"] = kq if "k" not in cache else np.concatenate([cache["k"], kq], 1)
+    cache["v"] = vq if "v" not in cache else np.concatenate([cache["v"], vq], 1)
+    a = attention_core(qq[..., :H].astype(F32) * s_kv, cache["k"].astype(F32) * s_kv, cache["v"].astype(F32) * s_kv,
+                       cfg.heads, None, cfg.head_dim ** -0.5, causal=True)
+    st.rec(p + ".attn", a)
+    x = res + qlinear(st, a.reshape(B * L, H), p + ".out").reshape(B, L, H)
+    res = x
+    h = layer_norm(x, st.w[p + ".ln2.g"], st.w[p + ".ln2.b"])
+    return (res + ffn(st, h.reshape(B * L, H), p, cfg).reshape(B, L, H)).astype(F32)
+
+
+class Gpt:
+    """GptEmbedding (token lookup -> emb_quant, ls_hf_gpt_layer.py:85-96) + learned positions + decoder-only
+    layers + final LayerNorm + lm_head sharing the embedding table and quantiser (:131-139); generation by
+    top-k sampling as QuantGptEncoder::run_one_sample (lightseq/inference/model/quant_gpt_encoder.cc.cu:300-397)."""
+
+    def __init__(self, cfg: Config, st: State):
+        self.cfg = cfg
+        self.st = st
+
+    def forward(self, ids: np.ndarray, start: int, caches) -> np.ndarray:
+        """ids [B,L] at absolute positions start..start+L-1 -> final-LayerNorm hidden states [B,L,H]."""
+        cfg, st = self.cfg, self.st
+        eq, s = st.weight_q("emb", "emb")[:2]
+        x = eq[ids].astype(F32) * s + st.w["pos"][start + np.arange(ids.shape[1])]
+        for l in range(cfg.n_dec):
+            x = gpt_layer(st, x.astype(F32), f"dec.{l}", cfg, caches[l])
+        return layer_norm(x, st.w["dec.ln.g"], st.w["dec.ln.b"])
+
+    def logits(self, h: np.ndarray):
+        """h [T,H] -> (int8 logits [T,V], scale)."""
+        _, lq, s = qlinear(self.st, h, "logits", wname="emb", w_amax="emb", bias=False, return_q=True)
+        return lq, s
+
+    def generate(self, prompt: np.ndarray, max_new: int, k: int, seed_lo: int, seed_hi: int):
+        from .beam import sample_topk_row
+
+        cfg = self.cfg
+        B, P = prompt.shape
+        caches = [dict() for _ in range(cfg.n_dec)]
+        seq = np.full((B, cfg.max_step), cfg.end_id, dtype=np.int32)
+        seq[:, :P] = prompt
+        h = self.forward(prompt, 0, caches)[:, -1]
+        cur = P - 1
+        while cur + 1 < min(cfg.max_step, P + max_new):
+            lq, s_l = self.logits(h)
+            for b in range(B):
+                if seq[b, cur] == cfg.end_id:
+                    seq[b, cur + 1] = cfg.end_id
+                else:
+                    seq[b, cur + 1] = sample_topk_row(lq[b], s_l, k, cur + 1, b, seed_lo, seed_hi)
+            cur += 1
+            if (seq[:, cur] == cfg.end_id).all():
+                break
+            if cur + 1 >= min(cfg.max_step, P + max_new):
+                break
+            h = self.forward(seq[:, cur:cur + 1], cur, caches)[:, 0]
+        return seq[:, :cur + 1].copy()

@@ -267,9 +267,61 @@ def golden_small_bert():
     print("small bert:", out["y1"].shape)
 
 
+@torch.no_grad()
+def golden_small_gpt():
+    """GPT-2 layout: quantised token embedding + learned positions, two decoder-only layers
+    (TransformerDecoderLayer with has_cross_attn=False -> causal self-attention on attention_quant(qkv)),
+    final LayerNorm and the lm_head QuantLinear that shares the embedding table and quantiser
+    (examples/training/huggingface/gpt/ls_hf_gpt_layer.py:44-139). Full-sequence forward, batch 3 x 10."""
+    H, heads, F, V, n_layer, S = 128, 2, 256, 150, 2, 10
+    conf, amax, w = synth.make_gpt(None, hidden=H, heads=heads, ffn=F, n_layer=n_layer, vocab=V, max_step=16, end_id=149, seed=31)
+    ids = synth.gpt_inputs(batch=3, prompt=S, vocab=V, seed=6)
+    from lightseq.training.pytorch_quantization.nn.modules.tensor_quantizer import TensorQuantizer
+
+    emb_quant = TensorQuantizer(qz.emb_quant_config)
+    emb_quant.clip.clip_value_max.data.fill_(amax["emb"])
+    emb_quant.apply(qz.enable_quant)
+    wte = torch.nn.Parameter(torch.from_numpy(w["emb"]))
+    layers = []
+    for l in range(n_layer):
+        p = f"dec.{l}"
+        cfg = tl.TransformerDecoderLayer.get_config(
+            max_batch_tokens=4096, max_seq_len=256, hidden_size=H, intermediate_size=F, nhead=heads,
+            attn_prob_dropout_ratio=0.0, activation_dropout_ratio=0.0, hidden_dropout_ratio=0.0,
+            pre_layer_norm=True, fp16=False, local_rank=-1, nlayer=n_layer, activation_fn="gelu", has_cross_attn=False)
+        lyr = tl.TransformerDecoderLayer(cfg)
+        load_linear(lyr.self_attn.qkv_proj, w, p + ".qkv", amax)
+        lyr.self_attn.attention_quant._amax.fill_(amax[p + ".kv"])
+        load_linear(lyr.self_attn.out_proj, w, p + ".out", amax)
+        load_linear(lyr.fc1, w, p + ".fc1", amax)
+        load_linear(lyr.fc2, w, p + ".fc2", amax)
+        load_ln(lyr.self_attn_layer_norm, w, p + ".ln1")
+        load_ln(lyr.final_layer_norm, w, p + ".ln2")
+        lyr.eval()
+        lyr.apply(qz.enable_quant)
+        layers.append(lyr)
+    ln_f = torch.nn.LayerNorm(H)
+    load_ln(ln_f, w, "dec.ln")
+    head = qz.QuantLinear(H, V, bias=False)
+    head.weight = wte
+    head.weight_quant = emb_quant
+    set_qlinear(head, amax, "logits")
+    head.eval()
+    head.apply(qz.enable_quant)
+    t = torch.from_numpy(ids.astype(np.int64))
+    x = emb_quant(torch.nn.functional.embedding(t, wte)) + torch.from_numpy(w["pos"][:S])
+    for lyr in layers:
+        x, _, _ = lyr(x)
+    h = ln_f(x)
+    logits = head(h)
+    np.savez_compressed(HERE / "small_gpt.npz", ids=ids, hidden=h.numpy(), logits=logits.numpy())
+    print("small gpt: logits", tuple(logits.shape))
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     golden_quantizer()
     golden_c0()
     golden_small_seq2seq()
     golden_small_bert()
+    golden_small_gpt()
