@@ -496,6 +496,54 @@ def run_ours(args):
     return 0
 
 
+def run_other_workload(args):
+    """``--workload bert|gpt|big``: the other BASELINE configurations on one GPU (reported in DESIGN.md; the
+    contract line of this file is the Transformer-base workload)."""
+    import torch
+
+    import lightseq_b200.inference as lsi
+    from lightseq_b200 import synth
+
+    torch.cuda.set_device(0)
+    td = tempfile.mkdtemp(prefix="ls100_bench_")
+    path = os.path.join(td, "model.ls100")
+    out = {"workload": args.workload}
+
+    def timed(fn, reps):
+        for _ in range(2):
+            r = fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            r = fn()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / reps, r
+
+    if args.workload == "bert":
+        synth.make_bert(path, max_step=512)
+        model = lsi.QuantBert(path, 128)
+        for B, S in ((128, 128), (32, 512)):
+            ids = synth.bert_inputs(batch=B, seq=S)
+            dt, y = timed(lambda: model.infer(ids), args.steps)
+            out[f"{B}x{S}"] = {"ms": dt * 1e3, "tokens_per_s": B * S / dt, "int8_gemm_tops": 2 * B * S * 12 * 7077888 / dt / 1e12}
+    elif args.workload == "gpt":
+        conf, _, _ = synth.make_gpt(path, max_step=256, max_new_tokens=192)
+        model = lsi.QuantGpt(path, 64)
+        model.benchmark_mode(True)
+        ids = synth.gpt_inputs(batch=64, prompt=64)
+        dt, y = timed(lambda: model.sample(ids), args.steps)
+        out["64x64+192"] = {"ms": dt * 1e3, "generated_tokens_per_s": 64 * (y.shape[1] - 64) / dt, "out_len": int(y.shape[1])}
+    else:  # transformer-big
+        src = synth.transformer_inputs(batch=256, min_len=20, max_len=100)
+        calib = synth.transformer_inputs(batch=8, min_len=20, max_len=100, seed=5)
+        synth.make_transformer(path, hidden=1024, heads=16, ffn=4096, max_step=160, calib_src=calib)
+        model = lsi.QuantTransformer(path, 256)
+        dt, (tok, sc) = timed(lambda: model.infer(src), args.steps)
+        out["256 x src20..100"] = {"ms": dt * 1e3, "tokens_per_s": tok.shape[0] * tok.shape[2] / dt, "out_len": int(tok.shape[2])}
+    print(json.dumps(out), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -507,6 +555,8 @@ def main():
                     help="cap the number of decode steps per generation (profiling aid; the result is not a bench value)")
     ap.add_argument("--kernel", default=None,
                     help="run one kernel family alone (gemm_dec, gemm_logits, attn_dec, attn_cross, beam_topk, ln_quant)")
+    ap.add_argument("--workload", default=None, choices=["bert", "gpt", "big"],
+                    help="run another BASELINE configuration (BERT-base, GPT-2 medium, Transformer-big) on one GPU")
     ap.add_argument("--quick", action="store_true",
                     help="device-resident arm only, warm-up exactly as given (for profiler launch lists)")
     args = ap.parse_args()
@@ -514,6 +564,8 @@ def main():
         return run_reference_arm(args)
     if args.kernel:
         return run_single_kernel(args)
+    if args.workload:
+        return run_other_workload(args)
     return run_ours(args)
 
 

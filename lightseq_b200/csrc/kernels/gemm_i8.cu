@@ -146,19 +146,30 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
     } else if (p.act == LS100_ACT_GELU) {
       const bool requant = (p.out_kind == LS100_OUT_REQ_S8 || p.out_kind == LS100_OUT_REQ_U8) && p.resid == nullptr;
       if (requant) {
-        // fp32 erff is within a few ulp of the float64 erf the oracle uses; that can only change the int8
-        // result when gelu(x)/s_req + 0.5 lands within ~1e-4 of an integer. Those rare elements are redone
-        // with the float64 erf, everything else keeps the cheap path.
+        // The fast GELU is good to ~1e-6 absolute; that can only change the int8 result when
+        // gelu(x)/s_req + 0.5 lands very close to an integer. Those rare elements (about one in ten thousand)
+        // are redone with the float64 erf the oracle uses; two passes so that the common path stays branch-free.
         const float shift = (p.out_kind == LS100_OUT_REQ_U8) ? -126.5f : 0.5f;
+        float g[32];
+        unsigned redo = 0;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          const float x = v[j];
-          float g = gelu_erf(x);
-          const float u = __fadd_rn(div_rn(g, p.s_req, p.rs_req), shift);
+          g[j] = gelu_fast(v[j]);
+          const float u = __fadd_rn(div_rn(g[j], p.s_req, p.rs_req), shift);
           const float r = __fsub_rn(__fadd_rn(u, 12582912.f), 12582912.f);  // nearest integer
-          if (fabsf(u) < 200.f && fabsf(__fsub_rn(u, r)) < 2e-4f * fmaxf(1.f, fabsf(u))) g = gelu_erf_exact(x);
-          v[j] = g;
+          // |gelu_fast - gelu| <= 0.5|x| * 5e-7 (erf approximation + ex2/rcp error) + a few ulp of g; in
+          // quantisation units that is the first two terms, the third covers the rounding of u itself.
+          const float tol = fmaf(fabsf(v[j]) * p.rs_req, 1e-6f, fmaf(fabsf(u), 2e-6f, 4e-6f));
+          const bool near = fabsf(u) < 200.f && fabsf(__fsub_rn(u, r)) < tol;
+          redo |= near ? (1u << j) : 0u;
         }
+        if (redo) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (redo & (1u << j)) g[j] = gelu_erf_exact(v[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = g[j];
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = gelu_erf_exact(v[j]);

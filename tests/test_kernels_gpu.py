@@ -114,10 +114,12 @@ def test_gemm_ffn_relu_unsigned_chain_bit_exact():
     assert np.array_equal(out.cpu().numpy(), y)
 
 
-def test_gemm_gelu_requant_bit_exact():
-    """GELU + requantise: the device uses fp32 erff and redoes with the float64 erf every element whose
-    quantisation could depend on the difference, so the int8 result equals the oracle's (scipy float64 erf)."""
-    m, n, k = 256, 768, 768
+@pytest.mark.parametrize("m,n,k", [(256, 768, 768), (4096, 3072, 256)])
+def test_gemm_gelu_requant_bit_exact(m, n, k):
+    """GELU + requantise: the device uses a branch-free fp32 erf and redoes with the float64 erf every element
+    whose quantisation could depend on the difference, so the int8 result equals the oracle's (scipy float64
+    erf). The large case has 12.6M outputs: an error bound that was too tight by 1e-5 of a quantisation step
+    would show as about a hundred mismatches."""
     st, x, w, b = _qlinear_case(11, m, n, k)
     pre = om.qlinear(st, x, "l")
     act = oq.gelu(pre)
