@@ -20,6 +20,8 @@
 // Epilogue arithmetic restates QuantLinear.forward
 // (lightseq/training/ops/pytorch/quantization.py:50-61) on exact int32
 // accumulators; see include/ls100.h for the per-element recipe.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "ctx.h"
 
@@ -90,7 +92,6 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
                                                bool rr_valid) {
   const bool row_ok = row < p.m;
   const bool full = (col0 + 32 <= p.n);
-  const int nmax = p.n - 1;
   int acc[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) acc[j] = (int)r[j];
@@ -118,12 +119,13 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
     return;
   }
   float v[32];
+  bool quantised = false;
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(__int2float_rn(acc[j]), p.s_acc);
   if (p.s_outq > 0.f) {
     if (p.out_kind == LS100_OUT_OUTQ_I8) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = quant_s(v[j], p.s_outq, p.rs_outq);
+      for (int j = 0; j < 32; ++j) v[j] = quant_s_biased(v[j], p.s_outq, p.rs_outq);
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(quant_s(v[j], p.s_outq, p.rs_outq), p.s_outq);
@@ -146,30 +148,35 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
     } else if (p.act == LS100_ACT_GELU) {
       const bool requant = (p.out_kind == LS100_OUT_REQ_S8 || p.out_kind == LS100_OUT_REQ_U8) && p.resid == nullptr;
       if (requant) {
-        // The fast GELU is good to ~1e-6 absolute; that can only change the int8 result when
-        // gelu(x)/s_req + 0.5 lands very close to an integer. Those rare elements (about one in ten thousand)
-        // are redone with the float64 erf the oracle uses; two passes so that the common path stays branch-free.
-        const float shift = (p.out_kind == LS100_OUT_REQ_U8) ? -126.5f : 0.5f;
-        float g[32];
+        // GELU and the requantiser in one pass. The fast GELU is good to ~1e-6; that can only change the int8
+        // result when gelu(x)/s_req + 0.5 lands very close to an integer. Those rare elements (about one in
+        // ten thousand) are redone with the float64 erf the oracle uses, in a second pass so that the common
+        // path stays branch-free.
+        const float sub = (p.out_kind == LS100_OUT_REQ_U8) ? 127.f : 0.f;
+        float q[32];
         unsigned redo = 0;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          g[j] = gelu_fast(v[j]);
-          const float u = __fadd_rn(div_rn(g[j], p.s_req, p.rs_req), shift);
-          const float r = __fsub_rn(__fadd_rn(u, 12582912.f), 12582912.f);  // nearest integer
+          const float g = gelu_fast(v[j]);
+          const float u = __fadd_rn(__fsub_rn(div_rn(g, p.s_req, p.rs_req), sub), 0.5f);
+          const float b = __fadd_rd(u, kQuantMagic);
+          const float d = __fsub_rn(u, __fsub_rn(b, kQuantMagic));  // u - floor(u), in [0, 1)
           // |gelu_fast - gelu| <= 0.5|x| * 5e-7 (erf approximation + ex2/rcp error) + a few ulp of g; in
           // quantisation units that is the first two terms, the third covers the rounding of u itself.
           const float tol = fmaf(fabsf(v[j]) * p.rs_req, 1e-6f, fmaf(fabsf(u), 2e-6f, 4e-6f));
-          const bool near = fabsf(u) < 200.f && fabsf(__fsub_rn(u, r)) < tol;
+          const bool near = fabsf(u) < 200.f && fabsf(__fsub_rn(d, 0.5f)) > __fsub_rn(0.5f, tol);
           redo |= near ? (1u << j) : 0u;
+          q[j] = fminf(fmaxf(b, kQuantMagic - 127.f), kQuantMagic + 127.f);
         }
         if (redo) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (redo & (1u << j)) g[j] = gelu_erf_exact(v[j]);
+            if (redo & (1u << j))
+              q[j] = quant_biased(__fsub_rn(div_rn(gelu_erf_exact(v[j]), p.s_req, p.rs_req), sub));
         }
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = g[j];
+        for (int j = 0; j < 32; ++j) v[j] = q[j];
+        quantised = true;
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = gelu_erf_exact(v[j]);
@@ -197,12 +204,13 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
         }
       }
     }
-    if (p.out_kind == LS100_OUT_REQ_S8) {
+    if (quantised) {
+    } else if (p.out_kind == LS100_OUT_REQ_S8) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = quant_s(v[j], p.s_req, p.rs_req);
+      for (int j = 0; j < 32; ++j) v[j] = quant_s_biased(v[j], p.s_req, p.rs_req);
     } else if (p.out_kind == LS100_OUT_REQ_U8) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = quant_u(v[j], p.s_req, p.rs_req);
+      for (int j = 0; j < 32; ++j) v[j] = quant_u_biased(v[j], p.s_req, p.rs_req);
     }
   }
   if (!row_ok) return;
@@ -235,22 +243,22 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
       for (int j = 0; j < 32; ++j)
         if (col0 + j < p.n) op[j] = __float2half_rn(v[j]);
     }
-  } else {  // int8 outputs: v[] holds the quantised integers
+  } else {  // int8 outputs: v[] holds the results of quant_biased
     int8_t* op = reinterpret_cast<int8_t*>(p.out) + (long long)row * p.ldo + col0;
     if (full && ((p.ldo & 15) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
 #pragma unroll
       for (int j = 0; j < 32; j += 16) {
         uint4 u;
-        u.x = pack_i8x4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        u.y = pack_i8x4(v[j + 4], v[j + 5], v[j + 6], v[j + 7]);
-        u.z = pack_i8x4(v[j + 8], v[j + 9], v[j + 10], v[j + 11]);
-        u.w = pack_i8x4(v[j + 12], v[j + 13], v[j + 14], v[j + 15]);
+        u.x = pack_biased_i8x4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        u.y = pack_biased_i8x4(v[j + 4], v[j + 5], v[j + 6], v[j + 7]);
+        u.z = pack_biased_i8x4(v[j + 8], v[j + 9], v[j + 10], v[j + 11]);
+        u.w = pack_biased_i8x4(v[j + 12], v[j + 13], v[j + 14], v[j + 15]);
         *reinterpret_cast<uint4*>(op + j) = u;
       }
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (col0 + j < p.n) op[j] = (int8_t)(int)v[j];
+        if (col0 + j < p.n) op[j] = (int8_t)(__float_as_uint(v[j]) & 0xffu);
     }
   }
 }
@@ -423,15 +431,202 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
   LS100_TRACE(6);
 }
 
-template <int BN, int STAGES>
-static int launch_gemm(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cudaStream_t stream) {
-  using SM = GemmSmem<BN, STAGES>;
-  auto kern = gemm_i8_tc_kernel<BN, STAGES>;
-  CUtensorMap ta, tb;
-  int rc = ls100_get_tmap_u8(ctx, a->a, (uint64_t)a->m, (uint64_t)a->k, (uint64_t)a->lda, BM, BK, &ta);
-  if (rc) return rc;
-  rc = ls100_get_tmap_u8(ctx, a->w, (uint64_t)a->n, (uint64_t)a->k, (uint64_t)a->ldw, BN, BK, &tb);
-  if (rc) return rc;
+// ---------------------------------------------------------------------------------------------
+// Persistent variant for problems of many tiles: one CTA per SM walks a static list of 128 x 256
+// tiles. The accumulator is double-buffered in TMEM (2 x 256 columns), so the MMAs of tile i+1 run
+// while eight epilogue warps (two per TMEM lane quarter, each pair splitting the 256 columns) drain
+// tile i; with K of a few hundred the epilogue is the longer of the two and it is no longer exposed.
+//   warp 0     TMA producer, one ring of P_STAGES stages running across tile boundaries
+//   warp 1     TMEM allocator + MMA issuer
+//   warps 2-9  epilogue
+// No barrier couples the epilogue warps to each other: each stages its own bias / offset slice.
+constexpr int P_BN = 256;
+constexpr int P_STAGES = 4;
+constexpr int P_EPI_WARPS = 8;
+constexpr int P_THREADS = 64 + 32 * P_EPI_WARPS;
+
+struct PersistSmem {
+  static constexpr int A_BYTES = BM * BK;
+  static constexpr int B_BYTES = P_BN * BK;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = P_STAGES * STAGE_BYTES;
+  static constexpr int VEC_OFFSET = BAR_OFFSET + 256;
+  static constexpr int VEC_PER_WARP = (P_BN / 2) * 8;  // 128 fp32 bias + 128 int32 offsets
+  static constexpr int TOTAL = VEC_OFFSET + P_EPI_WARPS * VEC_PER_WARP + 1024;
+};
+
+__global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __grid_constant__ CUtensorMap tma_a,
+                                                                        const __grid_constant__ CUtensorMap tma_b,
+                                                                        const GemmEpi p, int tiles_n, int num_tiles) {
+  using SM = PersistSmem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + P_STAGES;
+  uint64_t* tmem_full_bar = empty_bar + P_STAGES;  // [2]
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (p.k + BK - 1) / BK;
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+#pragma unroll
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full_bar[b], 1);
+      mbar_init(&tmem_empty_bar[b], P_EPI_WARPS);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * P_BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      pdl_wait();
+      uint32_t phase = 0;
+      int s = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int n0 = (tile % tiles_n) * P_BN;
+        const int m0 = (tile / tiles_n) * BM;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          // a stage that has never been filled reads as released (parity of the phase before the first)
+          if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
+            record_timeout(p.err);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * SM::STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], SM::STAGE_BYTES);
+          tma_load_2d(sa, &tma_a, &full_bar[s], kb * BK, m0);
+          tma_load_2d(sa + SM::A_BYTES, &tma_b, &full_bar[s], kb * BK, n0);
+          if (++s == P_STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_i8<P_BN>();
+      uint32_t phase = 0;
+      int s = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        if (!mbar_wait(&tmem_empty_bar[buf], ((uint32_t)(local >> 1) & 1u) ^ 1u)) {  // drained by the epilogue
+          record_timeout(p.err);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P_BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[s], phase)) {
+            record_timeout(p.err);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * SM::STAGE_BYTES);
+          const uint64_t adesc = make_smem_desc(sa);
+          const uint64_t bdesc = make_smem_desc(sa + SM::A_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            tc_mma_i8(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
+                      (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[s]);
+          if (++s == P_STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit(&tmem_full_bar[buf]);
+      }
+    }
+  } else {
+    const int ew = warp - 2;
+    const int quarter = warp & 3;  // the TMEM lanes a warp may read are fixed by its index modulo 4
+    const int half = ew >> 2;      // which 128 of the tile's 256 columns
+    float* s_bias = reinterpret_cast<float*>(smem + SM::VEC_OFFSET + ew * SM::VEC_PER_WARP);
+    int* s_off = reinterpret_cast<int*>(s_bias + P_BN / 2);
+    float rr[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) rr[j] = 0.f;
+    pdl_wait();  // the residual (and everything written below) belongs to the chain of kernels before this one
+    int local = 0;
+    bool dead = false;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const int n0 = (tile % tiles_n) * P_BN + half * (P_BN / 2);
+      const int row = (tile / tiles_n) * BM + quarter * 32 + lane;
+      __syncwarp();
+#pragma unroll
+      for (int i = lane; i < P_BN / 2; i += 32) {
+        const int n = n0 + i;
+        s_bias[i] = (p.bias != nullptr && n < p.n) ? __ldg(p.bias + n) : 0.f;
+        s_off[i] = (p.w_off != nullptr && n < p.n) ? __ldg(p.w_off + n) : 0;
+      }
+      __syncwarp();
+      if (dead) continue;
+      bool ok = mbar_wait(&tmem_full_bar[buf], (uint32_t)(local >> 1) & 1u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) record_timeout(p.err);
+        dead = true;
+        continue;
+      }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + half * (P_BN / 2));
+#pragma unroll 1
+      for (int c0 = 0; c0 < P_BN / 2; c0 += 32) {
+        const bool last = (c0 + 32 == P_BN / 2) || (n0 + c0 + 32 >= p.n);
+        if (n0 + c0 < p.n) {
+          uint32_t r[32];
+          tmem_ld32(t_addr + (uint32_t)c0, r);
+          tmem_ld_wait();
+          if (last) {  // this warp's part of the buffer is in registers: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+          }
+          epilogue_chunk<P_BN>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, false);
+        } else if (c0 == 0) {  // the whole half lies beyond N: nothing to read, release at once
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+        }
+        if (last) break;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * P_BN);
+  }
+}
+
+static GemmEpi make_epi(const ls100_ctx* ctx, const ls100_gemm_i8_args* a) {
   GemmEpi p;
   p.m = a->m;
   p.n = a->n;
@@ -450,6 +645,36 @@ static int launch_gemm(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cudaStream_t
   p.out = a->out;
   p.ldo = a->ldo;
   p.err = ctx->d_err;
+  return p;
+}
+
+static int launch_gemm_persist(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  int rc = ls100_get_tmap_u8(ctx, a->a, (uint64_t)a->m, (uint64_t)a->k, (uint64_t)a->lda, BM, BK, &ta);
+  if (rc) return rc;
+  rc = ls100_get_tmap_u8(ctx, a->w, (uint64_t)a->n, (uint64_t)a->k, (uint64_t)a->ldw, P_BN, BK, &tb);
+  if (rc) return rc;
+  const GemmEpi p = make_epi(ctx, a);
+  const int tiles_n = (a->n + P_BN - 1) / P_BN;
+  const long long tiles = (long long)tiles_n * ((a->m + BM - 1) / BM);
+  if (tiles > 0x7fffffffLL) return LS100_ERR_BAD_ARG;
+  const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+  return ls100_launch(gemm_i8_persist_kernel, dim3(grid), dim3(P_THREADS), PersistSmem::TOTAL, stream, ta, tb, p,
+                      tiles_n, (int)tiles) == cudaSuccess
+             ? LS100_OK
+             : LS100_ERR_CUDA;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cudaStream_t stream) {
+  using SM = GemmSmem<BN, STAGES>;
+  auto kern = gemm_i8_tc_kernel<BN, STAGES>;
+  CUtensorMap ta, tb;
+  int rc = ls100_get_tmap_u8(ctx, a->a, (uint64_t)a->m, (uint64_t)a->k, (uint64_t)a->lda, BM, BK, &ta);
+  if (rc) return rc;
+  rc = ls100_get_tmap_u8(ctx, a->w, (uint64_t)a->n, (uint64_t)a->k, (uint64_t)a->ldw, BN, BK, &tb);
+  if (rc) return rc;
+  const GemmEpi p = make_epi(ctx, a);
   dim3 grid((a->n + BN - 1) / BN, (a->m + BM - 1) / BM);
   return ls100_launch(kern, grid, dim3(192), SM::TOTAL, stream, ta, tb, p) == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
@@ -472,6 +697,9 @@ int ls100_gemm_i8_init_device() {
   if (!rc) rc = set_smem_attr<128, 3>();
   if (!rc) rc = set_smem_attr<64, 4>();
   if (!rc) rc = set_smem_attr<32, 4>();
+  if (!rc && cudaFuncSetAttribute(gemm_i8_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  PersistSmem::TOTAL) != cudaSuccess)
+    rc = LS100_ERR_CUDA;
   return rc;
 }
 
@@ -492,7 +720,10 @@ extern "C" int ls100_gemm_i8(ls100_ctx* ctx, const ls100_gemm_i8_args* a, ls100_
   auto ctas = [&](int bn) { return mt * ((a->n + bn - 1) / bn); };
   const long long sms = ctx->sm_count;
   // Largest tile that still fills the machine; small problems fall to BN=32.
-  if (ctas(256) >= 2 * sms) return launch_gemm<256, 4>(ctx, a, stream);
+  if (ctas(256) >= 2 * sms) {
+    static const bool persist = !(getenv("LS100_GEMM_PERSIST") && getenv("LS100_GEMM_PERSIST")[0] == '0');
+    return persist ? launch_gemm_persist(ctx, a, stream) : launch_gemm<256, 4>(ctx, a, stream);
+  }
   if (ctas(128) >= sms) return launch_gemm<128, 3>(ctx, a, stream);
   if (ctas(64) >= sms) return launch_gemm<64, 4>(ctx, a, stream);
   return launch_gemm<32, 4>(ctx, a, stream);

@@ -52,6 +52,38 @@ def test_gemm_int32_accumulators_bit_exact(m, n, k):
     assert np.array_equal(out.cpu().numpy().astype(np.int64), oq.int_matmul(a, w))
 
 
+@pytest.mark.parametrize("m,n,k", [(5000, 2440, 208), (19000, 512, 1040), (4096, 2560, 128), (2500, 4136, 400)])
+def test_gemm_many_tiles_int32_bit_exact(m, n, k):
+    """Problems of more than two tiles per SM take the persistent kernel (static tile list, double-buffered
+    accumulators): ragged M, N ending inside a 32-column group and inside either half of a 256-column tile, K
+    ending inside a k-block, more and fewer tiles per CTA than accumulator buffers."""
+    r = rng(m + n + k)
+    a = r.integers(-127, 128, size=(m, k), dtype=np.int8)
+    w = r.integers(-127, 128, size=(n, k), dtype=np.int8)
+    out = gemm(dev(a), dev(w), s_acc=1.0, out_kind=L.OUT_I32)
+    sync_check()
+    assert np.array_equal(out.cpu().numpy().astype(np.int64), oq.int_matmul(a, w))
+
+
+def test_gemm_many_tiles_bias_residual_and_offset_bit_exact():
+    """The persistent kernel with every epilogue input in use: unsigned input offset, bias, residual, fp32 out."""
+    m, n, k = 6000, 1800, 256
+    st, x, w, b = _qlinear_case(21, m, n, k, unsigned_in=True)
+    st.trace = {}
+    xq, s_x = oq.quantize(x, st.amax["l.in"], unsigned=True)
+    wq, s_w = oq.quantize(w, st.amax["l.w"])
+    s_o = oq.scale_of(st.amax["l.out"])
+    acc = oq.int_matmul(xq.astype(np.int64) + 127, wq)
+    y = (acc.astype(F32) * F32(s_x * s_w))
+    y = oq.quantize(y, st.amax["l.out"])[0].astype(F32) * s_o + b
+    resid = rng(22).standard_normal((m, n)).astype(F32)
+    off = dev((127 * wq.astype(np.int64).sum(1)).astype(np.int32))
+    out = gemm(dev(xq), dev(wq), s_acc=float(F32(s_x * s_w)), out_kind=L.OUT_F32, s_outq=float(s_o), bias=dev(b),
+               resid=dev(resid), w_off=off)
+    sync_check()
+    assert np.array_equal(out.cpu().numpy(), resid + y)
+
+
 def _qlinear_case(seed, m, n, k, unsigned_in=False):
     r = rng(seed)
     w = (r.standard_normal((n, k)) * 0.02).astype(F32)
