@@ -321,6 +321,59 @@ typedef struct {
 } ls100_sample_topk_args;
 int ls100_sample_topk(ls100_ctx* ctx, const ls100_sample_topk_args* args, ls100_stream_t stream);
 
+/* ------------------------------------------------------------- top-p (nucleus) sampling ---
+ * One new token per row. Int8 logits take at most 255 distinct values, so the nucleus is found exactly from a
+ * histogram of the row: with tokens ordered by (logit desc, token asc), w_q = exp((q - q_max) * s_logits) and
+ * n_q tokens at level q, the cumulative mass after j tokens of level q is C_q + float(j) * w_q, where C_q is the
+ * float32 sum, taken level by level from q_max down, of float(n_q') * w_q' over the levels above. The nucleus is
+ * the shortest prefix whose mass reaches p * total; its mass is M. With u as in ls100_sample_topk the token is
+ * the first of that order whose cumulative mass reaches u * M. Bookkeeping (seq, *cur, *stop) as in
+ * ls100_sample_topk. Replaces ker_topp_sample_i8I (lightseq/inference/kernels/transformerKernels_int8.cc.cu:
+ * 2131-2294, gptKernels_int8.cc.cu:432-656), whose nucleus is approximate: it keeps one candidate per thread
+ * (the maximum of a stride of the row), sorts those 1024 values with CUB and cuts by their cumulative sum. */
+typedef struct {
+  const int8_t* logits; /* [rows, ld_logits] */
+  int64_t ld_logits;
+  float s_logits;
+  float p;          /* in (0, 1] */
+  int32_t rows, vocab, max_step, end_id;
+  uint32_t seed_lo, seed_hi;
+  int32_t* seq;     /* [rows, max_step], in place */
+  int32_t* cur;     /* device int: index of the newest token of every row; advanced by one */
+  int32_t* ticket;  /* device int, zero before the call sequence starts; reset by the kernel */
+  int32_t* n_ended; /* device int, zero before the call sequence starts; reset by the kernel */
+  int32_t* stop;    /* device int, -1 until every row has produced end_id */
+  int32_t* stop_host; /* optional mapped host mirror of *stop */
+} ls100_sample_topp_args;
+int ls100_sample_topp(ls100_ctx* ctx, const ls100_sample_topp_args* args, ls100_stream_t stream);
+
+/* ------------------------------------------------------------- perplexity ---
+ * ls100_token_nll: for each of `rows` consecutive (sequence, position) rows starting at flat row `row0` of a
+ * [batch, seq] batch, nll = logsumexp_v(q_v * s_logits) - q_target * s_logits where the target is the NEXT token
+ * of the sequence, ids[b, t + 1] (0 for the last position of a sequence, which has no target). `logits` points
+ * at the int8 logits of flat row `row0`. ls100_seq_ppl then gives, per sequence, the mean of nll[b, t] over
+ * t < len_b - 1, where len_b counts the tokens different from `pad_id` (pad_id < 0: every token counts); a
+ * sequence of fewer than two tokens yields 0. Together they replace ker_ppl_i8I
+ * (lightseq/inference/kernels/gptKernels_int8.cc.cu:108-190), whose per-token atomicAdd makes the sum depend
+ * on the order in which the blocks finish; here each sequence is summed by one warp in a fixed order. */
+typedef struct {
+  const int8_t* logits; /* [rows, ld_logits], row 0 = flat row `row0` */
+  int64_t ld_logits;
+  float s_logits;
+  int32_t rows, row0, vocab;
+  const int32_t* ids; /* [batch, seq] */
+  int32_t batch, seq;
+  float* nll;         /* [batch * seq]; rows row0 .. row0 + rows - 1 are written */
+} ls100_token_nll_args;
+int ls100_token_nll(ls100_ctx* ctx, const ls100_token_nll_args* args, ls100_stream_t stream);
+typedef struct {
+  const float* nll;   /* [batch * seq] */
+  const int32_t* ids; /* [batch, seq] */
+  int32_t batch, seq, pad_id;
+  float* ppl;         /* [batch] */
+} ls100_seq_ppl_args;
+int ls100_seq_ppl(ls100_ctx* ctx, const ls100_seq_ppl_args* args, ls100_stream_t stream);
+
 /* ------------------------------------------------------------- load-time prep ---
  * fp32 -> int8 with the tensor's clip-max (quantize_weight, lightseq/inference/model/
  * cublas_helper.cc:553-593) and, optionally, off[n] = 127 * sum_k q[n,k]: the exact
@@ -363,6 +416,9 @@ int ls100_bert_infer_host(ls100_model* m, const int32_t* ids, int batch, int seq
 /* QuantGpt: prompt ids [batch, prompt_len] -> prompt + sampled tokens [batch, *out_len], written densely into
  * out_tokens (batch*max_step ints) (PyQuantGpt::sample, lightseq/inference/pywrapper/wrapper.cc:463-495). */
 int ls100_gpt_sample_host(ls100_model* m, const int32_t* ids, int batch, int prompt_len, int32_t* out_tokens, int* out_len);
+/* QuantGpt.ppl(int32[B,S]) -> float32[B] (PyQuantGpt::ppl, lightseq/inference/pywrapper/wrapper.cc:497-531): mean
+ * negative log-likelihood of every sequence's own next tokens. Host buffers; copies inside the call. */
+int ls100_gpt_ppl_host(ls100_model* m, const int32_t* ids, int batch, int seq_len, float* out_ppl);
 
 #ifdef __cplusplus
 }

@@ -119,6 +119,13 @@ class SampleTopkArgs(C.Structure):
                 ("ticket", C.c_void_p), ("n_ended", C.c_void_p), ("stop", C.c_void_p), ("stop_host", C.c_void_p)]
 
 
+class SampleToppArgs(C.Structure):
+    _fields_ = [("logits", C.c_void_p), ("ld_logits", C.c_int64), ("s_logits", C.c_float), ("p", C.c_float),
+                ("rows", C.c_int32), ("vocab", C.c_int32), ("max_step", C.c_int32), ("end_id", C.c_int32),
+                ("seed_lo", C.c_uint32), ("seed_hi", C.c_uint32), ("seq", C.c_void_p), ("cur", C.c_void_p),
+                ("ticket", C.c_void_p), ("n_ended", C.c_void_p), ("stop", C.c_void_p), ("stop_host", C.c_void_p)]
+
+
 lib.ls100_strerror.restype = C.c_char_p
 lib.ls100_strerror.argtypes = [C.c_int]
 lib.ls100_ctx_create.restype = C.c_int
@@ -136,7 +143,8 @@ lib.ls100_gemm_i8.argtypes = [C.c_void_p, C.POINTER(GemmI8Args), C.c_void_p]
 for _name, _cls in (("ls100_ln_quant", LnQuantArgs), ("ls100_embed", EmbedArgs), ("ls100_attn_self", AttnSelfArgs),
                     ("ls100_attn_dec", AttnDecArgs), ("ls100_attn_cross", AttnCrossArgs),
                     ("ls100_proj_f32", ProjF32Args), ("ls100_beam_topk", BeamTopkArgs),
-                    ("ls100_beam_update", BeamUpdateArgs), ("ls100_beam_update_noalloc", BeamUpdateArgs), ("ls100_sample_topk", SampleTopkArgs)):
+                    ("ls100_beam_update", BeamUpdateArgs), ("ls100_beam_update_noalloc", BeamUpdateArgs), ("ls100_sample_topk", SampleTopkArgs),
+                    ("ls100_sample_topp", SampleToppArgs)):
     _fn = getattr(lib, _name)
     _fn.restype = C.c_int
     _fn.argtypes = [C.c_void_p, C.POINTER(_cls), C.c_void_p]

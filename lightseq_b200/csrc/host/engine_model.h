@@ -11,4 +11,7 @@ class EngineModel : public LSModel {
   virtual ContextPtr context() const = 0;
 };
 
+// QuantGpt only (quant_gpt.cpp): device ids [batch, seq_len] -> device ppl [batch]; synchronises the stream.
+void quant_gpt_ppl(LSModel* m, const int32_t* d_ids, int batch, int seq_len, float* d_ppl);
+
 }  // namespace ls100

@@ -11,6 +11,7 @@
 
 namespace ls100 {
 cudaStream_t model_stream(LSModel* m);
+void quant_gpt_ppl(LSModel* m, const int32_t* d_ids, int batch, int seq_len, float* d_ppl);
 const float* quant_transformer_encoder_output(LSModel* m);
 const int8_t* quant_transformer_last_logits(LSModel* m, int* ld);
 int quant_transformer_steps_run(LSModel* m);
@@ -181,6 +182,20 @@ extern "C" int ls100_gpt_sample_host(ls100_model* m, const int32_t* ids, int bat
     const std::vector<int> shp = m->model->get_output_shape(0);
     LS_CUDA(cudaMemcpy(out_tokens, m->d_out0, prod(shp) * 4, cudaMemcpyDeviceToHost));
     *out_len = shp.at(1);
+  });
+}
+
+extern "C" int ls100_gpt_ppl_host(ls100_model* m, const int32_t* ids, int batch, int seq_len, float* out_ppl) {
+  if (!m || !ids || !out_ppl || batch < 1 || seq_len < 1) return LS100_ERR_BAD_ARG;
+  return guarded([&] {
+    const size_t nb = (size_t)batch * seq_len * 4;
+    if (nb > m->in_bytes) throw std::runtime_error("input larger than max_batch_size x max_step");
+    if ((size_t)batch * 4 > m->out0_bytes) throw std::runtime_error("batch larger than max_batch_size");
+    LS_CUDA(cudaSetDevice(m->device));
+    LS_CUDA(cudaMemcpy(m->d_in, ids, nb, cudaMemcpyHostToDevice));
+    ls100::quant_gpt_ppl(m->model.get(), static_cast<const int32_t*>(m->d_in), batch, seq_len,
+                         static_cast<float*>(m->d_out0));
+    LS_CUDA(cudaMemcpy(out_ppl, m->d_out0, (size_t)batch * 4, cudaMemcpyDeviceToHost));
   });
 }
 

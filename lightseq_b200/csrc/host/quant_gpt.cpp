@@ -25,12 +25,15 @@ class QuantGpt : public EngineModel {
     max_step_ = (int)wf.conf("max_step");
     end_id_ = (int)wf.conf("end_id");
     topk_ = (int)wf.conf_or("topk", 1);
+    topp_ = (float)wf.conf_or("topp", 0.0);  // > 0 selects nucleus sampling, as sampling_method "topp" does in the reference
     max_new_ = (int)wf.conf_or("max_new_tokens", max_step_);
+    pad_id_ = (int)wf.conf_or("pad_id", -1);
     const uint64_t seed = (uint64_t)wf.conf_or("rng_seed", 2024);
     seed_lo_ = (uint32_t)(seed & 0xffffffffu);
     seed_hi_ = (uint32_t)(seed >> 32);
     if (H_ != heads_ * 64) throw std::runtime_error("QuantGpt: head_dim must be 64");
     if (topk_ < 1 || topk_ > 8) throw std::runtime_error("QuantGpt: topk must be in [1, 8]");
+    if (topp_ < 0.f || topp_ > 1.f) throw std::runtime_error("QuantGpt: topp must be in [0, 1]");
     if (max_batch_size < 1) throw std::runtime_error("max_batch_size must be positive");
     ctx_ = Context::create(StatusType::Inference);
     Context& c = *ctx_;
@@ -142,10 +145,94 @@ class QuantGpt : public EngineModel {
   }
   void benchmark_mode(bool b) override { benchmark_ = b; }
   ContextPtr context() const override { return ctx_; }
+
+  // Mean negative log-likelihood of each sequence's own next tokens (QuantGptEncoder::run_one_infer +
+  // compute_ppl, lightseq/inference/model/quant_gpt_encoder.cc.cu:257-298,797-822): the prompt pass, then the
+  // logits of EVERY position, kPplRows rows at a time so that the int8 logits never need more than one slab.
+  void Ppl(const int32_t* d_ids, int B, int S, float* d_ppl) {
+    if (B > max_bs_) throw std::runtime_error("batch size of input greater than max_batch_size");
+    if (S > max_step_) throw std::runtime_error("seq len of input greater than max_step");
+    if (B < 1 || S < 1) throw std::runtime_error("empty input");
+    LS_CUDA(cudaSetDevice(ctx_->device()));
+    cudaStream_t st = ctx_->get_stream();
+    ls100_ctx* k = ctx_->kernels();
+    Context& c = *ctx_;
+    const int rows = B * S;
+    if (!ppl_logits_) {
+      ppl_logits_ = new Variable("ppl_logits", c, (size_t)kPplRows * ldv_);
+      vars_.emplace_back(ppl_logits_);
+      ppl_nll_ = c.alloc_n<float>((size_t)max_bs_ * max_step_);
+    }
+    const int32_t* saved = d_ids_;
+    d_ids_ = d_ids;
+    embed(B, S, false);
+    d_ids_ = saved;
+    for (auto& l : layers_) {
+      (*l)(&buf_, counters_);
+      l->before_forward(B, S);
+      l->forward();
+    }
+    ls100_ln_quant_args a;
+    memset(&a, 0, sizeof(a));
+    a.x = buf_.x->value<float>();
+    a.ldx = H_;
+    a.gamma = ln_f_.g;
+    a.beta = ln_f_.b;
+    a.rows = rows;
+    a.hidden = H_;
+    a.amax = emb_.amax_in;
+    a.out_q = buf_.a_q->value<int8_t>();
+    a.ldq = H_;
+    LS_RC(ls100_ln_quant(k, &a, st));
+    for (int r0 = 0; r0 < rows; r0 += kPplRows) {
+      const int n = std::min(kPplRows, rows - r0);
+      ls100_gemm_i8_args g;
+      memset(&g, 0, sizeof(g));
+      g.a = buf_.a_q->value<int8_t>() + (size_t)r0 * H_;
+      g.lda = H_;
+      g.w = emb_.w;
+      g.ldw = H_;
+      g.m = n;
+      g.n = V_;
+      g.k = H_;
+      g.s_acc = emb_.s_acc;
+      g.s_outq = emb_.s_out;
+      g.out_kind = LS100_OUT_OUTQ_I8;
+      g.out = ppl_logits_->value<int8_t>();
+      g.ldo = ldv_;
+      LS_RC(ls100_gemm_i8(k, &g, st));
+      ls100_token_nll_args t;
+      memset(&t, 0, sizeof(t));
+      t.logits = ppl_logits_->value<int8_t>();
+      t.ld_logits = ldv_;
+      t.s_logits = emb_.s_out;
+      t.rows = n;
+      t.row0 = r0;
+      t.vocab = V_;
+      t.ids = d_ids;
+      t.batch = B;
+      t.seq = S;
+      t.nll = ppl_nll_;
+      LS_RC(ls100_token_nll(k, &t, st));
+    }
+    ls100_seq_ppl_args p;
+    memset(&p, 0, sizeof(p));
+    p.nll = ppl_nll_;
+    p.ids = d_ids;
+    p.batch = B;
+    p.seq = S;
+    p.pad_id = pad_id_;
+    p.ppl = d_ppl;
+    LS_RC(ls100_seq_ppl(k, &p, st));
+    LS_CUDA(cudaStreamSynchronize(st));
+    const int err = ls100_ctx_poll_error(k, st);
+    if (err != 0) throw std::runtime_error(std::string("device reported: ") + ls100_strerror(err));
+  }
   int steps_run() const { return steps_run_; }
 
  private:
   static constexpr int kRing = 4;
+  static constexpr int kPplRows = 4096;
 
   void embed(int B, int P, bool decode) {
     ls100_embed_args e;
@@ -187,6 +274,28 @@ class QuantGpt : public EngineModel {
     logits(last_q_, logits_q_);
     logits.before_forward(B, ldv_);
     logits.forward();
+    if (topp_ > 0.f) {
+      ls100_sample_topp_args s;
+      memset(&s, 0, sizeof(s));
+      s.logits = logits_q_->value<int8_t>();
+      s.ld_logits = ldv_;
+      s.s_logits = emb_.s_out;
+      s.p = topp_;
+      s.rows = B;
+      s.vocab = V_;
+      s.max_step = max_step_;
+      s.end_id = end_id_;
+      s.seed_lo = seed_lo_;
+      s.seed_hi = seed_hi_;
+      s.seq = seq_;
+      s.cur = counters_;
+      s.ticket = counters_ + 1;
+      s.n_ended = counters_ + 2;
+      s.stop = counters_ + 3;
+      s.stop_host = stop_host_dev_;
+      LS_RC(ls100_sample_topp(k, &s, st));
+      return;
+    }
     ls100_sample_topk_args s;
     memset(&s, 0, sizeof(s));
     s.logits = logits_q_->value<int8_t>();
@@ -248,6 +357,10 @@ class QuantGpt : public EngineModel {
 
   int max_bs_, H_ = 0, heads_ = 0, F_ = 0, n_layer_ = 0, V_ = 0, max_step_ = 0, end_id_ = 0, topk_ = 1, max_new_ = 0;
   int n_pos_ = 0, ldv_ = 0;
+  float topp_ = 0.f;
+  int pad_id_ = -1;
+  Variable* ppl_logits_ = nullptr;
+  float* ppl_nll_ = nullptr;
   uint32_t seed_lo_ = 0, seed_hi_ = 0;
   ContextPtr ctx_;
   QLinearParams emb_;
@@ -268,5 +381,11 @@ class QuantGpt : public EngineModel {
 };
 
 LSMODEL_REGISTER(QuantGpt)
+
+void quant_gpt_ppl(LSModel* m, const int32_t* d_ids, int batch, int seq_len, float* d_ppl) {
+  auto* g = dynamic_cast<QuantGpt*>(m);
+  if (!g) throw std::runtime_error("ppl: the model is not a QuantGpt");
+  g->Ppl(d_ids, batch, seq_len, d_ppl);
+}
 
 }  // namespace ls100

@@ -119,6 +119,17 @@ class PyQuantGpt {
     std::copy(toks.begin(), toks.begin() + (size_t)batch * n, out.mutable_data());
     return out;
   }
+  // ppl(int32[B,S]) -> float32[B] (PyQuantGpt::ppl, lightseq/inference/pywrapper/wrapper.cc:497-531)
+  py::array_t<float> ppl(py::array_t<int, py::array::c_style | py::array::forcecast> input_seq) {
+    if (input_seq.ndim() != 2) throw std::runtime_error("input_seq must be a 2-D int32 array [batch, seq_len]");
+    const int batch = (int)input_seq.shape(0), seq = (int)input_seq.shape(1);
+    py::array_t<float> out({batch});
+    {
+      py::gil_scoped_release nogil;
+      check(ls100_gpt_ppl_host(m_, input_seq.data(), batch, seq, out.mutable_data()), "ppl");
+    }
+    return out;
+  }
   void benchmark_mode(bool on) { check(ls100_model_benchmark_mode(m_, on ? 1 : 0), "benchmark_mode"); }
   std::uintptr_t handle() const { return reinterpret_cast<std::uintptr_t>(m_); }
 
@@ -139,6 +150,7 @@ PYBIND11_MODULE(_ls100_py, m) {
   py::class_<PyQuantGpt>(m, "QuantGpt")
       .def(py::init<const std::string&, int>(), py::arg("weight_path"), py::arg("max_batch_size"))
       .def("sample", &PyQuantGpt::sample, py::arg("input_seq"))
+      .def("ppl", &PyQuantGpt::ppl, py::arg("input_seq"))
       .def("benchmark_mode", &PyQuantGpt::benchmark_mode)
       .def_property_readonly("_handle", &PyQuantGpt::handle);
   py::class_<PyQuantBert>(m, "QuantBert")

@@ -369,14 +369,16 @@ def calibrate_gpt(w, ids, *, heads: int, n_layer: int, k: float = 4.0) -> Dict[s
 
 
 def make_gpt(path: Optional[str] = None, *, hidden=1024, heads=16, ffn=4096, n_layer=24, vocab=50257, max_step=256,
-             end_id=50256, topk=8, max_new_tokens=192, seed=1234, rng_seed=2024, calib_ids: Optional[np.ndarray] = None):
+             end_id=50256, topk=8, topp=0.0, pad_id=-1, max_new_tokens=192, seed=1234, rng_seed=2024,
+             calib_ids: Optional[np.ndarray] = None):
     """Builds (conf, amax, tensors) of a seeded synthetic QuantGpt (GPT-2 layout: pre-LN, GELU, learned positions)."""
     w = gpt_weights(hidden, heads, ffn, n_layer, vocab, max_step, seed)
     if calib_ids is None:
         calib_ids = gpt_inputs(batch=4, prompt=min(24, max_step), vocab=vocab, seed=seed + 1)
     amax = calibrate_gpt(w, calib_ids, heads=heads, n_layer=n_layer)
     conf = dict(hidden=hidden, heads=heads, ffn=ffn, n_dec=n_layer, vocab=vocab, act_gelu=1.0, pre_ln=1.0,
-                max_step=max_step, end_id=end_id, topk=topk, max_new_tokens=max_new_tokens, rng_seed=rng_seed)
+                max_step=max_step, end_id=end_id, topk=topk, topp=topp, pad_id=pad_id, max_new_tokens=max_new_tokens,
+                rng_seed=rng_seed)
     if path is not None:
         from . import weights
 

@@ -136,3 +136,50 @@ def sample_topk_row(lq_row: np.ndarray, s_l, k: int, position: int, row: int, se
             pick = i
             break
     return int(order[pick])
+
+
+def _topp_rank(c, w, n: int, t) -> int:
+    """Smallest j in [1, n] with float32(c + float32(j) * w) >= t, n if there is none."""
+    for j in range(1, n + 1):
+        if F32(c + F32(F32(j) * w)) >= t:
+            return j
+    return n
+
+
+def sample_topp_row(lq_row: np.ndarray, s_l, p, position: int, row: int, seed_lo: int, seed_hi: int) -> int:
+    """Nucleus sampling of one row of int8 logits: the exact form of what ker_topp_sample_i8I approximates
+    (lightseq/inference/kernels/transformerKernels_int8.cc.cu:2131-2294). Tokens are ordered by (logit desc,
+    token asc); all float32; masses are accumulated level by level (there are at most 255 levels), a level of
+    n tokens of weight w contributing float32(n) * w; the nucleus is the shortest prefix whose mass reaches
+    p * total and the draw is the first token whose cumulative mass reaches u * mass(nucleus)."""
+    s_l, p = F32(s_l), F32(p)
+    lq = lq_row.astype(np.int32)
+    levels = sorted(set(lq.tolist()), reverse=True)
+    top = levels[0]
+    cnt = {q: int((lq == q).sum()) for q in levels}
+    wgt = {q: np.exp(F32(F32(q - top) * s_l), dtype=F32) for q in levels}
+    total = F32(0)
+    for q in levels:
+        total = F32(total + F32(F32(cnt[q]) * wgt[q]))
+    cut = F32(p * total)
+    c = F32(0)
+    for q in levels:
+        m = F32(F32(cnt[q]) * wgt[q])
+        cut_q, cut_n = q, cnt[q]
+        if F32(c + m) >= cut:
+            cut_n = _topp_rank(c, wgt[q], cnt[q], cut)
+            mass = F32(c + F32(F32(cut_n) * wgt[q]))
+            break
+        c = F32(c + m)
+        mass = c
+    u = F32(F32((philox4x32_10_first(position, row, 0, 0, seed_lo, seed_hi) >> 8) + 1) * F32(2.0 ** -24))
+    target = F32(u * mass)
+    c = F32(0)
+    for q in levels:
+        n = cut_n if q == cut_q else cnt[q]
+        m = F32(F32(n) * wgt[q])
+        if q == cut_q or F32(c + m) >= target:
+            rank = _topp_rank(c, wgt[q], n, target)
+            return int(np.flatnonzero(lq == q)[rank - 1])
+        c = F32(c + m)
+    raise AssertionError("unreachable")

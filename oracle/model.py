@@ -472,8 +472,27 @@ class Gpt:
         _, lq, s = qlinear(self.st, h, "logits", wname="emb", w_amax="emb", bias=False, return_q=True)
         return lq, s
 
-    def generate(self, prompt: np.ndarray, max_new: int, k: int, seed_lo: int, seed_hi: int):
-        from .beam import sample_topk_row
+    def ppl(self, ids: np.ndarray, pad_id: int = -1) -> np.ndarray:
+        """Mean negative log-likelihood of each sequence's own next tokens from the int8 logits, as ker_ppl_i8I
+        (lightseq/inference/kernels/gptKernels_int8.cc.cu:108-180): positions t < len - 1 of a sequence of len
+        non-pad tokens, each contributing logsumexp(logits_t) - logits_t[ids[t + 1]]."""
+        cfg = self.cfg
+        B, S = ids.shape
+        h = self.forward(ids, 0, [dict() for _ in range(cfg.n_dec)])
+        lq, s_l = self.logits(h.reshape(B * S, -1))
+        lg = lq.astype(np.float64).reshape(B, S, -1) * float(s_l)
+        mx = lg.max(-1, keepdims=True)
+        lse = np.log(np.exp(lg - mx).sum(-1)) + mx[..., 0]
+        out = np.zeros(B, dtype=F32)
+        for b in range(B):
+            n = int((ids[b] != pad_id).sum()) if pad_id >= 0 else S
+            if n > 1:
+                t = np.arange(n - 1)
+                out[b] = F32((lse[b, t] - lg[b, t, ids[b, t + 1]]).mean())
+        return out
+
+    def generate(self, prompt: np.ndarray, max_new: int, k: int, seed_lo: int, seed_hi: int, topp: float = 0.0):
+        from .beam import sample_topk_row, sample_topp_row
 
         cfg = self.cfg
         B, P = prompt.shape
@@ -488,7 +507,8 @@ class Gpt:
                 if seq[b, cur] == cfg.end_id:
                     seq[b, cur + 1] = cfg.end_id
                 else:
-                    seq[b, cur + 1] = sample_topk_row(lq[b], s_l, k, cur + 1, b, seed_lo, seed_hi)
+                    seq[b, cur + 1] = (sample_topp_row(lq[b], s_l, topp, cur + 1, b, seed_lo, seed_hi) if topp > 0
+                                       else sample_topk_row(lq[b], s_l, k, cur + 1, b, seed_lo, seed_hi))
             cur += 1
             if (seq[:, cur] == cfg.end_id).all():
                 break

@@ -68,3 +68,49 @@ def test_gpt_medium_width_teacher_forced(tmp_path):
             h = m.forward(out[:, pos:pos + 1].astype(np.int64), pos, caches)[:, 0]
     print("teacher-forced token agreement", match, "of", total)
     assert match / total >= 0.95
+
+
+def test_small_gpt_nucleus_sampling_matches_oracle(tmp_path):
+    """topp > 0 in the weight file selects nucleus sampling (sampling_method "topp" of the reference)."""
+    import lightseq_b200.inference as lsi
+
+    path = str(tmp_path / "gpt.ls100")
+    conf, amax, w = synth.make_gpt(path, hidden=128, heads=2, ffn=256, n_layer=2, vocab=300, max_step=40, end_id=299,
+                                   topk=1, topp=0.6, max_new_tokens=20, seed=5, rng_seed=78)
+    cfg = _cfg(conf)
+    ids = synth.gpt_inputs(batch=5, prompt=7, vocab=300, seed=2)
+    ref = om.Gpt(cfg, om.State(w=w, amax=amax)).generate(ids, 20, 1, 78, 0, topp=0.6)
+    out = lsi.QuantGpt(path, 8).sample(ids)
+    assert out.shape == ref.shape, (out.shape, ref.shape)
+    same = (out == ref).all(axis=1)
+    print("identical sequences", int(same.sum()), "of", len(same))
+    assert same.all()
+    assert len(set(out[:, 7:].ravel().tolist())) > 20  # a nucleus of 60 % of a flat distribution is wide
+
+
+def test_gpt_ppl_matches_oracle(tmp_path):
+    """QuantGpt.ppl: mean next-token negative log-likelihood per sequence from the int8 logits of every position;
+    right-padded sequences count only their own tokens. fp32 device sums vs the float64 oracle: 1e-5 relative."""
+    import lightseq_b200.inference as lsi
+
+    path = str(tmp_path / "gpt.ls100")
+    pad = 298
+    conf, amax, w = synth.make_gpt(path, hidden=128, heads=2, ffn=256, n_layer=2, vocab=300, max_step=40, end_id=299,
+                                   pad_id=pad, topk=4, max_new_tokens=8, seed=5)
+    cfg = _cfg(conf)
+    r = np.random.default_rng(4)
+    ids = r.integers(0, 298, size=(6, 23)).astype(np.int32)
+    lens = [23, 2, 1, 10, 17, 22]
+    for b, n in enumerate(lens):
+        ids[b, n:] = pad
+    ref = om.Gpt(cfg, om.State(w=w, amax=amax)).ppl(ids, pad)
+    model = lsi.QuantGpt(path, 8)
+    out = model.ppl(ids)
+    assert out.shape == (6,) and out.dtype == np.float32
+    print("ppl", out, "ref", ref)
+    assert out[2] == 0.0
+    np.testing.assert_allclose(out, ref, rtol=2e-5, atol=1e-6)
+    assert 4.0 < out[0] < 7.0  # about log(300) for an untrained model
+    np.testing.assert_array_equal(out, model.ppl(ids))  # fixed summation order
+    with pytest.raises(RuntimeError, match="max_step"):
+        model.ppl(np.zeros((2, 41), np.int32))

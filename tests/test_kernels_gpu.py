@@ -490,3 +490,47 @@ def test_sample_topk_matches_oracle(V, k):
         assert np.array_equal(d_seq.cpu().numpy(), seq), f"step {step}: sampled tokens differ"
         assert int(d_stop.cpu()[0]) == stop_ref
     assert stop_ref > 0
+
+
+@pytest.mark.parametrize("V,p,spread", [(50257, 0.9, 30), (1000, 0.5, 8), (37, 0.3, 2), (32000, 1.0, 30), (5000, 0.02, 40)])
+def test_sample_topp_matches_oracle(V, p, spread):
+    """Nucleus sampling over several steps: tokens equal the oracle's exact nucleus draw (same Philox counters),
+    from nearly flat rows (nucleus = most of the vocabulary) to peaked ones (nucleus inside the top level);
+    ended rows keep emitting EOS and the all-ended position is recorded."""
+    rows, ms, end_id = 9, 16, 3
+    r = rng(V + spread)
+    ldv = (V + 15) // 16 * 16
+    s_l = F32(0.06)
+    seq = np.full((rows, ms), end_id, np.int32)
+    seq[:, :2] = r.integers(4, V, size=(rows, 2))
+    d_seq = dev(seq)
+    d_cur = dev(np.array([1], np.int32))
+    d_ticket, d_ended, d_stop = dev(np.zeros(1, np.int32)), dev(np.zeros(1, np.int32)), dev(np.full(1, -1, np.int32))
+    seed_lo, seed_hi = 99, 5
+    stop_ref = -1
+    for step in range(5):
+        cur = 1 + step
+        lq = np.clip(np.rint(r.standard_normal((rows, ldv)) * spread), -127, 127).astype(np.int8)
+        if step >= 2:
+            lq[step % rows::3, :] = -127
+            lq[step % rows::3, end_id] = 127  # these rows end
+        if step == 4:
+            lq[:, :] = -127
+            lq[:, end_id] = 127
+        d_l = dev(lq)
+        a = L.SampleToppArgs(logits=ptr(d_l), ld_logits=ldv, s_logits=float(s_l), p=p, rows=rows, vocab=V, max_step=ms,
+                             end_id=end_id, seed_lo=seed_lo, seed_hi=seed_hi, seq=ptr(d_seq), cur=ptr(d_cur),
+                             ticket=ptr(d_ticket), n_ended=ptr(d_ended), stop=ptr(d_stop), stop_host=None)
+        L.call("ls100_sample_topp", ctx(), a)
+        sync_check()
+        for row in range(rows):
+            if seq[row, cur] == end_id:
+                seq[row, cur + 1] = end_id
+            else:
+                seq[row, cur + 1] = ob.sample_topp_row(lq[row, :V], s_l, p, cur + 1, row, seed_lo, seed_hi)
+        if stop_ref < 0 and (seq[:, cur + 1] == end_id).all():
+            stop_ref = cur + 1
+        assert int(d_cur.cpu()[0]) == cur + 1
+        assert np.array_equal(d_seq.cpu().numpy(), seq), f"step {step}: sampled tokens differ"
+        assert int(d_stop.cpu()[0]) == stop_ref
+    assert stop_ref > 0
