@@ -236,7 +236,7 @@ def kernel_cases(torch, L, conf, B, S, step):
     def attn_cross(i, st):
         a = L.AttnCrossArgs(q=o8.data_ptr(), ld_q=H, s_q=0.02, bias=bias.data_ptr(), k=kx[i % nx].data_ptr(),
                             v=vx[i % nx].data_ptr(), ld_kv=H, pad_mask=pm.data_ptr(), batch=B, beam=K, src_len=S, heads=heads,
-                            amax_out=1.0, out=o8.data_ptr(), ld_out=H)
+                            amax_out=1.0, out=o8.data_ptr(), ld_out=H, kv_static=1, kv_head_major=1)
         L.call("ls100_attn_cross", CTX[0], a, st)
 
     cases["attn_cross"] = (attn_cross, 2 * B * S * H * 4 + 2 * T * H, "hbm", f"attn_cross_kernel, batch {B} beam {K} src {S}")

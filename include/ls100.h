@@ -203,7 +203,7 @@ typedef struct {
   int64_t ld_q;
   float s_q;
   const float* bias; /* [hidden] */
-  const void* k;     /* fp32 [batch*src_len, hidden] */
+  const void* k;     /* fp32 [batch*src_len, hidden], or head-major: see kv_head_major */
   const void* v;
   int64_t ld_kv; /* elements */
   const uint8_t* pad_mask; /* [batch, src_len] */
@@ -211,6 +211,13 @@ typedef struct {
   float amax_out;
   int8_t* out;
   int64_t ld_out;
+  /* Nonzero: k, v and pad_mask were complete before a full stream dependency that precedes this launch (a graph
+   * launch, a copy, a kernel launched without programmatic serialisation), so the kernel may fetch them before
+   * its own grid dependency on the preceding kernel resolves. Zero is always safe. */
+  int32_t kv_static;
+  /* Nonzero: k and v are fp32 [batch, heads, src_len, 64] (ls100_proj_f32 with split_seq = src_len; ld_kv
+   * unused): a head's keys are one contiguous run of src_len * 256 bytes. Zero: [batch * src_len, ld_kv]. */
+  int32_t kv_head_major;
 } ls100_attn_cross_args;
 int ls100_attn_cross(ls100_ctx* ctx, const ls100_attn_cross_args* args, ls100_stream_t stream);
 
@@ -230,6 +237,10 @@ typedef struct {
   int32_t m, n, k;
   void* out; /* fp32 */
   int64_t ldo;
+  /* > 0: head-split output, as ker_arrange_encdec_kv does: row m = b * split_seq + s and column n = h * 64 + d
+   * are stored at out[((b * (N / 64) + h) * split_seq + s) * 64 + d], i.e. fp32 [batch, heads, split_seq, 64]
+   * (N a multiple of 64; ldo unused). 0: row-major [M, ldo]. */
+  int32_t split_seq;
 } ls100_proj_f32_args;
 int ls100_proj_f32(ls100_ctx* ctx, const ls100_proj_f32_args* args, ls100_stream_t stream);
 

@@ -87,13 +87,14 @@ class AttnCrossArgs(C.Structure):
     _fields_ = [("q", C.c_void_p), ("ld_q", C.c_int64), ("s_q", C.c_float), ("bias", C.c_void_p),
                 ("k", C.c_void_p), ("v", C.c_void_p), ("ld_kv", C.c_int64), ("pad_mask", C.c_void_p),
                 ("batch", C.c_int32), ("beam", C.c_int32), ("src_len", C.c_int32), ("heads", C.c_int32),
-                ("amax_out", C.c_float), ("out", C.c_void_p), ("ld_out", C.c_int64)]
+                ("amax_out", C.c_float), ("out", C.c_void_p), ("ld_out", C.c_int64), ("kv_static", C.c_int32),
+                ("kv_head_major", C.c_int32)]
 
 
 class ProjF32Args(C.Structure):
     _fields_ = [("x", C.c_void_p), ("ldx", C.c_int64), ("w", C.c_void_p), ("ldw", C.c_int64), ("s_w", C.c_float),
                 ("bias", C.c_void_p), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("out", C.c_void_p),
-                ("ldo", C.c_int64)]
+                ("ldo", C.c_int64), ("split_seq", C.c_int32)]
 
 
 class BeamTopkArgs(C.Structure):

@@ -214,6 +214,7 @@ class QuantTransformerDecoderLayer : public Layer {
       a.k = hidden_;
       a.out = which == 0 ? enc_k_ : enc_v_;
       a.ldo = hidden_;
+      a.split_seq = src_len_;  // [batch, heads, src_len, 64]: a head's keys are contiguous for the decode steps
       LS_RC(ls100_proj_f32(ctx_->kernels(), &a, ctx_->get_stream()));
     }
   }
@@ -261,6 +262,8 @@ class QuantTransformerDecoderLayer : public Layer {
       a.amax_out = xout_.amax_in;
       a.out = b_->attn_q->value<int8_t>();
       a.ld_out = hidden_;
+      a.kv_head_major = 1;
+      a.kv_static = 1;  // written by the projection, which copies and memsets separate from the decode kernels
       LS_RC(ls100_attn_cross(ctx_->kernels(), &a, ctx_->get_stream()));
     }
     gemm(b_->attn_q, xout_, rows, LS100_OUT_F32, b_->x, Act::None, b_->x, 0.f);

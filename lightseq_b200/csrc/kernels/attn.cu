@@ -16,6 +16,10 @@
 #include "common.cuh"
 #include "ctx.h"
 
+#ifndef LS100_TRACE
+#define LS100_TRACE(slot)
+#endif
+
 namespace ls100 {
 
 constexpr int DH = 64;
@@ -307,139 +311,307 @@ __global__ void __launch_bounds__(128, 7) attn_dec_kernel(const ls100_attn_dec_a
 }
 
 // ------------------------------------------------------------------ attn_cross
-// One CTA per (batch, head), one warp per beam. The head's fp32 keys and values are staged in
-// shared memory once per 128-key tile with coalesced 16-byte loads (all loads in flight
-// together, then shared by the beams), scores use one key per lane, the PV product two head
-// dims per lane; tiles are merged with an online softmax.
-constexpr int XT = 128;      // keys per tile
-constexpr int XKS = DH + 1;  // padded key row (conflict-free when lanes read different rows)
+// Persistent CTAs (three per SM for up to 4 beams) walk the (sentence, head) pairs. The head's fp32 keys and
+// values of a 64-key tile are brought into shared memory by four TMA box copies (K and V, each as two
+// 128-byte-wide halves of the 64 head dims, 128-byte swizzle) issued by one thread into one of two buffers, so
+// the copy of the next pair runs under the arithmetic of this one and costs no registers. When the caller
+// declares the keys and values static (kv_static), the first two copies are issued BEFORE the grid-dependency
+// wait and overlap the tail of the preceding kernel.
+// The arithmetic is bound by shared-memory bandwidth, so every key and value element is read from shared memory
+// ONCE for all beams: each of the four warps owns 16 keys of the tile and keeps one accumulator set per beam.
+// Scores: lane = (key, half of the head dims), 16-byte reads that are conflict-free under the swizzle, the two
+// halves added by one shuffle. PV: two head dims per lane. The warps' partial softmax results (max, sum,
+// weighted values) are merged through shared memory at the end of a pair.
+constexpr int XT = 64;                 // keys per tile
+constexpr int XHALF = XT * 128;        // bytes of one half tile: 64 rows x 128 B
+constexpr int XTILE = 4 * XHALF;       // K lo, K hi, V lo, V hi
+constexpr int XCTAS_PER_SM = 3;
+constexpr int XWARPS = 4;              // 16 keys of a tile each
+constexpr int XQ = 72;                 // floats per q row in shared memory: the two 32-float halves 36 apart,
+                                       // so that the two addresses a warp reads at once fall into different banks
 
-__global__ void __launch_bounds__(256) attn_cross_kernel(const ls100_attn_cross_args a, const float s_out, const float rs_out,
-                                                          const int tr /* tile rows held in shared memory, <= XT */) {
-  extern __shared__ float xs[];
-  pdl_launch_dependents();
-  pdl_wait();
-  float* Ks = xs;                    // [tr][XKS]
-  float* Vs = Ks + tr * XKS;         // [tr][DH]
-  float* qs = Vs + tr * DH;          // [beam][DH]
-  float* ps = qs + a.beam * DH;      // [beam][tr]
+__device__ __forceinline__ void xattn_issue(uint8_t* buf, uint64_t* bar, const CUtensorMap* tm_k, const CUtensorMap* tm_v,
+                                            int unit, int tiles, int heads, int S) {
+  const int item = unit / tiles, t = unit - item * tiles;
+  // token-major: the head is a 256-byte column window of row b * S + s; head-major (heads == 0 here): row item * S + s
+  int x = 0, y = item * S + t * XT;
+  if (heads > 0) {
+    const int b = item / heads, h = item - b * heads;
+    x = h * DH * 4;
+    y = b * S + t * XT;
+  }
+  mbar_expect_tx(bar, XTILE);
+  tma_load_2d(buf, tm_k, bar, x, y);
+  tma_load_2d(buf + XHALF, tm_k, bar, x + 128, y);
+  tma_load_2d(buf + 2 * XHALF, tm_v, bar, x, y);
+  tma_load_2d(buf + 3 * XHALF, tm_v, bar, x + 128, y);
+}
+
+template <int NB>  // beams rounded up to 1, 2, 4 or 8
+__global__ void __launch_bounds__(32 * XWARPS) attn_cross_kernel(const __grid_constant__ CUtensorMap tm_k,
+                                                                 const __grid_constant__ CUtensorMap tm_v,
+                                                                 const ls100_attn_cross_args a, const float s_out,
+                                                                 const float rs_out, int* err) {
+  extern __shared__ uint8_t xs_raw[];
+  uint8_t* xs = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(xs_raw) + 1023) & ~(uintptr_t)1023);
+  float* qs = reinterpret_cast<float*>(xs + 2 * XTILE);  // [NB][XQ]
+  float* ps = qs + NB * XQ;                               // [XWARPS][NB][16]
+  float* mg = ps + XWARPS * NB * 16;                      // [XWARPS][NB][DH + 2]
+  uint64_t* bar = reinterpret_cast<uint64_t*>(mg + XWARPS * NB * (DH + 2));  // [2]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.x, h = blockIdx.y;
-  const int r = b * a.beam + warp;
+  const int key = lane & 15, hf = lane >> 4;
   const int S = a.src_len;
-  {  // q of this beam -> shared memory, dequantised, biased, scaled
-    const int8_t* qp = a.q + (long long)r * a.ld_q + h * DH + lane * 2;
-    const short w = *reinterpret_cast<const short*>(qp);
-    float q0 = __fmul_rn((float)(int8_t)(w & 0xff), a.s_q), q1 = __fmul_rn((float)(int8_t)((w >> 8) & 0xff), a.s_q);
-    if (a.bias) {
-      const float2 bb = __ldg(reinterpret_cast<const float2*>(a.bias + h * DH + lane * 2));
-      q0 = __fadd_rn(q0, bb.x);
-      q1 = __fadd_rn(q1, bb.y);
+  const int tiles = (S + XT - 1) / XT;
+  const int items = a.batch * a.heads;
+  const int tm_heads = a.kv_head_major ? 0 : a.heads;
+  // this CTA's units: (item, tile) for item = blockIdx.x, blockIdx.x + gridDim.x, ...
+  const int my_items = (items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int my_units = my_items * tiles;
+  auto unit_global = [&](int u) {  // my u-th unit -> flat (item * tiles + tile)
+    const int it = u / tiles;
+    return ((int)blockIdx.x + it * (int)gridDim.x) * tiles + (u - it * tiles);
+  };
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    fence_barrier_init();
+    if (a.kv_static) {
+      if (my_units > 0) xattn_issue(xs, &bar[0], &tm_k, &tm_v, unit_global(0), tiles, tm_heads, S);
+      if (my_units > 1) xattn_issue(xs + XTILE, &bar[1], &tm_k, &tm_v, unit_global(1), tiles, tm_heads, S);
     }
-    qs[warp * DH + lane * 2] = __fmul_rn(q0, 0.125f);
-    qs[warp * DH + lane * 2 + 1] = __fmul_rn(q1, 0.125f);
   }
-  const float* kb = reinterpret_cast<const float*>(a.k) + (long long)b * S * a.ld_kv + h * DH;
-  const float* vb = reinterpret_cast<const float*>(a.v) + (long long)b * S * a.ld_kv + h * DH;
-  const uint8_t* pm = a.pad_mask ? a.pad_mask + (long long)b * S : nullptr;
-  float m = -INFINITY, l = 0.f, acc0 = 0.f, acc1 = 0.f;
-  for (int t0 = 0; t0 < S; t0 += tr) {
-    const int ns = min(tr, S - t0);
-    __syncthreads();
-    for (int i0 = threadIdx.x; i0 < ns * 16; i0 += 4 * blockDim.x) {
-      float4 k4[4], v4[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {  // 8 x 16-byte loads in flight per thread before any store
-        const int i = i0 + u * blockDim.x;
-        if (i < ns * 16) {
-          const int row = i >> 4, c4 = (i & 15) * 4;
-          k4[u] = *reinterpret_cast<const float4*>(kb + (long long)(t0 + row) * a.ld_kv + c4);
-          v4[u] = *reinterpret_cast<const float4*>(vb + (long long)(t0 + row) * a.ld_kv + c4);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = i0 + u * blockDim.x;
-        if (i < ns * 16) {
-          const int row = i >> 4, c4 = (i & 15) * 4;
-          float* kd = Ks + row * XKS + c4;
-          kd[0] = k4[u].x;
-          kd[1] = k4[u].y;
-          kd[2] = k4[u].z;
-          kd[3] = k4[u].w;
-          *reinterpret_cast<float4*>(Vs + row * DH + c4) = v4[u];
-        }
-      }
-    }
-    __syncthreads();
-    // scores: lane handles keys lane, lane+32, ...
-    float sc[XT / 32];
-    float tmax = -INFINITY;
-#pragma unroll
-    for (int u = 0; u < XT / 32; ++u) {
-      const int j = u * 32 + lane;
-      float sv = -INFINITY;
-      if (j < ns && !(pm && pm[t0 + j])) {
-        sv = 0.f;
-        const float* kr = Ks + j * XKS;
-        const float* qr = qs + warp * DH;
-#pragma unroll
-        for (int d = 0; d < DH; d += 4) {
-          const float4 q4 = *reinterpret_cast<const float4*>(qr + d);
-          sv = fmaf(q4.x, kr[d], sv);
-          sv = fmaf(q4.y, kr[d + 1], sv);
-          sv = fmaf(q4.z, kr[d + 2], sv);
-          sv = fmaf(q4.w, kr[d + 3], sv);
-        }
-      }
-      sc[u] = sv;
-      tmax = fmaxf(tmax, sv);
-    }
-    tmax = warp_max(tmax);
-    if (tmax == -INFINITY) continue;  // whole tile masked (uniform across the warp)
-    const float m_new = fmaxf(m, tmax);
-    const float resc = __expf(m - m_new);  // 0 when m = -inf
-    l *= resc;
-    acc0 *= resc;
-    acc1 *= resc;
-    m = m_new;
-    float lsum = 0.f;
-#pragma unroll
-    for (int u = 0; u < XT / 32; ++u) {
-      const int j = u * 32 + lane;
-      const float e = (sc[u] == -INFINITY) ? 0.f : expf(sc[u] - m);
-      if (j < tr) ps[warp * tr + j] = e;
-      lsum += e;
-    }
-    l += warp_sum(lsum);
-    __syncwarp();
-    const float* pr = ps + warp * tr;
-    for (int j = 0; j < ns; ++j) {
-      const float w = pr[j];
-      const float2 v2 = *reinterpret_cast<const float2*>(Vs + j * DH + lane * 2);
-      acc0 = fmaf(w, v2.x, acc0);
-      acc1 = fmaf(w, v2.y, acc1);
-    }
-    __syncwarp();
+  LS100_TRACE(0);
+  pdl_wait();
+  LS100_TRACE(1);
+  if (threadIdx.x == 0 && !a.kv_static) {
+    if (my_units > 0) xattn_issue(xs, &bar[0], &tm_k, &tm_v, unit_global(0), tiles, tm_heads, S);
+    if (my_units > 1) xattn_issue(xs + XTILE, &bar[1], &tm_k, &tm_v, unit_global(1), tiles, tm_heads, S);
   }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
-  const float o0 = quant_s(clipf(acc0 * inv, a.amax_out), s_out, rs_out);
-  const float o1 = quant_s(clipf(acc1 * inv, a.amax_out), s_out, rs_out);
-  const uint32_t pk = pack_i8x4(o0, o1, 0.f, 0.f);
-  *reinterpret_cast<unsigned short*>(a.out + (long long)r * a.ld_out + h * DH + lane * 2) = (unsigned short)(pk & 0xffff);
+  __syncthreads();  // barrier initialisation visible to every waiter
+
+  // q of a pair, fetched one pair ahead as RAW values (the int8 pair and the bias pair): the conversion happens
+  // when the values are stored to shared memory, so that no instruction waits for these loads before then.
+  // Warp w serves beams w and w + 4.
+  short qraw[2] = {0, 0};
+  float2 qbias[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+  auto load_q = [&](int item) {
+    const int b = item / a.heads, h = item - b * a.heads;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int bm = warp + i * XWARPS;
+      if (bm < NB && bm < a.beam) {
+        qraw[i] = *reinterpret_cast<const short*>(a.q + (long long)(b * a.beam + bm) * a.ld_q + h * DH + lane * 2);
+        if (a.bias) qbias[i] = __ldg(reinterpret_cast<const float2*>(a.bias + h * DH + lane * 2));
+      }
+    }
+  };
+  // pad-mask byte of this lane's key, likewise fetched one unit ahead
+  auto load_pad = [&](int u) -> int {
+    if (!a.pad_mask || u >= my_units) return 0;
+    const int it = u / tiles, t = u - it * tiles;
+    const int item = (int)blockIdx.x + it * (int)gridDim.x;
+    const int k = t * XT + warp * 16 + key;
+    return k < S ? (int)a.pad_mask[(long long)(item / a.heads) * S + k] : 1;
+  };
+  if (my_items > 0) load_q(blockIdx.x);
+  int pad_next = load_pad(0);
+
+  float m[NB], l[NB], acc[NB][2];
+  bool dead = false;  // a copy never landed: keep meeting the CTA barriers, do no work
+  for (int u = 0; u < my_units; ++u) {
+    const int it = u / tiles, t = u - it * tiles;
+    const int item = (int)blockIdx.x + it * (int)gridDim.x;
+    const int b = item / a.heads, h = item - b * a.heads;
+    const int t0 = t * XT + warp * 16;       // first key of this warp in the tile
+    const int ns = max(0, min(16, S - t0));  // its keys that exist
+    const uint8_t* buf = xs + (u & 1) * XTILE;
+    if (t == 0) {
+      if (u > 0) __syncthreads();  // every warp has finished with the previous pair's q and merge area
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int bm = warp + i * XWARPS;
+        if (bm < NB) {  // dims 2*lane, 2*lane+1 live in half (lane >> 4)
+          float q0 = 0.f, q1 = 0.f;
+          if (bm < a.beam) {
+            q0 = __fadd_rn(__fmul_rn((float)(int8_t)(qraw[i] & 0xff), a.s_q), qbias[i].x);
+            q1 = __fadd_rn(__fmul_rn((float)(int8_t)((qraw[i] >> 8) & 0xff), a.s_q), qbias[i].y);
+          }
+          float* qd = qs + bm * XQ + (lane >> 4) * 36 + ((lane * 2) & 31);
+          qd[0] = __fmul_rn(q0, 0.125f);
+          qd[1] = __fmul_rn(q1, 0.125f);
+        }
+      }
+      if (it + 1 < my_items) load_q(item + (int)gridDim.x);
+      __syncthreads();
+#pragma unroll
+      for (int bm = 0; bm < NB; ++bm) {
+        m[bm] = -INFINITY;
+        l[bm] = 0.f;
+        acc[bm][0] = 0.f;
+        acc[bm][1] = 0.f;
+      }
+    }
+    LS100_TRACE(2 + 5 * (u < 2 ? u : 2));
+    if (!dead) {
+      const bool ok = mbar_wait(&bar[u & 1], (uint32_t)(u >> 1) & 1u);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) atomicExch(err, (int)LS100_ERR_TIMEOUT);
+        dead = true;
+      }
+    }
+    LS100_TRACE(3 + 5 * (u < 2 ? u : 2));
+    const int pad_now = pad_next;
+    pad_next = load_pad(u + 1);
+    if (!dead && ns > 0) {
+      const int j = warp * 16 + key;  // row of the tile
+      const bool valid = key < ns && !pad_now;
+      // scores of key `key` against every beam: this lane's half of the head dims, then the other half by shuffle
+      float s[NB][4];
+#pragma unroll
+      for (int bm = 0; bm < NB; ++bm) s[bm][0] = s[bm][1] = s[bm][2] = s[bm][3] = 0.f;
+      {
+        const uint8_t* kr = buf + hf * XHALF + j * 128;
+        const float* qr = qs + hf * 36;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kr + ((c ^ (j & 7)) << 4));
+#pragma unroll
+          for (int bm = 0; bm < NB; ++bm) {
+            const float4 q4 = *reinterpret_cast<const float4*>(qr + bm * XQ + c * 4);
+            s[bm][0] = fmaf(q4.x, k4.x, s[bm][0]);
+            s[bm][1] = fmaf(q4.y, k4.y, s[bm][1]);
+            s[bm][2] = fmaf(q4.z, k4.z, s[bm][2]);
+            s[bm][3] = fmaf(q4.w, k4.w, s[bm][3]);
+          }
+        }
+      }
+      float* pr = ps + warp * NB * 16;
+      // partial softmax of the 16 keys for every beam, written stage by stage over the beams so that the
+      // shuffle chains of different beams overlap. Lanes 16-31 mirror lanes 0-15 after the first exchange.
+      float sv[NB], tmax[NB], ex[NB], es[NB];
+#pragma unroll
+      for (int bm = 0; bm < NB; ++bm) sv[bm] = (s[bm][0] + s[bm][1]) + (s[bm][2] + s[bm][3]);
+#pragma unroll
+      for (int bm = 0; bm < NB; ++bm) sv[bm] += __shfl_xor_sync(0xffffffffu, sv[bm], 16);
+#pragma unroll
+      for (int bm = 0; bm < NB; ++bm) tmax[bm] = sv[bm] = valid ? sv[bm] : -INFINITY;
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1)
+#pragma unroll
+        for (int bm = 0; bm < NB; ++bm) tmax[bm] = fmaxf(tmax[bm], __shfl_xor_sync(0xffffffffu, tmax[bm], o));
+      bool any = false;
+#pragma unroll
+      for (int bm = 0; bm < NB; ++bm) {
+        const float m_new = fmaxf(m[bm], tmax[bm]);
+        const float resc = (m[bm] == -INFINITY) ? 0.f : __expf(m[bm] - m_new);
+        ex[bm] = es[bm] = (sv[bm] == -INFINITY) ? 0.f : expf(sv[bm] - m_new);
+        l[bm] *= resc;
+        acc[bm][0] *= resc;
+        acc[bm][1] *= resc;
+        m[bm] = m_new;
+        any = any || (tmax[bm] != -INFINITY);
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1)
+#pragma unroll
+        for (int bm = 0; bm < NB; ++bm) es[bm] += __shfl_xor_sync(0xffffffffu, es[bm], o);
+#pragma unroll
+      for (int bm = 0; bm < NB; ++bm) {
+        l[bm] += es[bm];
+        if (hf == 0) pr[bm * 16 + key] = ex[bm];
+      }
+      __syncwarp();
+      LS100_TRACE(4 + 5 * (u < 2 ? u : 2));
+      if (any) {  // otherwise all of this warp's keys are masked (uniform across the warp)
+        // dims 2*lane, 2*lane+1: half (lane >> 4), 16-byte chunk ((lane & 15) >> 1), 8-byte offset (lane & 1)
+        const uint8_t* vb = buf + (2 + (lane >> 4)) * XHALF + (lane & 1) * 8 + warp * 16 * 128;
+        const int vc = (lane & 15) >> 1;
+        for (int jj = 0; jj < ns; jj += 4) {  // the probabilities beyond ns are zero
+          float2 v[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            v[i] = *reinterpret_cast<const float2*>(vb + (jj + i) * 128 + ((vc ^ ((jj + i) & 7)) << 4));
+#pragma unroll
+          for (int bm = 0; bm < NB; ++bm) {
+            const float4 w4 = *reinterpret_cast<const float4*>(pr + bm * 16 + jj);
+            acc[bm][0] = fmaf(w4.x, v[0].x, acc[bm][0]);
+            acc[bm][1] = fmaf(w4.x, v[0].y, acc[bm][1]);
+            acc[bm][0] = fmaf(w4.y, v[1].x, acc[bm][0]);
+            acc[bm][1] = fmaf(w4.y, v[1].y, acc[bm][1]);
+            acc[bm][0] = fmaf(w4.z, v[2].x, acc[bm][0]);
+            acc[bm][1] = fmaf(w4.z, v[2].y, acc[bm][1]);
+            acc[bm][0] = fmaf(w4.w, v[3].x, acc[bm][0]);
+            acc[bm][1] = fmaf(w4.w, v[3].y, acc[bm][1]);
+          }
+        }
+      }
+      __syncwarp();
+    }
+    LS100_TRACE(5 + 5 * (u < 2 ? u : 2));
+    if (t == tiles - 1) {  // merge the four key groups of each beam and write the rows
+#pragma unroll
+      for (int bm = 0; bm < NB; ++bm) {
+        float* mp = mg + (warp * NB + bm) * (DH + 2);
+        mp[lane * 2] = acc[bm][0];
+        mp[lane * 2 + 1] = acc[bm][1];
+        if (lane == 0) {
+          mp[DH] = m[bm];
+          mp[DH + 1] = l[bm];
+        }
+      }
+      __syncthreads();
+      for (int bm = warp; bm < a.beam; bm += XWARPS) {
+        if (dead) break;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < XWARPS; ++w) mm = fmaxf(mm, mg[(w * NB + bm) * (DH + 2) + DH]);
+        float lt = 0.f, o0 = 0.f, o1 = 0.f;
+        if (mm != -INFINITY) {
+#pragma unroll
+          for (int w = 0; w < XWARPS; ++w) {
+            const float* mp = mg + (w * NB + bm) * (DH + 2);
+            const float f = (mp[DH] == -INFINITY) ? 0.f : __expf(mp[DH] - mm);
+            lt = fmaf(mp[DH + 1], f, lt);
+            o0 = fmaf(mp[lane * 2], f, o0);
+            o1 = fmaf(mp[lane * 2 + 1], f, o1);
+          }
+        }
+        const float inv = lt > 0.f ? 1.f / lt : 0.f;
+        const uint32_t pk = pack_i8x4(quant_s(clipf(o0 * inv, a.amax_out), s_out, rs_out),
+                                      quant_s(clipf(o1 * inv, a.amax_out), s_out, rs_out), 0.f, 0.f);
+        *reinterpret_cast<unsigned short*>(a.out + (long long)(b * a.beam + bm) * a.ld_out + h * DH + lane * 2) =
+            (unsigned short)(pk & 0xffff);
+      }
+    }
+    LS100_TRACE(6 + 5 * (u < 2 ? u : 2));
+    if (u + 2 < my_units) {  // refill this buffer once every warp has finished with it
+      __syncthreads();
+      if (threadIdx.x == 0)
+        xattn_issue(xs + (u & 1) * XTILE, &bar[u & 1], &tm_k, &tm_v, unit_global(u + 2), tiles, tm_heads, S);
+    }
+  }
+}
+
+// two tiles + q, probabilities and merge area + two barriers + slack to align the tiles to the swizzle period
+static size_t attn_cross_smem(int nb) {
+  return 2 * XTILE + (size_t)(nb * XQ + XWARPS * nb * 16 + XWARPS * nb * (DH + 2)) * sizeof(float) + 16 + 1024;
 }
 
 }  // namespace ls100
 
 using namespace ls100;
 
-// Opts the cross-attention kernel into its largest shared-memory tile on the current device
+// Opts the cross-attention kernel into its shared-memory size (two K/V tiles) on the current device
 // (called once from ls100_ctx_create, never inside a stream capture).
 int ls100_attn_init_device() {
-  const size_t smem = (size_t)(XT * XKS + XT * DH + 8 * DH + 8 * XT) * sizeof(float);
-  return cudaFuncSetAttribute(attn_cross_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess
-             ? LS100_OK
-             : LS100_ERR_CUDA;
+  bool ok = cudaFuncSetAttribute(attn_cross_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_cross_smem(1)) == cudaSuccess;
+  ok = ok && cudaFuncSetAttribute(attn_cross_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_cross_smem(2)) == cudaSuccess;
+  ok = ok && cudaFuncSetAttribute(attn_cross_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_cross_smem(4)) == cudaSuccess;
+  ok = ok && cudaFuncSetAttribute(attn_cross_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_cross_smem(8)) == cudaSuccess;
+  return ok ? LS100_OK : LS100_ERR_CUDA;
 }
 
 extern "C" int ls100_attn_self(ls100_ctx* ctx, const ls100_attn_self_args* a, ls100_stream_t stream_) {
@@ -478,17 +650,31 @@ extern "C" int ls100_attn_cross(ls100_ctx* ctx, const ls100_attn_cross_args* a, 
   if (!ctx || !a || !a->q || !a->k || !a->v || !a->out) return LS100_ERR_BAD_ARG;
   if (a->batch <= 0 || a->beam <= 0 || a->src_len <= 0 || a->heads <= 0 || !(a->amax_out > 0.f)) return LS100_ERR_BAD_ARG;
   if (a->beam > 8 || a->src_len > 4096 || a->heads > 65535) return LS100_ERR_UNSUPPORTED;
-  if ((((uintptr_t)a->q) & 1) || (a->ld_q & 1) || (((uintptr_t)a->k) & 15) || (((uintptr_t)a->v) & 15) || (a->ld_kv & 3) ||
+  if ((((uintptr_t)a->q) & 1) || (a->ld_q & 1) || (((uintptr_t)a->k) & 15) || (((uintptr_t)a->v) & 15) || (!a->kv_head_major && (a->ld_kv & 3)) ||
       (((uintptr_t)a->out) & 1) || (a->ld_out & 1) || (a->bias && (((uintptr_t)a->bias) & 7)))
     return LS100_ERR_ALIGN;
-  dim3 grid(a->batch, a->heads);
-  // 32-key tiles keep a CTA at ~17 KB of shared memory, so that every (sentence, head) CTA of a large batch is
-  // resident at once and the tile loads of one CTA overlap the arithmetic of the others
-  const int tr = 32;
-  const size_t smem = (size_t)(tr * XKS + tr * DH + a->beam * DH + a->beam * tr) * sizeof(float);
+  if (!a->kv_head_major && a->ld_kv < a->heads * DH) return LS100_ERR_BAD_ARG;
+  CUtensorMap tk, tv;  // byte views of the fp32 matrices: 128-byte x 64-row boxes
+  uint64_t rows = (uint64_t)a->batch * a->src_len, cols = (uint64_t)a->heads * DH * 4, pitch = (uint64_t)a->ld_kv * 4;
+  if (a->kv_head_major) {
+    rows *= a->heads;
+    cols = pitch = DH * 4;
+  }
+  int rc = ls100_get_tmap_u8(ctx, a->k, rows, cols, pitch, XT, 128, &tk);
+  if (rc) return rc;
+  rc = ls100_get_tmap_u8(ctx, a->v, rows, cols, pitch, XT, 128, &tv);
+  if (rc) return rc;
+  const long long items = (long long)a->batch * a->heads;
+  if (items * ((a->src_len + XT - 1) / XT) > 0x3fffffffLL) return LS100_ERR_UNSUPPORTED;
+  const long long slots = (long long)XCTAS_PER_SM * ctx->sm_count;
+  dim3 grid((unsigned)(items < slots ? items : slots));
   const float so = a->amax_out / 127.0f;
-  return ls100_launch(attn_cross_kernel, grid, dim3(32 * a->beam), smem, (cudaStream_t)stream_, *a, so, 1.0f / so, tr) ==
-                 cudaSuccess
-             ? LS100_OK
-             : LS100_ERR_CUDA;
+  const cudaStream_t st = (cudaStream_t)stream_;
+  const dim3 block(32 * XWARPS);
+  cudaError_t e;
+  if (a->beam == 1) e = ls100_launch(attn_cross_kernel<1>, grid, block, attn_cross_smem(1), st, tk, tv, *a, so, 1.0f / so, ctx->d_err);
+  else if (a->beam == 2) e = ls100_launch(attn_cross_kernel<2>, grid, block, attn_cross_smem(2), st, tk, tv, *a, so, 1.0f / so, ctx->d_err);
+  else if (a->beam <= 4) e = ls100_launch(attn_cross_kernel<4>, grid, block, attn_cross_smem(4), st, tk, tv, *a, so, 1.0f / so, ctx->d_err);
+  else e = ls100_launch(attn_cross_kernel<8>, grid, block, attn_cross_smem(8), st, tk, tv, *a, so, 1.0f / so, ctx->d_err);
+  return e == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }

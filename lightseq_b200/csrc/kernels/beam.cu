@@ -1,8 +1,9 @@
 // Beam-search step on the device, no host round trip:
-//   beam_topk   one warp per (batch, beam) row: the row of int8 logits is streamed ONCE with
-//               16-byte loads; a 256-entry exp table + float64 per-lane sums give the
-//               log-sum-exp, per-lane register lists + a warp merge give the exact top-k by
-//               (logit desc, token asc), emitted with length-normalised scores.
+//   beam_topk   one CTA of eight warps per (batch, beam) row: the row of int8 logits is streamed ONCE
+//               with 16-byte loads, each warp taking every eighth 512-byte chunk; a 256-entry exp
+//               table + float64 sums give the log-sum-exp, a warp-wide threshold + candidate buffer
+//               per warp and a final merge give the exact top-k by (logit desc, token asc), emitted
+//               with length-normalised scores.
 //   beam_update one CTA per batch element: merges beam*beam candidates, rewrites the
 //               token history and the KV-cache ancestry table in place (staged through
 //               shared memory), updates probabilities/scores, counts finished beams and
@@ -26,7 +27,9 @@ constexpr float LOGIT_THRESH_MIN = -64.f;   // lightseq/inference/kernels/transf
 constexpr float MIN_LOG_PROB = -2000.f;     // transformerKernels.h:12
 constexpr int MAX_BEAM = 8;
 
-// One warp per row, four rows per CTA, ONE pass over the row with 16-byte loads:
+// One CTA per row, eight warps interleaved over the row's 512-byte chunks (a single warp per row leaves the
+// machine idle and is bound by the latency of its one chunk in flight), ONE pass with 16-byte loads, two
+// chunks per warp in flight. Per warp:
 //  * sum of exp: every byte indexes a 256-entry table exp((q - 127) * s) in shared memory;
 //    four independent fp32 partial sums per lane, combined in float64 at the end;
 //  * top-k: the warp keeps ONE threshold (the k-th best value seen so far by the whole
@@ -39,7 +42,7 @@ constexpr int MAX_BEAM = 8;
 // log-sum-exp is taken relative to the largest representable logit (127 * s) instead of the
 // row maximum; the reference's clamp of exp arguments at -64 can then never trigger, which
 // the launcher enforces by requiring 254 * s <= 64.
-constexpr int TOPK_WARPS = 4;
+constexpr int TOPK_WARPS = 8;
 constexpr int TOPK_BUF = 512 + 64;  // one chunk can add 512 candidates while the threshold is still open
 
 __device__ __forceinline__ int4 load_row16(const int8_t* lp, int off, int vocab) {
@@ -93,6 +96,8 @@ __device__ __forceinline__ int topk_flush(unsigned* buf, int n, int K, int lane,
 __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_beam_topk_args a) {
   __shared__ float s_lut[256];  // index = byte pattern (two's complement), value = exp((q - 127) * s); 0 for -128
   __shared__ unsigned s_buf[TOPK_WARPS][TOPK_BUF];
+  __shared__ double s_sum[TOPK_WARPS];
+  __shared__ int s_kept[TOPK_WARPS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
   for (int i = threadIdx.x; i < 256; i += blockDim.x) {  // the table depends on the scale only: built before the wait
@@ -101,16 +106,15 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
   }
   pdl_wait();
   __syncthreads();
-  const int row = blockIdx.x * TOPK_WARPS + warp;
-  if (row >= a.batch * a.beam) return;
+  const int row = blockIdx.x;
   const int step = *a.step_ptr;
   const int K = a.beam;
   float* cs = a.cand_score + (long long)row * K;
   int32_t* ct = a.cand_token + (long long)row * K;
-  if (step != 0 && a.alive[(long long)row * a.max_step + step] == a.end_id) {
-    if (lane < K) {
-      cs[lane] = (lane == 0) ? a.seq_score[row] : -FLT_MAX;
-      ct[lane] = a.end_id;
+  if (step != 0 && a.alive[(long long)row * a.max_step + step] == a.end_id) {  // uniform over the CTA
+    if (threadIdx.x < K) {
+      cs[threadIdx.x] = (threadIdx.x == 0) ? a.seq_score[row] : -FLT_MAX;
+      ct[threadIdx.x] = a.end_id;
     }
     return;
   }
@@ -121,13 +125,17 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
   unsigned thr4 = 0x80808080u;
   float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
   const int n_chunks = (a.vocab + 511) / 512;
-  int4 vnext = make_int4((int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080);
-  if (lane * 16 < a.vocab) vnext = load_row16(lp, lane * 16, a.vocab);
-  for (int ch = 0; ch < n_chunks; ++ch) {
+  const int4 none = make_int4((int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080);
+  // this warp's chunks: warp, warp + 8, ...; the next two are always in flight
+  int4 v1 = none, v2 = none;
+  if (warp * 512 + lane * 16 < a.vocab) v1 = load_row16(lp, warp * 512 + lane * 16, a.vocab);
+  if ((warp + TOPK_WARPS) * 512 + lane * 16 < a.vocab) v2 = load_row16(lp, (warp + TOPK_WARPS) * 512 + lane * 16, a.vocab);
+  for (int ch = warp; ch < n_chunks; ch += TOPK_WARPS) {
     const int off = ch * 512 + lane * 16;
-    const int4 v = vnext;
-    vnext = make_int4((int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080);
-    if (off + 512 < a.vocab) vnext = load_row16(lp, off + 512, a.vocab);  // next chunk in flight
+    const int4 v = v1;
+    v1 = v2;
+    v2 = none;
+    if (off + 2 * TOPK_WARPS * 512 < a.vocab) v2 = load_row16(lp, off + 2 * TOPK_WARPS * 512, a.vocab);
     const unsigned w4[4] = {(unsigned)v.x, (unsigned)v.y, (unsigned)v.z, (unsigned)v.w};
     unsigned hit = 0;
 #pragma unroll
@@ -174,10 +182,27 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
   double sum = ((double)ps0 + (double)ps1) + ((double)ps2 + (double)ps3);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane == 0) {
+    s_sum[warp] = sum;
+    s_kept[warp] = n_buf;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  // merge: the K best of the warps' K best (keys order by value, then lower token), sums in warp order
+  int n_all = n_buf;  // warp 0's own list already sits at buf[0 .. n_buf)
+  for (int w = 1; w < TOPK_WARPS; ++w) {
+    const int nk = s_kept[w];
+    if (lane < nk) buf[n_all + lane] = s_buf[w][lane];
+    n_all += nk;
+  }
+  __syncwarp();
+  topk_flush(buf, n_all, K, lane, &n_buf);
+  double tot = 0.0;
+  for (int w = 0; w < TOPK_WARPS; ++w) tot += s_sum[w];
   if (lane < K) {
     // log-sum-exp relative to 127*s:  lse = log(sum) + 127*s;  base = prefix - lse
     const float ref = __fmul_rn(127.f, a.s_logits);
-    const float lse = __fadd_rn(logf((float)sum), ref);
+    const float lse = __fadd_rn(logf((float)tot), ref);
     const float base = __fsub_rn(a.seq_probs[row], lse);
     const float ln = a.length_norm[step];
     if (lane >= n_buf) {
@@ -296,7 +321,7 @@ extern "C" int ls100_beam_topk(ls100_ctx* ctx, const ls100_beam_topk_args* a, ls
   if (254.f * a->s_logits > 64.f) return LS100_ERR_UNSUPPORTED;  // the -64 clamp of the reference would matter
   if ((((uintptr_t)a->logits) & 15) || (a->ld_logits & 15)) return LS100_ERR_ALIGN;
   const int rows = a->batch * a->beam;
-  return ls100_launch(beam_topk_kernel, dim3((rows + TOPK_WARPS - 1) / TOPK_WARPS), dim3(32 * TOPK_WARPS), 0,
+  return ls100_launch(beam_topk_kernel, dim3(rows), dim3(32 * TOPK_WARPS), 0,
                       (cudaStream_t)stream_, *a) == cudaSuccess
              ? LS100_OK
              : LS100_ERR_CUDA;

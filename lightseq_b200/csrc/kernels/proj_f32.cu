@@ -74,7 +74,12 @@ __global__ void __launch_bounds__(256) proj_f32_kernel(const ls100_proj_f32_args
       if (n >= a.n) continue;
       float v = __fmul_rn(acc[i][j], a.s_w);
       if (a.bias) v = __fadd_rn(v, __ldg(a.bias + n));
-      out[(long long)m * a.ldo + n] = v;
+      if (a.split_seq > 0) {  // [batch, heads, split_seq, 64]
+        const int b = m / a.split_seq, sq = m - b * a.split_seq;
+        out[(((long long)b * (a.n >> 6) + (n >> 6)) * a.split_seq + sq) * 64 + (n & 63)] = v;
+      } else {
+        out[(long long)m * a.ldo + n] = v;
+      }
     }
   }
 }
@@ -85,6 +90,7 @@ extern "C" int ls100_proj_f32(ls100_ctx* ctx, const ls100_proj_f32_args* a, ls10
   if (!ctx || !a || !a->x || !a->w || !a->out) return LS100_ERR_BAD_ARG;
   if (a->m <= 0 || a->n <= 0 || a->k <= 0 || !(a->s_w > 0.f)) return LS100_ERR_BAD_ARG;
   if ((((uintptr_t)a->x) & 15) || (a->ldx & 3)) return LS100_ERR_ALIGN;
+  if (a->split_seq < 0 || (a->split_seq > 0 && (a->n & 63))) return LS100_ERR_BAD_ARG;
   dim3 grid((a->n + 63) / 64, (a->m + 63) / 64);
   return ls100_launch(ls100::proj_f32_kernel, grid, dim3(256), 0, (cudaStream_t)stream_, *a) == cudaSuccess
              ? LS100_OK

@@ -321,8 +321,12 @@ def test_attn_dec_int8_cache_with_beam_ancestry():
     print("attn_dec worst one-step rate", worst)
 
 
-def test_attn_cross_matches_oracle():
-    B, K, S, heads = 5, 4, 37, 8
+@pytest.mark.parametrize("B,K,S,heads,kv_static,head_major",
+                         [(5, 4, 37, 8, 0, 0), (5, 4, 37, 8, 1, 1), (3, 2, 150, 4, 1, 0), (70, 4, 64, 8, 1, 1),
+                          (2, 1, 1, 2, 0, 1), (9, 8, 65, 16, 1, 1), (3, 2, 150, 4, 0, 1)])
+def test_attn_cross_matches_oracle(B, K, S, heads, kv_static, head_major):
+    """One and several 64-key tiles per (sentence, head), more pairs than resident CTAs (70 x 8 > 3 x SMs), the
+    keys fetched before and after the grid dependency, 1 to 8 beams."""
     H = heads * 64
     r = rng(23)
     q_q = r.integers(-127, 128, size=(B * K, H), dtype=np.int8)
@@ -337,10 +341,16 @@ def test_attn_cross_matches_oracle():
                           np.repeat(pad, K, 0), 64 ** -0.5)[:, 0]
     amax = float(F32(4 * a.std()))
     ref, _ = oq.quantize(a, amax)
-    dq, db, dk, dv, dp = dev(q_q), dev(bias), dev(k.reshape(B * S, H)), dev(v.reshape(B * S, H)), dev(pad.astype(np.uint8))
+    if head_major:  # [batch, heads, src_len, 64]
+        kd = np.ascontiguousarray(k.reshape(B, S, heads, 64).transpose(0, 2, 1, 3))
+        vd = np.ascontiguousarray(v.reshape(B, S, heads, 64).transpose(0, 2, 1, 3))
+    else:
+        kd, vd = k.reshape(B * S, H), v.reshape(B * S, H)
+    dq, db, dk, dv, dp = dev(q_q), dev(bias), dev(kd), dev(vd), dev(pad.astype(np.uint8))
     out = empty((B * K, H), torch.int8)
     args = L.AttnCrossArgs(q=ptr(dq), ld_q=H, s_q=float(s_q), bias=ptr(db), k=ptr(dk), v=ptr(dv), ld_kv=H,
-                           pad_mask=ptr(dp), batch=B, beam=K, src_len=S, heads=heads, amax_out=amax, out=ptr(out), ld_out=H)
+                           pad_mask=ptr(dp), batch=B, beam=K, src_len=S, heads=heads, amax_out=amax, out=ptr(out), ld_out=H,
+                           kv_static=kv_static, kv_head_major=head_major)
     L.call("ls100_attn_cross", ctx(), args)
     sync_check()
     _int8_close(out.cpu().numpy(), ref, 5e-3)
@@ -363,6 +373,14 @@ def test_proj_f32_weight_only_quant():
     d = np.abs(out.cpu().numpy() - ref)
     # fp32 accumulation in a different order than the oracle's float64 sum
     assert d.max() <= np.abs(ref).max() * 1e-5
+    # head-split output [batch, heads, seq, 64]: the same numbers, rearranged
+    out2 = empty((9, n // 64, 37, 64), torch.float32)
+    args = L.ProjF32Args(x=ptr(dx), ldx=k, w=ptr(dw), ldw=k, s_w=float(s_w), bias=ptr(db), m=m, n=n, k=k, out=ptr(out2), ldo=0,
+                         split_seq=37)
+    L.call("ls100_proj_f32", ctx(), args)
+    sync_check()
+    want = out.cpu().numpy().reshape(9, 37, n // 64, 64).transpose(0, 2, 1, 3)
+    assert np.array_equal(out2.cpu().numpy(), want)
 
 
 # ----------------------------------------------------------------------------- beam search
