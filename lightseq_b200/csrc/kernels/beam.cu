@@ -98,8 +98,10 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
   __shared__ unsigned s_buf[TOPK_WARPS][TOPK_BUF];
   __shared__ double s_sum[TOPK_WARPS];
   __shared__ int s_kept[TOPK_WARPS];
+  __shared__ int s_thr;  // highest k-th-best value any warp of the row has established so far
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
+  if (threadIdx.x == 0) s_thr = -128;
   for (int i = threadIdx.x; i < 256; i += blockDim.x) {  // the table depends on the scale only: built before the wait
     const int q = (int)(int8_t)i;
     s_lut[i] = (q == -128) ? 0.f : expf(__fmul_rn((float)(q - 127), a.s_logits));
@@ -122,7 +124,7 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
   unsigned* buf = s_buf[warp];
   int n_buf = 0;   // entries in buf (the first ones are the current best list)
   int thr = -128;  // bytes strictly above thr are candidates
-  unsigned thr4 = 0x80808080u;
+  unsigned add7 = 0x01010101u * 127u;
   float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
   const int n_chunks = (a.vocab + 511) / 512;
   const int4 none = make_int4((int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080);
@@ -137,6 +139,17 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
     v2 = none;
     if (off + 2 * TOPK_WARPS * 512 < a.vocab) v2 = load_row16(lp, off + 2 * TOPK_WARPS * 512, a.vocab);
     const unsigned w4[4] = {(unsigned)v.x, (unsigned)v.y, (unsigned)v.z, (unsigned)v.w};
+    {  // the other warps of the row raise the bar too: nothing below any warp's k-th best can be in the row's top k
+      const int shared_thr = *((volatile int*)&s_thr);
+      if (shared_thr > thr) {
+        thr = shared_thr;
+        add7 = 0x01010101u * (unsigned)(127 - max(thr, 0));
+      }
+    }
+    // Bytes above the threshold. With thr >= 0 only bytes with a clear sign bit qualify and, for those, adding
+    // (127 - thr) to the low seven bits carries into bit 7 exactly when the byte exceeds thr (no carry crosses a
+    // byte): three logic/add operations per word. While thr < 0 every word goes to the exact path below.
+    unsigned gt[4];
     unsigned hit = 0;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
@@ -144,15 +157,20 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
       ps1 += s_lut[(w4[w] >> 8) & 0xff];
       ps2 += s_lut[(w4[w] >> 16) & 0xff];
       ps3 += s_lut[w4[w] >> 24];
-      hit |= __vcmpgts4(w4[w], thr4);
+      gt[w] = ((w4[w] & 0x7f7f7f7fu) + add7) & ~w4[w] & 0x80808080u;
+      hit |= gt[w];
     }
-    if (__ballot_sync(0xffffffffu, hit != 0u) != 0u) {  // rare, warp-uniform
+    if (thr < 0) hit = 1u;
+    if (__ballot_sync(0xffffffffu, hit != 0u) != 0u) {  // rare once the threshold has risen, warp-uniform
       unsigned qbits = 0;
+      if (thr < 0) {
+        const unsigned thr4 = (unsigned)(thr & 0xff) * 0x01010101u;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const unsigned g = __vcmpgts4(w4[w], thr4);
-        qbits |= (((g >> 7) & 1u) | ((g >> 14) & 2u) | ((g >> 21) & 4u) | ((g >> 28) & 8u)) << (w * 4);
+        for (int w = 0; w < 4; ++w) gt[w] = __vcmpgts4(w4[w], thr4) & 0x80808080u;
       }
+#pragma unroll
+      for (int w = 0; w < 4; ++w)
+        qbits |= (((gt[w] >> 7) & 1u) | ((gt[w] >> 14) & 2u) | ((gt[w] >> 21) & 4u) | ((gt[w] >> 28) & 8u)) << (w * 4);
       const int mine = __popc(qbits);
       int pre = mine;
 #pragma unroll
@@ -172,8 +190,10 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
       n_buf += total;
       __syncwarp();
       if (n_buf > 32) {
-        thr = topk_flush(buf, n_buf, K, lane, &n_buf);
-        thr4 = (unsigned)(thr & 0xff) * 0x01010101u;
+        thr = max(thr, topk_flush(buf, n_buf, K, lane, &n_buf));
+        add7 = 0x01010101u * (unsigned)(127 - max(thr, 0));
+        // published one lower: another warp may hold an equal value at a lower token id, which wins the tie
+        if (lane == 0) atomicMax(&s_thr, thr - 1);
       }
     }
   }
