@@ -50,6 +50,15 @@ def peaks():
     return 6650.0, "fallback"
 
 
+def int8_tensor_peak():
+    """TOP/s an int8 contraction is held against: the driver measures no int8 figure, so twice the measured bf16
+    burst (the ratio of the nominal dense peaks, 4.5 : 2.25)."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return 2.0 * float(json.loads(p.read_text())["bf16_tflops"]), "2 x measured bf16 burst"
+    return 2.0 * 1590.0, "2 x fallback bf16 burst"
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -214,7 +223,28 @@ def kernel_cases(torch, L, conf, B, S, step):
                          out_kind=L.OUT_OUTQ_I8, out=lo[j].data_ptr(), ldo=ldv)
         L.call("ls100_gemm_i8", CTX[0], a, st)
 
-    cases["gemm_logits"] = (gemm_logits, T * H + V * H + T * V, "hbm", f"gemm_i8_tc_kernel<256,4>, {T}x{V}x{H}, int8 out")
+    cases["gemm_logits"] = (gemm_logits, T * H + V * H + T * V, "hbm", f"gemm_i8_persist_kernel, {T}x{V}x{H}, int8 out")
+    # tensor-bound GEMMs: the encoder's QKV projection over all source tokens of the batch, and a square problem
+    Te = B * S
+    ae, we = [i8(Te, H) for _ in range(4)], [i8(3 * H, H) for _ in range(4)]
+    oe = [torch.empty(Te, 3 * H, dtype=torch.int8, device=dev) for _ in range(4)]
+
+    def gemm_enc_qkv(i, st):
+        j = i % 4
+        a = L.GemmI8Args(a=ae[j].data_ptr(), lda=H, w=we[j].data_ptr(), ldw=H, m=Te, n=3 * H, k=H, s_acc=1e-4, s_outq=0.02,
+                         out_kind=L.OUT_OUTQ_I8, out=oe[j].data_ptr(), ldo=3 * H)
+        L.call("ls100_gemm_i8", CTX[0], a, st)
+
+    cases["gemm_enc_qkv"] = (gemm_enc_qkv, 2 * Te * 3 * H * H, "tensor", f"gemm_i8_persist_kernel, {Te}x{3 * H}x{H}, int8 out")
+    sq = 8192
+    asq, wsq, osq = i8(sq, sq), i8(sq, sq), torch.empty(sq, sq, dtype=torch.int8, device=dev)
+
+    def gemm_square(i, st):
+        a = L.GemmI8Args(a=asq.data_ptr(), lda=sq, w=wsq.data_ptr(), ldw=sq, m=sq, n=sq, k=sq, s_acc=1e-4, s_outq=0.02,
+                         out_kind=L.OUT_OUTQ_I8, out=osq.data_ptr(), ldo=sq)
+        L.call("ls100_gemm_i8", CTX[0], a, st)
+
+    cases["gemm_square"] = (gemm_square, 2 * sq ** 3, "tensor", f"gemm_i8_persist_kernel, {sq}x{sq}x{sq}, int8 out")
     # decoder self-attention at decode position `step`
     nk = max(2, int(200e6 // (2 * T * ms * H)) + 1)
     kcs, vcs = [i8(T, heads, ms, 64) for _ in range(nk)], [i8(T, heads, ms, 64) for _ in range(nk)]
@@ -303,9 +333,13 @@ def run_single_kernel(args):
     conf = dict(hidden=512, ffn=2048, vocab=WORKLOAD["vocab"], heads=8, beam=WORKLOAD["beam"], max_step=WORKLOAD["max_step"])
     cases = kernel_cases(torch, L, conf, WORKLOAD["batch"], WORKLOAD["max_len"], 54)
     launch, algo, bound, note = cases[args.kernel]
-    ms = time_kernel(torch, launch)
-    print(json.dumps({"kernel": args.kernel, "note": note, "launch_us": ms * 1e3, "algorithmic_bytes": algo,
-                      "achieved_gbs": algo / (ms / 1e3) / 1e9}), flush=True)
+    ms = time_kernel(torch, launch, iters=10 if args.kernel == "gemm_square" else 40)
+    if bound == "tensor":
+        print(json.dumps({"kernel": args.kernel, "note": note, "launch_us": ms * 1e3, "algorithmic_ops": algo,
+                          "achieved_tops": algo / (ms / 1e3) / 1e12}), flush=True)
+    else:
+        print(json.dumps({"kernel": args.kernel, "note": note, "launch_us": ms * 1e3, "algorithmic_bytes": algo,
+                          "achieved_gbs": algo / (ms / 1e3) / 1e9}), flush=True)
     return 0
 
 
@@ -454,7 +488,15 @@ def run_ours(args):
         except Exception:
             traffic_tab = {}
     per_kernel = {}
+    i8_peak, i8_src = int8_tensor_peak()
     for name, (launch, algo, bound, note) in cases.items():
+        if bound == "tensor":  # algo = integer operations (2MNK)
+            ms_k = time_kernel(torch, launch, iters=10 if name == "gemm_square" else 40)
+            ach = algo / (ms_k / 1e3) / 1e12
+            per_kernel[name] = {"kernel": note, "bound": bound, "achieved": ach, "peak": i8_peak, "unit": "TOP/s",
+                                "frac": ach / i8_peak, "traffic": traffic_tab.get(name), "launch_us": ms_k * 1e3,
+                                "algorithmic_ops": algo, "peak_source": i8_src}
+            continue
         ms_k = time_kernel(torch, launch)
         ach = algo / (ms_k / 1e3) / 1e9
         per_kernel[name] = {"kernel": note, "bound": bound, "achieved": ach, "peak": hbm_peak, "unit": "GB/s",
@@ -554,7 +596,7 @@ def main():
     ap.add_argument("--decode-steps", type=int, default=-1,
                     help="cap the number of decode steps per generation (profiling aid; the result is not a bench value)")
     ap.add_argument("--kernel", default=None,
-                    help="run one kernel family alone (gemm_dec, gemm_logits, attn_dec, attn_cross, beam_topk, ln_quant)")
+                    help="run one kernel family alone (gemm_dec, gemm_logits, gemm_enc_qkv, gemm_square, attn_dec, attn_cross, beam_topk, ln_quant)")
     ap.add_argument("--workload", default=None, choices=["bert", "gpt", "big"],
                     help="run another BASELINE configuration (BERT-base, GPT-2 medium, Transformer-big) on one GPU")
     ap.add_argument("--quick", action="store_true",

@@ -248,8 +248,8 @@ __global__ void __launch_bounds__(128, 7) attn_dec_kernel(const ls100_attn_dec_a
       v4[u] = make_int4(0, 0, 0, 0);
       if (p < step) {
         const long long o = slot_s[p] * slot_stride + head_off + (long long)p * DH;
-        k4[u] = *reinterpret_cast<const int4*>(a.k_cache + o);
-        v4[u] = *reinterpret_cast<const int4*>(a.v_cache + o);
+        k4[u] = __ldcs(reinterpret_cast<const int4*>(a.k_cache + o));  // streamed once per step: evict first
+        v4[u] = __ldcs(reinterpret_cast<const int4*>(a.v_cache + o));
       } else if (p == step) {
         k4[u] = knew;
         v4[u] = vnew;
@@ -340,11 +340,12 @@ __device__ __forceinline__ void xattn_issue(uint8_t* buf, uint64_t* bar, const C
     x = h * DH * 4;
     y = b * S + t * XT;
   }
+  const uint64_t once = l2_policy_evict_first();  // read once per step: do not displace the weights
   mbar_expect_tx(bar, XTILE);
-  tma_load_2d(buf, tm_k, bar, x, y);
-  tma_load_2d(buf + XHALF, tm_k, bar, x + 128, y);
-  tma_load_2d(buf + 2 * XHALF, tm_v, bar, x, y);
-  tma_load_2d(buf + 3 * XHALF, tm_v, bar, x + 128, y);
+  tma_load_2d_hint(buf, tm_k, bar, x, y, once);
+  tma_load_2d_hint(buf + XHALF, tm_k, bar, x + 128, y, once);
+  tma_load_2d_hint(buf + 2 * XHALF, tm_v, bar, x, y, once);
+  tma_load_2d_hint(buf + 3 * XHALF, tm_v, bar, x + 128, y, once);
 }
 
 template <int NB>  // beams rounded up to 1, 2, 4 or 8

@@ -312,10 +312,11 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
       // First ring fill: the weight tiles do not depend on the previous kernel, so they are requested
       // before the grid-dependency wait; the activation tiles follow it.
       const int n_pre = num_kb < STAGES ? num_kb : STAGES;
+      const uint64_t keep = l2_policy_evict_last();  // weights are re-read every step; activations are not
       for (int kb = 0; kb < n_pre; ++kb) {
         uint8_t* sb = smem + kb * SM::STAGE_BYTES + SM::A_BYTES;
         mbar_expect_tx(&full_bar[kb], SM::STAGE_BYTES);
-        tma_load_2d(sb, &tma_b, &full_bar[kb], kb * BK, n0);
+        tma_load_2d_hint(sb, &tma_b, &full_bar[kb], kb * BK, n0, keep);
       }
       pdl_wait();
       for (int kb = 0; kb < n_pre; ++kb) tma_load_2d(smem + kb * SM::STAGE_BYTES, &tma_a, &full_bar[kb], kb * BK, m0);
@@ -330,7 +331,7 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
         uint8_t* sb = sa + SM::A_BYTES;
         mbar_expect_tx(&full_bar[s], SM::STAGE_BYTES);
         tma_load_2d(sa, &tma_a, &full_bar[s], kb * BK, m0);
-        tma_load_2d(sb, &tma_b, &full_bar[s], kb * BK, n0);
+        tma_load_2d_hint(sb, &tma_b, &full_bar[s], kb * BK, n0, keep);
         if (++s == STAGES) {
           s = 0;
           phase ^= 1;
