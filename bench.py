@@ -212,6 +212,19 @@ def kernel_cases(torch, L, conf, B, S, step):
 
     cases["gemm_dec"] = (gemm_dec, T * H + H * H + 2 * T * H * 4 + H * 4, "hbm",
                          f"gemm_i8_tc_kernel<32,4>, {T}x{H}x{H}, fused fake-quant+bias+residual, fp32 out")
+    # the same GEMM with the LayerNorm + quantise of the next sublayer fused in (cluster per 128-row block)
+    gam, bet = torch.ones(H, device=dev), torch.zeros(H, device=dev)
+    lnq = [torch.empty(T, H, dtype=torch.int8, device=dev) for _ in range(4)]
+
+    def gemm_dec_ln(i, st):
+        j = i % n_sets
+        a = L.GemmI8Args(a=a_s[j].data_ptr(), lda=H, w=w_s[j].data_ptr(), ldw=H, m=T, n=H, k=H, s_acc=1e-4, s_outq=0.02,
+                         bias=bias.data_ptr(), resid=x_s[j].data_ptr(), ldr=H, out_kind=L.OUT_F32, out=x_s[j].data_ptr(), ldo=H,
+                         ln_gamma=gam.data_ptr(), ln_beta=bet.data_ptr(), ln_amax=4.0, ln_out=lnq[i % 4].data_ptr(), ln_ldq=H)
+        L.call("ls100_gemm_i8", CTX[0], a, st)
+
+    cases["gemm_dec_ln"] = (gemm_dec_ln, T * H + H * H + 2 * T * H * 4 + H * 4 + T * H + 2 * H * 4, "hbm",
+                            f"gemm_i8_tc_kernel<64,4,LN>, {T}x{H}x{H}, fused fake-quant+bias+residual+LayerNorm+quantise")
     # logits GEMM
     wl = [i8(V, H) for _ in range(8)]
     ldv = (V + 15) // 16 * 16
@@ -596,7 +609,7 @@ def main():
     ap.add_argument("--decode-steps", type=int, default=-1,
                     help="cap the number of decode steps per generation (profiling aid; the result is not a bench value)")
     ap.add_argument("--kernel", default=None,
-                    help="run one kernel family alone (gemm_dec, gemm_logits, gemm_enc_qkv, gemm_square, attn_dec, attn_cross, beam_topk, ln_quant)")
+                    help="run one kernel family alone (gemm_dec, gemm_dec_ln, gemm_logits, gemm_enc_qkv, gemm_square, attn_dec, attn_cross, beam_topk, ln_quant)")
     ap.add_argument("--workload", default=None, choices=["bert", "gpt", "big"],
                     help="run another BASELINE configuration (BERT-base, GPT-2 medium, Transformer-big) on one GPU")
     ap.add_argument("--quick", action="store_true",

@@ -52,6 +52,8 @@ class GemmI8Args(C.Structure):
         ("out_kind", C.c_int32),
         ("s_req", C.c_float),
         ("out", C.c_void_p), ("ldo", C.c_int64),
+        ("ln_gamma", C.c_void_p), ("ln_beta", C.c_void_p), ("ln_amax", C.c_float), ("ln_out", C.c_void_p),
+        ("ln_ldq", C.c_int64),
     ]
 
 

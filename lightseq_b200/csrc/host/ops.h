@@ -84,6 +84,13 @@ class QuantLinearOp : public Operator {
     resid_ = resid;
     return out;
   }
+  // LayerNorm + quantise of the finished fp32 rows in the same launch (the next sublayer's input quantiser)
+  void fuse_layer_norm(const float* gamma, const float* beta, float amax, Variable* out_q) {
+    ln_g_ = gamma;
+    ln_b_ = beta;
+    ln_amax_ = amax;
+    ln_out_ = out_q;
+  }
   void before_forward(int rows, int64_t ldo = 0) {
     rows_ = rows;
     ldo_ = ldo ? ldo : p_->n;
@@ -109,6 +116,13 @@ class QuantLinearOp : public Operator {
     a.s_req = s_req_;
     a.out = out_->value<void>();
     a.ldo = ldo_;
+    if (ln_out_) {
+      a.ln_gamma = ln_g_;
+      a.ln_beta = ln_b_;
+      a.ln_amax = ln_amax_;
+      a.ln_out = ln_out_->value<int8_t>();
+      a.ln_ldq = p_->n;
+    }
     LS_RC(ls100_gemm_i8(ctx_->kernels(), &a, ctx_->get_stream()));
   }
 
@@ -118,7 +132,9 @@ class QuantLinearOp : public Operator {
   Act act_;
   bool out_quant_, add_bias_;
   float s_req_;
-  Variable *in_ = nullptr, *out_ = nullptr, *resid_ = nullptr;
+  Variable *in_ = nullptr, *out_ = nullptr, *resid_ = nullptr, *ln_out_ = nullptr;
+  const float *ln_g_ = nullptr, *ln_b_ = nullptr;
+  float ln_amax_ = 0.f;
   int rows_ = 0;
   int64_t ldo_ = 0;
 };

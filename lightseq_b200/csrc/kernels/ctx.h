@@ -65,6 +65,27 @@ inline cudaError_t ls100_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, s
   return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
 }
 
+// The same with the CTAs grouped into thread-block clusters of cluster_x along grid.x.
+template <typename... KArgs, typename... Args>
+inline cudaError_t ls100_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                        unsigned cluster_x, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = cluster_x;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = ls100_pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
 // 2-D uint8 tensor map, 128-byte swizzle, box = box_cols (bytes, <=128) x box_rows.
 int ls100_get_tmap_u8(ls100_ctx* ctx, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld_bytes,
                       uint32_t box_rows, uint32_t box_cols, CUtensorMap* out);

@@ -20,7 +20,7 @@
 // Epilogue arithmetic restates QuantLinear.forward
 // (lightseq/training/ops/pytorch/quantization.py:50-61) on exact int32
 // accumulators; see include/ls100.h for the per-element recipe.
-#include <stdlib.h>
+#include <string.h>
 
 #include "common.cuh"
 #include "ctx.h"
@@ -42,6 +42,12 @@ struct GemmEpi {
   void* out;
   long long ldo;
   int* err;
+  // fused LayerNorm + quantise of the fp32 output rows (cluster variant only)
+  const float* ln_gamma;
+  const float* ln_beta;
+  float ln_amax, ln_scale, ln_rs;
+  int8_t* ln_out;
+  long long ln_ldq;
 };
 
 constexpr int BM = 128;
@@ -55,7 +61,8 @@ struct GemmSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int VEC_OFFSET = BAR_OFFSET + 256;          // per-tile bias (fp32) and w_off (int32)
-  static constexpr int TOTAL = VEC_OFFSET + BN * 8 + 1024;     // + alignment slack
+  static constexpr int PART_OFFSET = VEC_OFFSET + BN * 8;      // per-row (sum, sum of squares) of the fused LayerNorm
+  static constexpr int TOTAL = PART_OFFSET + BM * 16 + 1024;   // + alignment slack
 };
 
 // Shared-memory matrix descriptor, K-major, SWIZZLE_128B, 8-row groups 1024 B apart.
@@ -89,7 +96,7 @@ __device__ __forceinline__ void record_timeout(int* err) {
 template <int BN>
 __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t (&r)[32], int row, int col0,
                                                const float* s_bias, const int* s_off, const float (&rr)[32],
-                                               bool rr_valid) {
+                                               bool rr_valid, double* row_sum = nullptr, double* row_sq = nullptr) {
   const bool row_ok = row < p.m;
   const bool full = (col0 + 32 <= p.n);
   int acc[32];
@@ -213,6 +220,17 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
       for (int j = 0; j < 32; ++j) v[j] = quant_u_biased(v[j], p.s_req, p.rs_req);
     }
   }
+  if (row_sum != nullptr) {  // statistics of the finished fp32 values for the fused LayerNorm
+    double s[4] = {0.0, 0.0, 0.0, 0.0}, q[4] = {0.0, 0.0, 0.0, 0.0};  // four chains: fp64 latency, not rate, is the cost
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const double d = (col0 + j < p.n) ? (double)v[j] : 0.0;
+      s[j & 3] += d;
+      q[j & 3] = fma(d, d, q[j & 3]);
+    }
+    *row_sum += (s[0] + s[1]) + (s[2] + s[3]);
+    *row_sq += (q[0] + q[1]) + (q[2] + q[3]);
+  }
   if (!row_ok) return;
   if (p.out_kind == LS100_OUT_F32) {
     float* op = reinterpret_cast<float*>(p.out) + (long long)row * p.ldo + col0;
@@ -263,7 +281,12 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
   }
 }
 
-template <int BN, int STAGES>
+// LNF: the CTAs of one 128-row block form a thread-block cluster (grid.x CTAs) and finish with LayerNorm + quantise
+// of the fp32 rows they have just written: per-row (sum, sum of squares) in float64 are exchanged through
+// distributed shared memory, every CTA adds them in rank order (so all agree to the bit), then each thread
+// normalises and quantises its own columns. EVERY thread of the cluster meets both cluster barriers on every
+// path, including the time-out paths.
+template <int BN, int STAGES, bool LNF = false>
 __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                          const __grid_constant__ CUtensorMap tma_b,
                                                          const GemmEpi p) {
@@ -405,6 +428,7 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
     asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
     bool ok = mbar_wait(tmem_full_bar, 0);
     ok = __all_sync(0xffffffffu, ok);
+    double ln_s = 0.0, ln_q = 0.0;
     if (!ok) {
       if (lane == 0) record_timeout(p.err);
     } else {
@@ -417,9 +441,79 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
         tmem_ld_wait();
         if (c0 == 0) { LS100_TRACE(7); }
-        epilogue_chunk<BN>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, rr_ok && c0 == 0);
+        epilogue_chunk<BN>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, rr_ok && c0 == 0, LNF ? &ln_s : nullptr,
+                           LNF ? &ln_q : nullptr);
         LS100_TRACE(8 + c0 / 32);
       }
+    }
+    if constexpr (LNF) {
+      double* part = reinterpret_cast<double*>(smem + SM::PART_OFFSET) + (quarter * 32 + lane) * 2;
+      part[0] = ln_s;
+      part[1] = ln_q;
+      __syncwarp();
+      cluster_arrive();
+      cluster_wait();
+      LS100_TRACE(12);
+      double ps[8], pq[8];  // all remote reads in flight together, then added in rank order in every CTA
+#pragma unroll
+      for (uint32_t rk = 0; rk < 8; ++rk) {
+        const uint32_t src = rk < gridDim.x ? rk : 0u;  // the cluster is the whole grid row (at most 8 CTAs)
+        ps[rk] = dsmem_ld_f64(part, src);
+        pq[rk] = dsmem_ld_f64(part + 1, src);
+      }
+      double S = 0.0, Q = 0.0;
+#pragma unroll
+      for (uint32_t rk = 0; rk < 8; ++rk) {
+        if (rk < gridDim.x) {
+          S += ps[rk];
+          Q += pq[rk];
+        }
+      }
+      __syncwarp();
+      cluster_arrive();  // this thread no longer reads its peers' shared memory
+      LS100_TRACE(13);
+      if (ok && row < p.m) {
+        const double inv_n = 1.0 / (double)p.n;
+        const double mean = S * inv_n;
+        const double var = fmax(Q * inv_n - mean * mean, 0.0);
+        const double rstd = 1.0 / sqrt(var + 1e-5);
+        const float* xr = reinterpret_cast<const float*>(p.out) + (long long)row * p.ldo + n0;
+        int8_t* qr = p.ln_out + (long long)row * p.ln_ldq + n0;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (n0 + c0 >= p.n) break;
+          uint32_t pk[8];
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const float4 x4 = *reinterpret_cast<const float4*>(xr + c0 + j);  // written by this thread above
+            const float4 g4 = __ldg(reinterpret_cast<const float4*>(p.ln_gamma + n0 + c0 + j));
+            const float4 b4 = __ldg(reinterpret_cast<const float4*>(p.ln_beta + n0 + c0 + j));
+            const float y0 = __fadd_rn(__fmul_rn((float)(((double)x4.x - mean) * rstd), g4.x), b4.x);
+            const float y1 = __fadd_rn(__fmul_rn((float)(((double)x4.y - mean) * rstd), g4.y), b4.y);
+            const float y2 = __fadd_rn(__fmul_rn((float)(((double)x4.z - mean) * rstd), g4.z), b4.z);
+            const float y3 = __fadd_rn(__fmul_rn((float)(((double)x4.w - mean) * rstd), g4.w), b4.w);
+            pk[j >> 2] = pack_biased_i8x4(quant_s_biased(clipf(y0, p.ln_amax), p.ln_scale, p.ln_rs),
+                                          quant_s_biased(clipf(y1, p.ln_amax), p.ln_scale, p.ln_rs),
+                                          quant_s_biased(clipf(y2, p.ln_amax), p.ln_scale, p.ln_rs),
+                                          quant_s_biased(clipf(y3, p.ln_amax), p.ln_scale, p.ln_rs));
+          }
+          *reinterpret_cast<uint4*>(qr + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(qr + c0 + 16) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        }
+      }
+      __syncwarp();
+      LS100_TRACE(14);
+      cluster_wait();  // no CTA leaves while a peer may still read its partial sums
+      LS100_TRACE(15);
+    }
+  }
+  if constexpr (LNF) {
+    if (warp < 2) {  // producer and MMA warps only take part in the cluster barriers
+      __syncwarp();
+      cluster_arrive();
+      cluster_wait();
+      cluster_arrive();
+      cluster_wait();
     }
   }
   LS100_TRACE(5);
@@ -646,6 +740,13 @@ static GemmEpi make_epi(const ls100_ctx* ctx, const ls100_gemm_i8_args* a) {
   p.out = a->out;
   p.ldo = a->ldo;
   p.err = ctx->d_err;
+  p.ln_gamma = a->ln_gamma;
+  p.ln_beta = a->ln_beta;
+  p.ln_amax = a->ln_amax;
+  p.ln_scale = a->ln_amax / 127.0f;
+  p.ln_rs = a->ln_amax > 0.f ? 1.0f / p.ln_scale : 0.f;
+  p.ln_out = a->ln_out;
+  p.ln_ldq = a->ln_ldq;
   return p;
 }
 
@@ -666,10 +767,10 @@ static int launch_gemm_persist(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cuda
              : LS100_ERR_CUDA;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool LNF = false>
 static int launch_gemm(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cudaStream_t stream) {
   using SM = GemmSmem<BN, STAGES>;
-  auto kern = gemm_i8_tc_kernel<BN, STAGES>;
+  auto kern = gemm_i8_tc_kernel<BN, STAGES, LNF>;
   CUtensorMap ta, tb;
   int rc = ls100_get_tmap_u8(ctx, a->a, (uint64_t)a->m, (uint64_t)a->k, (uint64_t)a->lda, BM, BK, &ta);
   if (rc) return rc;
@@ -677,12 +778,15 @@ static int launch_gemm(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cudaStream_t
   if (rc) return rc;
   const GemmEpi p = make_epi(ctx, a);
   dim3 grid((a->n + BN - 1) / BN, (a->m + BM - 1) / BM);
+  if (LNF)  // one cluster per 128-row block
+    return ls100_launch_cluster(kern, grid, dim3(192), SM::TOTAL, stream, grid.x, ta, tb, p) == cudaSuccess ? LS100_OK
+                                                                                                             : LS100_ERR_CUDA;
   return ls100_launch(kern, grid, dim3(192), SM::TOTAL, stream, ta, tb, p) == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool LNF = false>
 static int set_smem_attr() {
-  return cudaFuncSetAttribute(gemm_i8_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  return cudaFuncSetAttribute(gemm_i8_tc_kernel<BN, STAGES, LNF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               GemmSmem<BN, STAGES>::TOTAL) == cudaSuccess
              ? LS100_OK
              : LS100_ERR_CUDA;
@@ -694,10 +798,12 @@ static int set_smem_attr() {
 // Called once from ls100_ctx_create so that no attribute call happens inside a stream capture.
 int ls100_gemm_i8_init_device() {
   using namespace ls100;
-  int rc = set_smem_attr<256, 4>();
-  if (!rc) rc = set_smem_attr<128, 3>();
+  int rc = set_smem_attr<128, 3>();
   if (!rc) rc = set_smem_attr<64, 4>();
   if (!rc) rc = set_smem_attr<32, 4>();
+  if (!rc) rc = set_smem_attr<32, 4, true>();
+  if (!rc) rc = set_smem_attr<64, 4, true>();
+  if (!rc) rc = set_smem_attr<128, 3, true>();
   if (!rc && cudaFuncSetAttribute(gemm_i8_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   PersistSmem::TOTAL) != cudaSuccess)
     rc = LS100_ERR_CUDA;
@@ -717,14 +823,39 @@ extern "C" int ls100_gemm_i8(ls100_ctx* ctx, const ls100_gemm_i8_args* a, ls100_
   if (a->resid && a->ldr < a->n) return LS100_ERR_BAD_ARG;
   if (a->ldo < a->n) return LS100_ERR_BAD_ARG;
   cudaStream_t stream = (cudaStream_t)stream_;
+  if (a->ln_out) {
+    if (a->out_kind != LS100_OUT_F32 || !a->ln_gamma || !a->ln_beta || !(a->ln_amax > 0.f) || a->ln_ldq < a->n)
+      return LS100_ERR_BAD_ARG;
+    if ((((uintptr_t)a->ln_out) & 15) || (a->ln_ldq & 15) || (((uintptr_t)a->out) & 15) || (a->ldo & 3) ||
+        (((uintptr_t)a->ln_gamma) & 15) || (((uintptr_t)a->ln_beta) & 15))
+      return LS100_ERR_ALIGN;
+    // cluster form: the CTAs of a 128-row block (at most 8) hold the whole row between them
+    if ((a->n & 31) == 0 && a->n <= 256) return launch_gemm<32, 4, true>(ctx, a, stream);
+    if ((a->n & 31) == 0 && a->n <= 512) return launch_gemm<64, 4, true>(ctx, a, stream);
+    if ((a->n & 31) == 0 && a->n <= 1024) return launch_gemm<128, 3, true>(ctx, a, stream);
+    // otherwise: the plain GEMM, then the stand-alone LayerNorm kernel
+    ls100_gemm_i8_args g = *a;
+    g.ln_out = nullptr;
+    const int rc = ls100_gemm_i8(ctx, &g, stream_);
+    if (rc != LS100_OK) return rc;
+    ls100_ln_quant_args l;
+    memset(&l, 0, sizeof(l));
+    l.x = static_cast<const float*>(a->out);
+    l.ldx = a->ldo;
+    l.gamma = a->ln_gamma;
+    l.beta = a->ln_beta;
+    l.rows = a->m;
+    l.hidden = a->n;
+    l.amax = a->ln_amax;
+    l.out_q = a->ln_out;
+    l.ldq = a->ln_ldq;
+    return ls100_ln_quant(ctx, &l, stream_);
+  }
   const long long mt = (a->m + BM - 1) / BM;
   auto ctas = [&](int bn) { return mt * ((a->n + bn - 1) / bn); };
   const long long sms = ctx->sm_count;
   // Largest tile that still fills the machine; small problems fall to BN=32.
-  if (ctas(256) >= 2 * sms) {
-    static const bool persist = !(getenv("LS100_GEMM_PERSIST") && getenv("LS100_GEMM_PERSIST")[0] == '0');
-    return persist ? launch_gemm_persist(ctx, a, stream) : launch_gemm<256, 4>(ctx, a, stream);
-  }
+  if (ctas(256) >= 2 * sms) return launch_gemm_persist(ctx, a, stream);
   if (ctas(128) >= sms) return launch_gemm<128, 3>(ctx, a, stream);
   if (ctas(64) >= sms) return launch_gemm<64, 4>(ctx, a, stream);
   return launch_gemm<32, 4>(ctx, a, stream);

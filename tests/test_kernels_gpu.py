@@ -115,6 +115,31 @@ def test_gemm_outq_int8_and_bias_residual_bit_exact():
     assert np.array_equal(out.cpu().numpy(), resid + y)
 
 
+@pytest.mark.parametrize("m,n,k", [(512, 512, 512), (300, 512, 2048), (512, 1024, 1024), (130, 256, 128), (260, 768, 768),
+                                   (200, 2048, 256), (64, 1024, 4096)])
+def test_gemm_fused_layernorm_bit_exact(m, n, k):
+    """Residual GEMM with the LayerNorm + quantise of the next sublayer in the same launch (thread-block cluster per
+    128-row block, row sums exchanged through distributed shared memory): the fp32 rows equal the oracle's and the
+    int8 LayerNorm output equals quantize(layer_norm(rows)). N = 2048 takes the two-launch fallback."""
+    st, x, w, b = _qlinear_case(31 + n, m, n, k)
+    y = om.qlinear(st, x, "l")
+    xq, s_x = oq.quantize(x, st.amax["l.in"])
+    wq, s_w = oq.quantize(w, st.amax["l.w"])
+    r = rng(m + n)
+    resid = r.standard_normal((m, n)).astype(F32)
+    g = (1 + 0.1 * r.standard_normal(n)).astype(F32)
+    be = (0.1 * r.standard_normal(n)).astype(F32)
+    rows = resid + y
+    z = om.layer_norm(rows, g, be)
+    amax = float(F32(4 * z.std()))
+    q_ref, _ = oq.quantize(z, amax)
+    out, ln_out = gemm(dev(xq), dev(wq), s_acc=float(F32(s_x * s_w)), out_kind=L.OUT_F32,
+                       s_outq=float(oq.scale_of(st.amax["l.out"])), bias=dev(b), resid=dev(resid), ln=(dev(g), dev(be), amax))
+    sync_check()
+    assert np.array_equal(out.cpu().numpy(), rows)
+    assert np.array_equal(ln_out.cpu().numpy(), q_ref)
+
+
 def test_gemm_ffn_relu_unsigned_chain_bit_exact():
     """fc1 (+bias, ReLU, unsigned requantise) then fc2 with the 127*rowsum offset."""
     m, h, f = 260, 512, 2048
