@@ -39,6 +39,8 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 METRIC = "int8 Transformer-base generated tokens/sec (beam 4)"
+WORKLOAD_NAME = ("transformer-base int8 (6+6 layers, H512, 8 heads, FFN2048, V32000) beam-4 generation, "
+                 "batch 128 per GPU, src len U{20..60}, max out = src+50")
 WORKLOAD = dict(batch=128, min_len=20, max_len=60, vocab=32000, beam=4, extra_decode_length=50, max_step=128)
 
 
@@ -175,8 +177,7 @@ def run_reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * secs / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "transformer-base int8 beam-4 generation, batch 128 x src 20..60 (+50)",
-                   "sample": f"first {n_sent} sentences of the batch per step"},
+        "config": {"workload": WORKLOAD_NAME, "sample": f"first {n_sent} sentences of the 128-sentence batch per step"},
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
                          "sample": f"first {n_sent} of 128 sentences, full beam-4 generation, numpy oracle"},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -535,8 +536,7 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": n_warm,
         "ms_per_step": max_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "transformer-base int8 (6+6 layers, H512, 8 heads, FFN2048, V32000) beam-4 generation, "
-                               "batch 128 per GPU, src len U{20..60}, max out = src+50",
+        "config": {"workload": WORKLOAD_NAME,
                    "global_batch": B * world, "src_len_padded": S, "decode_steps": steps_per_infer,
                    "tokens_per_sentence": n_out, "parallelism": f"replicas x{world} (batch sharding, no collective)",
                    "l2": "256 MB buffer written between timed iterations; per-step working set (KV caches, logits) > L2"},
