@@ -126,3 +126,20 @@ def test_replica_sharding_world_size_2_gloo(tmp_path):
                        capture_output=True, text=True, env=env, timeout=240)
     assert r.returncode == 0, r.stderr[-2000:]
     assert "MERGE_OK" in r.stdout
+
+
+def test_torch_extension_surface_has_the_reference_entry_points():
+    """The names the reference's training-side extension exports for the quantised layers
+    (lightseq/csrc/pybind/pybind_layer.cpp:480-571); calling them needs a GPU, importing does not."""
+    from lightseq_b200 import torch_ext as te
+
+    for name in ("create_quant_linear_layer_fp32", "create_quant_linear_layer_fp16", "quant_linear_layer_fw_fp32",
+                 "quant_linear_layer_fw_fp16", "create_transformer_encoder_layer_fp32", "create_transformer_encoder_layer_fp16",
+                 "transformer_encoder_layer_fw_fp32", "transformer_encoder_layer_fw_fp16", "assign_layer_weight_grad"):
+        assert callable(getattr(te, name))
+    assert te._gen_offset(4, 8)[-1] == 4 * 4 * 3 + 12 + 16 + 4 + 8 + 32 + 8 + 32 + 4 + 8 + 12
+    import torch
+
+    assert te.create_quant_linear_layer_fp32(1, 64, 32, 16) == 0
+    with pytest.raises(RuntimeError, match="CUDA"):
+        te.quant_linear_layer_fw_fp32(1, torch.zeros(1, 4, 64), torch.zeros(32, 64), torch.ones(3), True)
