@@ -69,6 +69,79 @@ __global__ void __launch_bounds__(256) ln_quant_kernel(const ls100_ln_quant_args
   }
 }
 
+// Few rows (decode steps: a few hundred rows of 512..1024 values): one CTA of four warps per row, so that a row is one
+// 16-byte load per thread (two for 1024 values) and the float64 arithmetic per thread is a handful of operations; the
+// statistics cross the warps through shared memory. Same arithmetic as the warp-per-row kernel (two-pass variance,
+// float64 statistics), different summation order of the float64 partial sums.
+constexpr int LN_ROW_THREADS = 128;
+
+template <int NV>  // float4 per thread
+__global__ void __launch_bounds__(LN_ROW_THREADS) ln_quant_row_kernel(const ls100_ln_quant_args a, const float scale,
+                                                                      const float rs) {
+  __shared__ double s_part[2][LN_ROW_THREADS / 32];
+  pdl_launch_dependents();
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  const int row = blockIdx.x;
+  // gamma / beta do not depend on the previous kernel: fetched before the grid-dependency wait
+  float4 g[NV], b[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * LN_ROW_THREADS + t) * 4;
+    if (c < a.hidden) {
+      g[i] = __ldg(reinterpret_cast<const float4*>(a.gamma + c));
+      b[i] = __ldg(reinterpret_cast<const float4*>(a.beta + c));
+    }
+  }
+  pdl_wait();
+  const float* xr = a.x + (long long)row * a.ldx;
+  float4 v[NV];
+  double s = 0.0;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * LN_ROW_THREADS + t) * 4;
+    if (c < a.hidden) {
+      v[i] = *reinterpret_cast<const float4*>(xr + c);
+      s += ((double)v[i].x + (double)v[i].y) + ((double)v[i].z + (double)v[i].w);
+    }
+  }
+  s = warp_sum_d(s);
+  if (lane == 0) s_part[0][warp] = s;
+  __syncthreads();
+  const double mean = ((s_part[0][0] + s_part[0][1]) + (s_part[0][2] + s_part[0][3])) / (double)a.hidden;
+  double sq = 0.0;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * LN_ROW_THREADS + t) * 4;
+    if (c < a.hidden) {
+      const double d0 = (double)v[i].x - mean, d1 = (double)v[i].y - mean;
+      const double d2 = (double)v[i].z - mean, d3 = (double)v[i].w - mean;
+      sq += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+    }
+  }
+  sq = warp_sum_d(sq);
+  if (lane == 0) s_part[1][warp] = sq;
+  __syncthreads();
+  const double var = ((s_part[1][0] + s_part[1][1]) + (s_part[1][2] + s_part[1][3])) / (double)a.hidden;
+  const double rstd = 1.0 / sqrt(var + 1e-5);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * LN_ROW_THREADS + t) * 4;
+    if (c < a.hidden) {
+      float4 y;
+      y.x = __fadd_rn(__fmul_rn((float)(((double)v[i].x - mean) * rstd), g[i].x), b[i].x);
+      y.y = __fadd_rn(__fmul_rn((float)(((double)v[i].y - mean) * rstd), g[i].y), b[i].y);
+      y.z = __fadd_rn(__fmul_rn((float)(((double)v[i].z - mean) * rstd), g[i].z), b[i].z);
+      y.w = __fadd_rn(__fmul_rn((float)(((double)v[i].w - mean) * rstd), g[i].w), b[i].w);
+      if (a.out_f) *reinterpret_cast<float4*>(a.out_f + (long long)row * a.ldf + c) = y;
+      if (a.out_q) {
+        const uint32_t p = pack_i8x4(quant_s(clipf(y.x, a.amax), scale, rs), quant_s(clipf(y.y, a.amax), scale, rs),
+                                     quant_s(clipf(y.z, a.amax), scale, rs), quant_s(clipf(y.w, a.amax), scale, rs));
+        *reinterpret_cast<uint32_t*>(a.out_q + (long long)row * a.ldq + c) = p;
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ embedding
 __global__ void __launch_bounds__(256) embed_kernel(const ls100_embed_args a) {
   pdl_launch_dependents();
@@ -160,6 +233,14 @@ extern "C" int ls100_ln_quant(ls100_ctx* ctx, const ls100_ln_quant_args* a, ls10
   const int nv = (a->hidden + 127) / 128;
   const float rs = 1.0f / scale;
   cudaError_t e;
+  if (a->rows <= 2048) {  // decode-step sizes: a CTA per row
+    const int nvr = (a->hidden + 4 * LN_ROW_THREADS - 1) / (4 * LN_ROW_THREADS);
+    if (nvr <= 1) e = ls100_launch(ln_quant_row_kernel<1>, dim3(a->rows), dim3(LN_ROW_THREADS), 0, stream, *a, scale, rs);
+    else if (nvr <= 2) e = ls100_launch(ln_quant_row_kernel<2>, dim3(a->rows), dim3(LN_ROW_THREADS), 0, stream, *a, scale, rs);
+    else if (nvr <= 4) e = ls100_launch(ln_quant_row_kernel<4>, dim3(a->rows), dim3(LN_ROW_THREADS), 0, stream, *a, scale, rs);
+    else e = ls100_launch(ln_quant_row_kernel<8>, dim3(a->rows), dim3(LN_ROW_THREADS), 0, stream, *a, scale, rs);
+    return e == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+  }
   if (nv <= 4) e = ls100_launch(ln_quant_kernel<4>, dim3(blocks), dim3(256), 0, stream, *a, scale, rs);
   else if (nv <= 8) e = ls100_launch(ln_quant_kernel<8>, dim3(blocks), dim3(256), 0, stream, *a, scale, rs);
   else if (nv <= 16) e = ls100_launch(ln_quant_kernel<16>, dim3(blocks), dim3(256), 0, stream, *a, scale, rs);

@@ -205,7 +205,7 @@ def test_gemm_rejects_bad_arguments():
 
 
 # ----------------------------------------------------------------------------- LayerNorm, embedding
-@pytest.mark.parametrize("rows,hidden", [(512, 512), (33, 64), (1000, 768), (7, 1024), (3, 2048)])
+@pytest.mark.parametrize("rows,hidden", [(512, 512), (33, 64), (1000, 768), (7, 1024), (3, 2048), (2, 4096), (3000, 512), (2500, 1024)])
 def test_ln_quant_bit_exact(rows, hidden):
     r = rng(rows)
     x = (r.standard_normal((rows, hidden)) * 1.7 + 0.3).astype(F32)
