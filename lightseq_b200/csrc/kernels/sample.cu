@@ -1,4 +1,4 @@
-// Top-k sampling step for decoder-only generation (QuantGpt): one warp per sequence streams the row of int8
+// Top-k sampling step for decoder-only generation (QuantGpt): one CTA of eight warps per sequence streams the row of int8
 // logits once (16-byte loads, SIMD byte compares against a warp-wide running threshold, candidate buffer in
 // shared memory — the same selection as the beam kernel), then lane 0 draws the token with a counter-based
 // Philox4x32-10 stream keyed by (seed, row, position), so results do not depend on launch order or history.
@@ -8,7 +8,7 @@
 
 namespace ls100 {
 
-constexpr int SMP_WARPS = 4;
+constexpr int SMP_WARPS = 8;
 constexpr int SMP_MAXK = 8;
 constexpr int SMP_BUF = 512 + 64;
 
@@ -72,73 +72,83 @@ __device__ __forceinline__ uint32_t philox4x32_10_first(uint32_t c0, uint32_t c1
 }
 
 __global__ void __launch_bounds__(32 * SMP_WARPS) sample_topk_kernel(const ls100_sample_topk_args a) {
+  // One CTA per row; the eight warps take every eighth 512-byte chunk of the row (two chunks per warp in flight),
+  // each keeps its own k best, warp 0 merges them and draws.
   __shared__ unsigned s_buf[SMP_WARPS][SMP_BUF];
-  __shared__ int s_ended;
+  __shared__ int s_kept[SMP_WARPS];
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) s_ended = 0;
-  __syncthreads();
-  const int row = blockIdx.x * SMP_WARPS + warp;
+  const int row = blockIdx.x;
   const int cur = *a.cur;
   const int K = a.k;
-  if (row < a.rows) {
-    int32_t* seq = a.seq + (long long)row * a.max_step;
-    int token;
-    if (seq[cur] == a.end_id) {
-      token = a.end_id;
-    } else {
-      const int8_t* lp = a.logits + (long long)row * a.ld_logits;
-      unsigned* buf = s_buf[warp];
-      int n_buf = 0, thr = -128;
-      unsigned thr4 = 0x80808080u;
-      const int n_chunks = (a.vocab + 511) / 512;
-      int4 vnext = make_int4((int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080);
-      if (lane * 16 < a.vocab) vnext = smp_load16(lp, lane * 16, a.vocab);
-      for (int ch = 0; ch < n_chunks; ++ch) {
-        const int off = ch * 512 + lane * 16;
-        const int4 v = vnext;
-        vnext = make_int4((int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080);
-        if (off + 512 < a.vocab) vnext = smp_load16(lp, off + 512, a.vocab);
-        const unsigned w4[4] = {(unsigned)v.x, (unsigned)v.y, (unsigned)v.z, (unsigned)v.w};
-        unsigned hit = 0;
+  int32_t* seq = a.seq + (long long)row * a.max_step;
+  int token = a.end_id;
+  if (seq[cur] != a.end_id) {  // uniform over the CTA
+    const int8_t* lp = a.logits + (long long)row * a.ld_logits;
+    unsigned* buf = s_buf[warp];
+    int n_buf = 0, thr = -128;
+    unsigned thr4 = 0x80808080u;
+    const int n_chunks = (a.vocab + 511) / 512;
+    const int4 none = make_int4((int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080);
+    int4 v1 = none, v2 = none;
+    if (warp * 512 + lane * 16 < a.vocab) v1 = smp_load16(lp, warp * 512 + lane * 16, a.vocab);
+    if ((warp + SMP_WARPS) * 512 + lane * 16 < a.vocab) v2 = smp_load16(lp, (warp + SMP_WARPS) * 512 + lane * 16, a.vocab);
+    for (int ch = warp; ch < n_chunks; ch += SMP_WARPS) {
+      const int off = ch * 512 + lane * 16;
+      const int4 v = v1;
+      v1 = v2;
+      v2 = none;
+      if (off + 2 * SMP_WARPS * 512 < a.vocab) v2 = smp_load16(lp, off + 2 * SMP_WARPS * 512, a.vocab);
+      const unsigned w4[4] = {(unsigned)v.x, (unsigned)v.y, (unsigned)v.z, (unsigned)v.w};
+      unsigned hit = 0;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) hit |= __vcmpgts4(w4[w], thr4);
-        if (__ballot_sync(0xffffffffu, hit != 0u) != 0u) {
-          unsigned qbits = 0;
+      for (int w = 0; w < 4; ++w) hit |= __vcmpgts4(w4[w], thr4);
+      if (__ballot_sync(0xffffffffu, hit != 0u) != 0u) {
+        unsigned qbits = 0;
 #pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            const unsigned g = __vcmpgts4(w4[w], thr4);
-            qbits |= (((g >> 7) & 1u) | ((g >> 14) & 2u) | ((g >> 21) & 4u) | ((g >> 28) & 8u)) << (w * 4);
-          }
-          const int mine = __popc(qbits);
-          int pre = mine;
+        for (int w = 0; w < 4; ++w) {
+          const unsigned g = __vcmpgts4(w4[w], thr4);
+          qbits |= (((g >> 7) & 1u) | ((g >> 14) & 2u) | ((g >> 21) & 4u) | ((g >> 28) & 8u)) << (w * 4);
+        }
+        const int mine = __popc(qbits);
+        int pre = mine;
 #pragma unroll
-          for (int o = 1; o < 32; o <<= 1) {
-            const int t = __shfl_up_sync(0xffffffffu, pre, o);
-            if (lane >= o) pre += t;
-          }
-          const int total = __shfl_sync(0xffffffffu, pre, 31);
-          int pos = n_buf + pre - mine;
-          unsigned bits = qbits;
-          while (bits) {
-            const int bpos = __ffs(bits) - 1;
-            bits &= bits - 1;
-            const int q = (int)(int8_t)((w4[bpos >> 2] >> ((bpos & 3) * 8)) & 0xff);
-            buf[pos++] = ((unsigned)(q + 128) << 22) | (unsigned)(0x3fffff - (off + bpos));
-          }
-          n_buf += total;
-          __syncwarp();
-          if (n_buf > 32) {
-            thr = smp_flush(buf, n_buf, K, lane, &n_buf);
-            thr4 = (unsigned)(thr & 0xff) * 0x01010101u;
-          }
+        for (int o = 1; o < 32; o <<= 1) {
+          const int t = __shfl_up_sync(0xffffffffu, pre, o);
+          if (lane >= o) pre += t;
+        }
+        const int total = __shfl_sync(0xffffffffu, pre, 31);
+        int pos = n_buf + pre - mine;
+        unsigned bits = qbits;
+        while (bits) {
+          const int bpos = __ffs(bits) - 1;
+          bits &= bits - 1;
+          const int q = (int)(int8_t)((w4[bpos >> 2] >> ((bpos & 3) * 8)) & 0xff);
+          buf[pos++] = ((unsigned)(q + 128) << 22) | (unsigned)(0x3fffff - (off + bpos));
+        }
+        n_buf += total;
+        __syncwarp();
+        if (n_buf > 32) {
+          thr = smp_flush(buf, n_buf, K, lane, &n_buf);
+          thr4 = (unsigned)(thr & 0xff) * 0x01010101u;
         }
       }
+    }
+    __syncwarp();
+    smp_flush(buf, n_buf, K, lane, &n_buf);
+    if (lane == 0) s_kept[warp] = n_buf;
+    __syncthreads();
+    if (warp == 0) {
+      int n_all = n_buf;  // warp 0's own list already sits at buf[0 .. n_buf)
+      for (int w = 1; w < SMP_WARPS; ++w) {
+        const int nk = s_kept[w];
+        if (lane < nk) buf[n_all + lane] = s_buf[w][lane];
+        n_all += nk;
+      }
       __syncwarp();
-      smp_flush(buf, n_buf, K, lane, &n_buf);
+      smp_flush(buf, n_all, K, lane, &n_buf);
       // softmax over the k kept logits and the draw (lane 0; k <= 8 values)
-      token = a.end_id;
       if (lane == 0) {
         const int v0 = (int)(buf[0] >> 22) - 128;
         float e[SMP_MAXK];
@@ -161,16 +171,11 @@ __global__ void __launch_bounds__(32 * SMP_WARPS) sample_topk_kernel(const ls100
         }
         token = 0x3fffff - (int)(buf[pick] & 0x3fffff);
       }
-      token = __shfl_sync(0xffffffffu, token, 0);
-    }
-    if (lane == 0) {
-      if (cur + 1 < a.max_step) seq[cur + 1] = token;
-      if (token == a.end_id) atomicAdd(&s_ended, 1);
     }
   }
-  __syncthreads();
   if (threadIdx.x == 0) {
-    atomicAdd(a.n_ended, s_ended);
+    if (cur + 1 < a.max_step) seq[cur + 1] = token;
+    if (token == a.end_id) atomicAdd(a.n_ended, 1);
     __threadfence();
     const int ticket = atomicAdd(a.ticket, 1);
     if (ticket == (int)gridDim.x - 1) {
@@ -394,7 +399,7 @@ extern "C" int ls100_sample_topk(ls100_ctx* ctx, const ls100_sample_topk_args* a
   if (!ctx || !a || !a->logits || !a->seq || !a->cur || !a->ticket || !a->n_ended || !a->stop) return LS100_ERR_BAD_ARG;
   if (a->rows <= 0 || a->vocab <= 0 || a->k <= 0 || a->max_step <= 0 || !(a->s_logits > 0.f)) return LS100_ERR_BAD_ARG;
   if (a->k > SMP_MAXK || a->vocab < a->k || a->vocab > (1 << 22)) return LS100_ERR_UNSUPPORTED;
-  return ls100_launch(sample_topk_kernel, dim3((a->rows + SMP_WARPS - 1) / SMP_WARPS), dim3(32 * SMP_WARPS), 0,
+  return ls100_launch(sample_topk_kernel, dim3(a->rows), dim3(32 * SMP_WARPS), 0,
                       (cudaStream_t)stream_, *a) == cudaSuccess
              ? LS100_OK
              : LS100_ERR_CUDA;
