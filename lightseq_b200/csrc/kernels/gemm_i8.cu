@@ -5,10 +5,11 @@
 // out[M,N] = epilogue(A[M,K] . W[N,K]^T): both operands are K-major, which is
 // the torch Linear weight layout, so no load-time transpose is needed.
 //
-// CTA = one 128 x BN output tile, 6 warps:
+// CTA = one 128 x BN output tile, 10 warps:
 //   warp 0     TMA producer (one elected lane)
 //   warp 1     TMEM allocator + MMA issuer (one elected lane)
-//   warps 2-5  epilogue; warp w reads TMEM lanes 32*(w%4)..+31 (one row per thread)
+//   warps 2-9  epilogue; warp w reads TMEM lanes 32*(w%4)..+31 (one row per thread), the two warps of a
+//              lane quarter take alternate 16-column pieces
 // Shared-memory ring of STAGES x (A 128x128 B + W BNx128 B); full/empty
 // mbarriers; tcgen05.commit releases a stage when the MMAs that read it retire.
 // Epilogue overlap comes from two co-resident CTAs per SM for BN <= 128.
@@ -61,8 +62,8 @@ struct GemmSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int VEC_OFFSET = BAR_OFFSET + 256;          // per-tile bias (fp32) and w_off (int32)
-  static constexpr int PART_OFFSET = VEC_OFFSET + BN * 8;      // per-row (sum, sum of squares) of the fused LayerNorm
-  static constexpr int TOTAL = PART_OFFSET + BM * 16 + 1024;   // + alignment slack
+  static constexpr int PART_OFFSET = VEC_OFFSET + BN * 8;      // per row and column group: (sum, sum of squares), fused LayerNorm
+  static constexpr int TOTAL = PART_OFFSET + BM * 32 + 1024;   // + alignment slack
 };
 
 // Shared-memory matrix descriptor, K-major, SWIZZLE_128B, 8-row groups 1024 B apart.
@@ -90,21 +91,21 @@ __device__ __forceinline__ void record_timeout(int* err) {
   if (err) atomicExch(err, (int)LS100_ERR_TIMEOUT);
 }
 
-// 32 consecutive columns of one output row. Written as a sequence of branch-free passes
+// NC (32 or 16) consecutive columns of one output row. Written as a sequence of branch-free passes
 // over the 32 registers, with the (warp-uniform) mode tests between the passes: a taken
 // branch per element costs more than the arithmetic it guards.
-template <int BN>
-__device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t (&r)[32], int row, int col0,
-                                               const float* s_bias, const int* s_off, const float (&rr)[32],
+template <int BN, int NC = 32>
+__device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t (&r)[NC], int row, int col0,
+                                               const float* s_bias, const int* s_off, const float (&rr)[NC],
                                                bool rr_valid, double* row_sum = nullptr, double* row_sq = nullptr) {
   const bool row_ok = row < p.m;
-  const bool full = (col0 + 32 <= p.n);
-  int acc[32];
+  const bool full = (col0 + NC <= p.n);
+  int acc[NC];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) acc[j] = (int)r[j];
+  for (int j = 0; j < NC; ++j) acc[j] = (int)r[j];
   if (p.w_off != nullptr) {
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) {
+    for (int j = 0; j < NC; j += 4) {
       const int4 o = *reinterpret_cast<const int4*>(s_off + j);  // staged in shared memory, zero beyond N
       acc[j] += o.x;
       acc[j + 1] += o.y;
@@ -117,31 +118,31 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
     int* op = reinterpret_cast<int*>(p.out) + (long long)row * p.ldo + col0;
     if (full && ((p.ldo & 3) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) *reinterpret_cast<int4*>(op + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+      for (int j = 0; j < NC; j += 4) *reinterpret_cast<int4*>(op + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
+      for (int j = 0; j < NC; ++j)
         if (col0 + j < p.n) op[j] = acc[j];
     }
     return;
   }
-  float v[32];
+  float v[NC];
   bool quantised = false;
 #pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(__int2float_rn(acc[j]), p.s_acc);
+  for (int j = 0; j < NC; ++j) v[j] = __fmul_rn(__int2float_rn(acc[j]), p.s_acc);
   if (p.s_outq > 0.f) {
     if (p.out_kind == LS100_OUT_OUTQ_I8) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = quant_s_biased(v[j], p.s_outq, p.rs_outq);
+      for (int j = 0; j < NC; ++j) v[j] = quant_s_biased(v[j], p.s_outq, p.rs_outq);
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(quant_s(v[j], p.s_outq, p.rs_outq), p.s_outq);
+      for (int j = 0; j < NC; ++j) v[j] = __fmul_rn(quant_s(v[j], p.s_outq, p.rs_outq), p.s_outq);
     }
   }
   if (p.out_kind != LS100_OUT_OUTQ_I8) {
     if (p.bias != nullptr) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
+      for (int j = 0; j < NC; j += 4) {
         const float4 b = *reinterpret_cast<const float4*>(s_bias + j);
         v[j] = __fadd_rn(v[j], b.x);
         v[j + 1] = __fadd_rn(v[j + 1], b.y);
@@ -151,7 +152,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
     }
     if (p.act == LS100_ACT_RELU) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+      for (int j = 0; j < NC; ++j) v[j] = fmaxf(v[j], 0.f);
     } else if (p.act == LS100_ACT_GELU) {
       const bool requant = (p.out_kind == LS100_OUT_REQ_S8 || p.out_kind == LS100_OUT_REQ_U8) && p.resid == nullptr;
       if (requant) {
@@ -160,10 +161,10 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
         // ten thousand) are redone with the float64 erf the oracle uses, in a second pass so that the common
         // path stays branch-free.
         const float sub = (p.out_kind == LS100_OUT_REQ_U8) ? 127.f : 0.f;
-        float q[32];
+        float q[NC];
         unsigned redo = 0;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < NC; ++j) {
           const float g = gelu_fast(v[j]);
           const float u = __fadd_rn(__fsub_rn(div_rn(g, p.s_req, p.rs_req), sub), 0.5f);
           const float b = __fadd_rd(u, kQuantMagic);
@@ -177,27 +178,27 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
         }
         if (redo) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
+          for (int j = 0; j < NC; ++j)
             if (redo & (1u << j))
               q[j] = quant_biased(__fsub_rn(div_rn(gelu_erf_exact(v[j]), p.s_req, p.rs_req), sub));
         }
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = q[j];
+        for (int j = 0; j < NC; ++j) v[j] = q[j];
         quantised = true;
       } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = gelu_erf_exact(v[j]);
+        for (int j = 0; j < NC; ++j) v[j] = gelu_erf_exact(v[j]);
       }
     }
     if (p.resid != nullptr && row_ok) {
       if (rr_valid) {  // prefetched before the accumulator was ready
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], rr[j]);
+        for (int j = 0; j < NC; ++j) v[j] = __fadd_rn(v[j], rr[j]);
       } else {
         const float* rp = p.resid + (long long)row * p.ldr + col0;
         if (full && ((p.ldr & 3) == 0) && ((((uintptr_t)p.resid) & 15) == 0)) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
+          for (int j = 0; j < NC; j += 4) {
             const float4 t = *reinterpret_cast<const float4*>(rp + j);
             v[j] = __fadd_rn(v[j], t.x);
             v[j + 1] = __fadd_rn(v[j + 1], t.y);
@@ -206,7 +207,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
+          for (int j = 0; j < NC; ++j)
             if (col0 + j < p.n) v[j] = __fadd_rn(v[j], rp[j]);
         }
       }
@@ -214,16 +215,16 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
     if (quantised) {
     } else if (p.out_kind == LS100_OUT_REQ_S8) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = quant_s_biased(v[j], p.s_req, p.rs_req);
+      for (int j = 0; j < NC; ++j) v[j] = quant_s_biased(v[j], p.s_req, p.rs_req);
     } else if (p.out_kind == LS100_OUT_REQ_U8) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = quant_u_biased(v[j], p.s_req, p.rs_req);
+      for (int j = 0; j < NC; ++j) v[j] = quant_u_biased(v[j], p.s_req, p.rs_req);
     }
   }
   if (row_sum != nullptr) {  // statistics of the finished fp32 values for the fused LayerNorm
     double s[4] = {0.0, 0.0, 0.0, 0.0}, q[4] = {0.0, 0.0, 0.0, 0.0};  // four chains: fp64 latency, not rate, is the cost
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
+    for (int j = 0; j < NC; ++j) {
       const double d = (col0 + j < p.n) ? (double)v[j] : 0.0;
       s[j & 3] += d;
       q[j & 3] = fma(d, d, q[j & 3]);
@@ -236,17 +237,17 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
     float* op = reinterpret_cast<float*>(p.out) + (long long)row * p.ldo + col0;
     if (full && ((p.ldo & 3) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(op + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      for (int j = 0; j < NC; j += 4) *reinterpret_cast<float4*>(op + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
+      for (int j = 0; j < NC; ++j)
         if (col0 + j < p.n) op[j] = v[j];
     }
   } else if (p.out_kind == LS100_OUT_F16) {
     __half* op = reinterpret_cast<__half*>(p.out) + (long long)row * p.ldo + col0;
     if (full && ((p.ldo & 7) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 8) {
+      for (int j = 0; j < NC; j += 8) {
         __half2 h0 = __floats2half2_rn(v[j], v[j + 1]), h1 = __floats2half2_rn(v[j + 2], v[j + 3]);
         __half2 h2 = __floats2half2_rn(v[j + 4], v[j + 5]), h3 = __floats2half2_rn(v[j + 6], v[j + 7]);
         uint4 u;
@@ -258,14 +259,14 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
+      for (int j = 0; j < NC; ++j)
         if (col0 + j < p.n) op[j] = __float2half_rn(v[j]);
     }
   } else {  // int8 outputs: v[] holds the results of quant_biased
     int8_t* op = reinterpret_cast<int8_t*>(p.out) + (long long)row * p.ldo + col0;
     if (full && ((p.ldo & 15) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 16) {
+      for (int j = 0; j < NC; j += 16) {
         uint4 u;
         u.x = pack_biased_i8x4(v[j], v[j + 1], v[j + 2], v[j + 3]);
         u.y = pack_biased_i8x4(v[j + 4], v[j + 5], v[j + 6], v[j + 7]);
@@ -275,7 +276,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
+      for (int j = 0; j < NC; ++j)
         if (col0 + j < p.n) op[j] = (int8_t)(__float_as_uint(v[j]) & 0xffu);
     }
   }
@@ -287,7 +288,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
 // normalises and quantises its own columns. EVERY thread of the cluster meets both cluster barriers on every
 // path, including the time-out paths.
 template <int BN, int STAGES, bool LNF = false>
-__global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tma_a,
+__global__ void __launch_bounds__(320) gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                          const __grid_constant__ CUtensorMap tma_b,
                                                          const GemmEpi p) {
   using SM = GemmSmem<BN, STAGES>;
@@ -394,27 +395,32 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
       LS100_TRACE(3);
     }
   } else {
+    // Eight epilogue warps: warp w reads TMEM lanes 32*(w%4)..+31 (one row per thread); the two warps of a lane
+    // quarter take alternate 16-column pieces of the tile, so that two instruction streams per SM sub-partition
+    // hide each other's issue latency.
     const int quarter = warp & 3;
+    const int grp = (warp - 2) >> 2;
     const int row = m0 + quarter * 32 + lane;
     // While the main loop runs: stage this tile's bias / weight offsets in shared memory and
-    // prefetch the first 32 residual values of this thread's row, so that no global-load latency
+    // prefetch the residual values of this thread's first piece, so that no global-load latency
     // is left between "accumulator ready" and the stores.
     {
       const int te = threadIdx.x - 64;
-      for (int i = te; i < BN; i += 128) {
+      for (int i = te; i < BN; i += 256) {
         const int n = n0 + i;
         s_bias[i] = (p.bias != nullptr && n < p.n) ? __ldg(p.bias + n) : 0.f;
         s_off[i] = (p.w_off != nullptr && n < p.n) ? __ldg(p.w_off + n) : 0;
       }
     }
     pdl_wait();  // the residual (and everything written below) belongs to the chain of kernels before this one
-    float rr[32];
-    const bool rr_ok = p.resid != nullptr && row < p.m && (n0 + 32 <= p.n) && ((p.ldr & 3) == 0) &&
+    float rr[16];
+    const int c_first = grp * 16;
+    const bool rr_ok = p.resid != nullptr && row < p.m && (n0 + c_first + 16 <= p.n) && ((p.ldr & 3) == 0) &&
                        ((((uintptr_t)p.resid) & 15) == 0) && p.out_kind != LS100_OUT_I32 && p.out_kind != LS100_OUT_OUTQ_I8;
     if (rr_ok) {
-      const float* rp = p.resid + (long long)row * p.ldr + n0;
+      const float* rp = p.resid + (long long)row * p.ldr + n0 + c_first;
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
+      for (int j = 0; j < 16; j += 4) {
         const float4 t = *reinterpret_cast<const float4*>(rp + j);
         rr[j] = t.x;
         rr[j + 1] = t.y;
@@ -423,9 +429,9 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) rr[j] = 0.f;
+      for (int j = 0; j < 16; ++j) rr[j] = 0.f;
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+    asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight epilogue warps only
     bool ok = mbar_wait(tmem_full_bar, 0);
     ok = __all_sync(0xffffffffu, ok);
     double ln_s = 0.0, ln_q = 0.0;
@@ -435,38 +441,42 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
       tc_fence_after();
       LS100_TRACE(4);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = c_first; c0 < BN; c0 += 32) {
         if (n0 + c0 >= p.n) break;
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+        uint32_t r[16];
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
         tmem_ld_wait();
-        if (c0 == 0) { LS100_TRACE(7); }
-        epilogue_chunk<BN>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, rr_ok && c0 == 0, LNF ? &ln_s : nullptr,
-                           LNF ? &ln_q : nullptr);
+        if (c0 == c_first) { LS100_TRACE(7); }
+        epilogue_chunk<BN, 16>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, rr_ok && c0 == c_first,
+                               LNF ? &ln_s : nullptr, LNF ? &ln_q : nullptr);
         LS100_TRACE(8 + c0 / 32);
       }
     }
     if constexpr (LNF) {
-      double* part = reinterpret_cast<double*>(smem + SM::PART_OFFSET) + (quarter * 32 + lane) * 2;
+      // this thread's partial sums: slot (row of the tile, column group)
+      double* part = reinterpret_cast<double*>(smem + SM::PART_OFFSET) + ((quarter * 32 + lane) * 2 + grp) * 2;
+      double* part_row = reinterpret_cast<double*>(smem + SM::PART_OFFSET) + (quarter * 32 + lane) * 4;
       part[0] = ln_s;
       part[1] = ln_q;
       __syncwarp();
       cluster_arrive();
       cluster_wait();
       LS100_TRACE(12);
-      double ps[8], pq[8];  // all remote reads in flight together, then added in rank order in every CTA
+      double ps[16], pq[16];  // all remote reads in flight together, then added in (rank, group) order in every CTA
 #pragma unroll
       for (uint32_t rk = 0; rk < 8; ++rk) {
         const uint32_t src = rk < gridDim.x ? rk : 0u;  // the cluster is the whole grid row (at most 8 CTAs)
-        ps[rk] = dsmem_ld_f64(part, src);
-        pq[rk] = dsmem_ld_f64(part + 1, src);
+        ps[2 * rk] = dsmem_ld_f64(part_row, src);
+        pq[2 * rk] = dsmem_ld_f64(part_row + 1, src);
+        ps[2 * rk + 1] = dsmem_ld_f64(part_row + 2, src);
+        pq[2 * rk + 1] = dsmem_ld_f64(part_row + 3, src);
       }
       double S = 0.0, Q = 0.0;
 #pragma unroll
       for (uint32_t rk = 0; rk < 8; ++rk) {
         if (rk < gridDim.x) {
-          S += ps[rk];
-          Q += pq[rk];
+          S += ps[2 * rk] + ps[2 * rk + 1];
+          Q += pq[2 * rk] + pq[2 * rk + 1];
         }
       }
       __syncwarp();
@@ -480,11 +490,11 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
         const float* xr = reinterpret_cast<const float*>(p.out) + (long long)row * p.ldo + n0;
         int8_t* qr = p.ln_out + (long long)row * p.ln_ldq + n0;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c0 = c_first; c0 < BN; c0 += 32) {  // this thread's own 16-column pieces
           if (n0 + c0 >= p.n) break;
-          uint32_t pk[8];
+          uint32_t pk[4];
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
+          for (int j = 0; j < 16; j += 4) {
             const float4 x4 = *reinterpret_cast<const float4*>(xr + c0 + j);  // written by this thread above
             const float4 g4 = __ldg(reinterpret_cast<const float4*>(p.ln_gamma + n0 + c0 + j));
             const float4 b4 = __ldg(reinterpret_cast<const float4*>(p.ln_beta + n0 + c0 + j));
@@ -498,7 +508,6 @@ __global__ void __launch_bounds__(192) gemm_i8_tc_kernel(const __grid_constant__
                                           quant_s_biased(clipf(y3, p.ln_amax), p.ln_scale, p.ln_rs));
           }
           *reinterpret_cast<uint4*>(qr + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-          *reinterpret_cast<uint4*>(qr + c0 + 16) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
         }
       }
       __syncwarp();
@@ -779,9 +788,9 @@ static int launch_gemm(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cudaStream_t
   const GemmEpi p = make_epi(ctx, a);
   dim3 grid((a->n + BN - 1) / BN, (a->m + BM - 1) / BM);
   if (LNF)  // one cluster per 128-row block
-    return ls100_launch_cluster(kern, grid, dim3(192), SM::TOTAL, stream, grid.x, ta, tb, p) == cudaSuccess ? LS100_OK
+    return ls100_launch_cluster(kern, grid, dim3(320), SM::TOTAL, stream, grid.x, ta, tb, p) == cudaSuccess ? LS100_OK
                                                                                                              : LS100_ERR_CUDA;
-  return ls100_launch(kern, grid, dim3(192), SM::TOTAL, stream, ta, tb, p) == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
+  return ls100_launch(kern, grid, dim3(320), SM::TOTAL, stream, ta, tb, p) == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
 
 template <int BN, int STAGES, bool LNF = false>
