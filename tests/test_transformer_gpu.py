@@ -224,3 +224,22 @@ def test_transformer_base_shape_guided_replay(tmp_path):
     assert tok.shape == (16, 1, n_ref)
     same = (tok[:, 0, :] == ref_tok).all(axis=1)
     print("free-running identical sequences", int(same.sum()), "of 16")
+
+
+def test_reference_protobuf_file_runs_unchanged(tmp_path):
+    """A model written in the reference's QuantTransformer protobuf format and converted back generates exactly what
+    the same model does when loaded from the engine's own container (the int8 weights survive the trip)."""
+    import lightseq_b200.inference as lsi
+    from lightseq_b200 import ls_proto, weights
+
+    conf, amax, w = synth.make_transformer(None, hidden=128, heads=2, ffn=256, n_enc=2, n_dec=2, vocab=120, max_step=40, seed=9)
+    for i in range(2):
+        amax[f"dec.{i}.xv.w"] = amax[f"dec.{i}.xk.w"]
+    direct, pb, conv = str(tmp_path / "a.ls100"), str(tmp_path / "m.pb"), str(tmp_path / "b.ls100")
+    weights.save(direct, "QuantTransformer", conf, amax, w)
+    ls_proto.write_quant_transformer(pb, conf, amax, w)
+    ls_proto.convert(pb, conv)
+    src = synth.transformer_inputs(batch=6, min_len=5, max_len=14, vocab=120, pad_id=1, seed=4)
+    t1, s1 = lsi.QuantTransformer(direct, 8).infer(src)
+    t2, s2 = lsi.QuantTransformer(conv, 8).infer(src)
+    assert np.array_equal(t1, t2) and np.array_equal(s1, s2)
