@@ -554,8 +554,8 @@ def run_ours(args):
 
 
 def run_other_workload(args):
-    """``--workload bert|gpt|big``: the other BASELINE configurations on one GPU (reported in DESIGN.md; the
-    contract line of this file is the Transformer-base workload)."""
+    """``--workload bert|gpt|big``: the other benchmark configurations (BERT-base, GPT-2 medium, Transformer-big) on
+    one GPU; the contract line of this file is the Transformer-base workload."""
     import torch
 
     import lightseq_b200.inference as lsi

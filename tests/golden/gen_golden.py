@@ -1,8 +1,8 @@
 """Generates tests/golden/*.npz by running the REAL reference modules
 (lightseq/training/ops/pytorch/{quantization,torch_transformer_layers}.py) on CPU.
 
-Needs a checkout of bytedance/lightseq (default /root/reference, or $LIGHTSEQ_REF);
-the tests only read the committed .npz files. Usage:  python tests/golden/gen_golden.py
+Needs a checkout of bytedance/lightseq, named by $LIGHTSEQ_REF or the first argument;
+the tests only read the committed .npz files. Usage:  LIGHTSEQ_REF=<checkout> python tests/golden/gen_golden.py
 
 The reference package's ``lightseq.training`` __init__ JIT-builds CUDA layers at
 import, so empty stub packages are registered for ``lightseq.training``,
@@ -21,7 +21,9 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-REF = os.environ.get("LIGHTSEQ_REF", "/root/reference")
+REF = os.environ.get("LIGHTSEQ_REF") or (sys.argv[1] if len(sys.argv) > 1 else "")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set LIGHTSEQ_REF (or pass the path) to a checkout of bytedance/lightseq")
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, REF)
 
