@@ -243,3 +243,11 @@ def test_reference_protobuf_file_runs_unchanged(tmp_path):
     t1, s1 = lsi.QuantTransformer(direct, 8).infer(src)
     t2, s2 = lsi.QuantTransformer(conv, 8).infer(src)
     assert np.array_equal(t1, t2) and np.array_equal(s1, s2)
+
+
+def test_entry_point_smoke_runs():
+    """The repository's smoke entry (one tcgen05 GEMM checked on its accumulators + a tiny generation checked token
+    for token against the oracle) is part of the suite so that it cannot go stale."""
+    import importlib
+
+    importlib.import_module("__graft_entry__").smoke()
