@@ -583,6 +583,24 @@ def run_other_workload(args):
             ids = synth.bert_inputs(batch=B, seq=S)
             dt, y = timed(lambda: model.infer(ids), args.steps)
             out[f"{B}x{S}"] = {"ms": dt * 1e3, "tokens_per_s": B * S / dt, "int8_gemm_tops": 2 * B * S * 12 * 7077888 / dt / 1e12}
+    elif args.workload == "eos":
+        # the benchmark model with EOS made competitive (a shared direction in the final LayerNorm bias and in the EOS
+        # embedding row), so that beams finish at different steps and the device-side early stop ends the generation
+        from lightseq_b200 import weights
+
+        _, conf, amax, w = build_model_file(td)
+        u = np.sign(np.random.default_rng(0).standard_normal(int(conf["hidden"]))).astype(np.float32)
+        w["dec.ln.b"] = (args.eos_boost * u).astype(np.float32)
+        w["emb"][int(conf["end_id"])] = (0.02 * u).astype(np.float32)
+        weights.save(path, "QuantTransformer", conf, amax, w)
+        model = lsi.QuantTransformer(path, WORKLOAD["batch"])
+        src = batch_for_rank(0)
+        dt, (tok, sc) = timed(lambda: model.infer(src), args.steps)
+        end = int(conf["end_id"])
+        lens = [count_tokens(tok[i:i + 1], end) for i in range(tok.shape[0])]
+        out["128 x src20..60, boosted EOS"] = {"ms": dt * 1e3, "tokens_per_s": float(sum(lens)) / dt, "steps_run": int(tok.shape[2]),
+                                                "mean_generated_length": float(np.mean(lens)), "min": int(min(lens)),
+                                                "max": int(max(lens)), "length_cap": int(src.shape[1]) + 50 - 1}
     elif args.workload == "gpt":
         conf, _, _ = synth.make_gpt(path, max_step=256, max_new_tokens=192)
         model = lsi.QuantGpt(path, 64)
@@ -612,8 +630,10 @@ def main():
                     help="cap the number of decode steps per generation (profiling aid; the result is not a bench value)")
     ap.add_argument("--kernel", default=None,
                     help="run one kernel family alone (gemm_dec, gemm_dec_ln, gemm_logits, gemm_enc_qkv, gemm_square, attn_dec, attn_cross, beam_topk, ln_quant)")
-    ap.add_argument("--workload", default=None, choices=["bert", "gpt", "big"],
-                    help="run another BASELINE configuration (BERT-base, GPT-2 medium, Transformer-big) on one GPU")
+    ap.add_argument("--workload", default=None, choices=["bert", "gpt", "big", "eos"],
+                    help="run another BASELINE configuration (BERT-base, GPT-2 medium, Transformer-big) on one GPU, or the "
+                         "benchmark model with a boosted EOS (early-stop bookkeeping)")
+    ap.add_argument("--eos-boost", type=float, default=0.13, help="size of the EOS direction in the final LayerNorm bias")
     ap.add_argument("--quick", action="store_true",
                     help="device-resident arm only, warm-up exactly as given (for profiler launch lists)")
     args = ap.parse_args()
