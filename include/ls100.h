@@ -258,6 +258,29 @@ typedef struct {
 } ls100_proj_f32_args;
 int ls100_proj_f32(ls100_ctx* ctx, const ls100_proj_f32_args* args, ls100_stream_t stream);
 
+/* The same projection on the tensor cores. The fp32 activations are split once into three bf16 terms
+ * (x = hi + mid + lo, remainder below 2^-27 |x|): ls100_split_bf16x3 writes x3 = [lo | mid | hi] as bf16 [M, 3K]
+ * (smallest terms first, which keeps the tensor core's running fp32 sum small for two thirds of the products);
+ * the int8 weight is exact in bf16 (ls100_i8_to_bf16, once at load). ls100_proj_tc then runs ONE tcgen05 kind::f16
+ * GEMM with K' = 3K against [W | W | W] (never materialised) with fp32 accumulation, scales by s_w, adds the bias
+ * and stores fp32 row-major or head-split like ls100_proj_f32. K must be a multiple of 64. Differs from
+ * ls100_proj_f32 only in the rounding of the fp32 accumulation (both within 1e-6 relative of the exact product). */
+int ls100_split_bf16x3(ls100_ctx* ctx, const float* x, int64_t ldx, int32_t m, int32_t k, void* out_bf16 /* [m, 3k] */,
+                       ls100_stream_t stream);
+int ls100_i8_to_bf16(ls100_ctx* ctx, const int8_t* w, int64_t ldw, int32_t n, int32_t k, void* out_bf16 /* [n, k] */,
+                     ls100_stream_t stream);
+typedef struct {
+  const void* x3;     /* bf16 [m, 3k] from ls100_split_bf16x3 */
+  const void* w_bf16; /* bf16 [n, k] from ls100_i8_to_bf16 */
+  float s_w;
+  const float* bias;
+  int32_t m, n, k;
+  void* out; /* fp32 */
+  int64_t ldo;
+  int32_t split_seq; /* as in ls100_proj_f32_args */
+} ls100_proj_tc_args;
+int ls100_proj_tc(ls100_ctx* ctx, const ls100_proj_tc_args* args, ls100_stream_t stream);
+
 /* ------------------------------------------------------------------ beam search ---
  * Step 1 (ls100_beam_topk): per (batch, beam) row of int8 logits, log-softmax base from
  * the 255-bin histogram (exp arguments clamped at -64), exact top-`beam` by (logit desc,

@@ -122,6 +122,11 @@ class SampleTopkArgs(C.Structure):
                 ("ticket", C.c_void_p), ("n_ended", C.c_void_p), ("stop", C.c_void_p), ("stop_host", C.c_void_p)]
 
 
+class ProjTcArgs(C.Structure):
+    _fields_ = [("x3", C.c_void_p), ("w_bf16", C.c_void_p), ("s_w", C.c_float), ("bias", C.c_void_p), ("m", C.c_int32),
+                ("n", C.c_int32), ("k", C.c_int32), ("out", C.c_void_p), ("ldo", C.c_int64), ("split_seq", C.c_int32)]
+
+
 class SampleToppArgs(C.Structure):
     _fields_ = [("logits", C.c_void_p), ("ld_logits", C.c_int64), ("s_logits", C.c_float), ("p", C.c_float),
                 ("rows", C.c_int32), ("vocab", C.c_int32), ("max_step", C.c_int32), ("end_id", C.c_int32),
@@ -147,10 +152,15 @@ for _name, _cls in (("ls100_ln_quant", LnQuantArgs), ("ls100_embed", EmbedArgs),
                     ("ls100_attn_dec", AttnDecArgs), ("ls100_attn_cross", AttnCrossArgs),
                     ("ls100_proj_f32", ProjF32Args), ("ls100_beam_topk", BeamTopkArgs),
                     ("ls100_beam_update", BeamUpdateArgs), ("ls100_beam_update_noalloc", BeamUpdateArgs), ("ls100_sample_topk", SampleTopkArgs),
-                    ("ls100_sample_topp", SampleToppArgs)):
+                    ("ls100_sample_topp", SampleToppArgs),
+                    ("ls100_proj_tc", ProjTcArgs)):
     _fn = getattr(lib, _name)
     _fn.restype = C.c_int
     _fn.argtypes = [C.c_void_p, C.POINTER(_cls), C.c_void_p]
+lib.ls100_split_bf16x3.restype = C.c_int
+lib.ls100_split_bf16x3.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
+lib.ls100_i8_to_bf16.restype = C.c_int
+lib.ls100_i8_to_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
 lib.ls100_quantize_weight.restype = C.c_int
 lib.ls100_quantize_weight.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_void_p,
                                       C.c_void_p, C.c_void_p]

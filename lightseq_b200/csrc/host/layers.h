@@ -198,9 +198,26 @@ class QuantTransformerDecoderLayer : public Layer {
     if ((long long)batch * src_len > max_enc_tokens_) throw std::runtime_error("encoder tokens exceed max_batch_tokens");
   }
   // cross-attention keys / values of this layer from the encoder output (once per request)
-  void project_encoder_output(const float* enc_out) {
+  // `enc_x3`: the encoder output split into three bf16 terms (ls100_split_bf16x3), or NULL for the fp32 SIMT kernel
+  void project_encoder_output(const float* enc_out, const void* enc_x3) {
     for (int which = 0; which < 2; ++which) {
       const QLinearParams& p = which == 0 ? xk_ : xv_;
+      if (enc_x3 && w_bf16_[which]) {  // tensor cores
+        ls100_proj_tc_args a;
+        memset(&a, 0, sizeof(a));
+        a.x3 = enc_x3;
+        a.w_bf16 = w_bf16_[which];
+        a.s_w = p.s_w;
+        a.bias = p.bias;
+        a.m = batch_ * src_len_;
+        a.n = hidden_;
+        a.k = hidden_;
+        a.out = which == 0 ? enc_k_ : enc_v_;
+        a.ldo = hidden_;
+        a.split_seq = src_len_;
+        LS_RC(ls100_proj_tc(ctx_->kernels(), &a, ctx_->get_stream()));
+        continue;
+      }
       ls100_proj_f32_args a;
       memset(&a, 0, sizeof(a));
       a.x = enc_out;
@@ -216,6 +233,16 @@ class QuantTransformerDecoderLayer : public Layer {
       a.ldo = hidden_;
       a.split_seq = src_len_;  // [batch, heads, src_len, 64]: a head's keys are contiguous for the decode steps
       LS_RC(ls100_proj_f32(ctx_->kernels(), &a, ctx_->get_stream()));
+    }
+  }
+  // bf16 copies of the two projection weights (exact: int8 values), made once so that the projection can run on the
+  // tensor cores; hidden sizes that are not a multiple of 64 keep the SIMT kernel
+  void prepare_tensor_core_projection() {
+    if (hidden_ % 64) return;
+    for (int which = 0; which < 2; ++which) {
+      const QLinearParams& p = which == 0 ? xk_ : xv_;
+      w_bf16_[which] = ctx_->alloc((size_t)hidden_ * hidden_ * 2);
+      LS_RC(ls100_i8_to_bf16(ctx_->kernels(), p.w, p.k, hidden_, hidden_, w_bf16_[which], ctx_->get_stream()));
     }
   }
   void forward() override {
@@ -302,6 +329,7 @@ class QuantTransformerDecoderLayer : public Layer {
   float amax_kv_ = 0, s_kv_ = 0;
   int8_t *k_cache_ = nullptr, *v_cache_ = nullptr;
   float *enc_k_ = nullptr, *enc_v_ = nullptr;
+  void* w_bf16_[2] = {nullptr, nullptr};
   StackBuffers* b_ = nullptr;
   Variable* pad_mask_ = nullptr;
   const int32_t* anc_ = nullptr;

@@ -65,6 +65,10 @@ class QuantTransformer : public EngineModel {
                                                                 max_step_, H_, heads_, F_, pre_ln, act, max_bs_, beam_,
                                                                 max_step_));
     dec_ln_.load(c, wf, "dec.ln", H_);
+    if (H_ % 64 == 0 && getenv("LS100_PROJ_SIMT") == nullptr) {  // cross K/V projection on the tensor cores
+      enc_x3_ = c.alloc((size_t)max_enc_tokens * 3 * H_ * 2);
+      for (auto& l : dec_layers_) l->prepare_tensor_core_projection();
+    }
 
     auto mk = [&](const char* n, size_t bytes) { vars_.emplace_back(new Variable(n, c, bytes)); return vars_.back().get(); };
     enc_.x = mk("enc.x", (size_t)max_enc_tokens * H_ * 4);
@@ -140,9 +144,11 @@ class QuantTransformer : public EngineModel {
     LS_CUDA(cudaSetDevice(ctx_->device()));
     cudaStream_t st = ctx_->get_stream();
     run_encoder(B, S);
+    if (enc_x3_)  // one split of the encoder output serves the 2 x n_dec projections
+      LS_RC(ls100_split_bf16x3(ctx_->kernels(), enc_out_->value<float>(), H_, B * S, H_, enc_x3_, st));
     for (auto& l : dec_layers_) {
       l->before_forward(B, beam_, S);
-      l->project_encoder_output(enc_out_->value<float>());
+      l->project_encoder_output(enc_out_->value<float>(), enc_x3_);
     }
     const int rows = B * beam_;
     LS_CUDA(cudaMemcpyAsync(alive_, h_alive_.data(), (size_t)rows * max_step_ * 4, cudaMemcpyHostToDevice, st));
@@ -406,6 +412,7 @@ class QuantTransformer : public EngineModel {
   cudaEvent_t ring_[kRing];
   std::map<long long, cudaGraphExec_t> graphs_;
   bool use_graph_ = true, benchmark_ = false;
+  void* enc_x3_ = nullptr;
   const int32_t* d_src_ = nullptr;
   int32_t* d_out_ids_ = nullptr;
   float* d_out_scores_ = nullptr;

@@ -6,6 +6,7 @@
 
 int ls100_gemm_i8_init_device();
 int ls100_attn_init_device();
+int ls100_proj_tc_init_device();
 
 bool ls100_pdl_enabled() {
   static const bool on = [] {
@@ -42,7 +43,8 @@ extern "C" int ls100_ctx_create(ls100_ctx** out, int device) {
     return LS100_ERR_NO_DRIVER;
   }
   c->encode = (ls100_encode_tiled_fn)fn;
-  if (ls100_gemm_i8_init_device() != LS100_OK || ls100_attn_init_device() != LS100_OK) {
+  if (ls100_gemm_i8_init_device() != LS100_OK || ls100_attn_init_device() != LS100_OK ||
+      ls100_proj_tc_init_device() != LS100_OK) {
     cudaFree(c->d_err);
     delete c;
     return LS100_ERR_CUDA;

@@ -408,6 +408,48 @@ def test_proj_f32_weight_only_quant():
     assert np.array_equal(out2.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("m,n,k,seq", [(333, 192, 512, 0), (7680, 512, 512, 60), (300, 1024, 1024, 0), (50, 64, 64, 25),
+                                        (1000, 200, 128, 0)])
+def test_proj_tc_matches_oracle_and_simt(m, n, k, seq):
+    """The K/V projection on the tensor cores (fp32 activations as three bf16 terms x the int8 weight as bf16): within
+    1e-5 of the output range of the float64 oracle, like the SIMT kernel, and within the same bound of that kernel;
+    row-major and head-split stores, ragged M and N, several tiles per CTA."""
+    r = rng(m + n + k)
+    x = (r.standard_normal((m, k)) * np.exp(r.standard_normal((m, 1)))).astype(F32)  # rows of different magnitude
+    w = (r.standard_normal((n, k)) * 0.02).astype(F32)
+    b = (r.standard_normal(n) * 0.1).astype(F32)
+    st = om.State(w={"l.w": w, "l.b": b}, amax={"l.w": float(F32(4 * w.std()))})
+    ref = om.qlinear(st, x, "l", quant_in=False, quant_out=False)
+    wq, s_w = oq.quantize(w, st.amax["l.w"])
+    dx, dw, db = dev(x), dev(wq), dev(b)
+    x3 = empty((m, 3 * k), torch.bfloat16)
+    wb = empty((n, k), torch.bfloat16)
+    L.check(L.lib.ls100_split_bf16x3(ctx().handle, ptr(dx), k, m, k, ptr(x3), None), "split")
+    L.check(L.lib.ls100_i8_to_bf16(ctx().handle, ptr(dw), k, n, k, ptr(wb), None), "i8->bf16")
+    sync_check()
+    assert np.array_equal(wb.float().cpu().numpy(), wq.astype(F32))
+    parts = x3.float().cpu().numpy().reshape(m, 3, k).astype(np.float64)
+    assert np.abs(parts.sum(1) - x.astype(np.float64)).max() <= np.abs(x).max() * 2.0 ** -26
+    shape = (m // seq, n // 64, seq, 64) if seq else (m, n)
+    out = empty(shape, torch.float32)
+    args = L.ProjTcArgs(x3=ptr(x3), w_bf16=ptr(wb), s_w=float(s_w), bias=ptr(db), m=m, n=n, k=k, out=ptr(out), ldo=n,
+                        split_seq=seq)
+    L.call("ls100_proj_tc", ctx(), args)
+    out2 = empty(shape, torch.float32)
+    a2 = L.ProjF32Args(x=ptr(dx), ldx=k, w=ptr(dw), ldw=k, s_w=float(s_w), bias=ptr(db), m=m, n=n, k=k, out=ptr(out2), ldo=n,
+                       split_seq=seq)
+    L.call("ls100_proj_f32", ctx(), a2)
+    sync_check()
+    got, simt = out.cpu().numpy(), out2.cpu().numpy()
+    if seq:
+        got = got.transpose(0, 2, 1, 3).reshape(m, n)
+        simt = simt.transpose(0, 2, 1, 3).reshape(m, n)
+    tol = np.abs(ref).max() * 1e-5
+    print("tensor-core vs oracle", np.abs(got - ref).max(), "SIMT vs oracle", np.abs(simt - ref).max(), "tol", tol)
+    assert np.abs(got - ref).max() <= tol
+    assert np.abs(got - simt).max() <= tol
+
+
 # ----------------------------------------------------------------------------- beam search
 @pytest.mark.parametrize("V,ties", [(32000, False), (1000, True), (37, True), (40000, False)])
 def test_beam_step_matches_oracle(V, ties):
