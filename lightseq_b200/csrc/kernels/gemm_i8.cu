@@ -538,15 +538,15 @@ __global__ void __launch_bounds__(320) gemm_i8_tc_kernel(const __grid_constant__
 // ---------------------------------------------------------------------------------------------
 // Persistent variant for problems of many tiles: one CTA per SM walks a static list of 128 x 256
 // tiles. The accumulator is double-buffered in TMEM (2 x 256 columns), so the MMAs of tile i+1 run
-// while eight epilogue warps (two per TMEM lane quarter, each pair splitting the 256 columns) drain
+// while sixteen epilogue warps (four per TMEM lane quarter, 64 of the 256 columns each) drain
 // tile i; with K of a few hundred the epilogue is the longer of the two and it is no longer exposed.
 //   warp 0     TMA producer, one ring of P_STAGES stages running across tile boundaries
 //   warp 1     TMEM allocator + MMA issuer
-//   warps 2-9  epilogue
+//   warps 2-17 epilogue
 // No barrier couples the epilogue warps to each other: each stages its own bias / offset slice.
 constexpr int P_BN = 256;
 constexpr int P_STAGES = 4;
-constexpr int P_EPI_WARPS = 8;
+constexpr int P_EPI_WARPS = 16;
 constexpr int P_THREADS = 64 + 32 * P_EPI_WARPS;
 
 struct PersistSmem {
@@ -555,7 +555,8 @@ struct PersistSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = P_STAGES * STAGE_BYTES;
   static constexpr int VEC_OFFSET = BAR_OFFSET + 256;
-  static constexpr int VEC_PER_WARP = (P_BN / 2) * 8;  // 128 fp32 bias + 128 int32 offsets
+  static constexpr int P_COLS = P_BN / (P_EPI_WARPS / 4);  // columns of a tile per epilogue warp: 64
+  static constexpr int VEC_PER_WARP = P_COLS * 8;          // 64 fp32 bias + 64 int32 offsets
   static constexpr int TOTAL = VEC_OFFSET + P_EPI_WARPS * VEC_PER_WARP + 1024;
 };
 
@@ -667,24 +668,25 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
       }
     }
   } else {
+    constexpr int COLS = SM::P_COLS;
     const int ew = warp - 2;
     const int quarter = warp & 3;  // the TMEM lanes a warp may read are fixed by its index modulo 4
-    const int half = ew >> 2;      // which 128 of the tile's 256 columns
+    const int grp = ew >> 2;       // which 64 of the tile's 256 columns
     float* s_bias = reinterpret_cast<float*>(smem + SM::VEC_OFFSET + ew * SM::VEC_PER_WARP);
-    int* s_off = reinterpret_cast<int*>(s_bias + P_BN / 2);
-    float rr[32];
+    int* s_off = reinterpret_cast<int*>(s_bias + COLS);
+    float rr[16];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) rr[j] = 0.f;
+    for (int j = 0; j < 16; ++j) rr[j] = 0.f;
     pdl_wait();  // the residual (and everything written below) belongs to the chain of kernels before this one
     int local = 0;
     bool dead = false;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const int buf = local & 1;
-      const int n0 = (tile % tiles_n) * P_BN + half * (P_BN / 2);
+      const int n0 = (tile % tiles_n) * P_BN + grp * COLS;
       const int row = (tile / tiles_n) * BM + quarter * 32 + lane;
       __syncwarp();
 #pragma unroll
-      for (int i = lane; i < P_BN / 2; i += 32) {
+      for (int i = lane; i < COLS; i += 32) {
         const int n = n0 + i;
         s_bias[i] = (p.bias != nullptr && n < p.n) ? __ldg(p.bias + n) : 0.f;
         s_off[i] = (p.w_off != nullptr && n < p.n) ? __ldg(p.w_off + n) : 0;
@@ -699,21 +701,21 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
         continue;
       }
       tc_fence_after();
-      const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + half * (P_BN / 2));
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + grp * COLS);
 #pragma unroll 1
-      for (int c0 = 0; c0 < P_BN / 2; c0 += 32) {
-        const bool last = (c0 + 32 == P_BN / 2) || (n0 + c0 + 32 >= p.n);
+      for (int c0 = 0; c0 < COLS; c0 += 16) {
+        const bool last = (c0 + 16 == COLS) || (n0 + c0 + 16 >= p.n);
         if (n0 + c0 < p.n) {
-          uint32_t r[32];
-          tmem_ld32(t_addr + (uint32_t)c0, r);
+          uint32_t r[16];
+          tmem_ld16(t_addr + (uint32_t)c0, r);
           tmem_ld_wait();
           if (last) {  // this warp's part of the buffer is in registers: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
           }
-          epilogue_chunk<P_BN>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, false);
-        } else if (c0 == 0) {  // the whole half lies beyond N: nothing to read, release at once
+          epilogue_chunk<P_BN, 16>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, false);
+        } else if (c0 == 0) {  // the whole group lies beyond N: nothing to read, release at once
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
