@@ -13,6 +13,8 @@
 // -inf for padding and -1e4 for the causal mask; both give probability 0 in fp32), softmax
 // in fp32. Summation order differs from torch's bmm, so outputs agree to rounding, not
 // bit for bit; the int8 result can differ by one step on a small fraction of elements.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ctx.h"
 
@@ -606,6 +608,11 @@ static size_t attn_cross_smem(int nb) {
 
 }  // namespace ls100
 
+namespace ls100 {  // attn_tc.cu
+int attn_self_tc_launch(ls100_ctx* ctx, const ls100_attn_self_args* a, cudaStream_t st);
+int attn_self_tc_init_device();
+}  // namespace ls100
+
 using namespace ls100;
 
 // Opts the cross-attention kernel into its shared-memory size (two K/V tiles) on the current device
@@ -615,6 +622,7 @@ int ls100_attn_init_device() {
   ok = ok && cudaFuncSetAttribute(attn_cross_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_cross_smem(2)) == cudaSuccess;
   ok = ok && cudaFuncSetAttribute(attn_cross_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_cross_smem(4)) == cudaSuccess;
   ok = ok && cudaFuncSetAttribute(attn_cross_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_cross_smem(8)) == cudaSuccess;
+  ok = ok && attn_self_tc_init_device() == LS100_OK;
   return ok ? LS100_OK : LS100_ERR_CUDA;
 }
 
@@ -627,6 +635,10 @@ extern "C" int ls100_attn_self(ls100_ctx* ctx, const ls100_attn_self_args* a, ls
   if (a->k_cache && (a->bias || a->max_step < a->seq || (((uintptr_t)a->k_cache) & 15) || (((uintptr_t)a->v_cache) & 15)))
     return LS100_ERR_BAD_ARG;
   if (a->heads > 65535 || a->batch > 65535) return LS100_ERR_UNSUPPORTED;
+  // tensor-core kernel: pairs of heads, no KV cache to fill, at least one full key tile's worth of work
+  static const bool simt_only = getenv("LS100_ATTN_SIMT") != nullptr;
+  if (!simt_only && (a->heads & 1) == 0 && !a->k_cache && a->seq >= 16 && (long long)a->batch * a->seq < (1ll << 31))
+    return attn_self_tc_launch(ctx, a, (cudaStream_t)stream_);
   dim3 grid((a->seq + 63) / 64, a->heads, a->batch);
   const float so = a->amax_out / 127.0f;
   return ls100_launch(attn_self_kernel, grid, dim3(64), 0, (cudaStream_t)stream_, *a, so, 1.0f / so) == cudaSuccess

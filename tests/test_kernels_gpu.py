@@ -273,7 +273,8 @@ def _int8_close(got, ref, max_rate):
 
 
 @pytest.mark.parametrize("B,S,heads,causal,with_bias", [(3, 60, 8, 0, 1), (2, 150, 4, 0, 1), (2, 100, 4, 1, 0),
-                                                       (1, 1, 2, 0, 1), (4, 64, 2, 0, 1)])
+                                                       (1, 1, 2, 0, 1), (4, 64, 2, 0, 1), (2, 512, 12, 0, 1), (2, 300, 4, 1, 1),
+                                                       (3, 130, 6, 0, 0), (2, 90, 3, 0, 1), (5, 17, 2, 1, 1)])
 def test_attn_self_matches_oracle(B, S, heads, causal, with_bias):
     H = heads * 64
     r = rng(B * S)
