@@ -272,6 +272,20 @@ def kernel_cases(torch, L, conf, B, S, step):
         L.call("ls100_attn_dec", CTX[0], a, st)
 
     cases["attn_dec"] = (attn_dec, T * H * (2 * (step + 1) + 3), "hbm", f"attn_dec_kernel, rows {T}, history {step + 1}")
+    # encoder self-attention at a BERT-base shape (32 sentences x 512 tokens, 12 heads), tensor-core kernel
+    eb, es, eh = 32, 512, 12
+    eqkv = [i8(eb * es, 3 * eh * 64) for _ in range(4)]
+    eo8 = torch.empty(eb * es, eh * 64, dtype=torch.int8, device=dev)
+    ebias = torch.zeros(3 * eh * 64, device=dev)
+    epm = torch.zeros(eb, es, dtype=torch.uint8, device=dev)
+
+    def attn_self(i, st):
+        a = L.AttnSelfArgs(qkv=eqkv[i % 4].data_ptr(), ld_qkv=3 * eh * 64, s_qkv=0.02, bias=ebias.data_ptr(), pad_mask=epm.data_ptr(),
+                           batch=eb, seq=es, heads=eh, causal=0, amax_out=1.0, out=eo8.data_ptr(), ld_out=eh * 64, k_cache=None,
+                           v_cache=None, max_step=0)
+        L.call("ls100_attn_self", CTX[0], a, st)
+
+    cases["attn_self"] = (attn_self, eb * es * eh * 64 * 4, "hbm", f"attn_self_tc_kernel, {eb} x {es} tokens, {eh} heads")
     # cross attention
     nx = 6
     kx, vx = [torch.randn(B * S, H, device=dev) for _ in range(nx)], [torch.randn(B * S, H, device=dev) for _ in range(nx)]
@@ -629,7 +643,7 @@ def main():
     ap.add_argument("--decode-steps", type=int, default=-1,
                     help="cap the number of decode steps per generation (profiling aid; the result is not a bench value)")
     ap.add_argument("--kernel", default=None,
-                    help="run one kernel family alone (gemm_dec, gemm_dec_ln, gemm_logits, gemm_enc_qkv, gemm_square, attn_dec, attn_cross, beam_topk, ln_quant)")
+                    help="run one kernel family alone (gemm_dec, gemm_dec_ln, gemm_logits, gemm_enc_qkv, gemm_square, attn_self, attn_dec, attn_cross, beam_topk, ln_quant)")
     ap.add_argument("--workload", default=None, choices=["bert", "gpt", "big", "eos"],
                     help="run another BASELINE configuration (BERT-base, GPT-2 medium, Transformer-big) on one GPU, or the "
                          "benchmark model with a boosted EOS (early-stop bookkeeping)")

@@ -9,30 +9,36 @@
 //                 V (int8) is exact in bf16. Threads write P and V^T into shared memory in the swizzled K-major layout.
 // The biases never enter a GEMM: with q = s*Qi + bq, k = s*Ki + bk the score is
 //   (q.k)/8 = s^2/8 * (Qi.Ki) + s/8 * (bq.Ki) + terms constant along a query's row (which softmax cancels),
-// and out = s * (P.Vi)/sum(P) + bv. Softmax is exact fp32, one thread per query row (no shuffles). Two passes over
-// the keys: the first finds each row's maximum (QK^T is cheap), the second accumulates O with that fixed maximum, so
-// the accumulator in TMEM never needs rescaling.
-// Warps: 0 = TMA + MMA issue (one elected lane), 1 = TMEM allocation, 2-9 = softmax / epilogue (head = (w-2)/4, TMEM
-// lane quarter = w % 4). Phases are separated by CTA barriers; every mbarrier wait is bounded.
+// and out = s * (P.Vi)/sum(P) + bv. Softmax is exact fp32, one thread per query row (no shuffles), in the log2
+// domain (2^x is one instruction). Two passes over the keys: the first finds each row's maximum (QK^T is cheap), the
+// second accumulates O with that fixed maximum, so the accumulator in TMEM never needs rescaling.
+// Warps: 0-1 = key mask and the bias term of the scores (thread 0 also issues every TMA load and MMA), 1 = TMEM
+// allocation, 2-9 = softmax / epilogue (head = (w-2)/4, TMEM lane quarter = w % 4) and the V^T conversion. Per key
+// tile the CTA meets at two barriers (preparation done; softmax done); the tensor pipe runs P.V of tile g and the
+// scores of tile g+1 while the threads prepare tile g+1, and the K tile of g+1 is fetched while tile g's softmax
+// runs. V comes by plain 16-byte loads issued at the start of a tile's preparation. Every mbarrier wait is bounded.
 #include <cuda_bf16.h>
 
 #include "common.cuh"
 #include "ctx.h"
+
+// Phase timestamps for experiment builds; compiles to nothing in the library.
+#ifndef AT_TRACE
+#define AT_TRACE(pass, kt, slot)
+#endif
 
 namespace ls100 {
 
 constexpr int AT_BQ = 128;  // queries per CTA
 constexpr int AT_BK = 64;   // keys per tile
 constexpr int AT_THREADS = 320;
-// shared memory map (every tile 1024-byte aligned). The raw V tile lands inside the P area: it is transposed into
-// AT_VT before the softmax threads write P, and the next V load is issued only after the P.V MMAs have completed.
-// 107 KB per CTA, so two CTAs share an SM (and its 512 TMEM columns).
+constexpr int AT_SOFTMAX_WARPS = 8;  // warps 2..9
+// shared memory map (every tile 1024-byte aligned): 107 KB per CTA, so two CTAs share an SM (and its 512 TMEM columns)
 constexpr int AT_Q = 0;                        // [128 q][128 B]  int8, two heads
 constexpr int AT_K = AT_Q + AT_BQ * 128;       // [64 keys][128 B]
 constexpr int AT_P = AT_K + AT_BK * 128;       // [head][hi|lo][128 q][64 keys bf16 = 128 B]
-constexpr int AT_V = AT_P;                     // [64 keys][128 B] raw int8 V, alive until transposed
 constexpr int AT_VT = AT_P + 4 * AT_BQ * 128;  // [head][64 dims][64 keys bf16 = 128 B]
-constexpr int AT_MISC = AT_VT + 2 * 64 * 128;  // cj[2][64] f32, key mask[64], bq[128] f32, barriers
+constexpr int AT_MISC = AT_VT + 2 * 64 * 128;  // bias terms, key-mask words, bq[128] f32, barriers
 constexpr int AT_SMEM = AT_MISC + 2048 + 1024;
 constexpr int AT_TMEM_COLS = 256;              // S: 2 heads x 64 columns (int32), O: 2 heads x 64 columns (fp32)
 
@@ -68,16 +74,22 @@ struct AttnTcParams {
   float s_out, rs_out;
   int* err;
 };
-// Bounded wait in time rather than in polls (a failed poll may itself suspend the thread for a while): gives up
-// after about 0.2 s of SM clock, and the caller then leaves the kernel with the error word set.
-__device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait, in time rather than in polls (a failed poll may itself suspend the thread for a while): gives up
+// after about 0.2 s of SM clock or as soon as another thread of the CTA has given up, and raises the CTA's abort
+// flag; the caller then skips its remaining work and the kernel ends with the error word set.
+__device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  while (clock64() - t0 < 400000000ll) {
+  while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag || clock64() - t0 > 400000000ll) {
+      *abort_flag = 1;
+      return false;
+    }
   }
-  return false;
 }
+// named barrier of warps 1..9 (the mask warp and the softmax warps); the issuer warp never joins it
+__device__ __forceinline__ void at_bar_prep() { asm volatile("bar.sync 1, 288;" ::: "memory"); }
 
 // 16 int8 -> 16 floats through the mantissa of 2^23 (no conversion unit), as in attn.cu
 __device__ __forceinline__ void at_unpack16(const int4 v, float (&f)[16]) {
@@ -92,17 +104,27 @@ __device__ __forceinline__ void at_unpack16(const int4 v, float (&f)[16]) {
   }
 }
 
+__device__ __forceinline__ float at_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                      const __grid_constant__ CUtensorMap tm_kv,
                                                                      const AttnTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  float* cj = reinterpret_cast<float*>(smem + AT_MISC);        // [2][64] bias term of the scores of this key tile
-  uint8_t* kmask = smem + AT_MISC + 512;                       // [64]    1 = key masked (padding or past the end)
-  float* bq = reinterpret_cast<float*>(smem + AT_MISC + 640);  // [128]   query bias of the two heads
-  uint64_t* bar_tma = reinterpret_cast<uint64_t*>(smem + AT_MISC + 1536);
-  uint64_t* bar_mma = bar_tma + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mma + 1);
+  float* cj = reinterpret_cast<float*>(smem + AT_MISC);                // [2 buffers][2 heads][64] bias term of a tile's scores
+  uint32_t* kmw = reinterpret_cast<uint32_t*>(smem + AT_MISC + 1024);  // [2 buffers][2] bit j of word w: key 32 w + j is masked
+  float* bq = reinterpret_cast<float*>(smem + AT_MISC + 1088);         // [128] query bias of the two heads
+  uint64_t* bar_k = reinterpret_cast<uint64_t*>(smem + AT_MISC + 1600);  // K tile (and, once, the Q tile) has landed
+  uint64_t* bar_s = bar_k + 1;                                           // the score MMAs of a tile have completed
+  uint64_t* bar_pv = bar_k + 2;                                          // the P.V MMAs of a tile have completed
+  uint64_t* bar_b = bar_k + 3;  // one arrival per softmax warp: it has read the K tile (bias term written)
+  uint64_t* bar_c = bar_k + 4;  // one arrival per softmax warp: S is in registers, P and V^T are in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_k + 5);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const ls100_attn_self_args& a = p.a;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -113,8 +135,12 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __gri
   if (tid == 0) {
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_kv);
-    mbar_init(bar_tma, 1);
-    mbar_init(bar_mma, 1);
+    mbar_init(bar_k, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_pv, 1);
+    mbar_init(bar_b, AT_SOFTMAX_WARPS);
+    mbar_init(bar_c, AT_SOFTMAX_WARPS);
+    *abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -129,141 +155,46 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __gri
   pdl_launch_dependents();  // only now: a dependent grid's CTAs must not take the TMEM columns this CTA still needs
   pdl_wait();
 
-  // softmax / epilogue identity (warps 2..9): one query row of one head per thread
-  const int head = (warp - 2) >> 2, quarter = warp & 3;
-  const int qrow = quarter * 32 + lane, q_idx = q0 + qrow;
-  const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
-  const float sc = __fmul_rn(__fmul_rn(a.s_qkv, a.s_qkv), 0.125f), cs = __fmul_rn(a.s_qkv, 0.125f);
   const int k_end = a.causal ? min(S, q0 + AT_BQ) : S;
   const int n_kt = (k_end + AT_BK - 1) / AT_BK;
+  const int n_g = 2 * n_kt;  // tile visits: pass 0 (row maxima) then pass 1 (P and O)
 
-  uint32_t ph_tma = 0, ph_mma = 0;
-  if (tid == 0) {
-    mbar_expect_tx(bar_tma, AT_BQ * 128);
-    tma_load_2d(smem + AT_Q, &tm_q, bar_tma, hp * 128, row_base + q0);
-  }
-  bool ok = at_wait(bar_tma, ph_tma);
-  ph_tma ^= 1;
-
-  float m_run = -INFINITY, l_run = 0.f;
-  bool alive = true;
-  for (int pass = 0; pass < 2 && alive; ++pass) {
-    for (int kt = 0; kt < n_kt; ++kt) {
-      const int k0 = kt * AT_BK;
-      // every reader of the previous tile (shared memory and the S columns of TMEM) is done
-      alive = __syncthreads_and(ok);
-      if (!alive) break;
-      if (tid == 0) {
-        mbar_expect_tx(bar_tma, pass ? 2 * AT_BK * 128 : AT_BK * 128);
-        tma_load_2d(smem + AT_K, &tm_kv, bar_tma, H + hp * 128, row_base + k0);
-        if (pass) tma_load_2d(smem + AT_V, &tm_kv, bar_tma, 2 * H + hp * 128, row_base + k0);
-      }
-      if (tid < 64) {
-        const int key = k0 + tid;
-        uint8_t mk = 1;
-        if (key < S) mk = a.pad_mask ? a.pad_mask[(long long)b * S + key] : 0;
-        kmask[tid] = mk;
-      }
-      ok = at_wait(bar_tma, ph_tma);
-      ph_tma ^= 1;
-      if (tid == 0) {  // S[head] = Q[head] . K[head]^T : 64 dims = two K = 32 MMAs per head
+  if (warp == 0) {
+    // ------------------------------------------------------------ issuer: every TMA load and every MMA
+    if (lane == 0) {
+      const uint64_t q_desc = at_desc(smem_u32(smem + AT_Q)), k_desc = at_desc(smem_u32(smem + AT_K));
+      // S[head] = Q[head] . K[head]^T for the K tile in shared memory (64 dims = two K = 32 MMAs per head)
+      auto issue_scores = [&]() {
         tc_fence_after();
-        const uint32_t qa = smem_u32(smem + AT_Q), ka = smem_u32(smem + AT_K);
-        const uint64_t qd = at_desc(qa), kd = at_desc(ka);
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
           for (int kk = 0; kk < 2; ++kk)
-            tc_mma_i8(tmem_base + (uint32_t)(hh * 64), qd + (uint64_t)((hh * 2 + kk) * 2), kd + (uint64_t)((hh * 2 + kk) * 2),
+            tc_mma_i8(tmem_base + (uint32_t)(hh * 64), q_desc + (uint64_t)((hh * 2 + kk) * 2), k_desc + (uint64_t)((hh * 2 + kk) * 2),
                       at_idesc_i8(), kk > 0 ? 1u : 0u);
-        tc_commit(bar_mma);
-      }
-      // meanwhile: the bias term s/8 * (bq . Ki) of this tile's scores
-      if (tid >= 64 && tid < 192) {
-        const int t = tid - 64, hh = t >> 6, key = t & 63;
-        float acc = 0.f;
-        if (a.bias) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            float f[16];
-            at_unpack16(*reinterpret_cast<const int4*>(smem + AT_K + at_sw(key, hh * 64 + c * 16)), f);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) acc = fmaf(bq[hh * 64 + c * 16 + i], f[i], acc);
-          }
+        tc_commit(bar_s);
+      };
+      mbar_expect_tx(bar_k, AT_BQ * 128 + AT_BK * 128);
+      tma_load_2d(smem + AT_Q, &tm_q, bar_k, hp * 128, row_base + q0);
+      tma_load_2d(smem + AT_K, &tm_kv, bar_k, H + hp * 128, row_base);
+      bool ok = at_wait(bar_k, 0, abort_flag);
+      if (ok) issue_scores();
+      for (int g = 0; g < n_g && ok; ++g) {
+        const int pass = g >= n_kt ? 1 : 0, kt = g - pass * n_kt;
+        AT_TRACE(pass, kt, 0);
+        if (g + 1 < n_g) {  // the K tile is free once its scores are done and the threads have read it: fetch the next
+          ok = at_wait(bar_s, (uint32_t)g & 1u, abort_flag) && at_wait(bar_b, (uint32_t)g & 1u, abort_flag);
+          if (!ok) break;
+          const int kn = (g + 1 >= n_kt) ? g + 1 - n_kt : g + 1;
+          mbar_expect_tx(bar_k, AT_BK * 128);
+          tma_load_2d(smem + AT_K, &tm_kv, bar_k, H + hp * 128, row_base + kn * AT_BK);
         }
-        cj[t] = __fmul_rn(acc, cs);
-      }
-      // and, in the second pass, V^T in bf16: task = (key, 16-byte chunk of the two heads' 128 bytes)
-      if (pass && tid >= 64) {
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          const int task = (tid - 64) + r * 256, key = task & 63, c = task >> 6;  // c in 0..7
-          float f[16];
-          at_unpack16(*reinterpret_cast<const int4*>(smem + AT_V + at_sw(key, c * 16)), f);
-          uint8_t* vt = smem + AT_VT + (c >> 2) * (64 * 128);
-          const int d0 = (c & 3) * 16;
-#pragma unroll
-          for (int i = 0; i < 16; ++i)  // a small integer is exact in bf16: keep the upper half of the float
-            *reinterpret_cast<uint16_t*>(vt + at_sw(d0 + i, key * 2)) = (uint16_t)(__float_as_uint(f[i]) >> 16);
-        }
-      }
-      alive = __syncthreads_and(ok);  // cj, kmask (and V^T) are written; raw V is consumed
-      if (!alive) break;
-      ok = at_wait(bar_mma, ph_mma);
-      ph_mma ^= 1;
-      tc_fence_after();
-
-      if (warp >= 2) {
-        const float* cjh = cj + head * 64;
-#pragma unroll 1
-        for (int c0 = 0; c0 < 64; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(t_lane + (uint32_t)(head * 64 + c0), r);
-          tmem_ld_wait();
-          float sv[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int kk = c0 + j;
-            const bool vis = !kmask[kk] && (!a.causal || k0 + kk <= q_idx);
-            // |Qi.Ki| <= 64 * 127^2 < 2^22: int -> float by adding into the mantissa of 1.5 * 2^23
-            const float sf = __fsub_rn(__uint_as_float(r[j] + 0x4B400000u), 12582912.f);
-            sv[j] = vis ? fmaf(sf, sc, cjh[kk]) : -INFINITY;
-          }
-          if (pass == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) m_run = fmaxf(m_run, sv[j]);
-          } else {
-            uint8_t* ph = smem + AT_P + (head * 2) * (AT_BQ * 128);
-            uint8_t* pl = ph + AT_BQ * 128;
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {  // 8 keys = one 16-byte chunk of bf16
-              uint32_t hi[4], lo[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float s0 = sv[g * 8 + e * 2], s1 = sv[g * 8 + e * 2 + 1];
-                const float p0 = (s0 == -INFINITY) ? 0.f : __expf(s0 - m_run);
-                const float p1 = (s1 == -INFINITY) ? 0.f : __expf(s1 - m_run);
-                l_run += p0 + p1;
-                const __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-                const float2 hf = __bfloat1622float2(h2);
-                const __nv_bfloat162 l2 = __floats2bfloat162_rn(p0 - hf.x, p1 - hf.y);
-                hi[e] = *reinterpret_cast<const uint32_t*>(&h2);
-                lo[e] = *reinterpret_cast<const uint32_t*>(&l2);
-              }
-              const int off = at_sw(qrow, (c0 + g * 8) * 2);
-              *reinterpret_cast<uint4*>(ph + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-              *reinterpret_cast<uint4*>(pl + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-            }
-          }
-        }
-      }
-      if (pass) {
-        fence_proxy_async();  // P and V^T were written by threads; the MMAs read them through the async proxy
-        tc_fence_before();
-        alive = __syncthreads_and(ok);
-        if (!alive) break;
-        if (tid == 0) {  // O[head] += P_hi . V + P_lo . V : 64 keys = four K = 16 MMAs per term
-          tc_fence_after();
+        AT_TRACE(pass, kt, 1);
+        ok = at_wait(bar_c, (uint32_t)g & 1u, abort_flag);  // softmax of tile g is done
+        if (!ok) break;
+        AT_TRACE(pass, kt, 2);
+        tc_fence_after();
+        if (pass) {  // O[head] += P_hi . V + P_lo . V : 64 keys = four K = 16 MMAs per term
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
             const uint64_t vd = at_desc(smem_u32(smem + AT_VT + hh * (64 * 128)));
@@ -276,50 +207,211 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __gri
                             (kt > 0 || term > 0 || kk > 0) ? 1u : 0u);
             }
           }
-          tc_commit(bar_mma);
+          tc_commit(bar_pv);
         }
-        ok = at_wait(bar_mma, ph_mma);  // P, V^T and the raw-V area may be overwritten after this
-        ph_mma ^= 1;
-      } else {
-        tc_fence_before();  // the S columns are read; ordered before the next tile's MMA by the barrier at the loop top
+        AT_TRACE(pass, kt, 3);
+        if (g + 1 < n_g) {  // scores of the next tile (the S columns are in the threads' registers by now)
+          ok = at_wait(bar_k, (uint32_t)(g + 1) & 1u, abort_flag);
+          if (ok) issue_scores();
+        }
+        AT_TRACE(pass, kt, 4);
       }
     }
-  }
-
-  // out = s * O / sum(P) + bv -> clip -> int8 (a row with every key masked gives 0, as the SIMT kernel does)
-  if (alive) alive = __syncthreads_and(ok);
-  if (alive && warp >= 2) {  // whole warps: the TMEM load is warp-collective, only the store is per row
-    tc_fence_after();
-    const float inv = (l_run > 0.f) ? __fdividef(a.s_qkv, l_run) : 0.f;
-    const float bsel = (l_run > 0.f && a.bias) ? 1.f : 0.f;
-    const float* bv = a.bias ? a.bias + 2 * H + hp * 128 + head * 64 : nullptr;
-    int8_t* op = a.out + ((long long)row_base + q_idx) * a.ld_out + hp * 128 + head * 64;
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ key mask of each tile, as two 32-bit words
+    for (int g = 0; g < n_g; ++g) {
+      const int kt = g >= n_kt ? g - n_kt : g, k0 = kt * AT_BK;
+      uint32_t m0 = 1, m1 = 1;
+      if (k0 + lane < S) m0 = a.pad_mask ? a.pad_mask[(long long)b * S + k0 + lane] : 0;
+      if (k0 + 32 + lane < S) m1 = a.pad_mask ? a.pad_mask[(long long)b * S + k0 + 32 + lane] : 0;
+      const uint32_t w0 = __ballot_sync(0xffffffffu, m0 != 0), w1 = __ballot_sync(0xffffffffu, m1 != 0);
+      if (lane == 0) {
+        kmw[(g & 1) * 2] = w0;
+        kmw[(g & 1) * 2 + 1] = w1;
+      }
+      at_bar_prep();  // with the softmax warps: mask and bias term of tile g are written
+    }
+  } else {
+    // ------------------------------------------------------------ softmax warps (2..9): one query row of one head per thread
+    const int idx = tid - 64;
+    const int head = (warp - 2) >> 2, quarter = warp & 3;
+    const int qrow = quarter * 32 + lane, q_idx = q0 + qrow;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    // scores are kept in the log2 domain: exp(x) = 2^(x log2 e)
+    const float sc = __fmul_rn(__fmul_rn(__fmul_rn(a.s_qkv, a.s_qkv), 0.125f), 1.4426950408889634f);
+    const float cs = __fmul_rn(__fmul_rn(a.s_qkv, 0.125f), 1.4426950408889634f);
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int g = 0; g < n_g; ++g) {
+      const int pass = g >= n_kt ? 1 : 0, kt = g - pass * n_kt, k0 = kt * AT_BK;
+      float* cjb = cj + (g & 1) * 128;
+      if (g == n_kt && m_run == -INFINITY) m_run = 0.f;  // a row with every key masked: all P are 0
+      AT_TRACE(pass, kt, 0);
+      // ---- preparation of tile g (the tensor pipe may still be running P.V of tile g-1 and the scores of tile g)
+      int4 vraw[2];
+      if (pass) {  // this thread's two 16-byte pieces of the V tile: issued first, used last
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int task = idx + r * 256, key = task & 63, c = task >> 6;  // c in 0..7: 16-byte chunk of the two heads
+          vraw[r] = make_int4(0, 0, 0, 0);
+          if (k0 + key < S)
+            vraw[r] = __ldg(reinterpret_cast<const int4*>(a.qkv + ((long long)row_base + k0 + key) * a.ld_qkv + 2 * H + hp * 128 + c * 16));
+        }
+      }
+      ok = ok && at_wait(bar_k, (uint32_t)g & 1u, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {  // bias term s/8 * (bq . Ki): four lanes share a key, 16 dims each
+        const int part = idx & 3, key = idx >> 2;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+          if (a.bias) {
+            float f[16];
+            at_unpack16(*reinterpret_cast<const int4*>(smem + AT_K + at_sw(key, hh * 64 + part * 16)), f);
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+              const float4 b4 = *reinterpret_cast<const float4*>(bq + hh * 64 + part * 16 + i);
+              acc[0] = fmaf(b4.x, f[i], acc[0]);
+              acc[1] = fmaf(b4.y, f[i + 1], acc[1]);
+              acc[2] = fmaf(b4.z, f[i + 2], acc[2]);
+              acc[3] = fmaf(b4.w, f[i + 3], acc[3]);
+            }
+          }
+          float d = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+          d += __shfl_xor_sync(0xffffffffu, d, 1);
+          d += __shfl_xor_sync(0xffffffffu, d, 2);
+          if (part == 0) cjb[hh * 64 + key] = __fmul_rn(d, cs);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_b);  // this warp no longer reads the K tile
+      if (pass && ok) {
+        if (kt > 0) ok = at_wait(bar_pv, (uint32_t)(kt - 1) & 1u, abort_flag);  // P.V of the previous tile no longer reads V^T and P
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {  // V^T in bf16, written in the swizzled K-major layout the MMA reads
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const int task = idx + r * 256, key = task & 63, c = task >> 6;
+            float f[16];
+            at_unpack16(vraw[r], f);
+            uint8_t* vt = smem + AT_VT + (c >> 2) * (64 * 128);
+            const int d0 = (c & 3) * 16;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)  // a small integer is exact in bf16: keep the upper half of the float
+              *reinterpret_cast<uint16_t*>(vt + at_sw(d0 + i, key * 2)) = (uint16_t)(__float_as_uint(f[i]) >> 16);
+          }
+          fence_proxy_async();
+        }
+      }
+      AT_TRACE(pass, kt, 1);
+      at_bar_prep();  // mask (warp 1) and bias term of tile g are visible to every softmax thread
+      if (ok) ok = at_wait(bar_s, (uint32_t)g & 1u, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      AT_TRACE(pass, kt, 2);
+      if (ok) {
+        tc_fence_after();
+        uint64_t vis = ~(((uint64_t)kmw[(g & 1) * 2 + 1] << 32) | (uint64_t)kmw[(g & 1) * 2]);
+        if (a.causal) {
+          const int d = q_idx - k0;  // keys 0..d of this tile are visible
+          vis &= d >= 63 ? ~0ull : (d < 0 ? 0ull : ((2ull << d) - 1ull));
+        }
+        const float* cjh = cjb + head * 64;
 #pragma unroll 1
-    for (int c0 = 0; c0 < 64; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(t_lane + (uint32_t)(128 + head * 64 + c0), r);
-      tmem_ld_wait();
-      uint32_t w[8];
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          const uint32_t vw = c0 ? (uint32_t)(vis >> 32) : (uint32_t)vis;
+          uint32_t r[32];
+          tmem_ld32(t_lane + (uint32_t)(head * 64 + c0), r);
+          tmem_ld_wait();
+          float sv[32];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float v[4];
+          for (int j4 = 0; j4 < 32; j4 += 4) {
+            const float4 c4 = *reinterpret_cast<const float4*>(cjh + c0 + j4);
+            const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float x = __fmul_rn(__uint_as_float(r[j * 4 + e]), inv);
-          if (bv) x = fmaf(bsel, __ldg(bv + c0 + j * 4 + e), x);
-          v[e] = quant_s(clipf(x, a.amax_out), p.s_out, p.rs_out);
+            for (int e = 0; e < 4; ++e) {
+              const int j = j4 + e;
+              // |Qi.Ki| <= 64 * 127^2 < 2^22: int -> float by adding into the mantissa of 1.5 * 2^23
+              const float sf = __fsub_rn(__uint_as_float(r[j] + 0x4B400000u), 12582912.f);
+              sv[j] = ((vw >> j) & 1u) ? fmaf(sf, sc, cc[e]) : -INFINITY;
+            }
+          }
+          if (pass == 0) {
+            float m0 = fmaxf(sv[0], sv[1]), m1 = fmaxf(sv[2], sv[3]);
+#pragma unroll
+            for (int j = 4; j < 32; j += 2) {
+              m0 = fmaxf(m0, sv[j]);
+              m1 = fmaxf(m1, sv[j + 1]);
+            }
+            m_run = fmaxf(m_run, fmaxf(m0, m1));
+          } else {
+            uint8_t* ph = smem + AT_P + (head * 2) * (AT_BQ * 128);
+            uint8_t* pl = ph + AT_BQ * 128;
+            float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+            for (int gq = 0; gq < 4; ++gq) {  // 8 keys = one 16-byte chunk of bf16
+              uint32_t hi[4], lo[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float p0 = at_ex2(sv[gq * 8 + e * 2] - m_run), p1 = at_ex2(sv[gq * 8 + e * 2 + 1] - m_run);  // 2^-inf = 0
+                l0 += p0;
+                l1 += p1;
+                // hi = p truncated to bf16 (exact), lo = bf16(p - hi): |p - hi - lo| < 2^-16 p
+                const uint32_t b0 = __float_as_uint(p0) & 0xffff0000u, b1 = __float_as_uint(p1) & 0xffff0000u;
+                hi[e] = __byte_perm(b0, b1, 0x7632);
+                const __nv_bfloat162 l2 = __floats2bfloat162_rn(p0 - __uint_as_float(b0), p1 - __uint_as_float(b1));
+                lo[e] = *reinterpret_cast<const uint32_t*>(&l2);
+              }
+              const int off = at_sw(qrow, (c0 + gq * 8) * 2);
+              *reinterpret_cast<uint4*>(ph + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+              *reinterpret_cast<uint4*>(pl + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            }
+            l_run += l0 + l1;
+          }
         }
-        w[j] = pack_i8x4(v[0], v[1], v[2], v[3]);
+        if (pass) fence_proxy_async();  // P was written by threads; the MMAs read it through the async proxy
+        tc_fence_before();
       }
-      if (q_idx < S) {
-        *reinterpret_cast<uint4*>(op + c0) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(op + c0 + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+      AT_TRACE(pass, kt, 3);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_c);  // this warp has S in registers, its P and V^T in shared memory
+    }
+
+    // out = s * O / sum(P) + bv -> clip -> int8 (a row with every key masked gives 0, as the SIMT kernel does)
+    if (ok) ok = at_wait(bar_pv, (uint32_t)(n_kt - 1) & 1u, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {  // whole warps: the TMEM load is warp-collective, only the store is per row
+      tc_fence_after();
+      const float inv = (l_run > 0.f) ? __fdividef(a.s_qkv, l_run) : 0.f;
+      const float bsel = (l_run > 0.f && a.bias) ? 1.f : 0.f;
+      const float* bv = a.bias ? a.bias + 2 * H + hp * 128 + head * 64 : nullptr;
+      int8_t* op = a.out + ((long long)row_base + q_idx) * a.ld_out + hp * 128 + head * 64;
+#pragma unroll 1
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(t_lane + (uint32_t)(128 + head * 64 + c0), r);
+        tmem_ld_wait();
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float v[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float x = __fmul_rn(__uint_as_float(r[j * 4 + e]), inv);
+            if (bv) x = fmaf(bsel, __ldg(bv + c0 + j * 4 + e), x);
+            v[e] = quant_s(clipf(x, a.amax_out), p.s_out, p.rs_out);
+          }
+          w[j] = pack_i8x4(v[0], v[1], v[2], v[3]);
+        }
+        if (q_idx < S) {
+          *reinterpret_cast<uint4*>(op + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(op + c0 + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
       }
     }
   }
-  if (!alive && tid == 0 && p.err) atomicExch(p.err, (int)LS100_ERR_TIMEOUT);
   tc_fence_before();
   __syncthreads();
+  if (tid == 0 && *abort_flag && p.err) atomicExch(p.err, (int)LS100_ERR_TIMEOUT);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, AT_TMEM_COLS);
