@@ -10,13 +10,15 @@
 // The biases never enter a GEMM: with q = s*Qi + bq, k = s*Ki + bk the score is
 //   (q.k)/8 = s^2/8 * (Qi.Ki) + s/8 * (bq.Ki) + terms constant along a query's row (which softmax cancels),
 // and out = s * (P.Vi)/sum(P) + bv. Softmax is exact fp32, one thread per query row (no shuffles), in the log2
-// domain (2^x is one instruction). Two passes over the keys: the first finds each row's maximum (QK^T is cheap), the
-// second accumulates O with that fixed maximum, so the accumulator in TMEM never needs rescaling.
-// Warps: 0-1 = key mask and the bias term of the scores (thread 0 also issues every TMA load and MMA), 1 = TMEM
-// allocation, 2-9 = softmax / epilogue (head = (w-2)/4, TMEM lane quarter = w % 4) and the V^T conversion. Per key
-// tile the CTA meets at two barriers (preparation done; softmax done); the tensor pipe runs P.V of tile g and the
-// scores of tile g+1 while the threads prepare tile g+1, and the K tile of g+1 is fetched while tile g's softmax
-// runs. V comes by plain 16-byte loads issued at the start of a tile's preparation. Every mbarrier wait is bounded.
+// domain (2^x is one instruction) with packed two-lane fp32 arithmetic. Two passes over the keys: the first finds
+// each row's maximum (QK^T is cheap), the second accumulates O with that fixed maximum, so the accumulator in TMEM
+// never needs rescaling.
+// Warps: 0 = issuer (one lane: every TMA load and every MMA), 1 = TMEM allocation and the key-mask words of each
+// tile, 2-9 = softmax / epilogue (head = (w-2)/4, TMEM lane quarter = w % 4), which also compute the bias term of the
+// scores and convert V. The issuer and the other warps meet only through mbarriers (K landed, scores done, P.V done,
+// K tile read, softmax done), warps 1-9 through one named barrier per tile; the K tile of g+1 is fetched while tile
+// g's softmax runs, P.V of tile g and the scores of tile g+1 run while the threads prepare tile g+1, and V comes by
+// plain 16-byte loads issued at the start of a tile's preparation. Every mbarrier wait is bounded in time.
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -81,7 +83,9 @@ __device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t parity, volatile
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)  // the clock and the abort flag are looked at once per 32 polls
+      if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag || clock64() - t0 > 400000000ll) {
       *abort_flag = 1;
       return false;
@@ -102,6 +106,36 @@ __device__ __forceinline__ void at_unpack16(const int4 v, float (&f)[16]) {
     f[i * 4 + 2] = __fsub_rn(__uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7442)), 8388736.f);
     f[i * 4 + 3] = __fsub_rn(__uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7443)), 8388736.f);
   }
+}
+
+// packed fp32 pairs (one instruction for two lanes of arithmetic on sm_100)
+__device__ __forceinline__ float2 at_fma2(float2 a, float2 b, float2 c) {
+  uint64_t ra, rb, rc, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ float2 at_sub2(float2 a, float2 b) {
+  uint64_t ra, rb, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ float2 at_add2(float2 a, float2 b) {
+  uint64_t ra, rb, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
 }
 
 __device__ __forceinline__ float at_ex2(float x) {
@@ -240,7 +274,8 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __gri
     // scores are kept in the log2 domain: exp(x) = 2^(x log2 e)
     const float sc = __fmul_rn(__fmul_rn(__fmul_rn(a.s_qkv, a.s_qkv), 0.125f), 1.4426950408889634f);
     const float cs = __fmul_rn(__fmul_rn(a.s_qkv, 0.125f), 1.4426950408889634f);
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY;
+    float2 l2 = make_float2(0.f, 0.f);
     bool ok = true;
     for (int g = 0; g < n_g; ++g) {
       const int pass = g >= n_kt ? 1 : 0, kt = g - pass * n_kt, k0 = kt * AT_BK;
@@ -285,27 +320,12 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __gri
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_b);  // this warp no longer reads the K tile
-      if (pass && ok) {
-        if (kt > 0) ok = at_wait(bar_pv, (uint32_t)(kt - 1) & 1u, abort_flag);  // P.V of the previous tile no longer reads V^T and P
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {  // V^T in bf16, written in the swizzled K-major layout the MMA reads
-#pragma unroll
-          for (int r = 0; r < 2; ++r) {
-            const int task = idx + r * 256, key = task & 63, c = task >> 6;
-            float f[16];
-            at_unpack16(vraw[r], f);
-            uint8_t* vt = smem + AT_VT + (c >> 2) * (64 * 128);
-            const int d0 = (c & 3) * 16;
-#pragma unroll
-            for (int i = 0; i < 16; ++i)  // a small integer is exact in bf16: keep the upper half of the float
-              *reinterpret_cast<uint16_t*>(vt + at_sw(d0 + i, key * 2)) = (uint16_t)(__float_as_uint(f[i]) >> 16);
-          }
-          fence_proxy_async();
-        }
-      }
       AT_TRACE(pass, kt, 1);
       at_bar_prep();  // mask (warp 1) and bias term of tile g are visible to every softmax thread
       if (ok) ok = at_wait(bar_s, (uint32_t)g & 1u, abort_flag);
+      // P.V of the previous tile was issued before these scores, so it has completed as well: this wait returns at once
+      // and only keeps every phase of bar_pv observed in order (parities alias two phases apart)
+      if (ok && pass && kt > 0) ok = at_wait(bar_pv, (uint32_t)(kt - 1) & 1u, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       AT_TRACE(pass, kt, 2);
       if (ok) {
@@ -322,53 +342,72 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __gri
           uint32_t r[32];
           tmem_ld32(t_lane + (uint32_t)(head * 64 + c0), r);
           tmem_ld_wait();
-          float sv[32];
+          // scores (log2 domain) of 32 keys, two per instruction; in pass 1 the row maximum is already subtracted
+          float2 sv[16];
+          const float2 sc2 = make_float2(sc, sc), magic2 = make_float2(12582912.f, 12582912.f);
+          const float2 mm = make_float2(pass ? m_run : 0.f, pass ? m_run : 0.f);
 #pragma unroll
           for (int j4 = 0; j4 < 32; j4 += 4) {
             const float4 c4 = *reinterpret_cast<const float4*>(cjh + c0 + j4);
-            const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
+            // |Qi.Ki| <= 64 * 127^2 < 2^22: int -> float by adding into the mantissa of 1.5 * 2^23
+            const float2 fa = at_sub2(make_float2(__uint_as_float(r[j4] + 0x4B400000u), __uint_as_float(r[j4 + 1] + 0x4B400000u)), magic2);
+            const float2 fb = at_sub2(make_float2(__uint_as_float(r[j4 + 2] + 0x4B400000u), __uint_as_float(r[j4 + 3] + 0x4B400000u)), magic2);
+            sv[j4 / 2] = at_fma2(fa, sc2, at_sub2(make_float2(c4.x, c4.y), mm));
+            sv[j4 / 2 + 1] = at_fma2(fb, sc2, at_sub2(make_float2(c4.z, c4.w), mm));
+          }
+          if (!__all_sync(0xffffffffu, vw == 0xffffffffu)) {  // some key of this half tile is masked for some row of the warp
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = j4 + e;
-              // |Qi.Ki| <= 64 * 127^2 < 2^22: int -> float by adding into the mantissa of 1.5 * 2^23
-              const float sf = __fsub_rn(__uint_as_float(r[j] + 0x4B400000u), 12582912.f);
-              sv[j] = ((vw >> j) & 1u) ? fmaf(sf, sc, cc[e]) : -INFINITY;
+            for (int j = 0; j < 16; ++j) {
+              if (!((vw >> (2 * j)) & 1u)) sv[j].x = -INFINITY;
+              if (!((vw >> (2 * j + 1)) & 1u)) sv[j].y = -INFINITY;
             }
           }
           if (pass == 0) {
-            float m0 = fmaxf(sv[0], sv[1]), m1 = fmaxf(sv[2], sv[3]);
+            float m0 = fmaxf(sv[0].x, sv[0].y), m1 = fmaxf(sv[1].x, sv[1].y);
 #pragma unroll
-            for (int j = 4; j < 32; j += 2) {
-              m0 = fmaxf(m0, sv[j]);
-              m1 = fmaxf(m1, sv[j + 1]);
+            for (int j = 2; j < 16; j += 2) {
+              m0 = fmaxf(m0, fmaxf(sv[j].x, sv[j].y));
+              m1 = fmaxf(m1, fmaxf(sv[j + 1].x, sv[j + 1].y));
             }
             m_run = fmaxf(m_run, fmaxf(m0, m1));
           } else {
             uint8_t* ph = smem + AT_P + (head * 2) * (AT_BQ * 128);
             uint8_t* pl = ph + AT_BQ * 128;
-            float l0 = 0.f, l1 = 0.f;
 #pragma unroll
             for (int gq = 0; gq < 4; ++gq) {  // 8 keys = one 16-byte chunk of bf16
               uint32_t hi[4], lo[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const float p0 = at_ex2(sv[gq * 8 + e * 2] - m_run), p1 = at_ex2(sv[gq * 8 + e * 2 + 1] - m_run);  // 2^-inf = 0
-                l0 += p0;
-                l1 += p1;
+                const float2 pp = make_float2(at_ex2(sv[gq * 4 + e].x), at_ex2(sv[gq * 4 + e].y));  // 2^-inf = 0
+                l2 = at_add2(l2, pp);
                 // hi = p truncated to bf16 (exact), lo = bf16(p - hi): |p - hi - lo| < 2^-16 p
-                const uint32_t b0 = __float_as_uint(p0) & 0xffff0000u, b1 = __float_as_uint(p1) & 0xffff0000u;
+                const uint32_t b0 = __float_as_uint(pp.x) & 0xffff0000u, b1 = __float_as_uint(pp.y) & 0xffff0000u;
                 hi[e] = __byte_perm(b0, b1, 0x7632);
-                const __nv_bfloat162 l2 = __floats2bfloat162_rn(p0 - __uint_as_float(b0), p1 - __uint_as_float(b1));
-                lo[e] = *reinterpret_cast<const uint32_t*>(&l2);
+                const float2 rem = at_sub2(pp, make_float2(__uint_as_float(b0), __uint_as_float(b1)));
+                const __nv_bfloat162 lo2 = __floats2bfloat162_rn(rem.x, rem.y);
+                lo[e] = *reinterpret_cast<const uint32_t*>(&lo2);
               }
               const int off = at_sw(qrow, (c0 + gq * 8) * 2);
               *reinterpret_cast<uint4*>(ph + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
               *reinterpret_cast<uint4*>(pl + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
             }
-            l_run += l0 + l1;
           }
         }
-        if (pass) fence_proxy_async();  // P was written by threads; the MMAs read it through the async proxy
+        if (pass) {  // V^T in bf16, written in the swizzled K-major layout the MMA reads. The scores of this tile were
+                     // issued after P.V of the previous tile, so their completion means V^T (and P) are no longer read.
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const int task = idx + r * 256, key = task & 63, c = task >> 6;
+            float f[16];
+            at_unpack16(vraw[r], f);
+            uint8_t* vt = smem + AT_VT + (c >> 2) * (64 * 128);
+            const int d0 = (c & 3) * 16;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)  // a small integer is exact in bf16: keep the upper half of the float
+              *reinterpret_cast<uint16_t*>(vt + at_sw(d0 + i, key * 2)) = (uint16_t)(__float_as_uint(f[i]) >> 16);
+          }
+          fence_proxy_async();  // P and V^T were written by threads; the MMAs read them through the async proxy
+        }
         tc_fence_before();
       }
       AT_TRACE(pass, kt, 3);
@@ -376,6 +415,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __gri
       if (lane == 0) mbar_arrive(bar_c);  // this warp has S in registers, its P and V^T in shared memory
     }
 
+    const float l_run = l2.x + l2.y;
     // out = s * O / sum(P) + bv -> clip -> int8 (a row with every key masked gives 0, as the SIMT kernel does)
     if (ok) ok = at_wait(bar_pv, (uint32_t)(n_kt - 1) & 1u, abort_flag);
     ok = __all_sync(0xffffffffu, ok);

@@ -309,7 +309,6 @@ __global__ void __launch_bounds__(320) gemm_i8_tc_kernel(const __grid_constant__
   const int num_kb = (p.k + BK - 1) / BK;
 
   LS100_TRACE(0);
-  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
@@ -329,6 +328,9 @@ __global__ void __launch_bounds__(320) gemm_i8_tc_kernel(const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // dependents may be scheduled only now: a dependent grid's CTAs that landed on this SM earlier could take the TMEM
+  // columns this CTA still needs while they wait for this grid to finish
+  pdl_launch_dependents();
   LS100_TRACE(1);
 
   if (warp == 0) {
@@ -576,7 +578,6 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.k + BK - 1) / BK;
 
-  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
@@ -600,6 +601,9 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // dependents may be scheduled only now: a dependent grid's CTAs that landed on this SM earlier could take the TMEM
+  // columns this CTA still needs while they wait for this grid to finish
+  pdl_launch_dependents();
 
   if (warp == 0) {
     if (elect_one()) {

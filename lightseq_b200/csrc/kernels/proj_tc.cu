@@ -115,7 +115,6 @@ __global__ void __launch_bounds__(T_THREADS, 1) proj_tc_kernel(const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = p.k3_bytes / T_BK_BYTES;  // K is a multiple of 64, checked by the launcher
 
-  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
@@ -139,6 +138,7 @@ __global__ void __launch_bounds__(T_THREADS, 1) proj_tc_kernel(const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();  // only once this CTA owns its TMEM columns (a dependent's CTAs must not take them first)
 
   if (warp == 0) {
     if (elect_one()) {
