@@ -5,8 +5,8 @@
 //   S = Q . K^T   int8 x int8 -> int32 (kind::i8): exact. Q and K tiles come by TMA straight out of the QKV GEMM's
 //                 int8 output; a tile row is 128 bytes = the 64 dims of the two heads, so the proven 128-byte-swizzle
 //                 K-major layout applies and each head is a 64-byte K-range of the same tile.
-//   O += P . V    bf16 x bf16 -> fp32 (kind::f16): P in [0,1] is split into two bf16 terms (remainder < 2^-17 p),
-//                 V (int8) is exact in bf16. Threads write P and V^T into shared memory in the swizzled K-major layout.
+//   O += P . V    fp16 x fp16 -> fp32 (kind::f16): P in [0,1] is split into two fp16 terms (remainder < 2^-23 p + 2^-25),
+//                 V (int8) is exact in fp16. Threads write P and V^T into shared memory in the swizzled K-major layout.
 // The biases never enter a GEMM: with q = s*Qi + bq, k = s*Ki + bk the score is
 //   (q.k)/8 = s^2/8 * (Qi.Ki) + s/8 * (bq.Ki) + terms constant along a query's row (which softmax cancels),
 // and out = s * (P.Vi)/sum(P) + bv. Softmax is exact fp32, one thread per query row (no shuffles), in the log2
@@ -19,7 +19,7 @@
 // K tile read, softmax done), warps 1-9 through one named barrier per tile; the K tile of g+1 is fetched while tile
 // g's softmax runs, P.V of tile g and the scores of tile g+1 run while the threads prepare tile g+1, and V comes by
 // plain 16-byte loads issued at the start of a tile's preparation. Every mbarrier wait is bounded in time.
-#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "common.cuh"
 #include "ctx.h"
@@ -38,8 +38,8 @@ constexpr int AT_SOFTMAX_WARPS = 8;  // warps 2..9
 // shared memory map (every tile 1024-byte aligned): 107 KB per CTA, so two CTAs share an SM (and its 512 TMEM columns)
 constexpr int AT_Q = 0;                        // [128 q][128 B]  int8, two heads
 constexpr int AT_K = AT_Q + AT_BQ * 128;       // [64 keys][128 B]
-constexpr int AT_P = AT_K + AT_BK * 128;       // [head][hi|lo][128 q][64 keys bf16 = 128 B]
-constexpr int AT_VT = AT_P + 4 * AT_BQ * 128;  // [head][64 dims][64 keys bf16 = 128 B]
+constexpr int AT_P = AT_K + AT_BK * 128;       // [head][hi|lo][128 q][64 keys fp16 = 128 B]
+constexpr int AT_VT = AT_P + 4 * AT_BQ * 128;  // [head][64 dims][64 keys fp16 = 128 B]
 constexpr int AT_MISC = AT_VT + 2 * 64 * 128;  // bias terms, key-mask words, bq[128] f32, barriers
 constexpr int AT_SMEM = AT_MISC + 2048 + 1024;
 constexpr int AT_TMEM_COLS = 256;              // S: 2 heads x 64 columns (int32), O: 2 heads x 64 columns (fp32)
@@ -53,14 +53,14 @@ __device__ __forceinline__ uint64_t at_desc(uint32_t saddr) {  // K-major, SWIZZ
   d |= (uint64_t)2 << 61;
   return d;
 }
-// M = 128, N = 64: int8 -> int32, and bf16 -> fp32
+// M = 128, N = 64: int8 -> int32, and fp16 -> fp32
 __device__ __forceinline__ constexpr uint32_t at_idesc_i8() {
   return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
-__device__ __forceinline__ constexpr uint32_t at_idesc_bf16() {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+__device__ __forceinline__ constexpr uint32_t at_idesc_f16() {  // A and B fp16 (format 0), D fp32
+  return (1u << 4) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
-__device__ __forceinline__ void at_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+__device__ __forceinline__ void at_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
   asm volatile(
       "{\n.reg .pred p;\n"
       "setp.ne.b32 p, %4, 0;\n"
@@ -136,6 +136,20 @@ __device__ __forceinline__ float2 at_add2(float2 a, float2 b) {
   float2 d;
   asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
   return d;
+}
+
+// 16 int8 -> 16 fp16 (8 packed pairs): the byte plus 128 dropped into the mantissa of 1024 (0x6400), minus 1152; exact
+__device__ __forceinline__ void at_unpack16_f16(const int4 v, uint32_t (&h)[8]) {
+  const unsigned w[4] = {(unsigned)v.x ^ 0x80808080u, (unsigned)v.y ^ 0x80808080u, (unsigned)v.z ^ 0x80808080u,
+                         (unsigned)v.w ^ 0x80808080u};
+  const __half2 off = __floats2half2_rn(1152.f, 1152.f);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t a = __byte_perm(w[i], 0x64646464u, 0x4140), b = __byte_perm(w[i], 0x64646464u, 0x4342);
+    const __half2 ra = __hsub2(*reinterpret_cast<const __half2*>(&a), off), rb = __hsub2(*reinterpret_cast<const __half2*>(&b), off);
+    h[i * 2] = *reinterpret_cast<const uint32_t*>(&ra);
+    h[i * 2 + 1] = *reinterpret_cast<const uint32_t*>(&rb);
+  }
 }
 
 __device__ __forceinline__ float at_ex2(float x) {
@@ -237,7 +251,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __gri
               const uint64_t pd = at_desc(smem_u32(smem + AT_P + (hh * 2 + term) * (AT_BQ * 128)));
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk)
-                at_mma_bf16(tmem_base + (uint32_t)(128 + hh * 64), pd + (uint64_t)(kk * 2), vd + (uint64_t)(kk * 2), at_idesc_bf16(),
+                at_mma_f16(tmem_base + (uint32_t)(128 + hh * 64), pd + (uint64_t)(kk * 2), vd + (uint64_t)(kk * 2), at_idesc_f16(),
                             (kt > 0 || term > 0 || kk > 0) ? 1u : 0u);
             }
           }
@@ -374,17 +388,17 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __gri
             uint8_t* ph = smem + AT_P + (head * 2) * (AT_BQ * 128);
             uint8_t* pl = ph + AT_BQ * 128;
 #pragma unroll
-            for (int gq = 0; gq < 4; ++gq) {  // 8 keys = one 16-byte chunk of bf16
+            for (int gq = 0; gq < 4; ++gq) {  // 8 keys = one 16-byte chunk of fp16
               uint32_t hi[4], lo[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const float2 pp = make_float2(at_ex2(sv[gq * 4 + e].x), at_ex2(sv[gq * 4 + e].y));  // 2^-inf = 0
                 l2 = at_add2(l2, pp);
-                // hi = p truncated to bf16 (exact), lo = bf16(p - hi): |p - hi - lo| < 2^-16 p
-                const uint32_t b0 = __float_as_uint(pp.x) & 0xffff0000u, b1 = __float_as_uint(pp.y) & 0xffff0000u;
-                hi[e] = __byte_perm(b0, b1, 0x7632);
-                const float2 rem = at_sub2(pp, make_float2(__uint_as_float(b0), __uint_as_float(b1)));
-                const __nv_bfloat162 lo2 = __floats2bfloat162_rn(rem.x, rem.y);
+                // hi = fp16(p), lo = fp16(p - hi): |p - hi - lo| < 2^-23 p + 2^-25 (p <= 1, so lo may be subnormal)
+                const __half2 h2 = __floats2half2_rn(pp.x, pp.y);
+                const float2 rem = at_sub2(pp, __half22float2(h2));
+                const __half2 lo2 = __floats2half2_rn(rem.x, rem.y);
+                hi[e] = *reinterpret_cast<const uint32_t*>(&h2);
                 lo[e] = *reinterpret_cast<const uint32_t*>(&lo2);
               }
               const int off = at_sw(qrow, (c0 + gq * 8) * 2);
@@ -393,18 +407,20 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __gri
             }
           }
         }
-        if (pass) {  // V^T in bf16, written in the swizzled K-major layout the MMA reads. The scores of this tile were
+        if (pass) {  // V^T in fp16, written in the swizzled K-major layout the MMA reads. The scores of this tile were
                      // issued after P.V of the previous tile, so their completion means V^T (and P) are no longer read.
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
             const int task = idx + r * 256, key = task & 63, c = task >> 6;
-            float f[16];
-            at_unpack16(vraw[r], f);
+            uint32_t h[8];
+            at_unpack16_f16(vraw[r], h);
             uint8_t* vt = smem + AT_VT + (c >> 2) * (64 * 128);
             const int d0 = (c & 3) * 16;
 #pragma unroll
-            for (int i = 0; i < 16; ++i)  // a small integer is exact in bf16: keep the upper half of the float
-              *reinterpret_cast<uint16_t*>(vt + at_sw(d0 + i, key * 2)) = (uint16_t)(__float_as_uint(f[i]) >> 16);
+            for (int i = 0; i < 8; ++i) {
+              *reinterpret_cast<uint16_t*>(vt + at_sw(d0 + 2 * i, key * 2)) = (uint16_t)(h[i] & 0xffffu);
+              *reinterpret_cast<uint16_t*>(vt + at_sw(d0 + 2 * i + 1, key * 2)) = (uint16_t)(h[i] >> 16);
+            }
           }
           fence_proxy_async();  // P and V^T were written by threads; the MMAs read them through the async proxy
         }
