@@ -245,6 +245,28 @@ def test_reference_protobuf_file_runs_unchanged(tmp_path):
     assert np.array_equal(t1, t2) and np.array_equal(s1, s2)
 
 
+def test_exported_checkpoint_generates_the_same_tokens(tmp_path):
+    """Checkpoint of the torch fake-quant layers (key names of the reference's modules) -> exporter -> protobuf file ->
+    engine: the same tokens and scores as the model loaded from the engine's own container."""
+    import lightseq_b200.inference as lsi
+    from lightseq_b200 import export, ls_proto, weights
+
+    conf, amax, w = synth.make_transformer(None, hidden=128, heads=2, ffn=256, n_enc=2, n_dec=2, vocab=120, max_step=40, seed=10)
+    for i in range(2):
+        amax[f"dec.{i}.xv.w"] = amax[f"dec.{i}.xk.w"]
+    direct, pb, conv = str(tmp_path / "a.ls100"), str(tmp_path / "m.pb"), str(tmp_path / "b.ls100")
+    weights.save(direct, "QuantTransformer", conf, amax, w)
+    state = export.engine_to_state_dict(conf, amax, w)
+    export.export_quant_transformer(state, pb, heads=2, beam=int(conf["beam"]), length_penalty=float(conf["length_penalty"]),
+                                    extra_decode_length=int(conf["extra_decode_length"]), max_step=40, pad_id=int(conf["pad_id"]),
+                                    bos_id=int(conf["start_id"]), eos_id=int(conf["end_id"]))
+    ls_proto.convert(pb, conv)
+    src = synth.transformer_inputs(batch=6, min_len=5, max_len=14, vocab=120, pad_id=int(conf["pad_id"]), seed=5)
+    t1, s1 = lsi.QuantTransformer(direct, 8).infer(src)
+    t2, s2 = lsi.QuantTransformer(conv, 8).infer(src)
+    assert np.array_equal(t1, t2) and np.array_equal(s1, s2)
+
+
 def test_entry_point_smoke_runs():
     """The repository's smoke entry (one tcgen05 GEMM checked on its accumulators + a tiny generation checked token
     for token against the oracle) is part of the suite so that it cannot go stale."""
