@@ -568,7 +568,7 @@ def run_ours(args):
 
 
 def run_other_workload(args):
-    """``--workload bert|gpt|big``: the other benchmark configurations (BERT-base, GPT-2 medium, Transformer-big) on
+    """``--workload bert|vit|gpt|big``: the other configurations (BERT-base, ViT-B/16, GPT-2 medium, Transformer-big) on
     one GPU; the contract line of this file is the Transformer-base workload."""
     import torch
 
@@ -633,6 +633,49 @@ def run_other_workload(args):
             assert np.array_equal(d_out.cpu().numpy(), y), "device-resident and host-buffer results differ"
             out[f"{B}x{S}"] = {"device_ms": dms, "tokens_per_s": B * S / dms * 1e3, "int8_gemm_tops": 2 * B * S * 12 * 7077888 / dms / 1e9,
                                "e2e_ms_numpy_in_out": dt * 1e3, "d2h_bytes": B * S * 768 * 4}
+    elif args.workload == "vit":
+        # ViT-B/16 at 224 x 224: 128 images = 25 216 tokens; device-resident pixels and output, CUDA events on the model's stream
+        from lightseq_b200 import _lib as L
+
+        synth.make_vit(path)
+        model = lsi.QuantVit(path, 128)
+        lib, handle = L.lib, C.c_void_p(model._handle)
+        lib.ls100_model_get_stream.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+        lib.ls100_model_set_input_ptr.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        lib.ls100_model_set_output_ptr.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        lib.ls100_model_set_input_shape.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_int32), C.c_int]
+        lib.ls100_model_infer.argtypes = [C.c_void_p]
+        sptr = C.c_void_p()
+        L.check(lib.ls100_model_get_stream(handle, C.byref(sptr)), "get_stream")
+        mstream = torch.cuda.ExternalStream(sptr.value)
+        B = 128
+        px = synth.vit_inputs(batch=B)
+        dt, y = timed(lambda: model.infer(px), args.steps)
+        d_px = torch.from_numpy(px).cuda()
+        d_out = torch.empty(y.shape, dtype=torch.float32, device="cuda")
+        dims = (C.c_int32 * 4)(B, 3, 224, 224)
+        L.check(lib.ls100_model_set_input_ptr(handle, 0, d_px.data_ptr()), "set_input_ptr")
+        L.check(lib.ls100_model_set_output_ptr(handle, 0, d_out.data_ptr()), "set_output_ptr")
+
+        def dev():
+            L.check(lib.ls100_model_set_input_shape(handle, 0, dims, 4), "set_input_shape")
+            if lib.ls100_model_infer(handle) != 0:
+                raise RuntimeError(lib.ls100_model_last_error())
+
+        for _ in range(3):
+            dev()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(mstream):
+            e0.record()
+            for _ in range(args.steps):
+                dev()
+            e1.record()
+        torch.cuda.synchronize()
+        dms = e0.elapsed_time(e1) / args.steps
+        assert np.array_equal(d_out.cpu().numpy(), y), "device-resident and host-buffer results differ"
+        out["128x3x224x224"] = {"device_ms": dms, "images_per_s": B / dms * 1e3, "tokens": int(y.shape[0] * y.shape[1]),
+                                "e2e_ms_numpy_in_out": dt * 1e3}
     elif args.workload == "eos":
         # the benchmark model with EOS made competitive (a shared direction in the final LayerNorm bias and in the EOS
         # embedding row), so that beams finish at different steps and the device-side early stop ends the generation
@@ -680,7 +723,7 @@ def main():
                     help="cap the number of decode steps per generation (profiling aid; the result is not a bench value)")
     ap.add_argument("--kernel", default=None,
                     help="run one kernel family alone (gemm_dec, gemm_dec_ln, gemm_logits, gemm_enc_qkv, gemm_square, attn_self, attn_dec, attn_cross, beam_topk, ln_quant)")
-    ap.add_argument("--workload", default=None, choices=["bert", "gpt", "big", "eos"],
+    ap.add_argument("--workload", default=None, choices=["bert", "vit", "gpt", "big", "eos"],
                     help="run another BASELINE configuration (BERT-base, GPT-2 medium, Transformer-big) on one GPU, or the "
                          "benchmark model with a boosted EOS (early-stop bookkeeping)")
     ap.add_argument("--eos-boost", type=float, default=0.13, help="size of the EOS direction in the final LayerNorm bias")

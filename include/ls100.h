@@ -155,6 +155,25 @@ typedef struct {
 } ls100_embed_args;
 int ls100_embed(ls100_ctx* ctx, const ls100_embed_args* args, ls100_stream_t stream);
 
+/* ---------------------------------------------------------- ViT patch embedding ---
+ * out[b, 0, :]     = cls + pos[0]
+ * out[b, 1 + n, :] = conv(patch n of image b) + conv_bias + pos[1 + n]
+ * with a convolution of kernel = stride = patch (patches in row-major order over the image, the weight index is
+ * (hidden, channel, row, col)); nothing is quantised here. The dot products are accumulated in float64 and rounded
+ * once to fp32, so the result does not depend on the summation order; bias and position are fp32 additions in that
+ * order. Replaces launch_patch_emb (lightseq/inference/kernels/embKernels.cc.cu:547-618; one CTA per output value
+ * there). conv_wt is the TRANSPOSED weight [channels*patch*patch, hidden]. hidden % 4 == 0. */
+typedef struct {
+  const float* pixels;   /* [batch, channels, image, image] fp32 */
+  const float* conv_wt;  /* [channels*patch*patch, hidden] fp32 */
+  const float* conv_bias; /* [hidden] */
+  const float* pos;      /* [1 + (image/patch)^2, hidden] */
+  const float* cls;      /* [hidden] */
+  int32_t batch, channels, image, patch, hidden;
+  float* out; /* [batch, 1 + (image/patch)^2, hidden] fp32 */
+} ls100_patch_embed_args;
+int ls100_patch_embed(ls100_ctx* ctx, const ls100_patch_embed_args* args, ls100_stream_t stream);
+
 /* ------------------------------------------------- encoder-style self attention ---
  * softmax((q*dh^-0.5) k^T + mask) v per (batch, head) over a full sequence, output
  * quantised with the out-projection's input clip-max. q,k,v are read from the QKV
@@ -432,7 +451,7 @@ int ls100_quantize_weight(ls100_ctx* ctx, const float* w, int64_t rows, int64_t 
 
 /* ------------------------------------------------------------- model level ---
  * The LSModel interface of lightseq/inference/pywrapper/model_base.h:59-148 as plain C:
- * create by name ("QuantTransformer", "QuantBert", "QuantGpt") from a weight file and
+ * create by name ("QuantTransformer", "QuantBert", "QuantGpt", "QuantVit") from a weight file and
  * max batch size, hand over caller-owned DEVICE pointers, run, read shapes back.
  * Every function returns 0 or a negative code; ls100_model_last_error() gives the
  * message of the last failure on the calling thread (what the C++ API throws as
@@ -461,6 +480,9 @@ int ls100_transformer_infer_host(ls100_model* m, const int32_t* ids, int batch, 
 /* QuantBert: ids [batch, seq_len] -> fp32 encoder output [batch, seq_len, hidden] (PyQuantBert::infer,
  * lightseq/inference/pywrapper/wrapper.cc:276-321). */
 int ls100_bert_infer_host(ls100_model* m, const int32_t* ids, int batch, int seq_len, float* out);
+/* QuantVit: pixels [batch, channels, image, image] fp32 -> fp32 encoder output [batch, 1 + patches, hidden]
+ * (PyQuantVit::infer, lightseq/inference/pywrapper/wrapper.cc). Host buffers. */
+int ls100_vit_infer_host(ls100_model* m, const float* pixels, int batch, int channels, int image, float* out);
 /* QuantGpt: prompt ids [batch, prompt_len] -> prompt + sampled tokens [batch, *out_len], written densely into
  * out_tokens (batch*max_step ints) (PyQuantGpt::sample, lightseq/inference/pywrapper/wrapper.cc:463-495). */
 int ls100_gpt_sample_host(ls100_model* m, const int32_t* ids, int batch, int prompt_len, int32_t* out_tokens, int* out_len);

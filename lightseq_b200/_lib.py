@@ -71,6 +71,12 @@ class EmbedArgs(C.Structure):
                 ("vocab", C.c_int32), ("out", C.c_void_p), ("pad_mask", C.c_void_p), ("pos_mode", C.c_int32)]
 
 
+class PatchEmbedArgs(C.Structure):
+    _fields_ = [("pixels", C.c_void_p), ("conv_wt", C.c_void_p), ("conv_bias", C.c_void_p), ("pos", C.c_void_p),
+                ("cls", C.c_void_p), ("batch", C.c_int32), ("channels", C.c_int32), ("image", C.c_int32),
+                ("patch", C.c_int32), ("hidden", C.c_int32), ("out", C.c_void_p)]
+
+
 class AttnSelfArgs(C.Structure):
     _fields_ = [("qkv", C.c_void_p), ("ld_qkv", C.c_int64), ("s_qkv", C.c_float), ("bias", C.c_void_p),
                 ("pad_mask", C.c_void_p), ("batch", C.c_int32), ("seq", C.c_int32), ("heads", C.c_int32),
@@ -153,7 +159,7 @@ for _name, _cls in (("ls100_ln_quant", LnQuantArgs), ("ls100_embed", EmbedArgs),
                     ("ls100_proj_f32", ProjF32Args), ("ls100_beam_topk", BeamTopkArgs),
                     ("ls100_beam_update", BeamUpdateArgs), ("ls100_beam_update_noalloc", BeamUpdateArgs), ("ls100_sample_topk", SampleTopkArgs),
                     ("ls100_sample_topp", SampleToppArgs),
-                    ("ls100_proj_tc", ProjTcArgs)):
+                    ("ls100_proj_tc", ProjTcArgs), ("ls100_patch_embed", PatchEmbedArgs)):
     _fn = getattr(lib, _name)
     _fn.restype = C.c_int
     _fn.argtypes = [C.c_void_p, C.POINTER(_cls), C.c_void_p]

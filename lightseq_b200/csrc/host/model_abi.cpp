@@ -167,6 +167,26 @@ extern "C" int ls100_bert_infer_host(ls100_model* m, const int32_t* ids, int bat
   });
 }
 
+extern "C" int ls100_vit_infer_host(ls100_model* m, const float* pixels, int batch, int channels, int image, float* out) {
+  if (!m || !pixels || !out || batch < 1) return LS100_ERR_BAD_ARG;
+  return guarded([&] {
+    std::vector<int> in = m->model->get_input_max_shape(0);  // [max_batch, channels, image, image]
+    if (in.size() != 4) throw std::runtime_error("not a QuantVit model");
+    if (batch > in[0]) throw std::runtime_error("batch size of input greater than max_batch_size");
+    if (channels != in[1] || image != in[2])
+      throw std::runtime_error("pixel_input must be [batch, " + std::to_string(in[1]) + ", " + std::to_string(in[2]) + ", " +
+                               std::to_string(in[3]) + "]");
+    in[0] = batch;
+    LS_CUDA(cudaSetDevice(m->device));
+    LS_CUDA(cudaMemcpy(m->d_in, pixels, prod(in) * 4, cudaMemcpyHostToDevice));
+    m->model->set_input_ptr(0, m->d_in);
+    m->model->set_input_shape(0, in);
+    m->model->set_output_ptr(0, m->d_out0);
+    m->model->Infer();
+    LS_CUDA(cudaMemcpy(out, m->d_out0, prod(m->model->get_output_shape(0)) * 4, cudaMemcpyDeviceToHost));
+  });
+}
+
 extern "C" int ls100_gpt_sample_host(ls100_model* m, const int32_t* ids, int batch, int prompt_len, int32_t* out_tokens,
                                      int* out_len) {
   if (!m || !ids || !out_tokens || !out_len || batch < 1 || prompt_len < 1) return LS100_ERR_BAD_ARG;

@@ -213,6 +213,61 @@ __global__ void __launch_bounds__(256) quantize_weight_kernel(const float* __res
   }
 }
 
+// ------------------------------------------------------------------ ViT patch embedding
+// CTA = 16 consecutive tokens (of the flattened [batch, 1 + patches] list) x 256 hidden channels; a thread owns one
+// channel and 16 float64 accumulators. The patch pixels are staged through shared memory 256 values at a time
+// (read back as broadcasts), the transposed weight is read coalesced, once per CTA.
+constexpr int PE_TOK = 16, PE_KC = 256;
+__global__ void __launch_bounds__(256) patch_embed_kernel(const ls100_patch_embed_args a) {
+  __shared__ float xs[PE_TOK][PE_KC];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int grid_w = a.image / a.patch, n_patch = grid_w * grid_w, seq = n_patch + 1;
+  const int K = a.channels * a.patch * a.patch, pp = a.patch * a.patch;
+  const long long tokens = (long long)a.batch * seq;
+  const long long t0 = (long long)blockIdx.x * PE_TOK;
+  const int h = blockIdx.y * 256 + threadIdx.x;
+  double acc[PE_TOK];
+#pragma unroll
+  for (int p = 0; p < PE_TOK; ++p) acc[p] = 0.0;
+  for (int k0 = 0; k0 < K; k0 += PE_KC) {
+    __syncthreads();
+    for (int id = threadIdx.x; id < PE_TOK * PE_KC; id += 256) {
+      const int p = id / PE_KC, kk = id % PE_KC, k = k0 + kk;
+      const long long tok = t0 + p;
+      float v = 0.f;
+      if (tok < tokens && k < K) {
+        const int b = (int)(tok / seq), n = (int)(tok % seq);
+        if (n > 0) {
+          const int pr = (n - 1) / grid_w, pc = (n - 1) % grid_w;
+          const int c = k / pp, r = (k % pp) / a.patch, q = k % a.patch;
+          v = __ldg(a.pixels + (((long long)b * a.channels + c) * a.image + (pr * a.patch + r)) * a.image + pc * a.patch + q);
+        }
+      }
+      xs[p][kk] = v;
+    }
+    __syncthreads();
+    if (h < a.hidden) {
+      const int kn = min(PE_KC, K - k0);
+      for (int kk = 0; kk < kn; ++kk) {
+        const double w = (double)__ldg(a.conv_wt + (long long)(k0 + kk) * a.hidden + h);
+#pragma unroll
+        for (int p = 0; p < PE_TOK; ++p) acc[p] = fma((double)xs[p][kk], w, acc[p]);
+      }
+    }
+  }
+  if (h >= a.hidden) return;
+  const float bias = __ldg(a.conv_bias + h), cls = __ldg(a.cls + h);
+#pragma unroll
+  for (int p = 0; p < PE_TOK; ++p) {
+    const long long tok = t0 + p;
+    if (tok >= tokens) break;
+    const int n = (int)(tok % seq);
+    const float pos = __ldg(a.pos + (long long)n * a.hidden + h);
+    a.out[tok * a.hidden + h] = n == 0 ? __fadd_rn(cls, pos) : __fadd_rn(__fadd_rn((float)acc[p], bias), pos);
+  }
+}
+
 }  // namespace ls100
 
 using namespace ls100;
@@ -256,6 +311,20 @@ extern "C" int ls100_embed(ls100_ctx* ctx, const ls100_embed_args* a, ls100_stre
   if ((((uintptr_t)a->table_q) & 3) || (((uintptr_t)a->pos) & 15) || (((uintptr_t)a->out) & 15)) return LS100_ERR_ALIGN;
   const int rows = a->batch * a->seq;
   return ls100_launch(embed_kernel, dim3((rows + 7) / 8), dim3(256), 0, (cudaStream_t)stream_, *a) == cudaSuccess
+             ? LS100_OK
+             : LS100_ERR_CUDA;
+}
+
+extern "C" int ls100_patch_embed(ls100_ctx* ctx, const ls100_patch_embed_args* a, ls100_stream_t stream_) {
+  if (!ctx || !a || !a->pixels || !a->conv_wt || !a->conv_bias || !a->pos || !a->cls || !a->out) return LS100_ERR_BAD_ARG;
+  if (a->batch <= 0 || a->channels <= 0 || a->image <= 0 || a->patch <= 0 || a->hidden <= 0) return LS100_ERR_BAD_ARG;
+  if (a->image % a->patch) return LS100_ERR_BAD_ARG;
+  if (a->hidden & 3) return LS100_ERR_UNSUPPORTED;
+  const long long g = a->image / a->patch, tokens = (long long)a->batch * (g * g + 1);
+  const long long bx = (tokens + PE_TOK - 1) / PE_TOK;
+  if (bx > 0x7fffffffll) return LS100_ERR_UNSUPPORTED;
+  return ls100_launch(patch_embed_kernel, dim3((unsigned)bx, (unsigned)((a->hidden + 255) / 256)), dim3(256), 0, (cudaStream_t)stream_,
+                      *a) == cudaSuccess
              ? LS100_OK
              : LS100_ERR_CUDA;
 }

@@ -92,6 +92,39 @@ class PyQuantBert {
   int hidden_ = 0;
 };
 
+// QuantVit(weight_path, max_batch_size).infer(float32[B,C,I,I]) -> float32[B,1+patches,H]
+// (PyQuantVit, lightseq/inference/pywrapper/wrapper.cc)
+class PyQuantVit {
+ public:
+  PyQuantVit(const std::string& weight_path, int max_batch_size) {
+    check(ls100_model_create("QuantVit", weight_path.c_str(), max_batch_size, &m_), "QuantVit");
+    int32_t dims[4];
+    int nd = 0;
+    check(ls100_model_get_output_max_shape(m_, 0, dims, &nd), "get_output_max_shape");
+    seq_ = dims[1];
+    hidden_ = dims[2];
+  }
+  ~PyQuantVit() { ls100_model_destroy(m_); }
+  PyQuantVit(const PyQuantVit&) = delete;
+  PyQuantVit& operator=(const PyQuantVit&) = delete;
+  py::array_t<float> infer(py::array_t<float, py::array::c_style | py::array::forcecast> pixel_input) {
+    if (pixel_input.ndim() != 4) throw std::runtime_error("pixel_input must be a 4-D float32 array [batch, channels, image, image]");
+    if (pixel_input.shape(2) != pixel_input.shape(3)) throw std::runtime_error("pixel_input must be square images");
+    const int batch = (int)pixel_input.shape(0), channels = (int)pixel_input.shape(1), image = (int)pixel_input.shape(2);
+    py::array_t<float> out({batch, seq_, hidden_});
+    {
+      py::gil_scoped_release nogil;
+      check(ls100_vit_infer_host(m_, pixel_input.data(), batch, channels, image, out.mutable_data()), "infer");
+    }
+    return out;
+  }
+  std::uintptr_t handle() const { return reinterpret_cast<std::uintptr_t>(m_); }
+
+ private:
+  ls100_model* m_ = nullptr;
+  int seq_ = 0, hidden_ = 0;
+};
+
 // QuantGpt(weight_path, max_batch_size).sample(int32[B,P]) -> int32[B,L]
 // (PyQuantGpt::sample, lightseq/inference/pywrapper/wrapper.cc:427-495)
 class PyQuantGpt {
@@ -157,4 +190,8 @@ PYBIND11_MODULE(_ls100_py, m) {
       .def(py::init<const std::string&, int>(), py::arg("weight_path"), py::arg("max_batch_size"))
       .def("infer", &PyQuantBert::infer, py::arg("input_seq"))
       .def_property_readonly("_handle", &PyQuantBert::handle);
+  py::class_<PyQuantVit>(m, "QuantVit")
+      .def(py::init<const std::string&, int>(), py::arg("weight_path"), py::arg("max_batch_size"))
+      .def("infer", &PyQuantVit::infer, py::arg("pixel_input"))
+      .def_property_readonly("_handle", &PyQuantVit::handle);
 }

@@ -10,7 +10,7 @@ The native module is required; there is no Python or CPU fallback.
 from . import _lib  # noqa: F401  (loads libls100.so first, and fails loudly if it is not built)
 
 try:
-    from ._ls100_py import QuantBert, QuantGpt, QuantTransformer  # noqa: F401
+    from ._ls100_py import QuantBert, QuantGpt, QuantTransformer, QuantVit  # noqa: F401
 except ImportError as e:  # pragma: no cover
     raise ImportError(
         "lightseq_b200._ls100_py is missing: build it with `python -m lightseq_b200.build`") from e

@@ -312,6 +312,79 @@ def make_bert(path: Optional[str] = None, *, hidden=768, heads=12, ffn=3072, n_l
     return conf, amax, w
 
 
+# ------------------------------------------------------------------------------------------- ViT
+def vit_weights(hidden=768, heads=12, ffn=3072, n_layer=12, image=224, patch=16, channels=3, seed=1234, std=0.02):
+    rng = np.random.default_rng(seed)
+
+    def nrm(*shape):
+        return (rng.standard_normal(shape, dtype=F32) * F32(std)).astype(F32)
+
+    n_tok = 1 + (image // patch) ** 2
+    w: Dict[str, np.ndarray] = {"conv.w": nrm(hidden, channels * patch * patch), "conv.b": nrm(hidden), "pos": nrm(n_tok, hidden),
+                                "cls": nrm(hidden), "enc.ln.g": np.ones(hidden, F32), "enc.ln.b": np.zeros(hidden, F32)}
+    for l in range(n_layer):
+        p = f"enc.{l}"
+        for name, (no, ni) in (("qkv", (3 * hidden, hidden)), ("out", (hidden, hidden)), ("fc1", (ffn, hidden)),
+                               ("fc2", (hidden, ffn))):
+            w[f"{p}.{name}.w"] = nrm(no, ni)
+            w[f"{p}.{name}.b"] = np.zeros(no, F32)
+        for ln in ("ln1", "ln2"):
+            w[f"{p}.{ln}.g"] = np.ones(hidden, F32)
+            w[f"{p}.{ln}.b"] = np.zeros(hidden, F32)
+    return w
+
+
+def vit_inputs(batch=128, image=224, channels=3, seed=4321) -> np.ndarray:
+    """pixels [batch, channels, image, image] fp32, N(0, 1) (normalised images)."""
+    return np.random.default_rng(seed).standard_normal((batch, channels, image, image), dtype=F32)
+
+
+def calibrate_vit(w, pixels, *, heads: int, n_layer: int, patch: int, k: float = 4.0) -> Dict[str, float]:
+    st = _Stats()
+    H = w["cls"].size
+    B, C, I, _ = pixels.shape
+    g = I // patch
+
+    def lin(name, x):
+        st.see(name + ".in", x)
+        y = x @ w[name + ".w"].T
+        st.see(name + ".out", y)
+        return (y + w[name + ".b"]).astype(F32)
+
+    xp = pixels.reshape(B, C, g, patch, g, patch).transpose(0, 2, 4, 1, 3, 5).reshape(B, g * g, -1)
+    y = xp @ w["conv.w"].T + w["conv.b"] + w["pos"][1:]
+    x = np.concatenate([np.broadcast_to(w["cls"] + w["pos"][0], (B, 1, H)), y], 1).astype(F32)
+    for l in range(n_layer):
+        p = f"enc.{l}"
+        h = _ln(x, w[p + ".ln1.g"], w[p + ".ln1.b"])
+        qkv = lin(p + ".qkv", h)
+        a = _attn(qkv[..., :H], qkv[..., H:2 * H], qkv[..., 2 * H:], heads, None)
+        x = x + lin(p + ".out", a)
+        h = _ln(x, w[p + ".ln2.g"], w[p + ".ln2.b"])
+        x = x + lin(p + ".fc2", _act(lin(p + ".fc1", h), "gelu"))
+    amax = st.amax(k)
+    for name, t in w.items():
+        if name.endswith(".w") and t.ndim == 2 and name != "conv.w":
+            amax[name] = float(F32(k * t.std()))
+    return amax
+
+
+def make_vit(path: Optional[str] = None, *, hidden=768, heads=12, ffn=3072, n_layer=12, image=224, patch=16, channels=3,
+             seed=1234, calib_pixels: Optional[np.ndarray] = None):
+    """Builds (conf, amax, tensors) of a seeded synthetic QuantVit (patch embedding, pre-LN GELU encoder, final LayerNorm)."""
+    w = vit_weights(hidden, heads, ffn, n_layer, image, patch, channels, seed)
+    if calib_pixels is None:
+        calib_pixels = vit_inputs(batch=2, image=image, channels=channels, seed=seed + 1)
+    amax = calibrate_vit(w, calib_pixels, heads=heads, n_layer=n_layer, patch=patch)
+    conf = dict(hidden=hidden, heads=heads, ffn=ffn, n_enc=n_layer, act_gelu=1.0, pre_ln=1.0, max_step=1 + (image // patch) ** 2,
+                image_size=image, patch_size=patch, channels=channels)
+    if path is not None:
+        from . import weights
+
+        weights.save(path, "QuantVit", conf, amax, w)
+    return conf, amax, w
+
+
 # ------------------------------------------------------------------------------------------- GPT-2
 def gpt_weights(hidden=1024, heads=16, ffn=4096, n_layer=24, vocab=50257, max_pos=1024, seed=1234, std=0.02):
     rng = np.random.default_rng(seed)

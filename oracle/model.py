@@ -425,6 +425,44 @@ class Bert:
         return x
 
 
+# --------------------------------------------------------------------------- ViT encoder
+def patch_embed(w: Dict[str, np.ndarray], pixels: np.ndarray, patch: int) -> np.ndarray:
+    """pixels [B,C,I,I] fp32 -> [B, 1+N, H]: token 0 = cls + pos[0]; token 1+n = conv(patch n) + bias + pos[1+n] with
+    kernel = stride = patch, patches in row-major order, weight index (hidden, channel, row, col)
+    (ker_patch_emb, lightseq/inference/kernels/embKernels.cc.cu:565-606). The dot products are taken in float64 and
+    rounded once to fp32 (the reference sums in fp32 in a block-reduction order of its own); bias and position are
+    fp32 additions in the reference's order."""
+    B, C, I, _ = pixels.shape
+    g = I // patch
+    x = pixels.reshape(B, C, g, patch, g, patch).transpose(0, 2, 4, 1, 3, 5).reshape(B, g * g, C * patch * patch)
+    y = (x.astype(np.float64) @ w["conv.w"].reshape(w["conv.w"].shape[0], -1).astype(np.float64).T).astype(F32)
+    y = (y + w["conv.b"].astype(F32)).astype(F32) + w["pos"][1:1 + g * g].astype(F32)
+    cls = (w["cls"].astype(F32) + w["pos"][0].astype(F32)).astype(F32)
+    return np.concatenate([np.broadcast_to(cls, (B, 1, cls.size)), y.astype(F32)], axis=1).astype(F32)
+
+
+class Vit:
+    """QuantVit: patch embedding (fp32) -> pre-LN int8 encoder layers -> final LayerNorm; output [B, 1+N, H] fp32 as
+    QuantVitEncoder::run_one_infer leaves it (lightseq/inference/model/quant_vit_encoder.cc.cu:189-232). No token is
+    padding."""
+
+    def __init__(self, cfg: Config, st: State, patch: int):
+        self.cfg = cfg
+        self.st = st
+        self.patch = patch
+
+    def forward(self, pixels: np.ndarray) -> np.ndarray:
+        cfg, st = self.cfg, self.st
+        x = patch_embed(st.w, pixels, self.patch)
+        st.rec("emb.out", x)
+        for l in range(cfg.n_enc):
+            x = encoder_layer(st, x, None, f"enc.{l}", cfg)
+            st.rec(f"enc.{l}.y", x)
+        if cfg.pre_ln:
+            x = layer_norm(x, st.w["enc.ln.g"], st.w["enc.ln.b"])
+        return x.astype(F32)
+
+
 # --------------------------------------------------------------------------- GPT-2 style decoder-only model
 def gpt_layer(st: State, x: np.ndarray, p: str, cfg: Config, cache: dict) -> np.ndarray:
     """Decoder-only layer (TransformerDecoderLayer with has_cross_attn=False, pre-LN, causal;
