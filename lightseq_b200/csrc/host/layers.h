@@ -43,7 +43,7 @@ class QuantTransformerEncoderLayer : public Layer {
     qkv_.load(*ctx, wf, prefix + ".qkv", false);
     out_.load(*ctx, wf, prefix + ".out", false);
     fc1_.load(*ctx, wf, prefix + ".fc1", false);
-    fc2_.load(*ctx, wf, prefix + ".fc2", relu);
+    fc2_.load(*ctx, wf, prefix + ".fc2", relu, true, true, "", "", true, true);  // the encoder-only file formats hold no fc2.out
     ln1_.load(*ctx, wf, prefix + ".ln1", hidden);
     ln2_.load(*ctx, wf, prefix + ".ln2", hidden);
   }
@@ -352,7 +352,7 @@ class QuantGptLayer : public Layer {
     qkv_.load(*ctx, wf, prefix + ".qkv", false);
     out_.load(*ctx, wf, prefix + ".out", false);
     fc1_.load(*ctx, wf, prefix + ".fc1", false);
-    fc2_.load(*ctx, wf, prefix + ".fc2", false);
+    fc2_.load(*ctx, wf, prefix + ".fc2", false, true, true, "", "", true, true);
     ln1_.load(*ctx, wf, prefix + ".ln1", hidden);
     ln2_.load(*ctx, wf, prefix + ".ln2", hidden);
     s_kv_ = wf.amax(prefix + ".kv") / 127.0f;

@@ -27,7 +27,8 @@ struct QLinearParams {
 
   // Uploads W (fp32), quantises it on the device (ls100_quantize_weight) and frees the staging copy.
   void load(Context& ctx, const WeightsFile& wf, const std::string& name, bool unsigned_in_, bool has_in = true,
-            bool has_out = true, const std::string& wname = "", const std::string& w_amax = "", bool has_bias = true) {
+            bool has_out = true, const std::string& wname = "", const std::string& w_amax = "", bool has_bias = true,
+            bool out_optional = false) {
     const std::string wn = wname.empty() ? name + ".w" : wname;
     const HostTensor& W = wf.tensor(wn);
     if (W.dims.size() != 2) throw std::runtime_error(wn + ": expected a matrix");
@@ -42,7 +43,8 @@ struct QLinearParams {
       s_acc = s_in * s_w;
     }
     if (has_out) {
-      amax_out = wf.amax(name + ".out");
+      // out_optional: 0 = the output stays unquantised (s_out 0 switches the epilogue's output quantiser off)
+      amax_out = out_optional ? wf.amax_or_unquantised(name + ".out") : wf.amax(name + ".out");
       s_out = amax_out / 127.0f;
     }
     float* staging = nullptr;

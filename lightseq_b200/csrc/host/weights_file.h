@@ -94,6 +94,13 @@ class WeightsFile {
     if (!(it->second > 0.f)) throw std::runtime_error("clip-max '" + k + "' is not positive");
     return it->second;
   }
+  // A clip-max that may be stored as 0 = "this output is not quantised" (file formats without that entry).
+  float amax_or_unquantised(const std::string& k) const {
+    auto it = amax_.find(k);
+    if (it == amax_.end()) throw std::runtime_error("weight file has no clip-max '" + k + "'");
+    if (it->second == 0.f) return 0.f;
+    return amax(k);
+  }
   const HostTensor& tensor(const std::string& k) const {
     auto it = tensors_.find(k);
     if (it == tensors_.end()) throw std::runtime_error("weight file has no tensor '" + k + "'");

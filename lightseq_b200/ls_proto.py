@@ -1,7 +1,8 @@
 """Reader and writer for the reference's ``QuantTransformer`` protobuf weight files
-(lightseq/inference/proto/quant_transformer.proto:10-165), without protoc or the protobuf package: a proto3
-wire-format codec (varint / 32-bit / length-delimited fields, packed and unpacked repeated floats) plus the
-field tables of the five messages.
+(lightseq/inference/proto/quant_transformer.proto:10-165) and, further down, its ``QuantBert``, ``QuantGpt`` and
+``QuantVit`` files (quant_bert.proto, quant_gpt.proto, quant_vit.proto), without protoc or the protobuf package: a
+proto3 wire-format codec (varint / 32-bit / length-delimited fields, packed and unpacked repeated floats) plus the
+field tables of the messages.
 
 Conventions of the files, taken from the exporter that writes them
 (examples/inference/python/export/fairseq/ls_torch_fs_quant_transformer_export.py:20-290,
@@ -309,17 +310,187 @@ def write_quant_transformer(path: str, conf, amax, t) -> None:
         f.write(out)
 
 
-def convert(pb_path: str, ls100_path: str) -> None:
-    """Reference protobuf file -> the engine's .ls100 container."""
+# ------------------------------------------------------------------------------------------------ QuantBert / QuantGpt / QuantVit
+# Their layer message is the encoder layer of QuantTransformer without ffn_second_output_clip_max (the reference's
+# encoder-only engines dequantise the second FFN GEMM straight from int32); QuantGpt adds self_qkv_bias_out_clip_max
+# as field 24. A clip-max the file does not hold is stored as 0 = "this output is not quantised".
+_ENC_CLIP_23 = _ENC_CLIP[:-1]
+
+
+def _read_stack(root, prefix: str, amax, t, dims, kv_field: int = 0) -> int:
+    layers = root.get(2, [])
+    for i, (_, m) in enumerate(layers):
+        msg = parse_message(m)
+        _read_layer(msg, f"{prefix}.{i}", _ENC_VEC, _ENC_KER, _ENC_CLIP_23, amax, t, dims)
+        amax[f"{prefix}.{i}.fc2.out"] = 0.0
+        if kv_field:
+            amax[f"{prefix}.{i}.kv"] = _float(msg, kv_field)
+    return len(layers)
+
+
+def _write_stack(prefix: str, n: int, amax, t, kv_field: int = 0) -> bytes:
+    out = bytearray()
+    for i in range(n):
+        if float(amax.get(f"{prefix}.{i}.fc2.out", 0.0)) != 0.0:
+            raise ValueError(f"{prefix}.{i}.fc2.out: this file format has no clip-max for the second FFN output (store 0)")
+        m = _write_layer(f"{prefix}.{i}", _ENC_VEC, _ENC_KER, _ENC_CLIP_23, amax, t)
+        if kv_field:
+            m += _enc_float(kv_field, amax[f"{prefix}.{i}.kv"])
+        out += _tag(2, 2) + _varint(len(m)) + m
+    return bytes(out)
+
+
+def _parts(path: str, what: str):
+    root = parse_message(open(path, "rb").read())
+    if 1 not in root or 3 not in root:
+        raise ValueError(f"not a {what} file: src_embedding and model_conf are required")
+    return root, parse_message(root[1][-1][1]), parse_message(root[3][-1][1])
+
+
+def read_quant_bert(path: str):
+    """Reference QuantBert protobuf file (lightseq/inference/proto/quant_bert.proto) -> (conf, amax, tensors). The file
+    holds ONE token table (word + token-type 0 already summed by the exporter): it becomes ``emb`` with a zero
+    ``type_emb``."""
+    root, src, mc = _parts(path, "QuantBert")
+    H = _floats(src, 3).size
+    if H == 0:
+        raise ValueError("src_embedding.norm_scale is empty")
+    amax: Dict[str, float] = {}
+    t: Dict[str, np.ndarray] = {}
+    emb_u = _bytes(src, 1)
+    V = emb_u.size // H
+    amax["emb"] = _float(src, 5)
+    t["emb"] = _dequant(emb_u, amax["emb"]).reshape(V, H)
+    t["type_emb"] = np.zeros((2, H), F32)
+    pos = _floats(src, 2)
+    t["pos"] = pos.reshape(pos.size // H, H)
+    t["emb.ln.g"], t["emb.ln.b"] = _floats(src, 3), _floats(src, 4)
+    dims: Dict[str, int] = {}
+    n = _read_stack(root, "enc", amax, t, dims)
+    if _int(mc, 3) == 0:
+        raise ValueError("pre-LN BERT models are not supported by the engine")
+    if _int(mc, 5) != 0:
+        raise ValueError("multilingual models are not supported by the engine")
+    conf = dict(hidden=H, heads=_int(mc, 1), ffn=dims.get("ffn", 0), n_enc=n, vocab=V, act_gelu=float(_int(mc, 4)), pre_ln=0.0,
+                max_step=pos.size // H, pad_id=_int(mc, 2))
+    return conf, amax, t
+
+
+def write_quant_bert(path: str, conf, amax, t) -> None:
+    if np.any(np.asarray(t["type_emb"])[0] != 0):
+        raise ValueError("the file format holds one token table: fold type_emb[0] into emb first")
+    src = (_enc_bytes(1, _quant_engine(t["emb"], amax["emb"]).tobytes()) + _enc_floats(2, t["pos"]) + _enc_floats(3, t["emb.ln.g"]) +
+           _enc_floats(4, t["emb.ln.b"]) + _enc_float(5, amax["emb"]))
+    mc = _enc_int(1, conf["heads"]) + _enc_int(2, conf["pad_id"]) + _enc_int(3, 1) + _enc_int(4, 1 if conf.get("act_gelu") else 0)
+    out = _tag(1, 2) + _varint(len(src)) + src + _write_stack("enc", int(conf["n_enc"]), amax, t) + _tag(3, 2) + _varint(len(mc)) + mc
+    with open(path, "wb") as f:
+        f.write(out)
+
+
+def read_quant_gpt(path: str):
+    """Reference QuantGpt protobuf file (lightseq/inference/proto/quant_gpt.proto) -> (conf, amax, tensors)."""
+    root, src, mc = _parts(path, "QuantGpt")
+    H = _floats(src, 3).size
+    if H == 0:
+        raise ValueError("src_embedding.norm_scale is empty")
+    amax: Dict[str, float] = {}
+    t: Dict[str, np.ndarray] = {}
+    emb_u = _bytes(src, 1)
+    V = emb_u.size // H
+    amax["emb"] = _float(src, 5)
+    t["emb"] = _dequant(emb_u, amax["emb"]).reshape(V, H)
+    pos = _floats(src, 2)
+    t["pos"] = pos.reshape(pos.size // H, H)
+    t["dec.ln.g"], t["dec.ln.b"] = _floats(src, 3), _floats(src, 4)
+    amax["logits.in"], amax["logits.out"] = _float(src, 6), _float(src, 7)
+    dims: Dict[str, int] = {}
+    n = _read_stack(root, "dec", amax, t, dims, kv_field=24)
+    method = _str(mc, 3, "topk")
+    if method not in ("topk", "topp"):
+        raise ValueError(f"sampling_method {method!r}: the QuantGpt engine implements topk and topp")
+    max_step = pos.size // H
+    extra = _int(mc, 7)
+    conf = dict(hidden=H, heads=_int(mc, 1), ffn=dims.get("ffn", 0), n_dec=n, vocab=V, act_gelu=1.0, pre_ln=1.0, max_step=max_step,
+                end_id=_int(mc, 6), topk=_int(mc, 5, 1) if method == "topk" else 1, topp=_float(mc, 4) if method == "topp" else 0.0,
+                pad_id=_int(mc, 2), max_new_tokens=extra if extra > 0 else max_step)
+    return conf, amax, t
+
+
+def write_quant_gpt(path: str, conf, amax, t) -> None:
+    src = (_enc_bytes(1, _quant_engine(t["emb"], amax["emb"]).tobytes()) + _enc_floats(2, t["pos"]) + _enc_floats(3, t["dec.ln.g"]) +
+           _enc_floats(4, t["dec.ln.b"]) + _enc_float(5, amax["emb"]) + _enc_float(6, amax["logits.in"]) + _enc_float(7, amax["logits.out"]))
+    topp = float(conf.get("topp", 0.0))
+    method = b"topp" if topp > 0 else b"topk"
+    mc = (_enc_int(1, conf["heads"]) + _enc_int(2, conf.get("pad_id", 0)) + _tag(3, 2) + _varint(len(method)) + method + _enc_float(4, topp) +
+          _enc_int(5, conf.get("topk", 1)) + _enc_int(6, conf["end_id"]) + _enc_int(7, conf.get("max_new_tokens", 0)))
+    out = (_tag(1, 2) + _varint(len(src)) + src + _write_stack("dec", int(conf["n_dec"]), amax, t, kv_field=24) +
+           _tag(3, 2) + _varint(len(mc)) + mc)
+    with open(path, "wb") as f:
+        f.write(out)
+
+
+def read_quant_vit(path: str):
+    """Reference QuantVit protobuf file (lightseq/inference/proto/quant_vit.proto) -> (conf, amax, tensors)."""
+    root, src, mc = _parts(path, "QuantVit")
+    H = _floats(src, 2).size
+    if H == 0:
+        raise ValueError("src_embedding.conv_bias is empty")
+    patch, image = _int(mc, 4), _int(mc, 3)
+    if patch < 1 or image < patch or image % patch:
+        raise ValueError(f"image_size {image} / patch_size {patch}")
+    amax: Dict[str, float] = {}
+    t: Dict[str, np.ndarray] = {}
+    cw = _floats(src, 1)
+    if cw.size % (H * patch * patch):
+        raise ValueError("conv_weight: size is not hidden * channels * patch * patch")
+    channels = cw.size // (H * patch * patch)
+    t["conv.w"] = cw.reshape(H, channels * patch * patch)
+    t["conv.b"] = _floats(src, 2)
+    n_tok = 1 + (image // patch) ** 2
+    pos = _floats(src, 3)
+    if pos.size < n_tok * H:
+        raise ValueError("position_embedding is shorter than 1 + (image_size / patch_size)^2 rows")
+    t["pos"] = pos.reshape(pos.size // H, H)[:n_tok].copy()
+    t["cls"] = _floats(src, 4)
+    t["enc.ln.g"], t["enc.ln.b"] = _floats(src, 5), _floats(src, 6)
+    dims: Dict[str, int] = {}
+    n = _read_stack(root, "enc", amax, t, dims)
+    if _int(mc, 5) != 0:
+        raise ValueError("post-LN ViT models are not supported by the engine")
+    conf = dict(hidden=H, heads=_int(mc, 1), ffn=dims.get("ffn", 0), n_enc=n, act_gelu=float(_int(mc, 2)), pre_ln=1.0, max_step=n_tok,
+                image_size=image, patch_size=patch, channels=channels)
+    return conf, amax, t
+
+
+def write_quant_vit(path: str, conf, amax, t) -> None:
+    src = (_enc_floats(1, t["conv.w"]) + _enc_floats(2, t["conv.b"]) + _enc_floats(3, t["pos"]) + _enc_floats(4, t["cls"]) +
+           _enc_floats(5, t["enc.ln.g"]) + _enc_floats(6, t["enc.ln.b"]))
+    mc = (_enc_int(1, conf["heads"]) + _enc_int(2, 1 if conf.get("act_gelu") else 0) + _enc_int(3, conf["image_size"]) +
+          _enc_int(4, conf["patch_size"]))
+    out = _tag(1, 2) + _varint(len(src)) + src + _write_stack("enc", int(conf["n_enc"]), amax, t) + _tag(3, 2) + _varint(len(mc)) + mc
+    with open(path, "wb") as f:
+        f.write(out)
+
+
+READERS = {"QuantTransformer": read_quant_transformer, "QuantBert": read_quant_bert, "QuantGpt": read_quant_gpt,
+           "QuantVit": read_quant_vit}
+WRITERS = {"QuantTransformer": write_quant_transformer, "QuantBert": write_quant_bert, "QuantGpt": write_quant_gpt,
+           "QuantVit": write_quant_vit}
+
+
+def convert(pb_path: str, ls100_path: str, model: str = "QuantTransformer") -> None:
+    """Reference protobuf file of the named model class -> the engine's .ls100 container."""
     from . import weights
 
-    conf, amax, t = read_quant_transformer(pb_path)
-    weights.save(ls100_path, "QuantTransformer", conf, amax, t)
+    if model not in READERS:
+        raise ValueError(f"model {model!r}: one of {sorted(READERS)}")
+    conf, amax, t = READERS[model](pb_path)
+    weights.save(ls100_path, model, conf, amax, t)
 
 
 if __name__ == "__main__":
     import sys
 
-    if len(sys.argv) != 3:
-        raise SystemExit("usage: python -m lightseq_b200.ls_proto <quant_transformer.pb> <out.ls100>")
-    convert(sys.argv[1], sys.argv[2])
+    if len(sys.argv) not in (3, 4):
+        raise SystemExit("usage: python -m lightseq_b200.ls_proto <model.pb> <out.ls100> [QuantTransformer|QuantBert|QuantGpt|QuantVit]")
+    convert(sys.argv[1], sys.argv[2], sys.argv[3] if len(sys.argv) == 4 else "QuantTransformer")

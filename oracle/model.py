@@ -150,6 +150,10 @@ def qlinear(st: State, x: np.ndarray, name: str, *, wname: Optional[str] = None,
     else:
         # weight-only quantisation (pre_activation="encoder_out", quantization.py:41-46)
         v = (x.astype(np.float64) @ wq64.T).astype(F32) * s_w
+    if quant_out and not st.amax.get(name + ".out", 0.0) > 0.0:
+        if return_q:
+            raise ValueError(name + ".out: the integer output was asked for but this output is not quantised")
+        quant_out = False  # a clip-max of 0 (or none): files of the encoder-only engines hold none for the second FFN output
     if quant_out:
         oq, s_o = Q.quantize(v, st.amax[name + ".out"], clip=False)
         st.rec(name + ".out_q", oq)

@@ -100,3 +100,70 @@ def test_rejects_what_the_engine_cannot_run(tmp_path):
         p = tmp_path / "junk.pb"
         p.write_bytes(lp._enc_int(1, 5))
         lp.read_quant_transformer(str(p))
+
+
+def _no_fc2_out(amax):
+    """The encoder-only file formats hold no clip-max for the second FFN output: 0 = not quantised."""
+    return {k: (0.0 if k.endswith(".fc2.out") else v) for k, v in amax.items()}
+
+
+def _same_model(a, b, skip_conf=()):
+    (conf, amax, w), (conf2, amax2, w2) = a, b
+    for k in conf:
+        if k not in skip_conf:
+            assert float(conf2[k]) == pytest.approx(float(conf[k]), rel=1e-6), k
+    assert set(amax2) == set(amax)
+    for k in amax:
+        assert F32(amax2[k]) == F32(amax[k]), k
+    assert set(w2) == set(w)
+    for k, t in w.items():
+        assert w2[k].shape == tuple(np.shape(t)), k
+        if (k.endswith(".w") and k != "conv.w") or k == "emb":
+            assert np.array_equal(lp._quant_engine(w2[k], amax[k]), lp._quant_engine(t, amax[k])), k
+        else:
+            assert np.array_equal(w2[k], np.asarray(t, F32)), k
+
+
+def test_quant_bert_file_round_trip(tmp_path):
+    conf, amax, w = synth.make_bert(None, hidden=64, heads=1, ffn=128, n_layer=2, vocab=50, max_step=24, seed=2)
+    w["emb"] = (w["emb"] + w["type_emb"][0]).astype(F32)  # the file holds one table
+    w["type_emb"] = np.zeros_like(w["type_emb"])
+    amax = _no_fc2_out(amax)
+    pb = str(tmp_path / "bert.pb")
+    lp.write_quant_bert(pb, conf, amax, w)
+    _same_model((conf, amax, w), lp.read_quant_bert(pb))
+    with pytest.raises(ValueError, match="second FFN"):
+        lp.write_quant_bert(pb, conf, dict(amax, **{"enc.0.fc2.out": 1.0}), w)
+
+
+def test_quant_gpt_file_round_trip(tmp_path):
+    conf, amax, w = synth.make_gpt(None, hidden=64, heads=1, ffn=128, n_layer=2, vocab=60, max_step=32, max_new_tokens=9, topk=4)
+    amax = _no_fc2_out(amax)
+    pb = str(tmp_path / "gpt.pb")
+    lp.write_quant_gpt(pb, conf, amax, w)
+    got = lp.read_quant_gpt(pb)
+    _same_model((conf, amax, w), got, skip_conf=("rng_seed",))  # the seed is not part of the file
+    assert int(got[0]["topk"]) == 4 and float(got[0]["topp"]) == 0.0 and int(got[0]["max_new_tokens"]) == 9
+    conf_p = dict(conf, topp=0.75)
+    lp.write_quant_gpt(pb, conf_p, amax, w)
+    c = lp.read_quant_gpt(pb)[0]
+    assert float(c["topp"]) == pytest.approx(0.75) and int(c["topk"]) == 1
+
+
+def test_quant_vit_file_round_trip(tmp_path):
+    conf, amax, w = synth.make_vit(None, hidden=64, heads=1, ffn=128, n_layer=2, image=16, patch=4, seed=4)
+    amax = _no_fc2_out(amax)
+    pb = str(tmp_path / "vit.pb")
+    lp.write_quant_vit(pb, conf, amax, w)
+    _same_model((conf, amax, w), lp.read_quant_vit(pb))
+
+
+def test_convert_names_the_model_class(tmp_path):
+    conf, amax, w = synth.make_vit(None, hidden=64, heads=1, ffn=128, n_layer=1, image=8, patch=4, seed=4)
+    pb, out = str(tmp_path / "vit.pb"), str(tmp_path / "vit.ls100")
+    lp.write_quant_vit(pb, conf, _no_fc2_out(amax), w)
+    lp.convert(pb, out, "QuantVit")
+    model, conf2, amax2, _ = weights.load(out)
+    assert model == "QuantVit" and int(conf2["patch_size"]) == 4 and amax2["enc.0.fc2.out"] == 0.0
+    with pytest.raises(ValueError, match="one of"):
+        lp.convert(pb, out, "QuantLlama")
