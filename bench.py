@@ -259,6 +259,29 @@ def kernel_cases(torch, L, conf, B, S, step):
         L.call("ls100_gemm_i8", CTX[0], a, st)
 
     cases["gemm_square"] = (gemm_square, 2 * sq ** 3, "tensor", f"gemm_i8_persist_kernel, {sq}x{sq}x{sq}, int8 out")
+    # BERT-base encoder GEMMs with fp32 residual output (32 x 512 tokens): out-projection and second FFN
+    er = 16384
+    ea = [i8(er, 3072) for _ in range(3)]
+    ew1, ew2 = i8(768, 768), i8(768, 3072)
+    ex = [torch.randn(er, 768, device=dev) for _ in range(3)]
+    ebz = torch.zeros(768, device=dev)
+
+    def gemm_enc_out(i, st):
+        j = i % 3
+        a = L.GemmI8Args(a=ea[j].data_ptr(), lda=3072, w=ew1.data_ptr(), ldw=768, m=er, n=768, k=768, s_acc=1e-4, s_outq=0.02,
+                         bias=ebz.data_ptr(), resid=ex[j].data_ptr(), ldr=768, out_kind=L.OUT_F32, out=ex[j].data_ptr(), ldo=768)
+        L.call("ls100_gemm_i8", CTX[0], a, st)
+
+    def gemm_enc_ffn2(i, st):
+        j = i % 3
+        a = L.GemmI8Args(a=ea[j].data_ptr(), lda=3072, w=ew2.data_ptr(), ldw=3072, m=er, n=768, k=3072, s_acc=1e-4, s_outq=0.02,
+                         bias=ebz.data_ptr(), resid=ex[j].data_ptr(), ldr=768, out_kind=L.OUT_F32, out=ex[j].data_ptr(), ldo=768)
+        L.call("ls100_gemm_i8", CTX[0], a, st)
+
+    cases["gemm_enc_out"] = (gemm_enc_out, er * 768 + 768 * 768 + 2 * er * 768 * 4, "hbm",
+                             f"gemm_i8_persist_kernel, {er}x768x768, fake-quant+bias+residual, fp32 out")
+    cases["gemm_enc_ffn2"] = (gemm_enc_ffn2, er * 3072 + 768 * 3072 + 2 * er * 768 * 4, "hbm",
+                              f"gemm_i8_persist_kernel, {er}x768x3072, fake-quant+bias+residual, fp32 out")
     # decoder self-attention at decode position `step`
     nk = max(2, int(200e6 // (2 * T * ms * H)) + 1)
     kcs, vcs = [i8(T, heads, ms, 64) for _ in range(nk)], [i8(T, heads, ms, 64) for _ in range(nk)]
@@ -722,7 +745,7 @@ def main():
     ap.add_argument("--decode-steps", type=int, default=-1,
                     help="cap the number of decode steps per generation (profiling aid; the result is not a bench value)")
     ap.add_argument("--kernel", default=None,
-                    help="run one kernel family alone (gemm_dec, gemm_dec_ln, gemm_logits, gemm_enc_qkv, gemm_square, attn_self, attn_dec, attn_cross, beam_topk, ln_quant)")
+                    help="run one kernel family alone (gemm_dec, gemm_dec_ln, gemm_logits, gemm_enc_qkv, gemm_enc_out, gemm_enc_ffn2, gemm_square, attn_self, attn_dec, attn_cross, beam_topk, ln_quant)")
     ap.add_argument("--workload", default=None, choices=["bert", "vit", "gpt", "big", "eos"],
                     help="run another BASELINE configuration (BERT-base, GPT-2 medium, Transformer-big) on one GPU, or the "
                          "benchmark model with a boosted EOS (early-stop bookkeeping)")

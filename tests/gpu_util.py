@@ -34,13 +34,13 @@ def sync_check():
 
 
 def gemm(a_q, w_q, *, s_acc, out_kind, s_outq=0.0, bias=None, act=L.ACT_NONE, resid=None, s_req=0.0, w_off=None,
-         out_dtype=None, ln=None):
+         out_dtype=None, ln=None, in_place=False):
     """a_q [M,K] int8 device, w_q [N,K] int8 device -> device tensor."""
     m, k = a_q.shape
     n = w_q.shape[0]
     dt = {L.OUT_OUTQ_I8: torch.int8, L.OUT_F32: torch.float32, L.OUT_REQ_S8: torch.int8, L.OUT_REQ_U8: torch.int8,
           L.OUT_F16: torch.float16, L.OUT_I32: torch.int32}[out_kind]
-    out = torch.full((m, n), 0, dtype=dt, device="cuda:0")
+    out = resid if in_place else torch.full((m, n), 0, dtype=dt, device="cuda:0")  # in_place: the residual buffer is the output
     args = L.GemmI8Args(a=ptr(a_q), lda=a_q.stride(0), w=ptr(w_q), ldw=w_q.stride(0), m=m, n=n, k=k, s_acc=s_acc,
                         w_off=ptr(w_off), s_outq=s_outq, bias=ptr(bias), act=act, resid=ptr(resid),
                         ldr=(resid.stride(0) if resid is not None else 0), out_kind=out_kind, s_req=s_req,

@@ -65,9 +65,12 @@ def test_gemm_many_tiles_int32_bit_exact(m, n, k):
     assert np.array_equal(out.cpu().numpy().astype(np.int64), oq.int_matmul(a, w))
 
 
-def test_gemm_many_tiles_bias_residual_and_offset_bit_exact():
-    """The persistent kernel with every epilogue input in use: unsigned input offset, bias, residual, fp32 out."""
-    m, n, k = 6000, 1800, 256
+@pytest.mark.parametrize("m,n,k,in_place", [(6000, 1800, 256, False), (16384, 768, 768, True), (4100, 2564, 384, True),
+                                            (9000, 772, 128, False)])
+def test_gemm_many_tiles_bias_residual_and_offset_bit_exact(m, n, k, in_place):
+    """The persistent kernel with every epilogue input in use: unsigned input offset, bias, residual, fp32 out (the
+    path that moves the residual and the result through per-warp staging tiles); N ending 4, 8 and 36 columns into a
+    256-column tile, ragged M, and the residual buffer doubling as the output as the engine layers use it."""
     st, x, w, b = _qlinear_case(21, m, n, k, unsigned_in=True)
     st.trace = {}
     xq, s_x = oq.quantize(x, st.amax["l.in"], unsigned=True)
@@ -79,9 +82,22 @@ def test_gemm_many_tiles_bias_residual_and_offset_bit_exact():
     resid = rng(22).standard_normal((m, n)).astype(F32)
     off = dev((127 * wq.astype(np.int64).sum(1)).astype(np.int32))
     out = gemm(dev(xq), dev(wq), s_acc=float(F32(s_x * s_w)), out_kind=L.OUT_F32, s_outq=float(s_o), bias=dev(b),
-               resid=dev(resid), w_off=off)
+               resid=dev(resid), w_off=off, in_place=in_place)
     sync_check()
     assert np.array_equal(out.cpu().numpy(), resid + y)
+
+
+def test_gemm_many_tiles_fp32_without_residual_bit_exact():
+    m, n, k = 7000, 1284, 256
+    st, x, w, b = _qlinear_case(31, m, n, k)
+    st.trace = {}
+    y = om.qlinear(st, x, "l")
+    xq, s_x = oq.quantize(x, st.amax["l.in"])
+    wq, s_w = oq.quantize(w, st.amax["l.w"])
+    out = gemm(dev(xq), dev(wq), s_acc=float(F32(s_x * s_w)), out_kind=L.OUT_F32, s_outq=float(oq.scale_of(st.amax["l.out"])),
+               bias=dev(b))
+    sync_check()
+    assert np.array_equal(out.cpu().numpy(), y)
 
 
 def _qlinear_case(seed, m, n, k, unsigned_in=False):
