@@ -108,36 +108,6 @@ __device__ __forceinline__ void at_unpack16(const int4 v, float (&f)[16]) {
   }
 }
 
-// packed fp32 pairs (one instruction for two lanes of arithmetic on sm_100)
-__device__ __forceinline__ float2 at_fma2(float2 a, float2 b, float2 c) {
-  uint64_t ra, rb, rc, rd;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
-  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
-  asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
-  float2 d;
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
-  return d;
-}
-__device__ __forceinline__ float2 at_sub2(float2 a, float2 b) {
-  uint64_t ra, rb, rd;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
-  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
-  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
-  float2 d;
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
-  return d;
-}
-__device__ __forceinline__ float2 at_add2(float2 a, float2 b) {
-  uint64_t ra, rb, rd;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
-  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
-  float2 d;
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
-  return d;
-}
-
 // 16 int8 -> 16 fp16 (8 packed pairs): the byte plus 128 dropped into the mantissa of 1024 (0x6400), minus 1152; exact
 __device__ __forceinline__ void at_unpack16_f16(const int4 v, uint32_t (&h)[8]) {
   const unsigned w[4] = {(unsigned)v.x ^ 0x80808080u, (unsigned)v.y ^ 0x80808080u, (unsigned)v.z ^ 0x80808080u,
@@ -364,10 +334,10 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __gri
           for (int j4 = 0; j4 < 32; j4 += 4) {
             const float4 c4 = *reinterpret_cast<const float4*>(cjh + c0 + j4);
             // |Qi.Ki| <= 64 * 127^2 < 2^22: int -> float by adding into the mantissa of 1.5 * 2^23
-            const float2 fa = at_sub2(make_float2(__uint_as_float(r[j4] + 0x4B400000u), __uint_as_float(r[j4 + 1] + 0x4B400000u)), magic2);
-            const float2 fb = at_sub2(make_float2(__uint_as_float(r[j4 + 2] + 0x4B400000u), __uint_as_float(r[j4 + 3] + 0x4B400000u)), magic2);
-            sv[j4 / 2] = at_fma2(fa, sc2, at_sub2(make_float2(c4.x, c4.y), mm));
-            sv[j4 / 2 + 1] = at_fma2(fb, sc2, at_sub2(make_float2(c4.z, c4.w), mm));
+            const float2 fa = f2_sub(make_float2(__uint_as_float(r[j4] + 0x4B400000u), __uint_as_float(r[j4 + 1] + 0x4B400000u)), magic2);
+            const float2 fb = f2_sub(make_float2(__uint_as_float(r[j4 + 2] + 0x4B400000u), __uint_as_float(r[j4 + 3] + 0x4B400000u)), magic2);
+            sv[j4 / 2] = f2_fma(fa, sc2, f2_sub(make_float2(c4.x, c4.y), mm));
+            sv[j4 / 2 + 1] = f2_fma(fb, sc2, f2_sub(make_float2(c4.z, c4.w), mm));
           }
           if (!__all_sync(0xffffffffu, vw == 0xffffffffu)) {  // some key of this half tile is masked for some row of the warp
 #pragma unroll
@@ -393,10 +363,10 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __gri
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const float2 pp = make_float2(at_ex2(sv[gq * 4 + e].x), at_ex2(sv[gq * 4 + e].y));  // 2^-inf = 0
-                l2 = at_add2(l2, pp);
+                l2 = f2_add(l2, pp);
                 // hi = fp16(p), lo = fp16(p - hi): |p - hi - lo| < 2^-23 p + 2^-25 (p <= 1, so lo may be subnormal)
                 const __half2 h2 = __floats2half2_rn(pp.x, pp.y);
-                const float2 rem = at_sub2(pp, __half22float2(h2));
+                const float2 rem = f2_sub(pp, __half22float2(h2));
                 const __half2 lo2 = __floats2half2_rn(rem.x, rem.y);
                 hi[e] = *reinterpret_cast<const uint32_t*>(&h2);
                 lo[e] = *reinterpret_cast<const uint32_t*>(&lo2);

@@ -126,17 +126,36 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
     }
     return;
   }
+  // From here on the elements go through the arithmetic two at a time (packed fp32 pairs, every lane rounded as
+  // the scalar instruction would): the epilogue is bound by instruction issue.
   float v[NC];
   bool quantised = false;
+  {
+    const float2 sa = f2_set(p.s_acc);
 #pragma unroll
-  for (int j = 0; j < NC; ++j) v[j] = __fmul_rn(__int2float_rn(acc[j]), p.s_acc);
+    for (int j = 0; j < NC; j += 2) {
+      const float2 t = f2_mul(make_float2(__int2float_rn(acc[j]), __int2float_rn(acc[j + 1])), sa);
+      v[j] = t.x;
+      v[j + 1] = t.y;
+    }
+  }
   if (p.s_outq > 0.f) {
+    const float2 so = f2_set(p.s_outq), rso = f2_set(p.rs_outq);
     if (p.out_kind == LS100_OUT_OUTQ_I8) {
 #pragma unroll
-      for (int j = 0; j < NC; ++j) v[j] = quant_s_biased(v[j], p.s_outq, p.rs_outq);
+      for (int j = 0; j < NC; j += 2) {
+        const float2 t = f2_quant_biased(f2_div_rn(make_float2(v[j], v[j + 1]), so, rso));
+        v[j] = t.x;
+        v[j + 1] = t.y;
+      }
     } else {
 #pragma unroll
-      for (int j = 0; j < NC; ++j) v[j] = __fmul_rn(quant_s(v[j], p.s_outq, p.rs_outq), p.s_outq);
+      for (int j = 0; j < NC; j += 2) {
+        const float2 q = f2_sub(f2_quant_biased(f2_div_rn(make_float2(v[j], v[j + 1]), so, rso)), f2_set(kQuantMagic));
+        const float2 t = f2_mul(q, so);
+        v[j] = t.x;
+        v[j + 1] = t.y;
+      }
     }
   }
   if (p.out_kind != LS100_OUT_OUTQ_I8) {
@@ -144,10 +163,12 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
 #pragma unroll
       for (int j = 0; j < NC; j += 4) {
         const float4 b = *reinterpret_cast<const float4*>(s_bias + j);
-        v[j] = __fadd_rn(v[j], b.x);
-        v[j + 1] = __fadd_rn(v[j + 1], b.y);
-        v[j + 2] = __fadd_rn(v[j + 2], b.z);
-        v[j + 3] = __fadd_rn(v[j + 3], b.w);
+        const float2 t0 = f2_add(make_float2(v[j], v[j + 1]), make_float2(b.x, b.y));
+        const float2 t1 = f2_add(make_float2(v[j + 2], v[j + 3]), make_float2(b.z, b.w));
+        v[j] = t0.x;
+        v[j + 1] = t0.y;
+        v[j + 2] = t1.x;
+        v[j + 3] = t1.y;
       }
     }
     if (p.act == LS100_ACT_RELU) {
@@ -163,18 +184,24 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
         const float sub = (p.out_kind == LS100_OUT_REQ_U8) ? 127.f : 0.f;
         float q[NC];
         unsigned redo = 0;
+        const float2 sr = f2_set(p.s_req), rsr = f2_set(p.rs_req), sub2 = f2_set(sub), magic2 = f2_set(kQuantMagic);
 #pragma unroll
-        for (int j = 0; j < NC; ++j) {
-          const float g = gelu_fast(v[j]);
-          const float u = __fadd_rn(__fsub_rn(div_rn(g, p.s_req, p.rs_req), sub), 0.5f);
-          const float b = __fadd_rd(u, kQuantMagic);
-          const float d = __fsub_rn(u, __fsub_rn(b, kQuantMagic));  // u - floor(u), in [0, 1)
+        for (int j = 0; j < NC; j += 2) {
+          const float2 x = make_float2(v[j], v[j + 1]);
+          const float2 g = f2_gelu_fast(x);
+          const float2 u = f2_add(f2_sub(f2_div_rn(g, sr, rsr), sub2), f2_set(0.5f));
+          const float2 b = f2_add_rd(u, magic2);
+          const float2 d = f2_sub(u, f2_sub(b, magic2));  // u - floor(u), in [0, 1)
           // |gelu_fast - gelu| <= 0.5|x| * 5e-7 (erf approximation + ex2/rcp error) + a few ulp of g; in
           // quantisation units that is the first two terms, the third covers the rounding of u itself.
-          const float tol = fmaf(fabsf(v[j]) * p.rs_req, 1e-6f, fmaf(fabsf(u), 2e-6f, 4e-6f));
-          const bool near = fabsf(u) < 200.f && fabsf(__fsub_rn(d, 0.5f)) > __fsub_rn(0.5f, tol);
-          redo |= near ? (1u << j) : 0u;
-          q[j] = fminf(fmaxf(b, kQuantMagic - 127.f), kQuantMagic + 127.f);
+          const float2 au = f2_abs(u);
+          const float2 tol = f2_fma(f2_mul(f2_abs(x), rsr), f2_set(1e-6f), f2_fma(au, f2_set(2e-6f), f2_set(4e-6f)));
+          const float2 dist = f2_abs(f2_sub(d, f2_set(0.5f)));
+          const float2 lim = f2_sub(f2_set(0.5f), tol);
+          const bool near0 = au.x < 200.f && dist.x > lim.x, near1 = au.y < 200.f && dist.y > lim.y;
+          redo |= (near0 ? (1u << j) : 0u) | (near1 ? (2u << j) : 0u);
+          q[j] = fminf(fmaxf(b.x, kQuantMagic - 127.f), kQuantMagic + 127.f);
+          q[j + 1] = fminf(fmaxf(b.y, kQuantMagic - 127.f), kQuantMagic + 127.f);
         }
         if (redo) {
 #pragma unroll
@@ -193,17 +220,23 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
     if (p.resid != nullptr && row_ok) {
       if (rr_valid) {  // prefetched before the accumulator was ready
 #pragma unroll
-        for (int j = 0; j < NC; ++j) v[j] = __fadd_rn(v[j], rr[j]);
+        for (int j = 0; j < NC; j += 2) {
+          const float2 t = f2_add(make_float2(v[j], v[j + 1]), make_float2(rr[j], rr[j + 1]));
+          v[j] = t.x;
+          v[j + 1] = t.y;
+        }
       } else {
         const float* rp = p.resid + (long long)row * p.ldr + col0;
         if (full && ((p.ldr & 3) == 0) && ((((uintptr_t)p.resid) & 15) == 0)) {
 #pragma unroll
           for (int j = 0; j < NC; j += 4) {
             const float4 t = *reinterpret_cast<const float4*>(rp + j);
-            v[j] = __fadd_rn(v[j], t.x);
-            v[j + 1] = __fadd_rn(v[j + 1], t.y);
-            v[j + 2] = __fadd_rn(v[j + 2], t.z);
-            v[j + 3] = __fadd_rn(v[j + 3], t.w);
+            const float2 t0 = f2_add(make_float2(v[j], v[j + 1]), make_float2(t.x, t.y));
+            const float2 t1 = f2_add(make_float2(v[j + 2], v[j + 3]), make_float2(t.z, t.w));
+            v[j] = t0.x;
+            v[j + 1] = t0.y;
+            v[j + 2] = t1.x;
+            v[j + 3] = t1.y;
           }
         } else {
 #pragma unroll
@@ -213,12 +246,14 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
       }
     }
     if (quantised) {
-    } else if (p.out_kind == LS100_OUT_REQ_S8) {
+    } else if (p.out_kind == LS100_OUT_REQ_S8 || p.out_kind == LS100_OUT_REQ_U8) {
+      const float2 sr = f2_set(p.s_req), rsr = f2_set(p.rs_req), sub2 = f2_set(p.out_kind == LS100_OUT_REQ_U8 ? 127.f : 0.f);
 #pragma unroll
-      for (int j = 0; j < NC; ++j) v[j] = quant_s_biased(v[j], p.s_req, p.rs_req);
-    } else if (p.out_kind == LS100_OUT_REQ_U8) {
-#pragma unroll
-      for (int j = 0; j < NC; ++j) v[j] = quant_u_biased(v[j], p.s_req, p.rs_req);
+      for (int j = 0; j < NC; j += 2) {  // x - 0 is x: one form serves the signed and the unsigned quantiser
+        const float2 t = f2_quant_biased(f2_sub(f2_div_rn(make_float2(v[j], v[j + 1]), sr, rsr), sub2));
+        v[j] = t.x;
+        v[j + 1] = t.y;
+      }
     }
   }
   if (row_sum != nullptr) {  // statistics of the finished fp32 values for the fused LayerNorm
