@@ -214,6 +214,7 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     import torch
 
+    # a Fairseq checkpoint pickles its argparse Namespace beside the tensors, hence the full unpickler: only load files you trust
     ck = torch.load(a.checkpoint, map_location="cpu", weights_only=False)
     args = ck.get("args")
     heads = int(getattr(args, "encoder_attention_heads"))
