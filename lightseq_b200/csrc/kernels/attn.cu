@@ -635,9 +635,9 @@ extern "C" int ls100_attn_self(ls100_ctx* ctx, const ls100_attn_self_args* a, ls
   if (a->k_cache && (a->bias || a->max_step < a->seq || (((uintptr_t)a->k_cache) & 15) || (((uintptr_t)a->v_cache) & 15)))
     return LS100_ERR_BAD_ARG;
   if (a->heads > 65535 || a->batch > 65535) return LS100_ERR_UNSUPPORTED;
-  // tensor-core kernel: pairs of heads, no KV cache to fill, at least one full key tile's worth of work
+  // tensor-core kernel: pairs of heads, sequences of at least 16 tokens
   static const bool simt_only = getenv("LS100_ATTN_SIMT") != nullptr;
-  if (!simt_only && (a->heads & 1) == 0 && !a->k_cache && a->seq >= 16 && (long long)a->batch * a->seq < (1ll << 31))
+  if (!simt_only && (a->heads & 1) == 0 && a->seq >= 16 && (long long)a->batch * a->seq < (1ll << 31))
     return attn_self_tc_launch(ctx, a, (cudaStream_t)stream_);
   dim3 grid((a->seq + 63) / 64, a->heads, a->batch);
   const float so = a->amax_out / 127.0f;

@@ -1,5 +1,6 @@
-// Encoder / BERT self-attention on the tensor cores (the same contract as attn_self_kernel in attn.cu; used when the
-// number of heads is even and no KV cache is written).
+// Encoder / BERT / GPT-prompt self-attention on the tensor cores (the same contract as attn_self_kernel in attn.cu,
+// including the optional store of the int8 K/V cache; used when the number of heads is even and the sequence has at
+// least 16 tokens).
 //
 // One CTA per (sentence, PAIR of heads, block of 128 queries). Both GEMMs of attention run as tcgen05 MMAs:
 //   S = Q . K^T   int8 x int8 -> int32 (kind::i8): exact. Q and K tiles come by TMA straight out of the QKV GEMM's
@@ -258,6 +259,17 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __gri
     // scores are kept in the log2 domain: exp(x) = 2^(x log2 e)
     const float sc = __fmul_rn(__fmul_rn(__fmul_rn(a.s_qkv, a.s_qkv), 0.125f), 1.4426950408889634f);
     const float cs = __fmul_rn(__fmul_rn(a.s_qkv, 0.125f), 1.4426950408889634f);
+    if (a.k_cache != nullptr && q_idx < S) {  // GPT prompt: keep this row's int8 K and V of this head for the decode steps
+      const int h = hp * 2 + head;
+      const int8_t* kp = a.qkv + ((long long)row_base + q_idx) * a.ld_qkv + H + h * 64;
+      const int8_t* vp = kp + H;
+      const long long co = (((long long)b * a.heads + h) * a.max_step + q_idx) * 64;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        *reinterpret_cast<int4*>(a.k_cache + co + c * 16) = __ldg(reinterpret_cast<const int4*>(kp + c * 16));
+        *reinterpret_cast<int4*>(a.v_cache + co + c * 16) = __ldg(reinterpret_cast<const int4*>(vp + c * 16));
+      }
+    }
     float m_run = -INFINITY;
     float2 l2 = make_float2(0.f, 0.f);
     bool ok = true;
@@ -450,7 +462,7 @@ int attn_self_tc_init_device() {
 }
 
 // Launches the tensor-core kernel; the caller (ls100_attn_self) has validated the arguments and checked that the
-// number of heads is even and that no KV cache is requested.
+// number of heads is even.
 int attn_self_tc_launch(ls100_ctx* ctx, const ls100_attn_self_args* a, cudaStream_t st) {
   const int H = a->heads * 64;
   const uint64_t rows = (uint64_t)a->batch * (uint64_t)a->seq;

@@ -319,6 +319,34 @@ def test_attn_self_matches_oracle(B, S, heads, causal, with_bias):
     print(f"attn_self B={B} S={S} heads={heads} causal={causal}: one-step mismatch rate {rate:.2e}")
 
 
+@pytest.mark.parametrize("B,S,heads,ms", [(3, 40, 4, 64), (2, 200, 2, 256), (2, 9, 2, 16), (2, 50, 3, 64)])
+def test_attn_self_causal_prompt_fills_the_kv_cache(B, S, heads, ms):
+    """GPT prompt form: causal, no bias, and the int8 keys / values of every position stored into the cache
+    [batch, heads, max_step, 64] (tensor-core kernel for even head counts and S >= 16, SIMT otherwise)."""
+    H = heads * 64
+    r = rng(S + heads)
+    qkv_q = r.integers(-127, 128, size=(B, S, 3 * H), dtype=np.int8)
+    s_qkv = F32(0.017)
+    qkv = qkv_q.astype(F32) * s_qkv
+    a = om.attention_core(qkv[..., :H], qkv[..., H:2 * H], qkv[..., 2 * H:], heads, None, 64 ** -0.5, True)
+    amax = float(F32(4 * a.std()))
+    ref, _ = oq.quantize(a, amax)
+    dq = dev(qkv_q.reshape(B * S, 3 * H))
+    out = empty((B * S, H), torch.int8)
+    kc, vc = empty((B, heads, ms, 64), torch.int8), empty((B, heads, ms, 64), torch.int8)
+    kc.fill_(77)
+    vc.fill_(77)
+    args = L.AttnSelfArgs(qkv=ptr(dq), ld_qkv=3 * H, s_qkv=float(s_qkv), bias=None, pad_mask=None, batch=B, seq=S, heads=heads,
+                          causal=1, amax_out=amax, out=ptr(out), ld_out=H, k_cache=ptr(kc), v_cache=ptr(vc), max_step=ms)
+    L.call("ls100_attn_self", ctx(), args)
+    sync_check()
+    _int8_close(out.cpu().numpy().reshape(B, S, H), ref, 5e-3)
+    k_ref = qkv_q[..., H:2 * H].reshape(B, S, heads, 64).transpose(0, 2, 1, 3)
+    v_ref = qkv_q[..., 2 * H:].reshape(B, S, heads, 64).transpose(0, 2, 1, 3)
+    assert np.array_equal(kc.cpu().numpy()[:, :, :S], k_ref) and np.array_equal(vc.cpu().numpy()[:, :, :S], v_ref)
+    assert (kc.cpu().numpy()[:, :, S:] == 77).all() and (vc.cpu().numpy()[:, :, S:] == 77).all()  # nothing past the prompt
+
+
 def test_attn_dec_int8_cache_with_beam_ancestry():
     """Five decode steps with a random beam reshuffle after each; the oracle permutes its
     cache physically, the kernel only follows the ancestry table."""
