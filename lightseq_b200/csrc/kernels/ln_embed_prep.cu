@@ -215,11 +215,11 @@ __global__ void __launch_bounds__(256) quantize_weight_kernel(const float* __res
 
 // ------------------------------------------------------------------ ViT patch embedding
 // CTA = 16 consecutive tokens (of the flattened [batch, 1 + patches] list) x 256 hidden channels; a thread owns one
-// channel and 16 float64 accumulators. The patch pixels are staged through shared memory 256 values at a time
-// (read back as broadcasts), the transposed weight is read coalesced, once per CTA.
+// channel and 16 float64 accumulators. The patch pixels are staged through shared memory 256 values at a time, already
+// converted to float64 (read back as broadcasts), the transposed weight is read coalesced, once per CTA.
 constexpr int PE_TOK = 16, PE_KC = 256;
 __global__ void __launch_bounds__(256) patch_embed_kernel(const ls100_patch_embed_args a) {
-  __shared__ float xs[PE_TOK][PE_KC];
+  __shared__ double xs[PE_TOK][PE_KC];  // converted once while staging: the inner loop is one broadcast load and one DFMA per token
   pdl_launch_dependents();
   pdl_wait();
   const int grid_w = a.image / a.patch, n_patch = grid_w * grid_w, seq = n_patch + 1;
@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(256) patch_embed_kernel(const ls100_patch_embe
           v = __ldg(a.pixels + (((long long)b * a.channels + c) * a.image + (pr * a.patch + r)) * a.image + pc * a.patch + q);
         }
       }
-      xs[p][kk] = v;
+      xs[p][kk] = (double)v;
     }
     __syncthreads();
     if (h < a.hidden) {
@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(256) patch_embed_kernel(const ls100_patch_embe
       for (int kk = 0; kk < kn; ++kk) {
         const double w = (double)__ldg(a.conv_wt + (long long)(k0 + kk) * a.hidden + h);
 #pragma unroll
-        for (int p = 0; p < PE_TOK; ++p) acc[p] = fma((double)xs[p][kk], w, acc[p]);
+        for (int p = 0; p < PE_TOK; ++p) acc[p] = fma(xs[p][kk], w, acc[p]);
       }
     }
   }
