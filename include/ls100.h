@@ -109,27 +109,6 @@ typedef struct {
 int ls100_gemm_i8(ls100_ctx* ctx, const ls100_gemm_i8_args* args, ls100_stream_t stream);
 
 
-/* ------------------------------------------------------- LayerNorm + quantise ---
- * y = LayerNorm(x) over the last dim (eps 1e-5, float64 statistics), optionally
- * written as fp32 and/or quantised to int8 with the consumer's input clip-max.
- * Replaces ker_norm_layer_resual_i8O (lightseq/inference/kernels/transformerKernels_int8.cc.cu:149-316);
- * restates the LayerNorm -> QuantLinear.input_quant edge of
- * lightseq/training/ops/pytorch/torch_transformer_layers.py:642-661.
- * hidden % 4 == 0, hidden <= 4096. */
-typedef struct {
-  const float* x;
-  int64_t ldx; /* elements */
-  const float* gamma;
-  const float* beta;
-  int32_t rows, hidden;
-  float amax;   /* clip-max of the int8 output (used when out_q != NULL) */
-  int8_t* out_q; /* optional [rows, hidden] */
-  int64_t ldq;
-  float* out_f; /* optional fp32 LayerNorm output */
-  int64_t ldf;
-} ls100_ln_quant_args;
-int ls100_ln_quant(ls100_ctx* ctx, const ls100_ln_quant_args* args, ls100_stream_t stream);
-
 /* ----------------------------------------------------------------- embedding ---
  * x[r, :] = sqrt_h * (table_q[id] * s_emb) + pos[p] * (id != pad_id), p = (#non-pad ids
  * up to and including this one) - 1 + pos_offset. Replaces launch_enc_emb_i8I /
@@ -154,6 +133,33 @@ typedef struct {
                         1: position = column index (+ *step_ptr), added to every token (BERT, GPT-2 learned tables) */
 } ls100_embed_args;
 int ls100_embed(ls100_ctx* ctx, const ls100_embed_args* args, ls100_stream_t stream);
+
+/* ------------------------------------------------------- LayerNorm + quantise ---
+ * y = LayerNorm(x) over the last dim (eps 1e-5, float64 statistics), optionally
+ * written as fp32 and/or quantised to int8 with the consumer's input clip-max.
+ * Replaces ker_norm_layer_resual_i8O (lightseq/inference/kernels/transformerKernels_int8.cc.cu:149-316);
+ * restates the LayerNorm -> QuantLinear.input_quant edge of
+ * lightseq/training/ops/pytorch/torch_transformer_layers.py:642-661.
+ * hidden % 4 == 0, hidden <= 4096. */
+typedef struct {
+  const float* x;
+  int64_t ldx; /* elements */
+  const float* gamma;
+  const float* beta;
+  int32_t rows, hidden;
+  float amax;   /* clip-max of the int8 output (used when out_q != NULL) */
+  int8_t* out_q; /* optional [rows, hidden] */
+  int64_t ldq;
+  float* out_f; /* optional fp32 LayerNorm output */
+  int64_t ldf;
+  /* optional (emb.table_q != NULL): the rows are not read from x but looked up, the decode-step form of
+   * ls100_embed (emb.seq == 1, emb.step_ptr != NULL, emb.batch == rows, emb.hidden == hidden); emb.out receives
+   * the looked-up rows (the residual stream) as ls100_embed would write them. One launch instead of two at the
+   * head of every decode step; rows <= 2048. */
+  ls100_embed_args emb;
+} ls100_ln_quant_args;
+int ls100_ln_quant(ls100_ctx* ctx, const ls100_ln_quant_args* args, ls100_stream_t stream);
+
 
 /* ---------------------------------------------------------- ViT patch embedding ---
  * out[b, 0, :]     = cls + pos[0]

@@ -58,17 +58,18 @@ class GemmI8Args(C.Structure):
 
 
 
-class LnQuantArgs(C.Structure):
-    _fields_ = [("x", C.c_void_p), ("ldx", C.c_int64), ("gamma", C.c_void_p), ("beta", C.c_void_p),
-                ("rows", C.c_int32), ("hidden", C.c_int32), ("amax", C.c_float),
-                ("out_q", C.c_void_p), ("ldq", C.c_int64), ("out_f", C.c_void_p), ("ldf", C.c_int64)]
-
-
 class EmbedArgs(C.Structure):
     _fields_ = [("ids", C.c_void_p), ("ld_ids", C.c_int64), ("batch", C.c_int32), ("seq", C.c_int32),
                 ("hidden", C.c_int32), ("step_ptr", C.c_void_p), ("table_q", C.c_void_p), ("s_emb", C.c_float),
                 ("sqrt_h", C.c_float), ("pos", C.c_void_p), ("n_pos", C.c_int32), ("pad_id", C.c_int32),
                 ("vocab", C.c_int32), ("out", C.c_void_p), ("pad_mask", C.c_void_p), ("pos_mode", C.c_int32)]
+
+
+class LnQuantArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("ldx", C.c_int64), ("gamma", C.c_void_p), ("beta", C.c_void_p),
+                ("rows", C.c_int32), ("hidden", C.c_int32), ("amax", C.c_float),
+                ("out_q", C.c_void_p), ("ldq", C.c_int64), ("out_f", C.c_void_p), ("ldf", C.c_int64),
+                ("emb", EmbedArgs)]  # optional: rows looked up instead of read (decode-step form)
 
 
 class PatchEmbedArgs(C.Structure):

@@ -154,6 +154,8 @@ class QuantTransformerEncoderLayer : public Layer {
 // cache and fp32 cross-attention keys/values computed once per request).
 class QuantTransformerDecoderLayer : public Layer {
  public:
+  // the decode-step embedding lookup to run inside this layer's first LayerNorm launch (first layer of a stack only)
+  void set_embed_source(const ls100_embed_args* e) { embed_src_ = e; }
   QuantTransformerDecoderLayer(ContextPtr ctx, const WeightsFile& wf, const std::string& prefix, int layer_id,
                                int max_batch_tokens, int max_seq_len, int hidden, int heads, int ffn, bool is_pre_ln,
                                const std::string& activation_fn, int max_batch_size, int beam_size, int max_step)
@@ -247,7 +249,7 @@ class QuantTransformerDecoderLayer : public Layer {
   }
   void forward() override {
     const int rows = batch_ * beam_;
-    ln_quant(rows, ln1_, qkv_.amax_in);
+    ln_quant(rows, ln1_, qkv_.amax_in, embed_src_);
     // qkv = attention_quant(fq_out(acc) + bias): int8 with the KV-cache clip-max
     gemm(b_->a_q, qkv_, rows, LS100_OUT_REQ_S8, b_->qkv_q, Act::None, nullptr, s_kv_);
     {
@@ -300,7 +302,7 @@ class QuantTransformerDecoderLayer : public Layer {
   }
 
  private:
-  void ln_quant(int rows, const LayerNormParams& ln, float amax) {
+  void ln_quant(int rows, const LayerNormParams& ln, float amax, const ls100_embed_args* lookup = nullptr) {
     ls100_ln_quant_args a;
     memset(&a, 0, sizeof(a));
     a.x = b_->x->value<float>();
@@ -312,6 +314,7 @@ class QuantTransformerDecoderLayer : public Layer {
     a.amax = amax;
     a.out_q = b_->a_q->value<int8_t>();
     a.ldq = hidden_;
+    if (lookup) a.emb = *lookup;  // the rows come from the embedding lookup of this decode step, in the same launch
     LS_RC(ls100_ln_quant(ctx_->kernels(), &a, ctx_->get_stream()));
   }
   void gemm(Variable* in, const QLinearParams& p, int rows, int out_kind, Variable* out, Act act, Variable* resid,
@@ -334,6 +337,7 @@ class QuantTransformerDecoderLayer : public Layer {
   Variable* pad_mask_ = nullptr;
   const int32_t* anc_ = nullptr;
   const int32_t* step_ptr_ = nullptr;
+  const ls100_embed_args* embed_src_ = nullptr;
   int batch_ = 0, beam_ = 0, src_len_ = 0;
 };
 
@@ -344,6 +348,8 @@ class QuantTransformerDecoderLayer : public Layer {
 // QuantGptEncoder::self_attention / self_attention_with_cache (lightseq/inference/model/quant_gpt_encoder.cc.cu:485-658).
 class QuantGptLayer : public Layer {
  public:
+  // the decode-step embedding lookup to run inside this layer's first LayerNorm launch (first layer of a stack only)
+  void set_embed_source(const ls100_embed_args* e) { embed_src_ = e; }
   QuantGptLayer(ContextPtr ctx, const WeightsFile& wf, const std::string& prefix, int layer_id, int max_batch_tokens,
                 int max_seq_len, int hidden, int heads, int ffn, int max_batch_size)
       : Layer(prefix, ctx), hidden_(hidden), heads_(heads), ffn_(ffn), max_tokens_(max_batch_tokens),
@@ -376,7 +382,7 @@ class QuantGptLayer : public Layer {
   }
   void forward() override {
     const int rows = prompt_ > 0 ? batch_ * prompt_ : batch_;
-    ln_quant(rows, ln1_, qkv_.amax_in);
+    ln_quant(rows, ln1_, qkv_.amax_in, embed_src_);
     gemm(b_->a_q, qkv_, rows, LS100_OUT_REQ_S8, b_->qkv_q, Act::None, nullptr, s_kv_);
     if (prompt_ > 0) {
       ls100_attn_self_args a;
@@ -419,7 +425,7 @@ class QuantGptLayer : public Layer {
   }
 
  private:
-  void ln_quant(int rows, const LayerNormParams& ln, float amax) {
+  void ln_quant(int rows, const LayerNormParams& ln, float amax, const ls100_embed_args* lookup = nullptr) {
     ls100_ln_quant_args a;
     memset(&a, 0, sizeof(a));
     a.x = b_->x->value<float>();
@@ -431,6 +437,7 @@ class QuantGptLayer : public Layer {
     a.amax = amax;
     a.out_q = b_->a_q->value<int8_t>();
     a.ldq = hidden_;
+    if (lookup) a.emb = *lookup;  // the rows come from the embedding lookup of this decode step, in the same launch
     LS_RC(ls100_ln_quant(ctx_->kernels(), &a, ctx_->get_stream()));
   }
   void gemm(Variable* in, const QLinearParams& p, int rows, int out_kind, Variable* out, Act act, Variable* resid, float s_req) {
@@ -446,6 +453,7 @@ class QuantGptLayer : public Layer {
   int8_t *k_cache_ = nullptr, *v_cache_ = nullptr;
   StackBuffers* b_ = nullptr;
   const int32_t* step_ptr_ = nullptr;
+  const ls100_embed_args* embed_src_ = nullptr;
   int batch_ = 0, prompt_ = 0;
 };
 

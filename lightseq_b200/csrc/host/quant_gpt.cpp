@@ -5,6 +5,7 @@
 // reference copies the whole cache every token, gptKernels_int8.cc.cu:658-812); sampling needs no host sync.
 #include <algorithm>
 #include <map>
+#include <cstdlib>
 #include <memory>
 
 #include "engine_model.h"
@@ -233,9 +234,13 @@ class QuantGpt : public EngineModel {
  private:
   static constexpr int kRing = 4;
   static constexpr int kPplRows = 4096;
+  ls100_embed_args embed_args_;  // outlives embed(): the first layer reads it during its forward()
 
+  // decode && fuse: the lookup is handed to the first layer, which runs it inside its first LayerNorm launch
   void embed(int B, int P, bool decode) {
-    ls100_embed_args e;
+    static const bool separate_embed = getenv("LS100_NO_EMBED_FUSE") != nullptr;
+    const bool fused = decode && !separate_embed && B <= 2048 && !layers_.empty();
+    ls100_embed_args& e = embed_args_;
     memset(&e, 0, sizeof(e));
     e.ids = decode ? seq_ : d_ids_;
     e.ld_ids = decode ? max_step_ : P;
@@ -252,7 +257,8 @@ class QuantGpt : public EngineModel {
     e.vocab = V_;
     e.out = buf_.x->value<float>();
     e.pos_mode = 1;
-    LS_RC(ls100_embed(ctx_->kernels(), &e, ctx_->get_stream()));
+    if (!layers_.empty()) layers_[0]->set_embed_source(fused ? &e : nullptr);
+    if (!fused) LS_RC(ls100_embed(ctx_->kernels(), &e, ctx_->get_stream()));
   }
   // final LayerNorm of the newest position of every row -> int8 -> logits -> sample
   void head(int B, int row_stride, int row_offset) {

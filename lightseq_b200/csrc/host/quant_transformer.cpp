@@ -13,6 +13,7 @@
 #include <stdlib.h>
 
 #include <map>
+#include <cstdlib>
 #include <memory>
 
 #include "engine_model.h"
@@ -304,12 +305,17 @@ class QuantTransformer : public EngineModel {
     e.pad_id = pad_id_;
     e.vocab = V_;
     e.out = dec_.x->value<float>();
-    LS_RC(ls100_embed(k, &e, st));
+    // the lookup runs inside the first layer's LayerNorm launch (one kernel less per step) unless switched off
+    static const bool separate_embed = getenv("LS100_NO_EMBED_FUSE") != nullptr;
+    const bool fused = !separate_embed && rows <= 2048 && !dec_layers_.empty();
+    if (!fused) LS_RC(ls100_embed(k, &e, st));
+    if (!dec_layers_.empty()) dec_layers_[0]->set_embed_source(fused ? &e : nullptr);
     for (auto& l : dec_layers_) {
       (*l)(&dec_, pad_mask_, anc_, step_ptr_);
       l->before_forward(B, beam_, S);
       l->forward();
     }
+    if (!dec_layers_.empty()) dec_layers_[0]->set_embed_source(nullptr);  // `e` goes out of scope with this call
     ls100_ln_quant_args a;
     memset(&a, 0, sizeof(a));
     a.x = dec_.x->value<float>();

@@ -93,15 +93,44 @@ __global__ void __launch_bounds__(LN_ROW_THREADS) ln_quant_row_kernel(const ls10
     }
   }
   pdl_wait();
-  const float* xr = a.x + (long long)row * a.ldx;
   float4 v[NV];
   double s = 0.0;
+  if (a.emb.table_q != nullptr) {
+    // decode-step embedding in place of the load (the arithmetic of embed_kernel's step form); the looked-up row is
+    // also written out: it is the residual stream of the layer stack
+    const ls100_embed_args& e = a.emb;
+    const int step = *e.step_ptr;
+    int id = e.ids[(long long)row * e.ld_ids + step];
+    int pos = (e.pos_mode == 1 || id != e.pad_id) ? step : 0;
+    const bool is_pad = (id == e.pad_id);
+    if (id < 0 || id >= e.vocab) id = (e.pad_id >= 0 && e.pad_id < e.vocab) ? e.pad_id : 0;
+    if (pos >= e.n_pos) pos = e.n_pos - 1;
+    const int8_t* er = e.table_q + (long long)id * a.hidden;
+    const float* pr = e.pos + (long long)pos * a.hidden;
+    const float m = (is_pad && e.pos_mode == 0) ? 0.f : 1.f;
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int c = (i * LN_ROW_THREADS + t) * 4;
-    if (c < a.hidden) {
-      v[i] = *reinterpret_cast<const float4*>(xr + c);
-      s += ((double)v[i].x + (double)v[i].y) + ((double)v[i].z + (double)v[i].w);
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * LN_ROW_THREADS + t) * 4;
+      if (c < a.hidden) {
+        const char4 q = *reinterpret_cast<const char4*>(er + c);
+        const float4 p = *reinterpret_cast<const float4*>(pr + c);
+        v[i].x = __fadd_rn(__fmul_rn(e.sqrt_h, __fmul_rn((float)q.x, e.s_emb)), __fmul_rn(p.x, m));
+        v[i].y = __fadd_rn(__fmul_rn(e.sqrt_h, __fmul_rn((float)q.y, e.s_emb)), __fmul_rn(p.y, m));
+        v[i].z = __fadd_rn(__fmul_rn(e.sqrt_h, __fmul_rn((float)q.z, e.s_emb)), __fmul_rn(p.z, m));
+        v[i].w = __fadd_rn(__fmul_rn(e.sqrt_h, __fmul_rn((float)q.w, e.s_emb)), __fmul_rn(p.w, m));
+        *reinterpret_cast<float4*>(e.out + (long long)row * a.hidden + c) = v[i];
+        s += ((double)v[i].x + (double)v[i].y) + ((double)v[i].z + (double)v[i].w);
+      }
+    }
+  } else {
+    const float* xr = a.x + (long long)row * a.ldx;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * LN_ROW_THREADS + t) * 4;
+      if (c < a.hidden) {
+        v[i] = *reinterpret_cast<const float4*>(xr + c);
+        s += ((double)v[i].x + (double)v[i].y) + ((double)v[i].z + (double)v[i].w);
+      }
     }
   }
   s = warp_sum_d(s);
@@ -273,11 +302,20 @@ __global__ void __launch_bounds__(256) patch_embed_kernel(const ls100_patch_embe
 using namespace ls100;
 
 extern "C" int ls100_ln_quant(ls100_ctx* ctx, const ls100_ln_quant_args* a, ls100_stream_t stream_) {
-  if (!ctx || !a || !a->x || !a->gamma || !a->beta || (!a->out_q && !a->out_f)) return LS100_ERR_BAD_ARG;
+  const bool lookup = a && a->emb.table_q != nullptr;
+  if (!ctx || !a || (!a->x && !lookup) || !a->gamma || !a->beta || (!a->out_q && !a->out_f)) return LS100_ERR_BAD_ARG;
+  if (lookup) {  // the decode-step form of ls100_embed feeding the LayerNorm directly
+    const ls100_embed_args& e = a->emb;
+    if (!e.ids || !e.pos || !e.out || !e.step_ptr || e.seq != 1 || e.batch != a->rows || e.hidden != a->hidden || e.n_pos <= 0 ||
+        e.vocab <= 0 || e.pad_mask != nullptr)
+      return LS100_ERR_BAD_ARG;
+    if (a->rows > 2048) return LS100_ERR_UNSUPPORTED;
+    if ((((uintptr_t)e.table_q) & 3) || (((uintptr_t)e.pos) & 15) || (((uintptr_t)e.out) & 15)) return LS100_ERR_ALIGN;
+  }
   if (a->rows <= 0 || a->hidden <= 0) return LS100_ERR_BAD_ARG;
   if ((a->hidden & 3) || a->hidden > LN_MAXV * 128) return LS100_ERR_UNSUPPORTED;
   if (a->out_q && !(a->amax > 0.f)) return LS100_ERR_BAD_ARG;
-  if ((((uintptr_t)a->x) & 15) || (a->ldx & 3) || (((uintptr_t)a->gamma) & 15) || (((uintptr_t)a->beta) & 15))
+  if ((!lookup && ((((uintptr_t)a->x) & 15) || (a->ldx & 3))) || (((uintptr_t)a->gamma) & 15) || (((uintptr_t)a->beta) & 15))
     return LS100_ERR_ALIGN;
   if (a->out_q && ((((uintptr_t)a->out_q) & 3) || (a->ldq & 3))) return LS100_ERR_ALIGN;
   if (a->out_f && ((((uintptr_t)a->out_f) & 15) || (a->ldf & 3))) return LS100_ERR_ALIGN;

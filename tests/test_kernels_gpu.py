@@ -277,6 +277,27 @@ def test_embed_encoder_and_decoder_forms_bit_exact():
     sync_check()
     ref = om.embed(st, hist[:, step:step + 1], step, cfg, pos)[:, 0]
     assert np.array_equal(out.cpu().numpy(), ref)
+    # the same lookup inside the LayerNorm launch (head of a decode step): residual stream, fp32 and int8 LN outputs
+    hist[2, step] = pad  # a finished row: no position added
+    dh = dev(hist)
+    ref = om.embed(st, hist[:, step:step + 1], step, cfg, pos)[:, 0]
+    g = (1 + 0.1 * r.standard_normal(H)).astype(F32)
+    b = (0.1 * r.standard_normal(H)).astype(F32)
+    y = om.layer_norm(ref, g, b)
+    amax_y = float(F32(4 * y.std()))
+    x_out, of_t, oq_t = empty((6, H), torch.float32), empty((6, H), torch.float32), empty((6, H), torch.int8)
+    dg, db = dev(g), dev(b)
+    args.ids, args.out = ptr(dh), ptr(x_out)
+    ln = L.LnQuantArgs(x=None, ldx=H, gamma=ptr(dg), beta=ptr(db), rows=6, hidden=H, amax=amax_y, out_q=ptr(oq_t), ldq=H,
+                       out_f=ptr(of_t), ldf=H, emb=args)
+    L.call("ls100_ln_quant", ctx(), ln)
+    sync_check()
+    assert np.array_equal(x_out.cpu().numpy(), ref)
+    assert np.array_equal(of_t.cpu().numpy(), y)
+    assert np.array_equal(oq_t.cpu().numpy(), oq.quantize(y, amax_y)[0])
+    ln.rows = 5  # rows must equal the lookup's batch
+    with pytest.raises(RuntimeError):
+        L.call("ls100_ln_quant", ctx(), ln)
 
 
 # ----------------------------------------------------------------------------- attention
