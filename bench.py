@@ -570,7 +570,12 @@ def run_ours(args):
                "sample": f"first {n_sent} of {B} sentences, full beam-4 generation with the numpy oracle ({dt:.1f} s)"}
     # kernels of this library launched in the timed region (per generation: encoder + cross-KV + decode steps)
     n_enc, n_dec = int(conf["n_enc"]), int(conf["n_dec"])
-    per_infer = (1 + 7 * n_enc + 1) + 2 * n_dec + steps_per_infer * (1 + 11 * n_dec + 2 + 2)
+    # encoder: embedding + 7 per layer + final LayerNorm; cross K/V: bf16 split (tensor-core projection) + 2 GEMMs per
+    # layer; a decode step: 11 per layer + final LayerNorm + logits GEMM + top-k + beam update, and the embedding lookup
+    # as a launch of its own only when it is not run inside the first LayerNorm
+    sep_embed = 1 if os.environ.get("LS100_NO_EMBED_FUSE") is not None else 0
+    split = 0 if os.environ.get("LS100_PROJ_SIMT") is not None else 1
+    per_infer = (1 + 7 * n_enc + 1) + split + 2 * n_dec + steps_per_infer * (sep_embed + 11 * n_dec + 2 + 2)
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": n_warm,
         "ms_per_step": max_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
