@@ -5,7 +5,9 @@
  * `_host`), plain sizes and fp32 scales by value, launches on the given stream
  * and returns 0 or a negative LS100_ERR_* code without launching. Nothing here
  * synchronises or allocates unless its comment says so. `stream` is a
- * cudaStream_t passed as void*.
+ * cudaStream_t passed as void*. Zero-initialise every `*_args` struct before
+ * filling it in: optional members (and members added in later versions) are
+ * off when zero.
  *
  * Each declaration cites the reference interface it replaces (paths are
  * relative to the bytedance/lightseq source tree).
