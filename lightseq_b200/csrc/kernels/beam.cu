@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
   int n_buf = 0;   // entries in buf (the first ones are the current best list)
   int thr = -128;  // bytes strictly above thr are candidates
   unsigned add7 = 0x01010101u * 127u;
-  float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
+  float2 ps01 = make_float2(0.f, 0.f), ps23 = make_float2(0.f, 0.f);  // four running sums, added as two packed pairs
   const int n_chunks = (a.vocab + 511) / 512;
   const int4 none = make_int4((int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080);
   // this warp's chunks: warp, warp + 8, ...; the next two are always in flight
@@ -153,10 +153,8 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
     unsigned hit = 0;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      ps0 += s_lut[w4[w] & 0xff];
-      ps1 += s_lut[(w4[w] >> 8) & 0xff];
-      ps2 += s_lut[(w4[w] >> 16) & 0xff];
-      ps3 += s_lut[w4[w] >> 24];
+      ps01 = f2_add(ps01, make_float2(s_lut[w4[w] & 0xff], s_lut[(w4[w] >> 8) & 0xff]));
+      ps23 = f2_add(ps23, make_float2(s_lut[(w4[w] >> 16) & 0xff], s_lut[w4[w] >> 24]));
       gt[w] = ((w4[w] & 0x7f7f7f7fu) + add7) & ~w4[w] & 0x80808080u;
       hit |= gt[w];
     }
@@ -199,7 +197,7 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
   }
   __syncwarp();
   topk_flush(buf, n_buf, K, lane, &n_buf);
-  double sum = ((double)ps0 + (double)ps1) + ((double)ps2 + (double)ps3);
+  double sum = ((double)ps01.x + (double)ps01.y) + ((double)ps23.x + (double)ps23.y);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   if (lane == 0) {
