@@ -123,12 +123,6 @@ __device__ __forceinline__ void at_unpack16_f16(const int4 v, uint32_t (&h)[8]) 
   }
 }
 
-__device__ __forceinline__ float at_ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                      const __grid_constant__ CUtensorMap tm_kv,
                                                                      const AttnTcParams p) {
@@ -374,7 +368,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_self_tc_kernel(const __gri
               uint32_t hi[4], lo[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const float2 pp = make_float2(at_ex2(sv[gq * 4 + e].x), at_ex2(sv[gq * 4 + e].y));  // 2^-inf = 0
+                const float2 pp = make_float2(ex2_approx(sv[gq * 4 + e].x), ex2_approx(sv[gq * 4 + e].y));  // 2^-inf = 0
                 l2 = f2_add(l2, pp);
                 // hi = fp16(p), lo = fp16(p - hi): |p - hi - lo| < 2^-23 p + 2^-25 (p <= 1, so lo may be subnormal)
                 const __half2 h2 = __floats2half2_rn(pp.x, pp.y);
