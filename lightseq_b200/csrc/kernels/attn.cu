@@ -485,12 +485,14 @@ __global__ void __launch_bounds__(32 * XWARPS) attn_cross_kernel(const __grid_co
         for (int c = 0; c < 8; ++c) {
           const float4 k4 = *reinterpret_cast<const float4*>(kr + ((c ^ (j & 7)) << 4));
 #pragma unroll
-          for (int bm = 0; bm < NB; ++bm) {
+          for (int bm = 0; bm < NB; ++bm) {  // four running sums per beam, two packed pairs
             const float4 q4 = *reinterpret_cast<const float4*>(qr + bm * XQ + c * 4);
-            s[bm][0] = fmaf(q4.x, k4.x, s[bm][0]);
-            s[bm][1] = fmaf(q4.y, k4.y, s[bm][1]);
-            s[bm][2] = fmaf(q4.z, k4.z, s[bm][2]);
-            s[bm][3] = fmaf(q4.w, k4.w, s[bm][3]);
+            const float2 s01 = f2_fma(make_float2(q4.x, q4.y), make_float2(k4.x, k4.y), make_float2(s[bm][0], s[bm][1]));
+            const float2 s23 = f2_fma(make_float2(q4.z, q4.w), make_float2(k4.z, k4.w), make_float2(s[bm][2], s[bm][3]));
+            s[bm][0] = s01.x;
+            s[bm][1] = s01.y;
+            s[bm][2] = s23.x;
+            s[bm][3] = s23.y;
           }
         }
       }
@@ -543,14 +545,13 @@ __global__ void __launch_bounds__(32 * XWARPS) attn_cross_kernel(const __grid_co
 #pragma unroll
           for (int bm = 0; bm < NB; ++bm) {
             const float4 w4 = *reinterpret_cast<const float4*>(pr + bm * 16 + jj);
-            acc[bm][0] = fmaf(w4.x, v[0].x, acc[bm][0]);
-            acc[bm][1] = fmaf(w4.x, v[0].y, acc[bm][1]);
-            acc[bm][0] = fmaf(w4.y, v[1].x, acc[bm][0]);
-            acc[bm][1] = fmaf(w4.y, v[1].y, acc[bm][1]);
-            acc[bm][0] = fmaf(w4.z, v[2].x, acc[bm][0]);
-            acc[bm][1] = fmaf(w4.z, v[2].y, acc[bm][1]);
-            acc[bm][0] = fmaf(w4.w, v[3].x, acc[bm][0]);
-            acc[bm][1] = fmaf(w4.w, v[3].y, acc[bm][1]);
+            float2 t = make_float2(acc[bm][0], acc[bm][1]);  // the two head dims of this lane as one packed pair
+            t = f2_fma(f2_set(w4.x), v[0], t);
+            t = f2_fma(f2_set(w4.y), v[1], t);
+            t = f2_fma(f2_set(w4.z), v[2], t);
+            t = f2_fma(f2_set(w4.w), v[3], t);
+            acc[bm][0] = t.x;
+            acc[bm][1] = t.y;
           }
         }
       }
