@@ -7,6 +7,7 @@
 
 #include "../../../include/ls100.h"
 #include "lsflow.h"
+#include "engine_model.h"
 #include "model_base.h"
 
 namespace ls100 {
@@ -225,6 +226,15 @@ extern "C" const float* ls100_debug_encoder_output(ls100_model* m) {
 }
 extern "C" const int8_t* ls100_debug_last_logits(ls100_model* m, int* ld) {
   return m ? ls100::quant_transformer_last_logits(m->model.get(), ld) : nullptr;
+}
+// every later Infer() copies the residual stream after the embedding and after each encoder layer into `device_buf`
+// (NULL switches the tap off); returns the number of floats the last Infer() wrote
+extern "C" long long ls100_debug_set_layer_tap(ls100_model* m, float* device_buf, long long capacity_floats) {
+  auto* e = m ? dynamic_cast<ls100::EngineModel*>(m->model.get()) : nullptr;
+  if (!e || capacity_floats < 0) return -1;
+  const long long used = (long long)e->layer_tap_floats();
+  e->set_layer_tap(device_buf, (size_t)capacity_floats);
+  return used;
 }
 extern "C" int ls100_debug_steps_run(ls100_model* m) {
   return m ? ls100::quant_transformer_steps_run(m->model.get()) : -1;

@@ -106,10 +106,13 @@ class QuantBert : public EngineModel {
     a.out_f = buf_.x->value<float>();
     a.ldf = H_;
     LS_RC(ls100_ln_quant(ctx_->kernels(), &a, st));
+    tap_reset();
+    tap(buf_.x->value<float>(), (size_t)B * S * H_, st);
     for (auto& l : layers_) {
       (*l)(&buf_, pad_mask_);
       l->before_forward(B, S);
       l->forward();
+      tap(buf_.x->value<float>(), (size_t)B * S * H_, st);
     }
     LS_CUDA(cudaMemcpyAsync(d_out_, buf_.x->value<float>(), (size_t)B * S * H_ * 4, cudaMemcpyDeviceToDevice, st));
     LS_CUDA(cudaStreamSynchronize(st));

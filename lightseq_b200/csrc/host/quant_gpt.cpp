@@ -324,10 +324,13 @@ class QuantGpt : public EngineModel {
   }
   void prefill(int B, int P) {
     embed(B, P, false);
+    tap_reset();
+    tap(buf_.x->value<float>(), (size_t)B * P * H_, ctx_->get_stream());
     for (auto& l : layers_) {
       (*l)(&buf_, counters_);
       l->before_forward(B, P);
       l->forward();
+      tap(buf_.x->value<float>(), (size_t)B * P * H_, ctx_->get_stream());
     }
     head(B, P, P - 1);
   }

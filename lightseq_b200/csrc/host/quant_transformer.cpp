@@ -267,10 +267,13 @@ class QuantTransformer : public EngineModel {
     e.out = enc_.x->value<float>();
     e.pad_mask = pad_mask_->value<uint8_t>();
     LS_RC(ls100_embed(ctx_->kernels(), &e, ctx_->get_stream()));
+    tap_reset();
+    tap(enc_.x->value<float>(), (size_t)B * S * H_, ctx_->get_stream());
     for (auto& l : enc_layers_) {
       (*l)(&enc_, pad_mask_);
       l->before_forward(B, S);
       l->forward();
+      tap(enc_.x->value<float>(), (size_t)B * S * H_, ctx_->get_stream());
     }
     ls100_ln_quant_args a;
     memset(&a, 0, sizeof(a));

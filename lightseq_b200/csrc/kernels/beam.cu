@@ -345,14 +345,23 @@ extern "C" int ls100_beam_topk(ls100_ctx* ctx, const ls100_beam_topk_args* a, ls
              : LS100_ERR_CUDA;
 }
 
-extern "C" int ls100_beam_update(ls100_ctx* ctx, const ls100_beam_update_args* a, ls100_stream_t stream_) {
+// Argument checks of the beam update; `need_scratch` is false when the caller's fin_count / ticket pointers are
+// going to be replaced by the library's own scratch. Nothing is enqueued before these pass.
+static int beam_update_check(const ls100_ctx* ctx, const ls100_beam_update_args* a, bool need_scratch) {
   if (!ctx || !a || !a->cand_score || !a->cand_token || !a->step_ptr || !a->length_norm || !a->alive || !a->seq_probs ||
-      !a->seq_score || !a->fin_count || !a->ticket || !a->stop_step)
+      !a->seq_score || !a->stop_step)
     return LS100_ERR_BAD_ARG;
+  if (need_scratch && (!a->fin_count || !a->ticket)) return LS100_ERR_BAD_ARG;
   if (a->batch <= 0 || a->beam <= 0 || a->max_step <= 0) return LS100_ERR_BAD_ARG;
   if (a->beam > MAX_BEAM) return LS100_ERR_UNSUPPORTED;
+  if ((size_t)2 * a->beam * a->max_step * sizeof(int) > 48 * 1024) return LS100_ERR_UNSUPPORTED;
+  return LS100_OK;
+}
+
+extern "C" int ls100_beam_update(ls100_ctx* ctx, const ls100_beam_update_args* a, ls100_stream_t stream_) {
+  const int rc = beam_update_check(ctx, a, true);
+  if (rc != LS100_OK) return rc;
   const size_t smem = (size_t)2 * a->beam * a->max_step * sizeof(int);
-  if (smem > 48 * 1024) return LS100_ERR_UNSUPPORTED;
   return ls100_launch(beam_update_kernel, dim3(a->batch), dim3(128), smem, (cudaStream_t)stream_, *a) == cudaSuccess
              ? LS100_OK
              : LS100_ERR_CUDA;
@@ -375,6 +384,10 @@ extern "C" int ls100_beam_update_noalloc(ls100_ctx* ctx, const ls100_beam_update
     fprintf(stderr, "ls100_beam_update_noalloc: max_step %d exceeds the built-in scratch (limit %d); use ls100_beam_update "
                     "with caller-provided fin_count/ticket arrays\n", a->max_step, LS100_BEAM_UPDATE_NOALLOC_MAX_STEP);
     return LS100_ERR_UNSUPPORTED;
+  }
+  {  // every other argument is checked before anything is enqueued: a rejected call leaves the stream and the scratch alone
+    const int rc = beam_update_check(ctx, a, false);
+    if (rc != LS100_OK) return rc;
   }
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess) return LS100_ERR_CUDA;

@@ -63,6 +63,13 @@ def _ln(x, g, b):
     return ((x - m) / np.sqrt(v + 1e-5) * g + b).astype(F32)
 
 
+def _ln_offset(x, valid):
+    """Mean over the valid tokens of mean(x) / std(x): what LayerNorm subtracts from every element, in output units."""
+    m = x.mean(-1)
+    sd = np.sqrt(((x - m[..., None]) ** 2).mean(-1) + 1e-5)
+    return float((m / sd)[valid].mean())
+
+
 def _softmax(s):
     s = s - s.max(-1, keepdims=True)
     e = np.exp(s)
@@ -149,9 +156,11 @@ def transformer_inputs(batch=128, min_len=20, max_len=60, vocab=32000, pad_id=1,
 
 
 def calibrate_transformer(w: Dict[str, np.ndarray], src: np.ndarray, *, heads: int, n_enc: int, n_dec: int,
-                          act: str = "relu", pad_id: int = 1, seed: int = 99, k: float = 4.0) -> Dict[str, float]:
+                          act: str = "relu", pad_id: int = 1, seed: int = 99, k: float = 4.0,
+                          ln_offsets: Optional[Dict[str, float]] = None) -> Dict[str, float]:
     """Clip-max table = k x std, from one fp32 pass: encoder on ``src``; decoder teacher-forced
-    on random target ids of the source lengths (causal self-attention)."""
+    on random target ids of the source lengths (causal self-attention). ``ln_offsets``, when given, receives the
+    average mean/std ratio of the inputs of the encoder's final LayerNorm and of every decoder ``ln2``."""
     st = _Stats()
     H = w["emb"].shape[1]
     V = w["emb"].shape[0]
@@ -181,6 +190,8 @@ def calibrate_transformer(w: Dict[str, np.ndarray], src: np.ndarray, *, heads: i
         x = x + lin(p + ".out", a)
         h = _act(lin(p + ".fc1", _ln(x, w[p + ".ln2.g"], w[p + ".ln2.b"])), act)
         x = x + lin(p + ".fc2", h)
+    if ln_offsets is not None:
+        ln_offsets["enc.ln"] = _ln_offset(x, ~pad)
     enc = _ln(x, w["enc.ln.g"], w["enc.ln.b"])
 
     lens = (~pad).sum(1)
@@ -197,6 +208,8 @@ def calibrate_transformer(w: Dict[str, np.ndarray], src: np.ndarray, *, heads: i
         a = _attn(qkv[..., :H], qkv[..., H:2 * H], qkv[..., 2 * H:], heads,
                   causal[None, None] | tpad[:, None, None, :])
         x = x + lin(p + ".out", a)
+        if ln_offsets is not None:
+            ln_offsets[p + ".ln2"] = _ln_offset(x, ~tpad)
         q = lin(p + ".xq", _ln(x, w[p + ".ln2.g"], w[p + ".ln2.b"]))
         kx = lin(p + ".xk", enc, False, False)
         vx = lin(p + ".xv", enc, False, False)
@@ -228,6 +241,80 @@ def make_transformer(path: Optional[str] = None, *, hidden=512, heads=8, ffn=204
                 act_gelu=float(act == "gelu"), pre_ln=1.0, beam=beam, length_penalty=length_penalty,
                 extra_decode_length=extra_decode_length, max_step=max_step, pad_id=pad_id, start_id=start_id,
                 end_id=end_id)
+    w["pos"] = sinusoid_table(max_step, hidden)
+    if path is not None:
+        from . import weights
+
+        weights.save(path, "QuantTransformer", conf, amax, w)
+    return conf, amax, w
+
+
+def copy_task_inputs(batch=32, min_len=20, max_len=60, vocab=32000, pad_id=1, end_id=2, seed=4321) -> np.ndarray:
+    """Source ids as ``transformer_inputs`` (lengths U{min_len..max_len}, ids U[4, vocab)) whose last token is EOS,
+    the way translation sources end: the copy-task model then ends its output where the source ends."""
+    src = transformer_inputs(batch, min_len, max_len, vocab, pad_id, seed)
+    lens = (src != pad_id).sum(1)
+    src[np.arange(batch), lens - 1] = end_id
+    return src
+
+
+def make_copy_transformer(path: Optional[str] = None, *, hidden=512, heads=8, ffn=2048, n_enc=6, n_dec=6, vocab=32000,
+                          beam=4, length_penalty=0.6, extra_decode_length=50, max_step=256, pad_id=1, start_id=3,
+                          end_id=2, seed=1234, calib_src: Optional[np.ndarray] = None, sharp=5.0, gain=4.0,
+                          logits_amax_sigmas=14.0):
+    """A seeded Transformer with a PEAKED output distribution, for free-running parity tests.
+
+    A randomly initialised model has an almost flat output distribution: beam search on it is chaotic, and one
+    int8 rounding flip anywhere reorders near-tied candidates. Trained translation models are peaked. This builder
+    keeps every weight of ``make_transformer`` (N(0, 0.02^2), same seed) except the cross-attention of the LAST
+    decoder layer, which is set so that the model copies its source: query and key projections select the sine/cosine
+    pairs of the 16 fastest positional frequencies for every head (q.k ~ ``sharp``^2/8 * 2 sum_i cos(w_i (t - s)), peaked at
+    source position s = decode position t; the embedding table is zero in those 32 dims), the value projection is the identity and the output
+    projection ``gain`` times the identity, so the residual stream going into the output projection is dominated by
+    the encoder state of source token t, whose own embedding row then wins the logits by tens of int8 steps.
+    Everything still runs through the int8 path (all other layers add their pseudo-random contributions, every
+    quantiser is live); the logits clip-max is widened to ``logits_amax_sigmas`` standard deviations so that the
+    winning logit is not clipped into a tie with the largest noise logits. Clip-max of the designed matrices is
+    their largest magnitude; all others are 4 x std from the calibration pass."""
+    w = transformer_weights(hidden, heads, ffn, n_enc, n_dec, vocab, pad_id, seed)
+    H, dh = hidden, hidden // heads
+    half = H // 2
+    p = f"dec.{n_dec - 1}"
+    sel = np.zeros((H, H), F32)
+    n_f = dh // 2
+    n_freq = n_f  # the dh/2 fastest frequencies (1 .. 0.33 rad per position for dh = 64), the same set for every head
+    for h in range(heads):
+        for j in range(n_f):
+            sel[h * dh + j, j] = 1.0                 # sin(w_j * pos)
+            sel[h * dh + n_f + j, half + j] = 1.0    # cos(w_j * pos)
+    # Those 2 x n_freq dims of the residual stream are kept as a clean positional channel: the token embedding is zero
+    # there and no sublayer writes to them (zero rows in every attention-output and second-FFN matrix), so a key's
+    # score depends on its position only and not on pseudo-random layer output that would favour some positions.
+    chan = np.concatenate([np.arange(n_freq), half + np.arange(n_freq)])
+    w["emb"][:, chan] = 0
+    for name in list(w):
+        if name.endswith((".out.w", ".xout.w", ".fc2.w")):
+            w[name][chan, :] = 0
+    w[p + ".xq.w"] = (F32(sharp) * sel).astype(F32)
+    w[p + ".xk.w"] = (F32(sharp) * sel).astype(F32)
+    w[p + ".xv.w"] = np.eye(H, dtype=F32)
+    w[p + ".xout.w"] = (F32(gain) * np.eye(H, dtype=F32)).astype(F32)
+    if calib_src is None:
+        calib_src = copy_task_inputs(batch=8, min_len=8, max_len=24, vocab=vocab, pad_id=pad_id, end_id=end_id, seed=seed + 1)
+    # LayerNorm subtracts the row mean (about 0.4: half of the positional table is cosines of slow frequencies, close
+    # to 1) from the channel as well; a constant LayerNorm bias on the channel dims puts it back, so that queries and
+    # keys are the bare sines and cosines (times 1/std). First pass measures the offset, second pass the clip-max table.
+    off: Dict[str, float] = {}
+    calibrate_transformer(w, calib_src, heads=heads, n_enc=n_enc, n_dec=n_dec, act="relu", pad_id=pad_id, ln_offsets=off)
+    w["enc.ln.b"][chan] = F32(off["enc.ln"])
+    w[p + ".ln2.b"][chan] = F32(off[p + ".ln2"])
+    amax = calibrate_transformer(w, calib_src, heads=heads, n_enc=n_enc, n_dec=n_dec, act="relu", pad_id=pad_id)
+    for name in (".xq.w", ".xk.w", ".xv.w", ".xout.w"):
+        amax[p + name] = float(np.abs(w[p + name]).max())
+    amax["logits.out"] = float(F32(amax["logits.out"] / 4.0 * logits_amax_sigmas))
+    conf = dict(hidden=hidden, heads=heads, ffn=ffn, n_enc=n_enc, n_dec=n_dec, vocab=vocab, act_gelu=0.0, pre_ln=1.0,
+                beam=beam, length_penalty=length_penalty, extra_decode_length=extra_decode_length, max_step=max_step,
+                pad_id=pad_id, start_id=start_id, end_id=end_id)
     w["pos"] = sinusoid_table(max_step, hidden)
     if path is not None:
         from . import weights

@@ -44,9 +44,10 @@ def test_c0_encoder_layer_matches_reference(golden_dir):
     # one int8 step of the fc2 output quantiser is the size of an isolated flip
     step = st.amax["enc.0.fc2.out"] / 127
     print("c0 max abs", d.max(), "mean abs", d.mean(), "fc2 step", step, "frac>step/2", (d > step / 2).mean())
-    assert d.mean() < 1e-3
-    assert d.max() < 2e-2 + 2 * step
-    assert (d > 1e-4).mean() < 0.02
+    # measured: max abs 1.02e-2 (one fc2 step), mean abs 3.7e-5, 0.40 % of elements moved; bounds are about twice that
+    assert d.mean() < 8e-5
+    assert d.max() < 2e-2
+    assert (d > step / 2).mean() < 0.008
 
 
 def test_small_seq2seq_matches_reference(golden_dir):
@@ -65,7 +66,7 @@ def test_small_seq2seq_matches_reference(golden_dir):
     assert np.abs(st.trace["enc.emb"] - g["enc_emb"]).max() < 1e-6
     d = np.abs(enc_out - g["enc_out"])[valid]
     print("enc_out max", d.max(), "mean", d.mean())
-    assert d.mean() < 1e-3 and d.max() < 5e-2
+    assert d.mean() < 2e-7 and d.max() < 2e-6  # measured 7.5e-8 / 8.4e-7: no quantiser flipped
     ks, vs = m.cross_kv(enc_out)
     T, steps = tgt.shape
     caches = [dict() for _ in range(cfg.n_dec)]
@@ -78,9 +79,9 @@ def test_small_seq2seq_matches_reference(golden_dir):
         dq = np.abs(lq.astype(np.float32) - ref_q)
         flips += int((dq > 0).sum())
         total += dq.size
-        assert dq.max() <= 3, f"step {s}: int8 logits differ by {dq.max()} steps"
+        assert dq.max() <= 1, f"step {s}: int8 logits differ by {dq.max()} steps"
     print("logit int8 mismatch rate", flips / total)
-    assert flips / total < 0.15
+    assert flips / total < 0.002  # measured 0.0: every int8 logit of every step equals the reference's
 
 
 def test_small_bert_matches_reference(golden_dir):
@@ -97,7 +98,7 @@ def test_small_bert_matches_reference(golden_dir):
     valid = ids != 0
     d = np.abs(y - g["y1"])[valid]
     print("bert y1 max", d.max(), "mean", d.mean())
-    assert d.mean() < 1e-3 and d.max() < 5e-2
+    assert d.mean() < 2e-7 and d.max() < 2e-6  # measured 6.7e-8 / 7.2e-7: no quantiser flipped
 
 
 def test_small_gpt_matches_reference(golden_dir):
@@ -115,12 +116,36 @@ def test_small_gpt_matches_reference(golden_dir):
     print("gpt hidden max", d.max(), "mean", d.mean(), "fraction identical to 1e-6", (d < 1e-6).mean())
     # the hidden state is a LayerNorm output (unit scale): one flipped quantiser step upstream (the reference's
     # fp32 GEMM vs exact integer accumulation) shows up as a few 1e-2 on that token
-    assert d.max() < 6e-2 and d.mean() < 1e-3
+    assert d.max() < 6e-2 and d.mean() < 6e-4  # measured 3.7e-2 / 2.9e-4 (one token of 30 carries a flip)
     lq, s = m.logits(h.reshape(-1, H))
     dq = np.abs(lq.astype(np.float32) - np.rint(g["logits"].reshape(-1, V) / s))
     print("gpt logits mismatch rate", (dq > 0).mean())
-    assert dq.max() <= 2 and (dq > 0).mean() < 0.05
+    assert dq.max() <= 2 and (dq > 0).mean() < 0.03  # measured 1.5 %
     # incremental decoding through the int8 cache gives the same hidden states as the full-sequence pass
     caches = [dict() for _ in range(2)]
     steps = [m.forward(ids[:, :4], 0, caches)] + [m.forward(ids[:, t:t + 1], t, caches) for t in range(4, 10)]
     assert np.array_equal(np.concatenate(steps, 1), h)
+
+
+def test_beam_step_equals_hand_worked_answer(golden_dir):
+    """oracle/beam.py against a beam step worked by hand (closed forms in the fixture): one finished beam that keeps
+    its frozen score and outranks a live candidate, a tie inside a row (lower token id) and a tie across beams (lower
+    beam), length normalisation, prefix bookkeeping. Pins the restated beam step to arithmetic that is not its own."""
+    import json
+
+    from oracle import beam as ob
+
+    fx = json.loads((golden_dir / "beam_step_hand_worked.json").read_text())
+    lq = np.array(fx["logits_q"], np.int8)
+    alive = np.array(fx["alive"], np.int32)
+    probs = np.array(fx["seq_probs"], np.float32)
+    score = np.array(fx["seq_score"], np.float32)
+    ln = ob.length_norm(fx["cur_step"] + 1, fx["length_penalty"])
+    assert abs(float(ln) - fx["length_norm"]) < 1e-7
+    na, npr, nsc, parent, n_fin = ob.beam_step(lq, np.float32(fx["s_logits"]), alive, probs, score, fx["cur_step"], ln, fx["end_id"])
+    e = fx["expect"]
+    assert np.array_equal(na, np.array(e["alive"], np.int32))
+    assert np.array_equal(parent, np.array(e["parent"]))
+    assert n_fin == e["n_finished"]
+    np.testing.assert_allclose(nsc, np.array(e["seq_score"]), rtol=0, atol=3e-6)
+    np.testing.assert_allclose(npr, np.array(e["seq_probs"]), rtol=0, atol=3e-6)

@@ -88,3 +88,44 @@ def test_noalloc_beam_update_rejects_sizes_beyond_its_scratch():
     import ctypes as C
 
     assert L.lib.ls100_beam_update_noalloc(ctx().handle, C.byref(a2), None) == L.ERR_UNSUPPORTED
+
+
+def test_noalloc_beam_update_rejected_call_enqueues_nothing():
+    """A call that fails its argument checks (beam 9 > 8) must not clear the shared scratch: the counters a valid call
+    left behind are still there afterwards, and the next valid call gives the same result as the allocating entry."""
+    import ctypes as C
+
+    B, K, ms, end_id, V = 3, 2, 16, 2, 64
+    ldv = 64
+    ln = dev(np.ones(ms, np.float32))
+    lq = dev(np.clip(np.rint(np.random.default_rng(3).standard_normal((B * K, ldv)) * 30), -127, 127).astype(np.int8))
+    sa, sb = _state(B, K, ms, end_id), _state(B, K, ms, end_id)
+    cs, ct = empty((B * K, K), torch.float32), empty((B * K, K), torch.int32)
+
+    def step(st, fn):
+        a1 = L.BeamTopkArgs(logits=ptr(lq), ld_logits=ldv, s_logits=0.05, batch=B, beam=K, vocab=V, max_step=ms, end_id=end_id,
+                            step_ptr=ptr(st["step"]), length_norm=ptr(ln), alive=ptr(st["alive"]), seq_probs=ptr(st["probs"]),
+                            seq_score=ptr(st["score"]), cand_score=ptr(cs), cand_token=ptr(ct))
+        L.call("ls100_beam_topk", ctx(), a1)
+        a2 = L.BeamUpdateArgs(cand_score=ptr(cs), cand_token=ptr(ct), batch=B, beam=K, max_step=ms, end_id=end_id,
+                              step_ptr=ptr(st["step"]), length_norm=ptr(ln), alive=ptr(st["alive"]), anc=ptr(st["anc"]),
+                              seq_probs=ptr(st["probs"]), seq_score=ptr(st["score"]),
+                              fin_count=ptr(st["fin"]) if fn == "ls100_beam_update" else None,
+                              ticket=ptr(st["ticket"]) if fn == "ls100_beam_update" else None,
+                              stop_step=ptr(st["stop"]), stop_host=None)
+        L.call(fn, ctx(), a2)
+        sync_check()
+        return a2
+
+    step(sa, "ls100_beam_update")
+    good = step(sb, "ls100_beam_update_noalloc")
+    bad = L.BeamUpdateArgs(cand_score=good.cand_score, cand_token=good.cand_token, batch=B, beam=9, max_step=ms, end_id=end_id,
+                           step_ptr=good.step_ptr, length_norm=good.length_norm, alive=good.alive, anc=good.anc,
+                           seq_probs=good.seq_probs, seq_score=good.seq_score, fin_count=None, ticket=None,
+                           stop_step=good.stop_step, stop_host=None)
+    assert L.lib.ls100_beam_update_noalloc(ctx().handle, C.byref(bad), None) == L.ERR_UNSUPPORTED
+    sync_check()
+    step(sa, "ls100_beam_update")
+    step(sb, "ls100_beam_update_noalloc")
+    for key in ("alive", "anc", "probs", "score", "step", "stop"):
+        assert torch.equal(sa[key], sb[key]), f"{key} differs after a rejected call"
