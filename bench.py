@@ -15,9 +15,13 @@ device->host copies inside the timed region. ``roofline`` is the dominant decode
 alone with CUDA events on the shapes of this workload; ``cpu_baseline`` is the numpy oracle of
 the same path on the host cores, on a bounded sample.
 
-``--impl reference`` times the reference path's CPU restatement (oracle/) on the host cores;
-the reference's own implementation is a Python/PyTorch module tree that cannot travel to the
-GPU box, so the oracle port pinned to it (tests/golden) stands in.
+``--impl reference`` times the reference's own CPU implementation of the path on the host cores: its
+PyTorch fake-quant modules (placed under oracle/_ref/ by oracle/make_ref.py, kind "reference"), assembled
+into the encoder-decoder with the beam step of oracle/beam.py between decoder calls (the beam step exists in
+the reference only as CUDA kernels). Without that tree the numpy oracle stands in (kind "port"). Each step is
+a bounded sample of the workload (the first sentences of the batch, full beam-4 generation). The line also
+carries the one-layer forward of the reference's TransformerEncoderLayer on its CPU-sized configuration
+(batch 8 x 64 tokens), all cores and one thread.
 """
 from __future__ import annotations
 
@@ -52,13 +56,32 @@ def peaks():
     return 6650.0, "fallback"
 
 
-def int8_tensor_peak():
-    """TOP/s an int8 contraction is held against: the driver measures no int8 figure, so twice the measured bf16
-    burst (the ratio of the nominal dense peaks, 4.5 : 2.25)."""
+def twice_bf16_peak():
+    """Twice the measured bf16 burst (the ratio of the nominal dense peaks, 4.5 : 2.25): the stand-in the int8
+    contractions were held against before this library measured its own ceiling; kept in the line for comparison."""
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         return 2.0 * float(json.loads(p.read_text())["bf16_tflops"]), "2 x measured bf16 burst"
     return 2.0 * 1590.0, "2 x fallback bf16 burst"
+
+
+def measure_i8_peak(L, ctx, iters: int = 4096):
+    """TOP/s of a steady tcgen05.mma kind::i8 issue loop on shared-memory-resident tiles, one CTA per SM, timed with
+    CUDA events inside the library call (best of three)."""
+    best, ms_best = 0.0, 0.0
+    for _ in range(3):
+        tops, ms = C.c_double(), C.c_float()
+        L.check(L.lib.ls100_measure_i8_mma_peak(ctx.handle, iters, None, C.byref(tops), C.byref(ms)), "i8 peak")
+        if tops.value > best:
+            best, ms_best = tops.value, ms.value
+    return best, ms_best
+
+
+def measure_phase_floor(L, ctx, phases: int = 100, grid: int = 64):
+    us = (C.c_float * 3)()
+    L.check(L.lib.ls100_measure_phase_floor(ctx.handle, phases, grid, None, us), "phase floor")
+    return {"grid": grid, "threads": 256, "phases": phases, "kernel_after_kernel_us": us[0],
+            "programmatic_dependent_launch_us": us[1], "persistent_kernel_grid_barrier_us": us[2]}
 
 
 class ClockSampler:
@@ -139,48 +162,136 @@ def count_tokens(tok: np.ndarray, end_id: int) -> int:
 
 
 # ------------------------------------------------------------------------------ CPU arm
-def cpu_generate_sample(conf, amax, w, src, n_sent: int):
+def _oracle_cfg(conf):
     from oracle import model as om
 
-    cfg = om.Config(hidden=int(conf["hidden"]), heads=int(conf["heads"]), ffn=int(conf["ffn"]), n_enc=int(conf["n_enc"]),
-                    n_dec=int(conf["n_dec"]), vocab=int(conf["vocab"]), max_step=int(conf["max_step"]),
-                    beam=int(conf["beam"]), length_penalty=float(conf["length_penalty"]),
-                    extra_decode_length=int(conf["extra_decode_length"]), pad_id=int(conf["pad_id"]),
-                    start_id=int(conf["start_id"]), end_id=int(conf["end_id"]))
-    st = om.State(w=w, amax=amax)
-    m = om.Seq2Seq(cfg, st)
-    sub = src[:n_sent]
-    m.generate(sub[:1, :4], max_len=3)  # quantise the weights outside the timed region
-    t0 = time.perf_counter()
-    tok, score, n = m.generate(sub)
-    dt = time.perf_counter() - t0
-    return count_tokens(tok, cfg.end_id), dt, tok
+    return om.Config(hidden=int(conf["hidden"]), heads=int(conf["heads"]), ffn=int(conf["ffn"]), n_enc=int(conf["n_enc"]),
+                     n_dec=int(conf["n_dec"]), vocab=int(conf["vocab"]), max_step=int(conf["max_step"]),
+                     beam=int(conf["beam"]), length_penalty=float(conf["length_penalty"]),
+                     extra_decode_length=int(conf["extra_decode_length"]), pad_id=int(conf["pad_id"]),
+                     start_id=int(conf["start_id"]), end_id=int(conf["end_id"]))
+
+
+def cpu_threads(n: int):
+    """All CPU legs set their thread count explicitly (torchrun exports OMP_NUM_THREADS=1 to its workers)."""
+    import torch
+
+    torch.set_num_threads(max(int(n), 1))
+    try:
+        from threadpoolctl import threadpool_limits
+
+        threadpool_limits(limits=max(int(n), 1))
+    except Exception:
+        pass
+
+
+def reference_modules():
+    """The reference's PyTorch fake-quant modules from oracle/_ref (None when that tree was not made)."""
+    from oracle import make_ref
+
+    if not make_ref.available():
+        return None
+    from oracle import ref_torch
+
+    return ref_torch.import_reference(str(make_ref.DEST))
+
+
+class CpuArm:
+    """The path on the host cores: the reference's own modules when available (kind "reference"), else the numpy
+    oracle (kind "port"). Weights are quantised / modules built once, outside any timed region."""
+
+    def __init__(self, conf, amax, w):
+        self.cfg = _oracle_cfg(conf)
+        mods = reference_modules()
+        if mods is not None:
+            from oracle import ref_torch
+
+            self.kind = "reference"
+            self.how = ("the reference's PyTorch fake-quant modules (TransformerEmbeddingLayer, TransformerEncoderLayer, "
+                        "TransformerDecoderLayer, QuantLinear) + the beam step of oracle/beam.py")
+            self.model = ref_torch.RefSeq2Seq(mods, self.cfg, w, amax)
+        else:
+            from oracle import model as om
+
+            self.kind = "port"
+            self.how = "numpy oracle (oracle/_ref not made)"
+            self.model = om.Seq2Seq(self.cfg, om.State(w=w, amax=amax))
+        self.model.generate(np.full((1, 4), 5, np.int32), max_len=3)  # first-use costs outside the timed region
+
+    def generate(self, src, n_sent):
+        sub = src[:n_sent]
+        t0 = time.perf_counter()
+        tok, score, n = self.model.generate(sub)
+        dt = time.perf_counter() - t0
+        return count_tokens(tok, self.cfg.end_id), dt, tok
+
+
+def cpu_config0():
+    """One int8 Transformer-base encoder layer forward (batch 8 x 64 padded tokens, lengths U{16..64}) through the
+    reference's own TransformerEncoderLayer: 5 warm-up + 20 timed iterations, with all cores and with one thread."""
+    mods = reference_modules()
+    if mods is None:
+        return None
+    import torch
+
+    from lightseq_b200 import synth
+    from oracle import ref_torch
+
+    g = np.load(ROOT / "tests" / "golden" / "c0_encoder_layer.npz")  # the clip-max table of that configuration
+    amax = dict(zip([str(x) for x in g["amax_names"]], [float(v) for v in g["amax_vals"]]))
+    w = synth.transformer_weights(512, 8, 2048, 1, 0, vocab=8, seed=1234)
+    rng = np.random.default_rng(4321)
+    x = torch.from_numpy(rng.standard_normal((8, 64, 512), dtype=np.float32))
+    lens = rng.integers(16, 65, size=8)
+    pad = torch.from_numpy(np.arange(64)[None, :] >= lens[:, None])
+    lyr = ref_torch.build_encoder_layer(mods, w, amax, "enc.0", 512, 8, 2048)
+    out = {"shape": "pre-LN, H 512, 8 heads, FFN 2048, ReLU; batch 8 x padded seq 64", "torch": torch.__version__}
+    for label, n in (("all_cores", os.cpu_count() or 1), ("one_thread", 1)):
+        cpu_threads(n)
+        with torch.no_grad():
+            for _ in range(5):
+                lyr(x, pad)
+            ts = []
+            for _ in range(20):
+                t0 = time.perf_counter()
+                lyr(x, pad)
+                ts.append(time.perf_counter() - t0)
+        med = statistics.median(ts)
+        out[label] = {"threads": n, "median_ms": med * 1e3, "min_ms": min(ts) * 1e3, "layer_forwards_per_s": 1.0 / med,
+                      "padded_tokens_per_s": 512.0 / med}
+    cpu_threads(os.cpu_count() or 1)
+    return out
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    cores = os.cpu_count() or 1
+    cpu_threads(cores)
     with tempfile.TemporaryDirectory() as td:
         _, conf, amax, w = build_model_file(td)
     src = batch_for_rank(0)
+    arm = CpuArm(conf, amax, w)
     n_sent = 4
     for _ in range(min(args.warmup, 1)):
-        cpu_generate_sample(conf, amax, w, src, 1)
+        arm.generate(src, 1)
     toks, secs = 0, 0.0
     for _ in range(args.steps):
-        n, dt, _ = cpu_generate_sample(conf, amax, w, src, n_sent)
+        n, dt, _ = arm.generate(src, n_sent)
         toks += n
         secs += dt
     val = toks / secs
+    sample = (f"first {n_sent} of 128 sentences per step, full beam-4 generation; {arm.how}; one process on rank 0 "
+              f"with {cores} threads (single-rank at every --gpus N)")
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * secs / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": WORKLOAD_NAME, "sample": f"first {n_sent} sentences of the 128-sentence batch per step"},
-        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
-                         "sample": f"first {n_sent} of 128 sentences, full beam-4 generation, numpy oracle"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": arm.kind, "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "cpu_config0_encoder_layer": cpu_config0(),
     }
     print(json.dumps(line), flush=True)
     return 0
@@ -308,7 +419,11 @@ def kernel_cases(torch, L, conf, B, S, step):
                            v_cache=None, max_step=0)
         L.call("ls100_attn_self", CTX[0], a, st)
 
-    cases["attn_self"] = (attn_self, eb * es * eh * 64 * 4, "hbm", f"attn_self_tc_kernel, {eb} x {es} tokens, {eh} heads")
+    # both contractions run on the tensor cores (int8 Q.K^T, split-fp16 P.V), so the entry is held against the tensor
+    # ceiling; what limits the kernel is the softmax between them (one exponential and ~8 instructions per score)
+    cases["attn_self"] = (attn_self, 4 * eb * eh * es * es * 64, "tensor",
+                          f"attn_self_tc_kernel, {eb} x {es} tokens, {eh} heads (2 S^2 dh ops per head for Q.K^T + 2 S^2 dh for "
+                          f"P.V; limited by softmax instruction issue, {eb * eh * es * es / 1e6:.0f} M exponentials)")
     # cross attention
     nx = 6
     kx, vx = [torch.randn(B * S, H, device=dev) for _ in range(nx)], [torch.randn(B * S, H, device=dev) for _ in range(nx)]
@@ -381,6 +496,17 @@ def run_single_kernel(args):
 
     torch.cuda.set_device(0)
     CTX[0] = L.Context(0)
+    if args.kernel == "i8_peak":
+        tops, ms = measure_i8_peak(L, CTX[0])
+        ref, src = twice_bf16_peak()
+        print(json.dumps({"kernel": "i8_peak", "note": "tcgen05.mma kind::i8 128x256x32 issue loop, operands resident in shared "
+                          "memory, one CTA per SM", "achieved_tops": tops, "launch_ms": ms, "twice_bf16_tops": ref,
+                          "twice_bf16_source": src}), flush=True)
+        return 0
+    if args.kernel == "phase_floor":
+        print(json.dumps({"kernel": "phase_floor", "results": [measure_phase_floor(L, CTX[0], 100, g) for g in (64, 148, 296)]}),
+              flush=True)
+        return 0
     conf = dict(hidden=512, ffn=2048, vocab=WORKLOAD["vocab"], heads=8, beam=WORKLOAD["beam"], max_step=WORKLOAD["max_step"])
     cases = kernel_cases(torch, L, conf, WORKLOAD["batch"], WORKLOAD["max_len"], 54)
     launch, algo, bound, note = cases[args.kernel]
@@ -489,6 +615,21 @@ def run_ours(args):
         dist.all_reduce(tk, op=dist.ReduceOp.SUM)
     max_ms, all_tokens = float(t.item()), float(tk.item())
     value = all_tokens / (max_ms / 1e3)
+    # the same generation cut off before its first decode step: encoder + cross K/V projection alone
+    lib.ls100_debug_set_step_limit.argtypes = [C.c_void_p, C.c_int]
+    lib.ls100_debug_set_step_limit(handle, 0)
+    enc_ms = 0.0
+    for i in range(4):
+        flush.fill_(1)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(mstream)
+        infer_device()
+        e1.record(mstream)
+        e1.synchronize()
+        if i > 0:
+            enc_ms += e0.elapsed_time(e1) / 3
+    lib.ls100_debug_set_step_limit(handle, args.decode_steps)
 
     if args.quick:
         if rank == 0:
@@ -539,7 +680,9 @@ def run_ours(args):
         except Exception:
             traffic_tab = {}
     per_kernel = {}
-    i8_peak, i8_src = int8_tensor_peak()
+    i8_peak, _ = measure_i8_peak(L, CTX[0])
+    i8_src = "measured tcgen05 kind::i8 issue loop (this run)"
+    i8_ref, i8_ref_src = twice_bf16_peak()
     for name, (launch, algo, bound, note) in cases.items():
         if name == "gemm_dec_ln":  # the cluster variant is not on the model's path (--kernel gemm_dec_ln times it)
             continue
@@ -548,7 +691,7 @@ def run_ours(args):
             ach = algo / (ms_k / 1e3) / 1e12
             per_kernel[name] = {"kernel": note, "bound": bound, "achieved": ach, "peak": i8_peak, "unit": "TOP/s",
                                 "frac": ach / i8_peak, "traffic": traffic_tab.get(name), "launch_us": ms_k * 1e3,
-                                "algorithmic_ops": algo, "peak_source": i8_src}
+                                "algorithmic_ops": algo, "peak_source": i8_src, "frac_of_" + i8_ref_src.replace(" ", "_"): ach / i8_ref}
             continue
         ms_k = time_kernel(torch, launch)
         ach = algo / (ms_k / 1e3) / 1e9
@@ -564,10 +707,13 @@ def run_ours(args):
                             "stream; achieved = algorithmic bytes / mean launch time"})
     cpu = None
     if world == 1 and not args.no_cpu:
-        n_sent = 4
-        n, dt, _ = cpu_generate_sample(conf, amax, w, src, n_sent)
-        cpu = {"value": n / dt, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
-               "sample": f"first {n_sent} of {B} sentences, full beam-4 generation with the numpy oracle ({dt:.1f} s)"}
+        cores = os.cpu_count() or 1
+        cpu_threads(cores)
+        arm = CpuArm(conf, amax, w)
+        n_sent = 8
+        n, dt, _ = arm.generate(src, n_sent)
+        cpu = {"value": n / dt, "unit": "tokens/s", "cores": cores, "kind": arm.kind,
+               "sample": f"first {n_sent} of {B} sentences, full beam-4 generation ({dt:.1f} s); {arm.how}"}
     # kernels of this library launched in the timed region (per generation: encoder + cross-KV + decode steps)
     n_enc, n_dec = int(conf["n_enc"]), int(conf["n_dec"])
     # encoder: embedding + 7 per layer + final LayerNorm; cross K/V: bf16 split (tensor-core projection) + 2 GEMMs per
@@ -576,6 +722,26 @@ def run_ours(args):
     sep_embed = 1 if os.environ.get("LS100_NO_EMBED_FUSE") is not None else 0
     split = 0 if os.environ.get("LS100_PROJ_SIMT") is not None else 1
     per_infer = (1 + 7 * n_enc + 1) + split + 2 * n_dec + steps_per_infer * (sep_embed + 11 * n_dec + 2 + 2)
+    # the decode step as a whole against the HBM roofline: the streams a step must read from HBM (activations of a
+    # few MB per kernel are produced and consumed out of L2)
+    H_, F_, V_, K_ = int(conf["hidden"]), int(conf["ffn"]), int(conf["vocab"]), int(conf["beam"])
+    T_ = B * K_
+    mean_hist = (steps_per_infer + 1) / 2.0
+    step_bytes = {
+        "weights": n_dec * (6 * H_ * H_ + 2 * H_ * F_) + V_ * H_,
+        "self_kv_int8": n_dec * T_ * H_ * (2 * mean_hist + 3),
+        "cross_kv_fp32_as_stored": n_dec * 2 * B * S * H_ * 4,
+        "logits_int8_write_then_read": 2 * T_ * V_,
+    }
+    step_us = (max_ms / args.steps - enc_ms) / max(steps_per_infer, 1) * 1e3
+    step_total = float(sum(step_bytes.values()))
+    step_roofline = {"bound": "hbm", "achieved": step_total / (step_us * 1e-6) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                     "frac": step_total / (step_us * 1e-6) / 1e9 / hbm_peak, "decode_step_us": step_us,
+                     "encoder_and_cross_kv_ms": enc_ms, "algorithmic_bytes": step_bytes,
+                     "algorithmic_bytes_with_fp16_cross_kv": step_total - step_bytes["cross_kv_fp32_as_stored"] / 2,
+                     "launches_per_step": sep_embed + 11 * n_dec + 2 + 2, "peak_source": peak_src}
+    phase_floor = measure_phase_floor(L, CTX[0], 100, 64)
+    strong = strong_scaling(torch, lsi, L, path, conf, src, world, td) if not args.no_strong else None
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": n_warm,
         "ms_per_step": max_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -588,11 +754,100 @@ def run_ours(args):
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": int(src.nbytes), "d2h_bytes_per_step": int(d2h)},
         "roofline": roofline, "roofline_other_kernels": {k: v for k, v in per_kernel.items() if k != "gemm_dec"},
         "cpu_baseline": cpu,
+        "step_roofline": step_roofline, "int8_tensor_peak": {"tops": i8_peak, "source": i8_src, i8_ref_src.replace(" ", "_"): i8_ref},
+        "dependent_phase_floor": phase_floor, "strong_scaling": strong,
     }
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
     return 0
+
+
+def strong_scaling(torch, lsi, L, path_c1, conf_c1, src_c1, n_gpus, tmpdir):
+    """ONE request batch split over ``n_gpus`` GPUs of this host (strong scaling): a replica, a host thread and a
+    stream per GPU, the batch dealt out by length (lightseq_b200.sharding), ids resident in HBM, every GPU timed
+    with CUDA events on its model's stream; a generation costs the slowest GPU's time. Runs on rank 0 after the
+    other ranks have finished. Workloads: the benchmark batch (128 sentences) and Transformer-big (256 sentences of
+    20..100 tokens)."""
+    import threading
+
+    from lightseq_b200 import sharding, synth
+
+    n_gpus = min(n_gpus, torch.cuda.device_count())
+    out = {"n_gpus": n_gpus, "how": "one process, one host thread + replica + stream per GPU, length-sorted round-robin shards "
+                                    "trimmed to their own longest sentence, no collective; CUDA events per GPU, max over GPUs"}
+    big_path = os.path.join(tmpdir, "transformer_big_int8.ls100")
+    calib = synth.transformer_inputs(batch=8, min_len=20, max_len=100, seed=5)
+    conf_c2, _, _ = synth.make_transformer(big_path, hidden=1024, heads=16, ffn=4096, max_step=160, calib_src=calib)
+    src_c2 = synth.transformer_inputs(batch=256, min_len=20, max_len=100)
+    lib = L.lib
+    for name, path, conf, src in (("transformer_base_128", path_c1, conf_c1, src_c1), ("transformer_big_256", big_path, conf_c2, src_c2)):
+        pad_id, end_id, beam, max_step = int(conf["pad_id"]), int(conf["end_id"]), int(conf["beam"]), int(conf["max_step"])
+        shards = sharding.shard_batch(src, pad_id, n_gpus)
+        iters = 3
+        gate = threading.Barrier(n_gpus)
+        times = [[0.0] * iters for _ in range(n_gpus)]
+        toks = [0] * n_gpus
+        errs = []
+
+        def work(g):
+            try:
+                torch.cuda.set_device(g)
+                rows, sub = shards[g]
+                b, s_len = sub.shape
+                model = lsi.QuantTransformer(path, b)
+                handle = C.c_void_p(model._handle)
+                sptr = C.c_void_p()
+                L.check(lib.ls100_model_get_stream(handle, C.byref(sptr)), "get_stream")
+                stream = torch.cuda.ExternalStream(sptr.value, device=torch.device("cuda", g))
+                d_src = torch.from_numpy(sub).to(f"cuda:{g}")
+                d_tok = torch.empty((b, beam, max_step), dtype=torch.int32, device=f"cuda:{g}")
+                d_score = torch.empty((b, beam), dtype=torch.float32, device=f"cuda:{g}")
+                L.check(lib.ls100_model_set_input_ptr(handle, 0, d_src.data_ptr()), "set_input_ptr")
+                L.check(lib.ls100_model_set_output_ptr(handle, 0, d_tok.data_ptr()), "set_output_ptr")
+                L.check(lib.ls100_model_set_output_ptr(handle, 1, d_score.data_ptr()), "set_output_ptr")
+                dims = (C.c_int32 * 2)(b, s_len)
+
+                def run():
+                    L.check(lib.ls100_model_set_input_shape(handle, 0, dims, 2), "set_input_shape")
+                    if lib.ls100_model_infer(handle) != 0:
+                        raise RuntimeError(lib.ls100_model_last_error())
+                    od, nd = (C.c_int32 * 4)(), C.c_int()
+                    lib.ls100_model_get_output_shape(handle, 0, od, C.byref(nd))
+                    return int(od[2])
+
+                for _ in range(2):
+                    n_out = run()
+                for i in range(iters):
+                    torch.cuda.synchronize(g)
+                    gate.wait()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(stream)
+                    n_out = run()
+                    e1.record(stream)
+                    e1.synchronize()
+                    times[g][i] = e0.elapsed_time(e1)
+                tok = d_tok.view(-1)[: b * n_out].view(b, n_out).cpu().numpy()
+                toks[g] = count_tokens(tok, end_id)
+            except Exception as e:  # a thread must not leave the others waiting at the gate
+                errs.append(repr(e))
+                gate.abort()
+
+        threads = [threading.Thread(target=work, args=(g,)) for g in range(n_gpus)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        if errs:
+            out[name] = {"error": errs[0]}
+            continue
+        per_iter = [max(times[g][i] for g in range(n_gpus)) for i in range(iters)]
+        ms = sum(per_iter) / iters
+        out[name] = {"sentences": int(src.shape[0]), "ms_per_generation": ms, "tokens_per_s": sum(toks) / (ms / 1e3),
+                     "sentences_per_gpu": [int(len(r)) for r, _ in shards],
+                     "padded_src_len_per_gpu": [int(sub.shape[1]) for _, sub in shards],
+                     "per_gpu_ms": [sum(times[g]) / iters for g in range(n_gpus)]}
+    return out
 
 
 def run_other_workload(args):
@@ -747,10 +1002,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling leg (one batch split over the GPUs)")
     ap.add_argument("--decode-steps", type=int, default=-1,
                     help="cap the number of decode steps per generation (profiling aid; the result is not a bench value)")
     ap.add_argument("--kernel", default=None,
-                    help="run one kernel family alone (gemm_dec, gemm_dec_ln, gemm_logits, gemm_enc_qkv, gemm_enc_out, gemm_enc_ffn2, gemm_square, attn_self, attn_dec, attn_cross, beam_topk, ln_quant)")
+                    help="run one kernel family alone (gemm_dec, gemm_dec_ln, gemm_logits, gemm_enc_qkv, gemm_enc_out, gemm_enc_ffn2, gemm_square, attn_self, attn_dec, attn_cross, beam_topk, ln_quant), or a measurement: i8_peak, phase_floor")
     ap.add_argument("--workload", default=None, choices=["bert", "vit", "gpt", "big", "eos"],
                     help="run another BASELINE configuration (BERT-base, GPT-2 medium, Transformer-big) on one GPU, or the "
                          "benchmark model with a boosted EOS (early-stop bookkeeping)")

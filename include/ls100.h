@@ -353,6 +353,22 @@ typedef struct {
 } ls100_beam_update_args;
 int ls100_beam_update(ls100_ctx* ctx, const ls100_beam_update_args* args, ls100_stream_t stream);
 
+/* Result of a finished generation from the beam state: `mode` 0 = beam 0 of every sentence
+ * (ker_write_trg_tokenid_pos_penalty, lightseq/inference/kernels/transformerKernels.cc.cu:1722-1733), 1 = the beam
+ * with the best score per non-EOS token, for a negative length penalty after an early stop
+ * (ker_write_trg_tokenid_neg_penalty, :1752-1784), 2 = every beam with the last position forced to EOS
+ * (ker_write_topk_result, :1803-1813). Tokens are positions 1 .. n_out of the histories. */
+typedef struct {
+  const int32_t* alive;    /* [batch, beam, max_step] */
+  const float* seq_score;  /* [batch, beam] */
+  int32_t batch, beam, max_step, end_id;
+  int32_t n_out;           /* tokens per output row */
+  int32_t mode;
+  int32_t* out_tokens;     /* [batch, n_out] (modes 0, 1) or [batch * beam, n_out] (mode 2) */
+  float* out_scores;       /* [batch] or [batch * beam] */
+} ls100_beam_result_args;
+int ls100_beam_write_result(ls100_ctx* ctx, const ls100_beam_result_args* args, ls100_stream_t stream);
+
 /* Allocation-free form of ls100_beam_update. It has no counterpart in the reference.
  * For callers that cannot provide the two scratch arrays because they cannot allocate device memory at all:
  * a serving process that handed every byte of the GPU to its own arena at start-up, or a latency-critical
@@ -457,6 +473,28 @@ int ls100_seq_ppl(ls100_ctx* ctx, const ls100_seq_ppl_args* args, ls100_stream_t
 int ls100_quantize_weight(ls100_ctx* ctx, const float* w, int64_t rows, int64_t cols, float amax, int8_t* out_q,
                           int32_t* row_off /* optional [rows] */, ls100_stream_t stream);
 
+/* ------------------------------------------------------------- measurement and diagnostics ---
+ * No counterparts in the reference (its tensor ceilings come from cuBLASLt's autotuner tables,
+ * tests/gemm_test/configs/igemm_*.cfg). These run no model work; they allocate their own small buffers and
+ * synchronise the stream.
+ *
+ * ls100_measure_i8_mma_peak: one CTA per SM issues `iters` x 4 tcgen05.mma kind::i8 instructions (128 x 256 x 32
+ * each) back to back from operands resident in shared memory into two TMEM accumulators; *tops_out = integer
+ * operations per second / 1e12 over the whole device, timed with CUDA events on `stream`. The measured ceiling of
+ * the tensor pipe for int8, the denominator of the GEMM rooflines.
+ *
+ * ls100_measure_phase_floor: time per dependent phase (every thread reads a float another CTA wrote in the
+ * previous phase) for `phases` phases of `grid` CTAs x 256 threads: us_per_phase[0] kernel after kernel,
+ * [1] kernel after kernel with programmatic dependent launch, [2] phases of one persistent cooperative kernel
+ * separated by a global-memory grid barrier (bounded wait).
+ *
+ * ls100_debug_expire_wait: launches one CTA that waits about 0.1 ms on an mbarrier nobody arrives at, gives up,
+ * records LS100_ERR_TIMEOUT in the context's error word and returns normally (nothing traps, the context stays
+ * usable); ls100_ctx_poll_error then reports the code once. */
+int ls100_measure_i8_mma_peak(ls100_ctx* ctx, int iters, ls100_stream_t stream, double* tops_out, float* ms_out /* optional */);
+int ls100_measure_phase_floor(ls100_ctx* ctx, int phases, int grid, ls100_stream_t stream, float* us_per_phase /* [3] */);
+int ls100_debug_expire_wait(ls100_ctx* ctx, ls100_stream_t stream);
+
 /* ------------------------------------------------------------- model level ---
  * The LSModel interface of lightseq/inference/pywrapper/model_base.h:59-148 as plain C:
  * create by name ("QuantTransformer", "QuantBert", "QuantGpt", "QuantVit") from a weight file and
@@ -485,6 +523,12 @@ int ls100_model_get_stream(ls100_model* m, ls100_stream_t* stream);
  * the model and allocated at creation. */
 int ls100_transformer_infer_host(ls100_model* m, const int32_t* ids, int batch, int seq_len, int32_t* out_tokens,
                                  float* out_scores, int* out_len);
+/* The same for models that return several sequences per sentence (every beam: `output_topk`, or a sampling method;
+ * QuantTransformer::Infer sets the output shapes to {batch, output_k, len}, lightseq/inference/pywrapper/
+ * quant_transformer.cc:100-109): tokens [batch, *out_k, *out_len] into out_tokens (batch * beam * max_step ints),
+ * scores [batch, *out_k] into out_scores (batch * beam floats). */
+int ls100_transformer_infer_host_k(ls100_model* m, const int32_t* ids, int batch, int seq_len, int32_t* out_tokens,
+                                   float* out_scores, int* out_k, int* out_len);
 /* QuantBert: ids [batch, seq_len] -> fp32 encoder output [batch, seq_len, hidden] (PyQuantBert::infer,
  * lightseq/inference/pywrapper/wrapper.cc:276-321). */
 int ls100_bert_infer_host(ls100_model* m, const int32_t* ids, int batch, int seq_len, float* out);

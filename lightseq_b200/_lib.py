@@ -171,6 +171,12 @@ lib.ls100_i8_to_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C
 lib.ls100_quantize_weight.restype = C.c_int
 lib.ls100_quantize_weight.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_void_p,
                                       C.c_void_p, C.c_void_p]
+lib.ls100_measure_i8_mma_peak.restype = C.c_int
+lib.ls100_measure_i8_mma_peak.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_float)]
+lib.ls100_measure_phase_floor.restype = C.c_int
+lib.ls100_measure_phase_floor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float)]
+lib.ls100_debug_expire_wait.restype = C.c_int
+lib.ls100_debug_expire_wait.argtypes = [C.c_void_p, C.c_void_p]
 
 
 def call(name: str, ctx: "Context", args, stream: int = 0) -> None:

@@ -131,21 +131,43 @@ extern "C" int ls100_model_get_stream(ls100_model* m, ls100_stream_t* stream) {
   return LS100_OK;
 }
 
+// H2D copy of the ids + Infer() into the model's staging buffers; k sequences of n tokens per sentence come out
+static void transformer_run_host(ls100_model* m, const int32_t* ids, int batch, int seq_len, int* k, int* n) {
+  const size_t nb = (size_t)batch * seq_len * 4;
+  if (nb > m->in_bytes) throw std::runtime_error("input larger than max_batch_size x max_step");
+  LS_CUDA(cudaSetDevice(m->device));
+  LS_CUDA(cudaMemcpy(m->d_in, ids, nb, cudaMemcpyHostToDevice));
+  m->model->set_input_ptr(0, m->d_in);
+  m->model->set_input_shape(0, {batch, seq_len});
+  m->model->set_output_ptr(0, m->d_out0);
+  m->model->set_output_ptr(1, m->d_out1);
+  m->model->Infer();
+  const std::vector<int> shp = m->model->get_output_shape(0);
+  *k = shp.at(1);
+  *n = shp.at(2);
+}
+
+extern "C" int ls100_transformer_infer_host_k(ls100_model* m, const int32_t* ids, int batch, int seq_len,
+                                              int32_t* out_tokens, float* out_scores, int* out_k, int* out_len) {
+  if (!m || !ids || !out_tokens || !out_scores || !out_k || !out_len || batch < 1 || seq_len < 1) return LS100_ERR_BAD_ARG;
+  return guarded([&] {
+    int k = 0, n = 0;
+    transformer_run_host(m, ids, batch, seq_len, &k, &n);
+    LS_CUDA(cudaMemcpy(out_tokens, m->d_out0, (size_t)batch * k * n * 4, cudaMemcpyDeviceToHost));
+    LS_CUDA(cudaMemcpy(out_scores, m->d_out1, (size_t)batch * k * 4, cudaMemcpyDeviceToHost));
+    *out_k = k;
+    *out_len = n;
+  });
+}
+
 extern "C" int ls100_transformer_infer_host(ls100_model* m, const int32_t* ids, int batch, int seq_len,
                                             int32_t* out_tokens, float* out_scores, int* out_len) {
   if (!m || !ids || !out_tokens || !out_scores || !out_len || batch < 1 || seq_len < 1) return LS100_ERR_BAD_ARG;
   return guarded([&] {
-    const size_t nb = (size_t)batch * seq_len * 4;
-    if (nb > m->in_bytes) throw std::runtime_error("input larger than max_batch_size x max_step");
-    LS_CUDA(cudaSetDevice(m->device));
-    LS_CUDA(cudaMemcpy(m->d_in, ids, nb, cudaMemcpyHostToDevice));
-    m->model->set_input_ptr(0, m->d_in);
-    m->model->set_input_shape(0, {batch, seq_len});
-    m->model->set_output_ptr(0, m->d_out0);
-    m->model->set_output_ptr(1, m->d_out1);
-    m->model->Infer();
-    const std::vector<int> shp = m->model->get_output_shape(0);
-    const int n = shp.at(2);
+    int k = 0, n = 0;
+    transformer_run_host(m, ids, batch, seq_len, &k, &n);
+    if (k != 1)  // the caller's buffers hold one sequence per sentence: nothing is copied
+      throw std::runtime_error("this model returns several sequences per sentence: call ls100_transformer_infer_host_k");
     LS_CUDA(cudaMemcpy(out_tokens, m->d_out0, (size_t)batch * n * 4, cudaMemcpyDeviceToHost));
     LS_CUDA(cudaMemcpy(out_scores, m->d_out1, (size_t)batch * 4, cudaMemcpyDeviceToHost));
     *out_len = n;
@@ -235,6 +257,13 @@ extern "C" long long ls100_debug_set_layer_tap(ls100_model* m, float* device_buf
   const long long used = (long long)e->layer_tap_floats();
   e->set_layer_tap(device_buf, (size_t)capacity_floats);
   return used;
+}
+// launches the expiring wait of ls100_debug_expire_wait on the model's own context and stream: the next Infer() must
+// surface LS100_ERR_TIMEOUT as an error
+extern "C" int ls100_debug_model_expire_wait(ls100_model* m) {
+  auto* e = m ? dynamic_cast<ls100::EngineModel*>(m->model.get()) : nullptr;
+  if (!e) return LS100_ERR_BAD_ARG;
+  return ls100_debug_expire_wait(e->context()->kernels(), (ls100_stream_t)e->context()->get_stream());
 }
 extern "C" int ls100_debug_steps_run(ls100_model* m) {
   return m ? ls100::quant_transformer_steps_run(m->model.get()) : -1;

@@ -41,6 +41,18 @@ class QuantTransformer : public EngineModel {
     length_penalty_ = (float)wf.conf("length_penalty");
     const bool gelu = wf.conf_or("act_gelu", 0.0) != 0.0;
     const bool pre_ln = wf.conf_or("pre_ln", 1.0) != 0.0;
+    // generator options (lightseq/inference/proto/quant_transformer.proto:140-149, quant_decoder.cc.cu:388-397)
+    sampling_ = (int)wf.conf_or("sampling_method", 0.0);  // 0 beam_search, 1 topk, 2 topp, 3 topk_greedy
+    topk_ = (int)wf.conf_or("topk", 1.0);
+    topp_ = (float)wf.conf_or("topp", 0.0);
+    seed_lo_ = (uint32_t)wf.conf_or("rng_seed", 0.0);
+    output_topk_ = wf.conf_or("output_topk", 0.0) != 0.0 || sampling_ != 0;
+    no_scale_embedding_ = wf.conf_or("no_scale_embedding", 0.0) != 0.0;
+    if (sampling_ < 0 || sampling_ > 3) throw std::runtime_error("QuantTransformer: unknown sampling_method");
+    if (wf.conf_or("diverse_lambda", 0.0) != 0.0) throw std::runtime_error("QuantTransformer: diverse beam search is not supported");
+    if (sampling_ == 1 && (topk_ < 1 || topk_ > 32)) throw std::runtime_error("QuantTransformer: topk must be in [1, 32]");
+    if (sampling_ == 2 && !(topp_ > 0.f && topp_ <= 1.f)) throw std::runtime_error("QuantTransformer: topp must be in (0, 1]");
+    if (sampling_ == 1 || sampling_ == 2) beam_ = 1;  // one sampled sequence per sentence (pywrapper/quant_transformer.cc:35-37)
     if (H_ != heads_ * 64) throw std::runtime_error("QuantTransformer: head_dim must be 64");
     if (beam_ < 1 || beam_ > 8) throw std::runtime_error("QuantTransformer: beam size must be in [1, 8]");
     if (max_batch_size < 1) throw std::runtime_error("max_batch_size must be positive");
@@ -94,11 +106,13 @@ class QuantTransformer : public EngineModel {
     seq_score_ = c.alloc_n<float>(max_rows);
     cand_score_ = c.alloc_n<float>((size_t)max_rows * beam_);
     cand_token_ = c.alloc_n<int32_t>((size_t)max_rows * beam_);
-    counters_ = c.alloc_n<int32_t>(2 * max_step_ + 2);  // [step, stop, fin[max_step], ticket[max_step]]
+    counters_ = c.alloc_n<int32_t>(2 * max_step_ + 4);  // [step, stop, fin[max_step], ticket[max_step], 2 for sampling]
     step_ptr_ = counters_;
     stop_ptr_ = counters_ + 1;
     fin_ptr_ = counters_ + 2;
     ticket_ptr_ = counters_ + 2 + max_step_;
+    sample_ticket_ = counters_ + 2 + 2 * max_step_;
+    sample_ended_ = sample_ticket_ + 1;
     stop_host_ = static_cast<int32_t*>(c.alloc_host_mapped(sizeof(int32_t)));
     LS_CUDA(cudaHostGetDevicePointer((void**)&stop_host_dev_, stop_host_, 0));
 
@@ -116,8 +130,14 @@ class QuantTransformer : public EngineModel {
     for (int r = 0; r < max_rows; ++r) h_alive_[(size_t)r * max_step_] = start_id_;
     h_probs_.assign(max_rows, -1000.f);  // min_log_probability / 2 (quant_decoder.cc.cu:57-66)
     for (int r = 0; r < max_rows; r += beam_) h_probs_[r] = 0.f;
-    h_counters_.assign(2 * max_step_ + 2, 0);
+    h_counters_.assign(2 * max_step_ + 4, 0);
     h_counters_[1] = -1;
+    if (sampling_ != 0) {  // rows keep their own cache slots once they are sampled independently
+      h_anc_.resize((size_t)max_rows * max_step_);
+      for (int r = 0; r < max_rows; ++r)
+        for (int p = 0; p < max_step_; ++p) h_anc_[(size_t)r * max_step_ + p] = r;
+      LS_CUDA(cudaHostRegister(h_anc_.data(), h_anc_.size() * 4, cudaHostRegisterDefault));
+    }
     LS_CUDA(cudaHostRegister(h_alive_.data(), h_alive_.size() * 4, cudaHostRegisterDefault));
     LS_CUDA(cudaHostRegister(h_probs_.data(), h_probs_.size() * 4, cudaHostRegisterDefault));
     LS_CUDA(cudaHostRegister(h_counters_.data(), h_counters_.size() * 4, cudaHostRegisterDefault));
@@ -133,6 +153,7 @@ class QuantTransformer : public EngineModel {
     cudaHostUnregister(h_alive_.data());
     cudaHostUnregister(h_probs_.data());
     cudaHostUnregister(h_counters_.data());
+    if (!h_anc_.empty()) cudaHostUnregister(h_anc_.data());
   }
 
   void Infer() override {
@@ -156,22 +177,23 @@ class QuantTransformer : public EngineModel {
     LS_CUDA(cudaMemcpyAsync(seq_probs_, h_probs_.data(), (size_t)rows * 4, cudaMemcpyHostToDevice, st));
     LS_CUDA(cudaMemcpyAsync(counters_, h_counters_.data(), h_counters_.size() * 4, cudaMemcpyHostToDevice, st));
     LS_CUDA(cudaMemsetAsync(seq_score_, 0, (size_t)rows * 4, st));
-    LS_CUDA(cudaMemsetAsync(anc_, 0, (size_t)rows * max_step_ * 4, st));
+    if (sampling_ != 0) LS_CUDA(cudaMemcpyAsync(anc_, h_anc_.data(), (size_t)rows * max_step_ * 4, cudaMemcpyHostToDevice, st));
+    else LS_CUDA(cudaMemsetAsync(anc_, 0, (size_t)rows * max_step_ * 4, st));
     *stop_host_ = -1;
 
-    // _batch_max_decode_length of the reference (quant_decoder.cc.cu:428-430)
-    const int max_decode = std::min(max_step_, S + extra_len_) - 1;
+    // _batch_max_decode_length of the reference (quant_decoder.cc.cu:428-436): sampling runs to max_step
+    const int max_decode = sampling_ != 0 ? max_step_ : std::min(max_step_, S + extra_len_) - 1;
     int n_steps = std::max(max_decode - 1, 0);
     if (debug_step_limit_ >= 0) n_steps = std::min(n_steps, debug_step_limit_);
-    cudaGraphExec_t exec = use_graph_ ? decode_graph(B, S) : nullptr;
     int launched = 0;
     for (int s = 0; s < n_steps; ++s) {
       if (s >= kRing) {
         LS_CUDA(cudaEventSynchronize(ring_[s % kRing]));
         if (!benchmark_ && *((volatile int32_t*)stop_host_) >= 0) break;
       }
-      if (exec) LS_CUDA(cudaGraphLaunch(exec, st));
-      else decode_step(B, S);
+      const bool beam_step = sampling_ == 0 || (sampling_ == 3 && s == 0);  // topk_greedy: a beam step, then greedy rows
+      if (use_graph_) LS_CUDA(cudaGraphLaunch(decode_graph(B, S, beam_step), st));
+      else decode_step(B, S, beam_step);
       LS_CUDA(cudaEventRecord(ring_[s % kRing], st));
       ++launched;
     }
@@ -180,17 +202,31 @@ class QuantTransformer : public EngineModel {
     LS_CUDA(cudaStreamSynchronize(st));
     const int err = ls100_ctx_poll_error(ctx_->kernels(), st);
     if (err != 0) throw std::runtime_error(std::string("device reported: ") + ls100_strerror(err));
+    // the beam kernels report the step at which every beam had finished, the sampling kernels the position written then
+    const bool stopped_in_sampling = sampling_ == 1 || sampling_ == 2 || (sampling_ == 3 && launched > 1);
     int cur_step;
-    if (!benchmark_ && h_stop >= 0) cur_step = h_stop;
+    if (!benchmark_ && h_stop >= 0) cur_step = stopped_in_sampling ? h_stop - 1 : h_stop;
     else cur_step = std::max(max_decode - 1, 0);
-    const int n_out = cur_step + 1;
-    // tokens of beam 0, positions 1..n_out (ker_write_trg_tokenid_pos_penalty, transformerKernels.cc.cu:1722-1733)
-    LS_CUDA(cudaMemcpy2DAsync(d_out_ids_, (size_t)n_out * 4, alive_ + 1, (size_t)beam_ * max_step_ * 4, (size_t)n_out * 4, B,
-                              cudaMemcpyDeviceToDevice, st));
-    LS_CUDA(cudaMemcpy2DAsync(d_out_scores_, 4, seq_score_, (size_t)beam_ * 4, 4, B, cudaMemcpyDeviceToDevice, st));
+    const int n_out = std::min(cur_step + 1, max_step_ - 1);
+    // what the reference writes out (quant_decoder.cc.cu:456-478): every beam when the model outputs its top k or
+    // samples; else beam 0, or, for a negative length penalty, the beam with the best score per token
+    ls100_beam_result_args r;
+    memset(&r, 0, sizeof(r));
+    r.alive = alive_;
+    r.seq_score = seq_score_;
+    r.batch = B;
+    r.beam = beam_;
+    r.max_step = max_step_;
+    r.end_id = end_id_;
+    r.n_out = n_out;
+    r.mode = output_topk_ ? 2 : (length_penalty_ < 0.f ? 1 : 0);
+    r.out_tokens = d_out_ids_;
+    r.out_scores = d_out_scores_;
+    LS_RC(ls100_beam_write_result(ctx_->kernels(), &r, st));
     LS_CUDA(cudaStreamSynchronize(st));
-    set_output_shape(0, {B, 1, n_out});
-    set_output_shape(1, {B, 1});
+    const int out_k = output_topk_ ? beam_ : 1;
+    set_output_shape(0, {B, out_k, n_out});
+    set_output_shape(1, {B, out_k});
     steps_run_ = launched;
   }
 
@@ -259,7 +295,7 @@ class QuantTransformer : public EngineModel {
     e.hidden = H_;
     e.table_q = emb_.w;
     e.s_emb = emb_.s_w;
-    e.sqrt_h = sqrtf((float)H_);
+    e.sqrt_h = no_scale_embedding_ ? 1.0f : sqrtf((float)H_);
     e.pos = pos_;
     e.n_pos = n_pos_;
     e.pad_id = pad_id_;
@@ -288,7 +324,7 @@ class QuantTransformer : public EngineModel {
     LS_RC(ls100_ln_quant(ctx_->kernels(), &a, ctx_->get_stream()));
   }
 
-  void decode_step(int B, int S) {
+  void decode_step(int B, int S, bool beam_step) {
     const int rows = B * beam_;
     ls100_ctx* k = ctx_->kernels();
     cudaStream_t st = ctx_->get_stream();
@@ -302,7 +338,7 @@ class QuantTransformer : public EngineModel {
     e.step_ptr = step_ptr_;
     e.table_q = emb_.w;
     e.s_emb = emb_.s_w;
-    e.sqrt_h = sqrtf((float)H_);
+    e.sqrt_h = no_scale_embedding_ ? 1.0f : sqrtf((float)H_);
     e.pos = pos_;
     e.n_pos = n_pos_;
     e.pad_id = pad_id_;
@@ -335,6 +371,10 @@ class QuantTransformer : public EngineModel {
     logits(dec_.a_q, logits_q_);
     logits.before_forward(rows, ldv_);
     logits.forward();
+    if (!beam_step) {  // QuantDecoder::sample / topk_greedy_search (quant_decoder.cc.cu:951-985, 1101-1133)
+      sample_step(rows);
+      return;
+    }
     ls100_beam_topk_args t;
     memset(&t, 0, sizeof(t));
     t.logits = logits_q_->value<int8_t>();
@@ -374,15 +414,63 @@ class QuantTransformer : public EngineModel {
     LS_RC(ls100_beam_update(k, &u, st));
   }
 
-  cudaGraphExec_t decode_graph(int B, int S) {
-    const long long key = (long long)B * 100000 + S;
+  // one new token per row, each row on its own: top-k (k = 1 for topk_greedy) or nucleus sampling, Philox keyed by
+  // (seed; position, row); EOS bookkeeping and the stop word stay on the device
+  void sample_step(int rows) {
+    ls100_ctx* k = ctx_->kernels();
+    cudaStream_t st = ctx_->get_stream();
+    if (sampling_ == 2) {
+      ls100_sample_topp_args s;
+      memset(&s, 0, sizeof(s));
+      s.logits = logits_q_->value<int8_t>();
+      s.ld_logits = ldv_;
+      s.s_logits = emb_.s_out;
+      s.p = topp_;
+      s.rows = rows;
+      s.vocab = V_;
+      s.max_step = max_step_;
+      s.end_id = end_id_;
+      s.seed_lo = seed_lo_;
+      s.seed_hi = 0;
+      s.seq = alive_;
+      s.cur = step_ptr_;
+      s.ticket = sample_ticket_;
+      s.n_ended = sample_ended_;
+      s.stop = stop_ptr_;
+      s.stop_host = stop_host_dev_;
+      LS_RC(ls100_sample_topp(k, &s, st));
+      return;
+    }
+    ls100_sample_topk_args s;
+    memset(&s, 0, sizeof(s));
+    s.logits = logits_q_->value<int8_t>();
+    s.ld_logits = ldv_;
+    s.s_logits = emb_.s_out;
+    s.rows = rows;
+    s.vocab = V_;
+    s.k = sampling_ == 3 ? 1 : topk_;
+    s.max_step = max_step_;
+    s.end_id = end_id_;
+    s.seed_lo = seed_lo_;
+    s.seed_hi = 0;
+    s.seq = alive_;
+    s.cur = step_ptr_;
+    s.ticket = sample_ticket_;
+    s.n_ended = sample_ended_;
+    s.stop = stop_ptr_;
+    s.stop_host = stop_host_dev_;
+    LS_RC(ls100_sample_topk(k, &s, st));
+  }
+
+  cudaGraphExec_t decode_graph(int B, int S, bool beam_step) {
+    const long long key = ((long long)B * 100000 + S) * 2 + (beam_step ? 1 : 0);
     auto it = graphs_.find(key);
     if (it != graphs_.end()) return it->second;
     cudaStream_t st = ctx_->get_stream();
     cudaGraph_t g = nullptr;
     LS_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
     try {
-      decode_step(B, S);
+      decode_step(B, S, beam_step);
     } catch (...) {
       cudaStreamEndCapture(st, &g);
       if (g) cudaGraphDestroy(g);
@@ -414,7 +502,12 @@ class QuantTransformer : public EngineModel {
   Variable *enc_out_ = nullptr, *pad_mask_ = nullptr, *logits_q_ = nullptr;
   int32_t *alive_ = nullptr, *anc_ = nullptr, *cand_token_ = nullptr, *counters_ = nullptr;
   int32_t *step_ptr_ = nullptr, *stop_ptr_ = nullptr, *fin_ptr_ = nullptr, *ticket_ptr_ = nullptr;
-  int32_t *stop_host_ = nullptr, *stop_host_dev_ = nullptr;
+  int32_t *stop_host_ = nullptr, *stop_host_dev_ = nullptr, *sample_ticket_ = nullptr, *sample_ended_ = nullptr;
+  int sampling_ = 0, topk_ = 1;
+  float topp_ = 0.f;
+  uint32_t seed_lo_ = 0;
+  bool output_topk_ = false, no_scale_embedding_ = false;
+  std::vector<int32_t> h_anc_;
   float *seq_probs_ = nullptr, *seq_score_ = nullptr, *cand_score_ = nullptr, *length_norm_ = nullptr;
   std::vector<int32_t> h_alive_, h_counters_;
   std::vector<float> h_probs_;

@@ -326,9 +326,67 @@ __global__ void __launch_bounds__(128) beam_update_kernel(const ls100_beam_updat
   }
 }
 
+// Writes the result of a finished generation from the beam state (one CTA per output row):
+//   mode 0  beam 0 of every sentence, tokens at positions 1 .. n_out, its score
+//           (ker_write_trg_tokenid_pos_penalty, lightseq/inference/kernels/transformerKernels.cc.cu:1722-1733)
+//   mode 1  the beam with the best score / (number of non-EOS tokens + 1e-12), for a negative length penalty when
+//           the generation stopped early (ker_write_trg_tokenid_neg_penalty, :1752-1784); ties keep the lower beam
+//   mode 2  every beam, the last position forced to EOS (ker_write_topk_result, :1803-1813)
+__global__ void __launch_bounds__(128) beam_write_result_kernel(const ls100_beam_result_args a) {
+  __shared__ int s_pick;
+  __shared__ float s_best;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int K = a.beam, ms = a.max_step, n = a.n_out;
+  const int row_out = blockIdx.x;
+  int src_row;
+  if (a.mode == 2) {
+    src_row = row_out;
+  } else if (a.mode == 0) {
+    src_row = row_out * K;
+  } else {
+    if (threadIdx.x < 32) {
+      int pick = 0;
+      float best = -INFINITY;
+      for (int j = 0; j < K; ++j) {  // beams in order: an equal later score does not replace an earlier one
+        const int32_t* seq = a.alive + ((long long)row_out * K + j) * ms + 1;
+        int len = 0;
+        for (int p = threadIdx.x; p < n; p += 32) len += (seq[p] != a.end_id) ? 1 : 0;
+        len = warp_sum_i(len);
+        const float sc = __fdiv_rn(a.seq_score[row_out * K + j], __fadd_rn((float)len, 1e-12f));
+        if (sc > best) {
+          best = sc;
+          pick = j;
+        }
+      }
+      if (threadIdx.x == 0) {
+        s_pick = pick;
+        s_best = best;
+      }
+    }
+    __syncthreads();
+    src_row = row_out * K + s_pick;
+  }
+  const int32_t* seq = a.alive + (long long)src_row * ms + 1;
+  int32_t* out = a.out_tokens + (long long)row_out * n;
+  for (int p = threadIdx.x; p < n; p += blockDim.x) out[p] = (a.mode == 2 && p == n - 1) ? a.end_id : seq[p];
+  if (threadIdx.x == 0) a.out_scores[row_out] = (a.mode == 1) ? s_best : a.seq_score[src_row];
+}
+
 }  // namespace ls100
 
 using namespace ls100;
+
+extern "C" int ls100_beam_write_result(ls100_ctx* ctx, const ls100_beam_result_args* a, ls100_stream_t stream_) {
+  if (!ctx || !a || !a->alive || !a->seq_score || !a->out_tokens || !a->out_scores) return LS100_ERR_BAD_ARG;
+  if (a->batch <= 0 || a->beam <= 0 || a->max_step <= 1 || a->n_out <= 0 || a->n_out >= a->max_step) return LS100_ERR_BAD_ARG;
+  if (a->mode < 0 || a->mode > 2) return LS100_ERR_BAD_ARG;
+  if (a->beam > MAX_BEAM) return LS100_ERR_UNSUPPORTED;
+  const int rows = a->mode == 2 ? a->batch * a->beam : a->batch;
+  return ls100_launch(beam_write_result_kernel, dim3(rows), dim3(128), 0, (cudaStream_t)stream_, *a) == cudaSuccess
+             ? LS100_OK
+             : LS100_ERR_CUDA;
+}
 
 extern "C" int ls100_beam_topk(ls100_ctx* ctx, const ls100_beam_topk_args* a, ls100_stream_t stream_) {
   if (!ctx || !a || !a->logits || !a->step_ptr || !a->length_norm || !a->alive || !a->seq_probs || !a->seq_score ||

@@ -31,6 +31,7 @@ class PyQuantTransformer {
     int32_t dims[4];
     int nd = 0;
     check(ls100_model_get_output_max_shape(m_, 0, dims, &nd), "get_output_max_shape");
+    beam_ = dims[1];
     max_step_ = dims[2];
   }
   ~PyQuantTransformer() { ls100_model_destroy(m_); }
@@ -41,16 +42,17 @@ class PyQuantTransformer {
       py::array_t<int, py::array::c_style | py::array::forcecast> input_seq) {
     if (input_seq.ndim() != 2) throw std::runtime_error("input_seq must be a 2-D int32 array [batch, seq_len]");
     const int batch = (int)input_seq.shape(0), seq = (int)input_seq.shape(1);
-    std::vector<int32_t> toks((size_t)batch * max_step_);
-    py::array_t<float> scores({batch, 1});
-    int n = 0;
+    std::vector<int32_t> toks((size_t)batch * beam_ * max_step_);
+    std::vector<float> sc((size_t)batch * beam_);
+    int n = 0, k = 0;
     {
       py::gil_scoped_release nogil;
-      check(ls100_transformer_infer_host(m_, input_seq.data(), batch, seq, toks.data(), scores.mutable_data(), &n),
-            "infer");
+      check(ls100_transformer_infer_host_k(m_, input_seq.data(), batch, seq, toks.data(), sc.data(), &k, &n), "infer");
     }
-    py::array_t<int> tokens({batch, 1, n});
-    std::copy(toks.begin(), toks.begin() + (size_t)batch * n, tokens.mutable_data());
+    py::array_t<int> tokens({batch, k, n});
+    py::array_t<float> scores({batch, k});
+    std::copy(toks.begin(), toks.begin() + (size_t)batch * k * n, tokens.mutable_data());
+    std::copy(sc.begin(), sc.begin() + (size_t)batch * k, scores.mutable_data());
     return std::make_tuple(tokens, scores);
   }
   void benchmark_mode(bool on) { check(ls100_model_benchmark_mode(m_, on ? 1 : 0), "benchmark_mode"); }
@@ -58,7 +60,7 @@ class PyQuantTransformer {
 
  private:
   ls100_model* m_ = nullptr;
-  int max_step_ = 0;
+  int beam_ = 1, max_step_ = 0;
 };
 
 // QuantBert(weight_path, max_batch_size).infer(int32[B,S]) -> float32[B,S,H]

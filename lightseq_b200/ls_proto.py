@@ -236,16 +236,30 @@ def read_quant_transformer(path: str):
             amax[f"dec.{i}.{nm}.w"] = float(kv_c[i])
     if _int(mc, 12) != 0:
         raise ValueError("post-LN encoder-decoder models are not supported by the engine")
-    if _int(mc, 13) != 0:
-        raise ValueError("no_scale_embedding models are not supported by the engine")
     if _int(mc, 15) != 0:
         raise ValueError("multilingual models are not supported by the engine")
+    # fields that change the reference's output and that the engine does not implement are refused, not dropped
+    if _float(mc, 7) != 0.0:
+        raise ValueError("diverse_lambda != 0 (diverse beam search) is not supported by the engine")
+    bias = _floats(trg, 7)
+    if bias.size and np.any(bias != 0):
+        raise ValueError("a non-zero shared_bias (logit bias) is not supported by the engine")
+    if _floats(src, 8).size or _floats(trg, 8).size:
+        raise ValueError("language embeddings (lang_emb) are not supported by the engine")
+    trg_pos = _floats(trg, 2)
+    if trg_pos.size and (trg_pos.size != t["pos"].size or not np.array_equal(trg_pos, t["pos"].reshape(-1))):
+        raise ValueError("the target position table differs from the source one: the engine holds a single table")
     method = _str(mc, 8, "beam_search")
-    if method != "beam_search":
-        raise ValueError(f"sampling_method {method!r}: the QuantTransformer engine implements beam_search")
+    methods = ("beam_search", "topk", "topp", "topk_greedy")
+    if method not in methods:
+        raise ValueError(f"unknown sampling_method {method!r}")
+    # QuantTransformer of the reference returns every beam (its decoder is built with output_topk = true,
+    # lightseq/inference/pywrapper/quant_transformer.cc:60-62): files in its format keep that behaviour
     conf = dict(hidden=H, heads=_int(mc, 1), ffn=dims.get("ffn", 0), n_enc=len(enc_layers), n_dec=n_dec, vocab=V,
                 act_gelu=float(_int(mc, 14)), pre_ln=1.0, beam=_int(mc, 2), length_penalty=_float(mc, 4),
-                extra_decode_length=_int(mc, 3), max_step=max_step, pad_id=_int(mc, 5), start_id=_int(mc, 6), end_id=_int(mc, 11))
+                extra_decode_length=_int(mc, 3), max_step=max_step, pad_id=_int(mc, 5), start_id=_int(mc, 6), end_id=_int(mc, 11),
+                sampling_method=float(methods.index(method)), topk=float(max(_int(mc, 10), 1)), topp=_float(mc, 9),
+                output_topk=1.0, no_scale_embedding=float(_int(mc, 13)))
     return conf, amax, t
 
 
@@ -292,10 +306,12 @@ def write_quant_transformer(path: str, conf, amax, t) -> None:
            _enc_floats(4, t["dec.ln.b"]) + _enc_bytes(5, kv_u.tobytes()) + _enc_floats(6, kv_b) +
            _tag(7, 2) + _varint(4 * V) + np.zeros(V, "<f4").tobytes() +  # shared_bias: zeros, as the reference exporter writes
            _enc_float(9, amax["emb"]) + _enc_floats(10, kv_c) + _enc_float(11, amax["logits.in"]) + _enc_float(12, amax["logits.out"]))
-    method = b"beam_search"
+    method = ("beam_search", "topk", "topp", "topk_greedy")[int(conf.get("sampling_method", 0))].encode()
     mc = (_enc_int(1, conf["heads"]) + _enc_int(2, conf["beam"]) + _enc_int(3, conf["extra_decode_length"]) +
           _enc_float(4, conf["length_penalty"]) + _enc_int(5, conf["pad_id"]) + _enc_int(6, conf["start_id"]) +
-          _tag(8, 2) + _varint(len(method)) + method + _enc_int(11, conf["end_id"]) + _enc_int(14, 1 if conf.get("act_gelu") else 0))
+          _tag(8, 2) + _varint(len(method)) + method + _enc_float(9, conf.get("topp", 0.0)) + _enc_int(10, int(conf.get("topk", 1))) +
+          _enc_int(11, conf["end_id"]) + _enc_int(13, 1 if conf.get("no_scale_embedding") else 0) +
+          _enc_int(14, 1 if conf.get("act_gelu") else 0))
     out = bytearray()
     out += _tag(1, 2) + _varint(len(src)) + src
     for i in range(n_enc):

@@ -155,9 +155,12 @@ def transformer_inputs(batch=128, min_len=20, max_len=60, vocab=32000, pad_id=1,
     return ids
 
 
+SAMPLING_METHODS = ("beam_search", "topk", "topp", "topk_greedy")  # the code stored in a model's configuration
+
+
 def calibrate_transformer(w: Dict[str, np.ndarray], src: np.ndarray, *, heads: int, n_enc: int, n_dec: int,
                           act: str = "relu", pad_id: int = 1, seed: int = 99, k: float = 4.0,
-                          ln_offsets: Optional[Dict[str, float]] = None) -> Dict[str, float]:
+                          ln_offsets: Optional[Dict[str, float]] = None, no_scale_embedding: bool = False) -> Dict[str, float]:
     """Clip-max table = k x std, from one fp32 pass: encoder on ``src``; decoder teacher-forced
     on random target ids of the source lengths (causal self-attention). ``ln_offsets``, when given, receives the
     average mean/std ratio of the inputs of the encoder's final LayerNorm and of every decoder ``ln2``."""
@@ -179,7 +182,8 @@ def calibrate_transformer(w: Dict[str, np.ndarray], src: np.ndarray, *, heads: i
     def emb(ids):
         mask = ids != pad_id
         p = (np.cumsum(mask, 1) - 1) * mask
-        return (F32(math.sqrt(H)) * w["emb"][ids] + pos[p] * mask[..., None]).astype(F32)
+        scale = F32(1.0) if no_scale_embedding else F32(math.sqrt(H))
+        return (scale * w["emb"][ids] + pos[p] * mask[..., None]).astype(F32)
 
     pad = src == pad_id
     x = emb(src)
@@ -230,17 +234,24 @@ def calibrate_transformer(w: Dict[str, np.ndarray], src: np.ndarray, *, heads: i
 
 def make_transformer(path: Optional[str] = None, *, hidden=512, heads=8, ffn=2048, n_enc=6, n_dec=6, vocab=32000,
                      act="relu", beam=4, length_penalty=0.6, extra_decode_length=50, max_step=256, pad_id=1,
-                     start_id=3, end_id=2, seed=1234, calib_src: Optional[np.ndarray] = None
+                     start_id=3, end_id=2, seed=1234, calib_src: Optional[np.ndarray] = None,
+                     sampling_method: str = "beam_search", topk: int = 1, topp: float = 0.0, output_topk: bool = False,
+                     no_scale_embedding: bool = False, rng_seed: int = 0
                      ) -> Tuple[Dict[str, float], Dict[str, float], Dict[str, np.ndarray]]:
-    """Builds (conf, amax, tensors) of a seeded synthetic QuantTransformer and optionally writes ``path``."""
+    """Builds (conf, amax, tensors) of a seeded synthetic QuantTransformer and optionally writes ``path``. The
+    generator options are those of the reference's model configuration (sampling_method, topk, topp; every beam in
+    the output; embeddings not scaled by sqrt(hidden))."""
     w = transformer_weights(hidden, heads, ffn, n_enc, n_dec, vocab, pad_id, seed)
     if calib_src is None:
         calib_src = transformer_inputs(batch=8, min_len=8, max_len=24, vocab=vocab, pad_id=pad_id, seed=seed + 1)
-    amax = calibrate_transformer(w, calib_src, heads=heads, n_enc=n_enc, n_dec=n_dec, act=act, pad_id=pad_id)
+    amax = calibrate_transformer(w, calib_src, heads=heads, n_enc=n_enc, n_dec=n_dec, act=act, pad_id=pad_id,
+                                 no_scale_embedding=no_scale_embedding)
     conf = dict(hidden=hidden, heads=heads, ffn=ffn, n_enc=n_enc, n_dec=n_dec, vocab=vocab,
                 act_gelu=float(act == "gelu"), pre_ln=1.0, beam=beam, length_penalty=length_penalty,
                 extra_decode_length=extra_decode_length, max_step=max_step, pad_id=pad_id, start_id=start_id,
-                end_id=end_id)
+                end_id=end_id, sampling_method=float(SAMPLING_METHODS.index(sampling_method)), topk=float(topk),
+                topp=float(topp), output_topk=float(output_topk), no_scale_embedding=float(no_scale_embedding),
+                rng_seed=float(rng_seed))
     w["pos"] = sinusoid_table(max_step, hidden)
     if path is not None:
         from . import weights

@@ -63,12 +63,14 @@ class _QuantLinearLayer:
         return b
 
     def _clip_max(self, clip_max: torch.Tensor):
-        key = (clip_max.data_ptr(), clip_max._version)
-        if key != self.cmax_key:
+        # The host copy is reused only for the SAME tensor object at the same version. An address is not an identity:
+        # a fresh tensor built per call usually gets the previous one's address back from the caching allocator, and
+        # its new values must not be ignored. The cached object is kept alive so that `is` cannot be fooled either.
+        if self.cmax_key is None or self.cmax_key[0] is not clip_max or self.cmax_key[1] != clip_max._version:
             v = [float(x) for x in clip_max.detach().float().cpu().tolist()]
             if len(v) != 3 or not all(x > 0 for x in v):
                 raise RuntimeError("clip_max must hold three positive values: input, weight, output")
-            self.cmax_key, self.cmax = key, v
+            self.cmax_key, self.cmax = (clip_max, clip_max._version), v
         return self.cmax
 
     def forward(self, inputs: torch.Tensor, weight: torch.Tensor, clip_max: torch.Tensor, quant_mode: bool) -> torch.Tensor:
@@ -174,6 +176,8 @@ class _EncoderLayer:
     def assign(self, weight: torch.Tensor):
         if weight.numel() != self.offset[-1]:
             raise RuntimeError(f"parameter tensor has {weight.numel()} elements, the layer needs {self.offset[-1]}")
+        if weight is not self.para:
+            self.key = None  # a new tensor may sit at the old one's address: never reuse the prepared state for it
         self.para = weight
 
     def _prepare(self, ctx, st):

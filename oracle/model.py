@@ -59,6 +59,14 @@ class Config:
     beam: int = 4
     length_penalty: float = 0.6
     extra_decode_length: int = 50
+    # generator options of the reference's decoder (lightseq/inference/proto/quant_transformer.proto:140-149)
+    sampling_method: str = "beam_search"   # beam_search | topk | topp | topk_greedy
+    topk: int = 1
+    topp: float = 0.0
+    output_topk: bool = False              # every beam in the result, last position forced to EOS
+    no_scale_embedding: bool = False
+    seed_lo: int = 0
+    seed_hi: int = 0
 
     @property
     def head_dim(self) -> int:
@@ -249,7 +257,7 @@ def embed(st: State, ids: np.ndarray, step: int, cfg: Config, pos_table: np.ndar
     else:
         eq, s = st.weight_q("emb", "emb")[:2]
         e = eq[ids].astype(F32) * s
-    x = F32(math.sqrt(cfg.hidden)) * e
+    x = e if cfg.no_scale_embedding else F32(math.sqrt(cfg.hidden)) * e
     mask = (ids != cfg.pad_id)
     pos = (np.cumsum(mask, axis=1) - 1 + step) * mask
     return (x + pos_table[pos] * mask[..., None].astype(F32)).astype(F32)
@@ -359,21 +367,30 @@ class Seq2Seq:
 
     # beam search ---------------------------------------------------------
     def generate(self, src: np.ndarray, max_len: Optional[int] = None, early_stop: bool = True):
-        """Beam search following the reference engine's bookkeeping
-        (lightseq/inference/model/quant_decoder.cc.cu:415-484,987-1098;
+        """Generation following the reference engine's bookkeeping
+        (lightseq/inference/model/quant_decoder.cc.cu:415-484,951-1133;
         lightseq/inference/kernels/transformerKernels_int8.cc.cu:1690-1844;
-        lightseq/inference/kernels/transformerKernels.cc.cu:1398-1463,1722-1784), with an
+        lightseq/inference/kernels/transformerKernels.cc.cu:1398-1463,1722-1813), with an
         exact per-row top-``beam`` instead of the rough threshold, no float batch offsets,
         and the deterministic tie-break: higher score, then lower beam, then lower token id.
-        Returns (tokens [B, n_steps+1] of the best beam, scores [B], n_steps)."""
-        from .beam import beam_step, length_norm
+
+        ``sampling_method`` beam_search: returns (tokens [B, n] of the best beam, scores [B], n); with
+        ``output_topk`` (tokens [B, K, n], scores [B, K], n), the last position forced to EOS. A negative length
+        penalty picks, per sentence, the beam with the best score per non-EOS token.
+        topk / topp: one sequence per sentence sampled token by token (counter-based Philox draw keyed by position and
+        row), up to ``max_step`` tokens; returns (tokens [B, 1, n], scores [B, 1] = 0, n).
+        topk_greedy: the first step is a beam step (K different first tokens), every later step takes each row's
+        best token; returns all K rows like ``output_topk``."""
+        from .beam import beam_step, length_norm, sample_topk_row, sample_topp_row
 
         cfg = self.cfg
         B, S = src.shape
-        K = cfg.beam
+        method = cfg.sampling_method
+        sampling = method in ("topk", "topp")
+        K = 1 if sampling else cfg.beam
         enc_out, src_pad = self.encode(src)
         ks, vs = self.cross_kv(enc_out)
-        max_decode = min(cfg.max_step, S + cfg.extra_decode_length) - 1
+        max_decode = cfg.max_step if method != "beam_search" else min(cfg.max_step, S + cfg.extra_decode_length) - 1
         if max_len is not None:
             max_decode = min(max_decode, max_len)
         alive = np.full((B, K, cfg.max_step), cfg.end_id, dtype=np.int32)
@@ -386,18 +403,48 @@ class Seq2Seq:
         for cur in range(max_decode - 1):
             tokens = alive[:, :, cur].reshape(-1)
             lq, s_l = self.decode_step(tokens, cur, caches, ks, vs, src_pad)
-            ln = length_norm(cur + 1, cfg.length_penalty)
-            alive, probs, score, parent, n_fin = beam_step(
-                lq.reshape(B, K, -1), s_l, alive, probs, score, cur, ln, cfg.end_id)
-            if early_stop and n_fin == B * K:
+            if method == "beam_search" or (method == "topk_greedy" and cur == 0):
+                ln = length_norm(cur + 1, cfg.length_penalty)
+                alive, probs, score, parent, n_fin = beam_step(
+                    lq.reshape(B, K, -1), s_l, alive, probs, score, cur, ln, cfg.end_id)
+                if early_stop and n_fin == B * K:
+                    break
+                flat = (parent + np.arange(B)[:, None] * K).reshape(-1)
+                for c in caches:
+                    c["k"] = c["k"][flat]
+                    c["v"] = c["v"][flat]
+                continue
+            flat_alive = alive.reshape(B * K, -1)
+            for r in range(B * K):
+                if flat_alive[r, cur] == cfg.end_id and cur != 0:
+                    flat_alive[r, cur + 1] = cfg.end_id
+                elif method == "topp":
+                    flat_alive[r, cur + 1] = sample_topp_row(lq[r], s_l, cfg.topp, cur + 1, r, cfg.seed_lo, cfg.seed_hi)
+                else:
+                    k = 1 if method == "topk_greedy" else cfg.topk
+                    flat_alive[r, cur + 1] = sample_topk_row(lq[r], s_l, k, cur + 1, r, cfg.seed_lo, cfg.seed_hi)
+            if early_stop and (flat_alive[:, cur + 1] == cfg.end_id).all():
                 break
-            flat = (parent + np.arange(B)[:, None] * K).reshape(-1)
-            for c in caches:
-                c["k"] = c["k"][flat]
-                c["v"] = c["v"][flat]
         else:
             cur = max(max_decode - 1, 0)
-        n = cur + 1
+        n = min(cur + 1, cfg.max_step - 1)
+        if method != "beam_search" or cfg.output_topk:
+            tok = alive[:, :, 1:n + 1].copy()
+            tok[:, :, n - 1] = cfg.end_id
+            return tok, score.copy(), n
+        if cfg.length_penalty < 0:
+            out_t = np.zeros((B, n), np.int32)
+            out_s = np.zeros(B, F32)
+            for b in range(B):
+                best, pick = F32(-np.inf), 0
+                for j in range(K):
+                    ln_j = int((alive[b, j, 1:n + 1] != cfg.end_id).sum())
+                    sc = F32(score[b, j] / F32(F32(ln_j) + F32(1e-12)))
+                    if sc > best:
+                        best, pick = sc, j
+                out_t[b] = alive[b, pick, 1:n + 1]
+                out_s[b] = best
+            return out_t, out_s, n
         return alive[:, 0, 1:n + 1].copy(), score[:, 0].copy(), n
 
 

@@ -686,3 +686,19 @@ def test_sample_topp_matches_oracle(V, p, spread):
         assert np.array_equal(d_seq.cpu().numpy(), seq), f"step {step}: sampled tokens differ"
         assert int(d_stop.cpu()[0]) == stop_ref
     assert stop_ref > 0
+
+
+def test_bounded_wait_runs_out_and_reports_once():
+    """A wait that nothing satisfies gives up after its budget: the kernel returns normally, the context's error word
+    holds LS100_ERR_TIMEOUT exactly once, and the context keeps working (the next GEMM is bit-exact)."""
+    c = ctx()
+    assert c.poll_error() == 0
+    assert L.lib.ls100_debug_expire_wait(c.handle, None) == 0
+    assert c.poll_error() == L.ERR_TIMEOUT
+    assert c.poll_error() == 0  # reading clears it
+    r = np.random.default_rng(1)
+    a = r.integers(-127, 128, size=(128, 256), dtype=np.int8)
+    w = r.integers(-127, 128, size=(64, 256), dtype=np.int8)
+    out = gemm(dev(a), dev(w), s_acc=1.0, out_kind=L.OUT_I32)
+    sync_check()
+    assert np.array_equal(out.cpu().numpy().astype(np.int64), oq.int_matmul(a, w))
