@@ -740,8 +740,17 @@ def run_ours(args):
                      "encoder_and_cross_kv_ms": enc_ms, "algorithmic_bytes": step_bytes,
                      "algorithmic_bytes_with_fp16_cross_kv": step_total - step_bytes["cross_kv_fp32_as_stored"] / 2,
                      "launches_per_step": sep_embed + 11 * n_dec + 2 + 2, "peak_source": peak_src}
-    phase_floor = measure_phase_floor(L, CTX[0], 100, 64)
-    strong = strong_scaling(torch, lsi, L, path, conf, src, world, td) if not args.no_strong else None
+    # auxiliary legs must never cost the line
+    try:
+        phase_floor = measure_phase_floor(L, CTX[0], 100, 64)
+    except Exception as e:
+        phase_floor = {"error": repr(e)}
+    strong = None
+    if not args.no_strong:
+        try:
+            strong = strong_scaling(torch, lsi, L, path, conf, src, world, td)
+        except Exception as e:
+            strong = {"error": repr(e)}
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": n_warm,
         "ms_per_step": max_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

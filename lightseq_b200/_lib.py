@@ -134,6 +134,12 @@ class ProjTcArgs(C.Structure):
                 ("n", C.c_int32), ("k", C.c_int32), ("out", C.c_void_p), ("ldo", C.c_int64), ("split_seq", C.c_int32)]
 
 
+class BeamResultArgs(C.Structure):
+    _fields_ = [("alive", C.c_void_p), ("seq_score", C.c_void_p), ("batch", C.c_int32), ("beam", C.c_int32),
+                ("max_step", C.c_int32), ("end_id", C.c_int32), ("n_out", C.c_int32), ("mode", C.c_int32),
+                ("out_tokens", C.c_void_p), ("out_scores", C.c_void_p)]
+
+
 class SampleToppArgs(C.Structure):
     _fields_ = [("logits", C.c_void_p), ("ld_logits", C.c_int64), ("s_logits", C.c_float), ("p", C.c_float),
                 ("rows", C.c_int32), ("vocab", C.c_int32), ("max_step", C.c_int32), ("end_id", C.c_int32),
@@ -160,7 +166,8 @@ for _name, _cls in (("ls100_ln_quant", LnQuantArgs), ("ls100_embed", EmbedArgs),
                     ("ls100_proj_f32", ProjF32Args), ("ls100_beam_topk", BeamTopkArgs),
                     ("ls100_beam_update", BeamUpdateArgs), ("ls100_beam_update_noalloc", BeamUpdateArgs), ("ls100_sample_topk", SampleTopkArgs),
                     ("ls100_sample_topp", SampleToppArgs),
-                    ("ls100_proj_tc", ProjTcArgs), ("ls100_patch_embed", PatchEmbedArgs)):
+                    ("ls100_proj_tc", ProjTcArgs), ("ls100_patch_embed", PatchEmbedArgs),
+                    ("ls100_beam_write_result", BeamResultArgs)):
     _fn = getattr(lib, _name)
     _fn.restype = C.c_int
     _fn.argtypes = [C.c_void_p, C.POINTER(_cls), C.c_void_p]

@@ -24,7 +24,10 @@ def _build(tmp_path, **kw):
                     n_dec=int(conf["n_dec"]), vocab=int(conf["vocab"]), max_step=int(conf["max_step"]),
                     beam=int(conf["beam"]), length_penalty=float(conf["length_penalty"]),
                     extra_decode_length=int(conf["extra_decode_length"]), pad_id=int(conf["pad_id"]),
-                    start_id=int(conf["start_id"]), end_id=int(conf["end_id"]))
+                    start_id=int(conf["start_id"]), end_id=int(conf["end_id"]),
+                    sampling_method=synth.SAMPLING_METHODS[int(conf["sampling_method"])], topk=int(conf["topk"]),
+                    topp=float(conf["topp"]), output_topk=bool(conf["output_topk"]),
+                    no_scale_embedding=bool(conf["no_scale_embedding"]), seed_lo=int(conf["rng_seed"]))
     return path, cfg, om.State(w=w, amax=amax)
 
 
@@ -313,3 +316,115 @@ def test_batch_split_over_two_gpus_is_bit_identical(tmp_path):
     tok3, sc3 = runner.infer(src, cfg.pad_id, cfg.end_id)  # trimmed shards: each decodes to its own length cap
     assert tok3.shape[0] == 11 and tok3.shape[2] <= tok1.shape[2]
     runner.close()
+
+
+SMALL = dict(hidden=128, heads=2, ffn=256, n_enc=2, n_dec=2, vocab=500, max_step=24, beam=4, extra_decode_length=12, seed=7)
+
+
+def _boost_eos(path, cfg, st, amount=0.3):
+    """Makes EOS competitive (a shared direction in the final LayerNorm bias and the EOS embedding row), so that
+    sequences end at different steps."""
+    from lightseq_b200 import weights
+
+    u = np.sign(np.random.default_rng(0).standard_normal(cfg.hidden)).astype(np.float32)
+    st.w["dec.ln.b"] = (amount * u).astype(np.float32)
+    st.w["emb"][cfg.end_id] = (0.02 * u).astype(np.float32)
+    _, conf, amax, _ = weights.load(path)
+    weights.save(path, "QuantTransformer", conf, amax, st.w)
+
+
+@pytest.mark.parametrize("method,extra", [("topk", dict(topk=4)), ("topk", dict(topk=1)), ("topp", dict(topp=0.7)),
+                                          ("topk_greedy", dict())])
+def test_sampling_methods_match_oracle(tmp_path, method, extra):
+    """sampling_method topk / topp (one sampled sequence per sentence, up to max_step tokens) and topk_greedy (a beam
+    step, then every row takes its best token) of the reference's decoder: same tokens as the oracle, draw for draw
+    (QuantDecoder::sample and topk_greedy_search, lightseq/inference/model/quant_decoder.cc.cu:951-985, 1101-1133)."""
+    import lightseq_b200.inference as lsi
+
+    path, cfg, st = _build(tmp_path, sampling_method=method, rng_seed=123, **extra, **SMALL)
+    _boost_eos(path, cfg, st)
+    src = synth.transformer_inputs(batch=5, min_len=3, max_len=10, vocab=cfg.vocab, pad_id=cfg.pad_id, seed=3)
+    ref_tok, ref_score, n_ref = om.Seq2Seq(cfg, st).generate(src)
+    tok, score = lsi.QuantTransformer(path, 5).infer(src)
+    k = cfg.beam if method == "topk_greedy" else 1
+    assert tok.shape == (5, k, n_ref) and score.shape == (5, k), (tok.shape, n_ref)
+    same = (tok == ref_tok).all(axis=(1, 2))
+    print(method, extra, "identical", int(same.sum()), "of 5, steps", n_ref, "distinct tokens", len(set(tok.ravel().tolist())))
+    assert same.all()
+    assert (tok[:, :, -1] == cfg.end_id).all()  # the last position is EOS whatever was generated there
+
+
+def test_every_beam_is_returned_when_asked(tmp_path):
+    """output_topk: tokens [batch, beam, len] and scores [batch, beam] (what the reference's QuantTransformer always
+    returns, lightseq/inference/pywrapper/quant_transformer.cc:100-109); beam 0 is the single-beam answer."""
+    import lightseq_b200.inference as lsi
+
+    path, cfg, st = _build(tmp_path, output_topk=True, **SMALL)
+    _boost_eos(path, cfg, st)
+    src = synth.transformer_inputs(batch=6, min_len=3, max_len=10, vocab=cfg.vocab, pad_id=cfg.pad_id, seed=4)
+    ref_tok, ref_score, n_ref = om.Seq2Seq(cfg, st).generate(src)
+    tok, score = lsi.QuantTransformer(path, 6).infer(src)
+    assert tok.shape == (6, cfg.beam, n_ref)
+    assert np.array_equal(tok, ref_tok)
+    np.testing.assert_allclose(score, ref_score, rtol=1e-4, atol=1e-4)
+    assert (np.diff(score, axis=1) <= 1e-6).all()  # beams are ordered by score
+
+
+def test_negative_length_penalty_picks_the_best_score_per_token(tmp_path):
+    """length_penalty < 0: scores are normalised by 1/len during the search and the result is the beam with the best
+    score per non-EOS token, not beam 0 (ker_write_trg_tokenid_neg_penalty,
+    lightseq/inference/kernels/transformerKernels.cc.cu:1752-1784)."""
+    import lightseq_b200.inference as lsi
+
+    path, cfg, st = _build(tmp_path, length_penalty=-1.0, **SMALL)
+    _boost_eos(path, cfg, st)
+    src = synth.transformer_inputs(batch=8, min_len=3, max_len=10, vocab=cfg.vocab, pad_id=cfg.pad_id, seed=5)
+    ref_tok, ref_score, n_ref = om.Seq2Seq(cfg, st).generate(src)
+    tok, score = lsi.QuantTransformer(path, 8).infer(src)
+    assert tok.shape == (8, 1, n_ref)
+    assert np.array_equal(tok[:, 0], ref_tok)
+    np.testing.assert_allclose(score[:, 0], ref_score, rtol=1e-4, atol=1e-4)
+
+
+def test_unscaled_embeddings(tmp_path):
+    """no_scale_embedding: the token embedding is not multiplied by sqrt(hidden) (quant_transformer.proto:148)."""
+    import lightseq_b200.inference as lsi
+
+    path, cfg, st = _build(tmp_path, no_scale_embedding=True, **SMALL)
+    src = synth.transformer_inputs(batch=4, min_len=3, max_len=10, vocab=cfg.vocab, pad_id=cfg.pad_id, seed=6)
+    ref_tok, ref_score, n_ref = om.Seq2Seq(cfg, st).generate(src)
+    tok, score = lsi.QuantTransformer(path, 4).infer(src)
+    assert tok.shape == (4, 1, n_ref) and np.array_equal(tok[:, 0], ref_tok)
+
+
+def test_beam_result_writer_modes():
+    """ls100_beam_write_result against a direct numpy statement of the three output forms."""
+    B, K, ms, end_id, n = 3, 4, 12, 2, 7
+    r = np.random.default_rng(9)
+    alive = r.integers(3, 50, size=(B, K, ms)).astype(np.int32)
+    alive[0, 1, 4:] = end_id
+    alive[1, 2, 2:] = end_id
+    score = -r.random((B, K)).astype(np.float32) * 5
+    from tests.gpu_util import ctx, dev, empty, ptr, sync_check
+
+    d_alive, d_score = dev(alive), dev(score)
+    for mode in (0, 1, 2):
+        rows = B * K if mode == 2 else B
+        out_t, out_s = empty((rows, n), torch.int32), empty((rows,), torch.float32)
+        a = L.BeamResultArgs(alive=ptr(d_alive), seq_score=ptr(d_score), batch=B, beam=K, max_step=ms, end_id=end_id, n_out=n,
+                             mode=mode, out_tokens=ptr(out_t), out_scores=ptr(out_s))
+        L.call("ls100_beam_write_result", ctx(), a)
+        sync_check()
+        t, s = out_t.cpu().numpy(), out_s.cpu().numpy()
+        if mode == 0:
+            assert np.array_equal(t, alive[:, 0, 1:n + 1]) and np.array_equal(s, score[:, 0])
+        elif mode == 2:
+            want = alive[:, :, 1:n + 1].reshape(B * K, n).copy()
+            want[:, -1] = end_id
+            assert np.array_equal(t, want) and np.array_equal(s, score.reshape(-1))
+        else:
+            for b in range(B):
+                lens = (alive[b, :, 1:n + 1] != end_id).sum(1).astype(np.float32)
+                per = score[b] / (lens + np.float32(1e-12))
+                j = int(np.argmax(per))
+                assert np.array_equal(t[b], alive[b, j, 1:n + 1]) and s[b] == per[j]
