@@ -316,28 +316,28 @@ __global__ void __launch_bounds__(128, 7) attn_dec_kernel(const ls100_attn_dec_a
 }
 
 // ------------------------------------------------------------------ attn_cross
-// Persistent CTAs (three per SM for up to 4 beams) walk the (sentence, head) pairs. The head's fp32 keys and
-// values of a 64-key tile are brought into shared memory by four TMA box copies (K and V, each as two
-// 128-byte-wide halves of the 64 head dims, 128-byte swizzle) issued by one thread into one of two buffers, so
-// the copy of the next pair runs under the arithmetic of this one and costs no registers. When the caller
-// declares the keys and values static (kv_static), the first two copies are issued BEFORE the grid-dependency
-// wait and overlap the tail of the preceding kernel.
-// The arithmetic is bound by shared-memory bandwidth, so every key and value element is read from shared memory
-// ONCE for all beams: each of the four warps owns 16 keys of the tile and keeps one accumulator set per beam.
-// Scores: lane = (key, half of the head dims), 16-byte reads that are conflict-free under the swizzle, the two
-// halves added by one shuffle. PV: two head dims per lane. The warps' partial softmax results (max, sum,
-// weighted values) are merged through shared memory at the end of a pair.
+// One CTA of four warps per (sentence, head). The head's fp32 keys and values of a 64-key tile are brought into
+// shared memory by four TMA box copies (K and V, each as two 128-byte-wide halves of the 64 head dims, 128-byte
+// swizzle) issued by one thread. When the caller declares the keys and values static (kv_static: written once per
+// request, before the decode kernels), the copies are issued BEFORE the grid-dependency wait, so that they travel
+// while the preceding kernel is still running. One tile buffer per CTA (32 KB) instead of a persistent CTA with
+// two: residency is what hides the latency of this kernel (its arithmetic is a chain of dependent shuffles and
+// small FMAs), and six CTAs per SM hold nearly every (sentence, head) of a decode step at once. Sources longer than
+// 64 tokens reuse the buffer tile after tile.
+// Every key and value element is read from shared memory ONCE for all beams: each of the four warps owns 16 keys
+// of the tile and keeps one accumulator set per beam. Scores: lane = (key, half of the head dims), 16-byte reads
+// that are conflict-free under the swizzle, the two halves added by one shuffle. PV: two head dims per lane. The
+// warps' partial softmax results (max, sum, weighted values) are merged through shared memory at the end.
 constexpr int XT = 64;                 // keys per tile
 constexpr int XHALF = XT * 128;        // bytes of one half tile: 64 rows x 128 B
 constexpr int XTILE = 4 * XHALF;       // K lo, K hi, V lo, V hi
-constexpr int XCTAS_PER_SM = 3;
+constexpr int XCTAS_PER_SM = 6;
 constexpr int XWARPS = 4;              // 16 keys of a tile each
 constexpr int XQ = 72;                 // floats per q row in shared memory: the two 32-float halves 36 apart,
                                        // so that the two addresses a warp reads at once fall into different banks
 
 __device__ __forceinline__ void xattn_issue(uint8_t* buf, uint64_t* bar, const CUtensorMap* tm_k, const CUtensorMap* tm_v,
-                                            int unit, int tiles, int heads, int S) {
-  const int item = unit / tiles, t = unit - item * tiles;
+                                            int item, int t, int heads, int S) {
   // token-major: the head is a 256-byte column window of row b * S + s; head-major (heads == 0 here): row item * S + s
   int x = 0, y = item * S + t * XT;
   if (heads > 0) {
@@ -354,123 +354,78 @@ __device__ __forceinline__ void xattn_issue(uint8_t* buf, uint64_t* bar, const C
 }
 
 template <int NB>  // beams rounded up to 1, 2, 4 or 8
-__global__ void __launch_bounds__(32 * XWARPS) attn_cross_kernel(const __grid_constant__ CUtensorMap tm_k,
-                                                                 const __grid_constant__ CUtensorMap tm_v,
-                                                                 const ls100_attn_cross_args a, const float s_out,
-                                                                 const float rs_out, int* err) {
+__global__ void __launch_bounds__(32 * XWARPS, NB <= 4 ? XCTAS_PER_SM : 3)
+attn_cross_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                  const ls100_attn_cross_args a, const float s_out, const float rs_out, int* err) {
   extern __shared__ uint8_t xs_raw[];
   uint8_t* xs = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(xs_raw) + 1023) & ~(uintptr_t)1023);
-  float* qs = reinterpret_cast<float*>(xs + 2 * XTILE);  // [NB][XQ]
+  float* qs = reinterpret_cast<float*>(xs + XTILE);      // [NB][XQ]
   float* ps = qs + NB * XQ;                               // [XWARPS][NB][16]
-  float* mg = ps + XWARPS * NB * 16;                      // [XWARPS][NB][DH + 2]
-  uint64_t* bar = reinterpret_cast<uint64_t*>(mg + XWARPS * NB * (DH + 2));  // [2]
+  float* mg = reinterpret_cast<float*>(xs);               // [XWARPS][NB][DH + 2]: the tile buffer, once the tiles are done
+  uint64_t* bar = reinterpret_cast<uint64_t*>(ps + XWARPS * NB * 16);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int key = lane & 15, hf = lane >> 4;
   const int S = a.src_len;
   const int tiles = (S + XT - 1) / XT;
-  const int items = a.batch * a.heads;
   const int tm_heads = a.kv_head_major ? 0 : a.heads;
-  // this CTA's units: (item, tile) for item = blockIdx.x, blockIdx.x + gridDim.x, ...
-  const int my_items = (items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-  const int my_units = my_items * tiles;
-  auto unit_global = [&](int u) {  // my u-th unit -> flat (item * tiles + tile)
-    const int it = u / tiles;
-    return ((int)blockIdx.x + it * (int)gridDim.x) * tiles + (u - it * tiles);
-  };
+  const int item = blockIdx.x;
+  const int b = item / a.heads, h = item - b * a.heads;
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
-    mbar_init(&bar[0], 1);
-    mbar_init(&bar[1], 1);
+    mbar_init(bar, 1);
     fence_barrier_init();
-    if (a.kv_static) {
-      if (my_units > 0) xattn_issue(xs, &bar[0], &tm_k, &tm_v, unit_global(0), tiles, tm_heads, S);
-      if (my_units > 1) xattn_issue(xs + XTILE, &bar[1], &tm_k, &tm_v, unit_global(1), tiles, tm_heads, S);
-    }
+    if (a.kv_static) xattn_issue(xs, bar, &tm_k, &tm_v, item, 0, tm_heads, S);
   }
   LS100_TRACE(0);
   pdl_wait();
   LS100_TRACE(1);
-  if (threadIdx.x == 0 && !a.kv_static) {
-    if (my_units > 0) xattn_issue(xs, &bar[0], &tm_k, &tm_v, unit_global(0), tiles, tm_heads, S);
-    if (my_units > 1) xattn_issue(xs + XTILE, &bar[1], &tm_k, &tm_v, unit_global(1), tiles, tm_heads, S);
-  }
-  __syncthreads();  // barrier initialisation visible to every waiter
-
-  // q of a pair, fetched one pair ahead as RAW values (the int8 pair and the bias pair): the conversion happens
-  // when the values are stored to shared memory, so that no instruction waits for these loads before then.
-  // Warp w serves beams w and w + 4.
-  short qraw[2] = {0, 0};
-  float2 qbias[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-  auto load_q = [&](int item) {
-    const int b = item / a.heads, h = item - b * a.heads;
+  if (threadIdx.x == 0 && !a.kv_static) xattn_issue(xs, bar, &tm_k, &tm_v, item, 0, tm_heads, S);
+  // q of this (sentence, head): warp w converts beams w and w + 4 (dims 2*lane, 2*lane+1 live in half (lane >> 4))
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int bm = warp + i * XWARPS;
-      if (bm < NB && bm < a.beam) {
-        qraw[i] = *reinterpret_cast<const short*>(a.q + (long long)(b * a.beam + bm) * a.ld_q + h * DH + lane * 2);
-        if (a.bias) qbias[i] = __ldg(reinterpret_cast<const float2*>(a.bias + h * DH + lane * 2));
+  for (int i = 0; i < 2; ++i) {
+    const int bm = warp + i * XWARPS;
+    if (bm < NB) {
+      float q0 = 0.f, q1 = 0.f;
+      if (bm < a.beam) {
+        const short qraw = *reinterpret_cast<const short*>(a.q + (long long)(b * a.beam + bm) * a.ld_q + h * DH + lane * 2);
+        float2 qb = make_float2(0.f, 0.f);
+        if (a.bias) qb = __ldg(reinterpret_cast<const float2*>(a.bias + h * DH + lane * 2));
+        q0 = __fadd_rn(__fmul_rn((float)(int8_t)(qraw & 0xff), a.s_q), qb.x);
+        q1 = __fadd_rn(__fmul_rn((float)(int8_t)((qraw >> 8) & 0xff), a.s_q), qb.y);
       }
+      float* qd = qs + bm * XQ + (lane >> 4) * 36 + ((lane * 2) & 31);
+      qd[0] = __fmul_rn(q0, 0.125f);
+      qd[1] = __fmul_rn(q1, 0.125f);
     }
-  };
-  // pad-mask byte of this lane's key, likewise fetched one unit ahead
-  auto load_pad = [&](int u) -> int {
-    if (!a.pad_mask || u >= my_units) return 0;
-    const int it = u / tiles, t = u - it * tiles;
-    const int item = (int)blockIdx.x + it * (int)gridDim.x;
-    const int k = t * XT + warp * 16 + key;
-    return k < S ? (int)a.pad_mask[(long long)(item / a.heads) * S + k] : 1;
-  };
-  if (my_items > 0) load_q(blockIdx.x);
-  int pad_next = load_pad(0);
+  }
+  __syncthreads();  // q and the barrier initialisation visible to every warp
 
   float m[NB], l[NB], acc[NB][2];
+#pragma unroll
+  for (int bm = 0; bm < NB; ++bm) {
+    m[bm] = -INFINITY;
+    l[bm] = 0.f;
+    acc[bm][0] = 0.f;
+    acc[bm][1] = 0.f;
+  }
   bool dead = false;  // a copy never landed: keep meeting the CTA barriers, do no work
-  for (int u = 0; u < my_units; ++u) {
-    const int it = u / tiles, t = u - it * tiles;
-    const int item = (int)blockIdx.x + it * (int)gridDim.x;
-    const int b = item / a.heads, h = item - b * a.heads;
+  for (int t = 0; t < tiles; ++t) {
     const int t0 = t * XT + warp * 16;       // first key of this warp in the tile
     const int ns = max(0, min(16, S - t0));  // its keys that exist
-    const uint8_t* buf = xs + (u & 1) * XTILE;
-    if (t == 0) {
-      if (u > 0) __syncthreads();  // every warp has finished with the previous pair's q and merge area
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int bm = warp + i * XWARPS;
-        if (bm < NB) {  // dims 2*lane, 2*lane+1 live in half (lane >> 4)
-          float q0 = 0.f, q1 = 0.f;
-          if (bm < a.beam) {
-            q0 = __fadd_rn(__fmul_rn((float)(int8_t)(qraw[i] & 0xff), a.s_q), qbias[i].x);
-            q1 = __fadd_rn(__fmul_rn((float)(int8_t)((qraw[i] >> 8) & 0xff), a.s_q), qbias[i].y);
-          }
-          float* qd = qs + bm * XQ + (lane >> 4) * 36 + ((lane * 2) & 31);
-          qd[0] = __fmul_rn(q0, 0.125f);
-          qd[1] = __fmul_rn(q1, 0.125f);
-        }
-      }
-      if (it + 1 < my_items) load_q(item + (int)gridDim.x);
-      __syncthreads();
-#pragma unroll
-      for (int bm = 0; bm < NB; ++bm) {
-        m[bm] = -INFINITY;
-        l[bm] = 0.f;
-        acc[bm][0] = 0.f;
-        acc[bm][1] = 0.f;
-      }
-    }
-    LS100_TRACE(2 + 5 * (u < 2 ? u : 2));
+    const int kpos = t0 + key;
+    const int pad_now = (a.pad_mask && kpos < S) ? (int)a.pad_mask[(long long)b * S + kpos] : (kpos < S ? 0 : 1);
+    LS100_TRACE(2);
     if (!dead) {
-      const bool ok = mbar_wait(&bar[u & 1], (uint32_t)(u >> 1) & 1u);
+      const bool ok = mbar_wait(bar, (uint32_t)t & 1u);
       if (!__all_sync(0xffffffffu, ok)) {
         if (lane == 0) atomicExch(err, (int)LS100_ERR_TIMEOUT);
         dead = true;
       }
     }
-    LS100_TRACE(3 + 5 * (u < 2 ? u : 2));
-    const int pad_now = pad_next;
-    pad_next = load_pad(u + 1);
+    LS100_TRACE(3);
+    const uint8_t* buf = xs;
     if (!dead && ns > 0) {
       const int j = warp * 16 + key;  // row of the tile
       const bool valid = key < ns && !pad_now;
@@ -532,7 +487,7 @@ __global__ void __launch_bounds__(32 * XWARPS) attn_cross_kernel(const __grid_co
         if (hf == 0) pr[bm * 16 + key] = ex[bm];
       }
       __syncwarp();
-      LS100_TRACE(4 + 5 * (u < 2 ? u : 2));
+      LS100_TRACE(4);
       if (any) {  // otherwise all of this warp's keys are masked (uniform across the warp)
         // dims 2*lane, 2*lane+1: half (lane >> 4), 16-byte chunk ((lane & 15) >> 1), 8-byte offset (lane & 1)
         const uint8_t* vb = buf + (2 + (lane >> 4)) * XHALF + (lane & 1) * 8 + warp * 16 * 128;
@@ -545,66 +500,65 @@ __global__ void __launch_bounds__(32 * XWARPS) attn_cross_kernel(const __grid_co
 #pragma unroll
           for (int bm = 0; bm < NB; ++bm) {
             const float4 w4 = *reinterpret_cast<const float4*>(pr + bm * 16 + jj);
-            float2 t = make_float2(acc[bm][0], acc[bm][1]);  // the two head dims of this lane as one packed pair
-            t = f2_fma(f2_set(w4.x), v[0], t);
-            t = f2_fma(f2_set(w4.y), v[1], t);
-            t = f2_fma(f2_set(w4.z), v[2], t);
-            t = f2_fma(f2_set(w4.w), v[3], t);
-            acc[bm][0] = t.x;
-            acc[bm][1] = t.y;
+            float2 tt = make_float2(acc[bm][0], acc[bm][1]);  // the two head dims of this lane as one packed pair
+            tt = f2_fma(f2_set(w4.x), v[0], tt);
+            tt = f2_fma(f2_set(w4.y), v[1], tt);
+            tt = f2_fma(f2_set(w4.z), v[2], tt);
+            tt = f2_fma(f2_set(w4.w), v[3], tt);
+            acc[bm][0] = tt.x;
+            acc[bm][1] = tt.y;
           }
         }
       }
       __syncwarp();
     }
-    LS100_TRACE(5 + 5 * (u < 2 ? u : 2));
-    if (t == tiles - 1) {  // merge the four key groups of each beam and write the rows
-#pragma unroll
-      for (int bm = 0; bm < NB; ++bm) {
-        float* mp = mg + (warp * NB + bm) * (DH + 2);
-        mp[lane * 2] = acc[bm][0];
-        mp[lane * 2 + 1] = acc[bm][1];
-        if (lane == 0) {
-          mp[DH] = m[bm];
-          mp[DH + 1] = l[bm];
-        }
-      }
+    LS100_TRACE(5);
+    if (t + 1 < tiles) {  // the next tile of a long source goes into the same buffer once every warp has finished with it
       __syncthreads();
-      for (int bm = warp; bm < a.beam; bm += XWARPS) {
-        if (dead) break;
-        float mm = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < XWARPS; ++w) mm = fmaxf(mm, mg[(w * NB + bm) * (DH + 2) + DH]);
-        float lt = 0.f, o0 = 0.f, o1 = 0.f;
-        if (mm != -INFINITY) {
-#pragma unroll
-          for (int w = 0; w < XWARPS; ++w) {
-            const float* mp = mg + (w * NB + bm) * (DH + 2);
-            const float f = (mp[DH] == -INFINITY) ? 0.f : __expf(mp[DH] - mm);
-            lt = fmaf(mp[DH + 1], f, lt);
-            o0 = fmaf(mp[lane * 2], f, o0);
-            o1 = fmaf(mp[lane * 2 + 1], f, o1);
-          }
-        }
-        const float inv = lt > 0.f ? 1.f / lt : 0.f;
-        const uint32_t pk = pack_i8x4(quant_s(clipf(o0 * inv, a.amax_out), s_out, rs_out),
-                                      quant_s(clipf(o1 * inv, a.amax_out), s_out, rs_out), 0.f, 0.f);
-        *reinterpret_cast<unsigned short*>(a.out + (long long)(b * a.beam + bm) * a.ld_out + h * DH + lane * 2) =
-            (unsigned short)(pk & 0xffff);
-      }
-    }
-    LS100_TRACE(6 + 5 * (u < 2 ? u : 2));
-    if (u + 2 < my_units) {  // refill this buffer once every warp has finished with it
-      __syncthreads();
-      if (threadIdx.x == 0)
-        xattn_issue(xs + (u & 1) * XTILE, &bar[u & 1], &tm_k, &tm_v, unit_global(u + 2), tiles, tm_heads, S);
+      if (threadIdx.x == 0) xattn_issue(xs, bar, &tm_k, &tm_v, item, t + 1, tm_heads, S);
     }
   }
+  // merge the four key groups of each beam and write the rows
+  __syncthreads();  // every warp has finished reading the last tile: its buffer becomes the merge area
+#pragma unroll
+  for (int bm = 0; bm < NB; ++bm) {
+    float* mp = mg + (warp * NB + bm) * (DH + 2);
+    mp[lane * 2] = acc[bm][0];
+    mp[lane * 2 + 1] = acc[bm][1];
+    if (lane == 0) {
+      mp[DH] = m[bm];
+      mp[DH + 1] = l[bm];
+    }
+  }
+  __syncthreads();
+  for (int bm = warp; bm < a.beam; bm += XWARPS) {
+    if (dead) break;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < XWARPS; ++w) mm = fmaxf(mm, mg[(w * NB + bm) * (DH + 2) + DH]);
+    float lt = 0.f, o0 = 0.f, o1 = 0.f;
+    if (mm != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < XWARPS; ++w) {
+        const float* mp = mg + (w * NB + bm) * (DH + 2);
+        const float f = (mp[DH] == -INFINITY) ? 0.f : __expf(mp[DH] - mm);
+        lt = fmaf(mp[DH + 1], f, lt);
+        o0 = fmaf(mp[lane * 2], f, o0);
+        o1 = fmaf(mp[lane * 2 + 1], f, o1);
+      }
+    }
+    const float inv = lt > 0.f ? 1.f / lt : 0.f;
+    const uint32_t pk = pack_i8x4(quant_s(clipf(o0 * inv, a.amax_out), s_out, rs_out),
+                                  quant_s(clipf(o1 * inv, a.amax_out), s_out, rs_out), 0.f, 0.f);
+    *reinterpret_cast<unsigned short*>(a.out + (long long)(b * a.beam + bm) * a.ld_out + h * DH + lane * 2) =
+        (unsigned short)(pk & 0xffff);
+  }
+  LS100_TRACE(6);
 }
 
-// two tiles + q, probabilities and merge area + two barriers + slack to align the tiles to the swizzle period
+// one tile (reused as the merge area) + q and probabilities + the barrier + slack to align the tile to the swizzle period
 static size_t attn_cross_smem(int nb) {
-  return 2 * XTILE + (size_t)(nb * XQ + XWARPS * nb * 16 + XWARPS * nb * (DH + 2)) * sizeof(float) + 16 + 1024;
+  return XTILE + (size_t)(nb * XQ + XWARPS * nb * 16) * sizeof(float) + 16 + 1024;
 }
 
 }  // namespace ls100
@@ -682,9 +636,8 @@ extern "C" int ls100_attn_cross(ls100_ctx* ctx, const ls100_attn_cross_args* a, 
   rc = ls100_get_tmap_u8(ctx, a->v, rows, cols, pitch, XT, 128, &tv);
   if (rc) return rc;
   const long long items = (long long)a->batch * a->heads;
-  if (items * ((a->src_len + XT - 1) / XT) > 0x3fffffffLL) return LS100_ERR_UNSUPPORTED;
-  const long long slots = (long long)XCTAS_PER_SM * ctx->sm_count;
-  dim3 grid((unsigned)(items < slots ? items : slots));
+  if (items > 0x7fffffffLL) return LS100_ERR_UNSUPPORTED;
+  dim3 grid((unsigned)items);
   const float so = a->amax_out / 127.0f;
   const cudaStream_t st = (cudaStream_t)stream_;
   const dim3 block(32 * XWARPS);
