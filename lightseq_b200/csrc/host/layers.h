@@ -160,10 +160,9 @@ class QuantTransformerDecoderLayer : public Layer {
                                int max_batch_tokens, int max_seq_len, int hidden, int heads, int ffn, bool is_pre_ln,
                                const std::string& activation_fn, int max_batch_size, int beam_size, int max_step)
       : Layer(prefix, ctx), hidden_(hidden), heads_(heads), ffn_(ffn), act_(activation_fn == "gelu" ? Act::Gelu : Act::Relu),
-        max_rows_(max_batch_size * beam_size), max_step_(max_step), max_enc_tokens_(max_batch_tokens) {
+        max_rows_(max_batch_size * beam_size), max_step_(max_step), max_enc_tokens_(max_batch_tokens), pre_ln_(is_pre_ln) {
     (void)layer_id;
     (void)max_seq_len;
-    if (!is_pre_ln) throw std::runtime_error("post-LN decoder layers are not supported");
     const bool relu = act_ == Act::Relu;
     qkv_.load(*ctx, wf, prefix + ".qkv", false);
     out_.load(*ctx, wf, prefix + ".out", false);
@@ -247,9 +246,17 @@ class QuantTransformerDecoderLayer : public Layer {
       LS_RC(ls100_i8_to_bf16(ctx_->kernels(), p.w, p.k, hidden_, hidden_, w_bf16_[which], ctx_->get_stream()));
     }
   }
+  // Post-LN layers hand their output to the next consumer already quantised with that consumer's input clip-max
+  // (the next layer's QKV projection, or the output projection after the last layer).
+  void set_next_input_amax(float amax) { next_amax_ = amax; }
+  float qkv_input_amax() const { return qkv_.amax_in; }
+
   void forward() override {
     const int rows = batch_ * beam_;
-    ln_quant(rows, ln1_, qkv_.amax_in, embed_src_);
+    // pre-LN: LayerNorm opens every sublayer. Post-LN (torch_transformer_layers.py:844-965 with normalize_before
+    // false): x is the previous LayerNorm's output and a_q its int8 form; LayerNorm closes every sublayer, writing the
+    // residual stream in place and the int8 input of the next GEMM.
+    if (pre_ln_) ln_quant(rows, ln1_, qkv_.amax_in, embed_src_);
     // qkv = attention_quant(fq_out(acc) + bias): int8 with the KV-cache clip-max
     gemm(b_->a_q, qkv_, rows, LS100_OUT_REQ_S8, b_->qkv_q, Act::None, nullptr, s_kv_);
     {
@@ -271,7 +278,8 @@ class QuantTransformerDecoderLayer : public Layer {
       LS_RC(ls100_attn_dec(ctx_->kernels(), &a, ctx_->get_stream()));
     }
     gemm(b_->attn_q, out_, rows, LS100_OUT_F32, b_->x, Act::None, b_->x, 0.f);
-    ln_quant(rows, ln2_, xq_.amax_in);
+    if (pre_ln_) ln_quant(rows, ln2_, xq_.amax_in);
+    else ln_quant(rows, ln1_, xq_.amax_in, nullptr, true);
     gemm(b_->a_q, xq_, rows, LS100_OUT_OUTQ_I8, b_->q_q, Act::None, nullptr, 0.f, false);
     {
       ls100_attn_cross_args a;
@@ -296,13 +304,16 @@ class QuantTransformerDecoderLayer : public Layer {
       LS_RC(ls100_attn_cross(ctx_->kernels(), &a, ctx_->get_stream()));
     }
     gemm(b_->attn_q, xout_, rows, LS100_OUT_F32, b_->x, Act::None, b_->x, 0.f);
-    ln_quant(rows, ln3_, fc1_.amax_in);
+    if (pre_ln_) ln_quant(rows, ln3_, fc1_.amax_in);
+    else ln_quant(rows, ln2_, fc1_.amax_in, nullptr, true);
     gemm(b_->a_q, fc1_, rows, act_ == Act::Relu ? LS100_OUT_REQ_U8 : LS100_OUT_REQ_S8, b_->h_q, act_, nullptr, fc2_.s_in);
     gemm(b_->h_q, fc2_, rows, LS100_OUT_F32, b_->x, Act::None, b_->x, 0.f);
+    if (!pre_ln_) ln_quant(rows, ln3_, next_amax_, nullptr, true);
   }
 
  private:
-  void ln_quant(int rows, const LayerNormParams& ln, float amax, const ls100_embed_args* lookup = nullptr) {
+  // write_f: also write the fp32 LayerNorm output over the residual stream (post-LN; a row is read before it is written)
+  void ln_quant(int rows, const LayerNormParams& ln, float amax, const ls100_embed_args* lookup = nullptr, bool write_f = false) {
     ls100_ln_quant_args a;
     memset(&a, 0, sizeof(a));
     a.x = b_->x->value<float>();
@@ -314,6 +325,10 @@ class QuantTransformerDecoderLayer : public Layer {
     a.amax = amax;
     a.out_q = b_->a_q->value<int8_t>();
     a.ldq = hidden_;
+    if (write_f) {
+      a.out_f = b_->x->value<float>();
+      a.ldf = hidden_;
+    }
     if (lookup) a.emb = *lookup;  // the rows come from the embedding lookup of this decode step, in the same launch
     LS_RC(ls100_ln_quant(ctx_->kernels(), &a, ctx_->get_stream()));
   }
@@ -327,6 +342,8 @@ class QuantTransformerDecoderLayer : public Layer {
   int hidden_, heads_, ffn_;
   Act act_;
   int max_rows_, max_step_, max_enc_tokens_;
+  bool pre_ln_ = true;
+  float next_amax_ = 0.f;
   QLinearParams qkv_, out_, xq_, xk_, xv_, xout_, fc1_, fc2_;
   LayerNormParams ln1_, ln2_, ln3_;
   float amax_kv_ = 0, s_kv_ = 0;

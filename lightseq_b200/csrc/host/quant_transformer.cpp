@@ -78,6 +78,13 @@ class QuantTransformer : public EngineModel {
                                                                 max_step_, H_, heads_, F_, pre_ln, act, max_bs_, beam_,
                                                                 max_step_));
     dec_ln_.load(c, wf, "dec.ln", H_);
+    pre_ln_ = pre_ln;
+    if (!pre_ln_) {  // post-LN: every layer's closing LayerNorm quantises for the next consumer; no final LayerNorms
+      for (int l = 0; l < n_enc_; ++l)
+        enc_layers_[l]->set_next_input_amax(l + 1 < n_enc_ ? enc_layers_[l + 1]->qkv().amax_in : 0.f);
+      for (int l = 0; l < n_dec_; ++l)
+        dec_layers_[l]->set_next_input_amax(l + 1 < n_dec_ ? dec_layers_[l + 1]->qkv_input_amax() : emb_.amax_in);
+    }
     if (H_ % 64 == 0 && getenv("LS100_PROJ_SIMT") == nullptr) {  // cross K/V projection on the tensor cores
       enc_x3_ = c.alloc((size_t)max_enc_tokens * 3 * H_ * 2);
       for (auto& l : dec_layers_) l->prepare_tensor_core_projection();
@@ -305,11 +312,19 @@ class QuantTransformer : public EngineModel {
     LS_RC(ls100_embed(ctx_->kernels(), &e, ctx_->get_stream()));
     tap_reset();
     tap(enc_.x->value<float>(), (size_t)B * S * H_, ctx_->get_stream());
+    if (!pre_ln_ && !enc_layers_.empty())  // post-LN: the first layer reads the embedding already quantised
+      LS_RC(ls100_quantize_weight(ctx_->kernels(), enc_.x->value<float>(), (int64_t)B * S, H_, enc_layers_[0]->qkv().amax_in,
+                                  enc_.a_q->value<int8_t>(), nullptr, ctx_->get_stream()));
     for (auto& l : enc_layers_) {
       (*l)(&enc_, pad_mask_);
       l->before_forward(B, S);
       l->forward();
       tap(enc_.x->value<float>(), (size_t)B * S * H_, ctx_->get_stream());
+    }
+    if (!pre_ln_) {  // the last layer's own LayerNorm closed the stack
+      LS_CUDA(cudaMemcpyAsync(enc_out_->value<float>(), enc_.x->value<float>(), (size_t)B * S * H_ * 4, cudaMemcpyDeviceToDevice,
+                              ctx_->get_stream()));
+      return;
     }
     ls100_ln_quant_args a;
     memset(&a, 0, sizeof(a));
@@ -346,8 +361,11 @@ class QuantTransformer : public EngineModel {
     e.out = dec_.x->value<float>();
     // the lookup runs inside the first layer's LayerNorm launch (one kernel less per step) unless switched off
     static const bool separate_embed = getenv("LS100_NO_EMBED_FUSE") != nullptr;
-    const bool fused = !separate_embed && rows <= 2048 && !dec_layers_.empty();
+    const bool fused = pre_ln_ && !separate_embed && rows <= 2048 && !dec_layers_.empty();
     if (!fused) LS_RC(ls100_embed(k, &e, st));
+    if (!pre_ln_ && !dec_layers_.empty())  // post-LN: the first layer reads the embedding already quantised
+      LS_RC(ls100_quantize_weight(k, dec_.x->value<float>(), rows, H_, dec_layers_[0]->qkv_input_amax(), dec_.a_q->value<int8_t>(),
+                                  nullptr, st));
     if (!dec_layers_.empty()) dec_layers_[0]->set_embed_source(fused ? &e : nullptr);
     for (auto& l : dec_layers_) {
       (*l)(&dec_, pad_mask_, anc_, step_ptr_);
@@ -355,18 +373,20 @@ class QuantTransformer : public EngineModel {
       l->forward();
     }
     if (!dec_layers_.empty()) dec_layers_[0]->set_embed_source(nullptr);  // `e` goes out of scope with this call
-    ls100_ln_quant_args a;
-    memset(&a, 0, sizeof(a));
-    a.x = dec_.x->value<float>();
-    a.ldx = H_;
-    a.gamma = dec_ln_.g;
-    a.beta = dec_ln_.b;
-    a.rows = rows;
-    a.hidden = H_;
-    a.amax = emb_.amax_in;
-    a.out_q = dec_.a_q->value<int8_t>();
-    a.ldq = H_;
-    LS_RC(ls100_ln_quant(k, &a, st));
+    if (pre_ln_) {  // post-LN: the last layer's closing LayerNorm already wrote the int8 input of the output projection
+      ls100_ln_quant_args a;
+      memset(&a, 0, sizeof(a));
+      a.x = dec_.x->value<float>();
+      a.ldx = H_;
+      a.gamma = dec_ln_.g;
+      a.beta = dec_ln_.b;
+      a.rows = rows;
+      a.hidden = H_;
+      a.amax = emb_.amax_in;
+      a.out_q = dec_.a_q->value<int8_t>();
+      a.ldq = H_;
+      LS_RC(ls100_ln_quant(k, &a, st));
+    }
     QuantLinearOp logits(ctx_, "logits", &emb_, LS100_OUT_OUTQ_I8, Act::None, true, false);
     logits(dec_.a_q, logits_q_);
     logits.before_forward(rows, ldv_);
@@ -506,7 +526,7 @@ class QuantTransformer : public EngineModel {
   int sampling_ = 0, topk_ = 1;
   float topp_ = 0.f;
   uint32_t seed_lo_ = 0;
-  bool output_topk_ = false, no_scale_embedding_ = false;
+  bool output_topk_ = false, no_scale_embedding_ = false, pre_ln_ = true;
   std::vector<int32_t> h_anc_;
   float *seq_probs_ = nullptr, *seq_score_ = nullptr, *cand_score_ = nullptr, *length_norm_ = nullptr;
   std::vector<int32_t> h_alive_, h_counters_;

@@ -234,8 +234,6 @@ def read_quant_transformer(path: str):
             t[f"dec.{i}.{nm}.w"] = np.ascontiguousarray(_dequant(kv_u[:, i, j, :], float(kv_c[i])).T)
             t[f"dec.{i}.{nm}.b"] = kv_b[i, j].copy()
             amax[f"dec.{i}.{nm}.w"] = float(kv_c[i])
-    if _int(mc, 12) != 0:
-        raise ValueError("post-LN encoder-decoder models are not supported by the engine")
     if _int(mc, 15) != 0:
         raise ValueError("multilingual models are not supported by the engine")
     # fields that change the reference's output and that the engine does not implement are refused, not dropped
@@ -256,7 +254,7 @@ def read_quant_transformer(path: str):
     # QuantTransformer of the reference returns every beam (its decoder is built with output_topk = true,
     # lightseq/inference/pywrapper/quant_transformer.cc:60-62): files in its format keep that behaviour
     conf = dict(hidden=H, heads=_int(mc, 1), ffn=dims.get("ffn", 0), n_enc=len(enc_layers), n_dec=n_dec, vocab=V,
-                act_gelu=float(_int(mc, 14)), pre_ln=1.0, beam=_int(mc, 2), length_penalty=_float(mc, 4),
+                act_gelu=float(_int(mc, 14)), pre_ln=float(not _int(mc, 12)), beam=_int(mc, 2), length_penalty=_float(mc, 4),
                 extra_decode_length=_int(mc, 3), max_step=max_step, pad_id=_int(mc, 5), start_id=_int(mc, 6), end_id=_int(mc, 11),
                 sampling_method=float(methods.index(method)), topk=float(max(_int(mc, 10), 1)), topp=_float(mc, 9),
                 output_topk=1.0, no_scale_embedding=float(_int(mc, 13)))
@@ -285,8 +283,6 @@ def write_quant_transformer(path: str, conf, amax, t) -> None:
     per decoder layer for both cross-attention projections: dec.i.xk.w and dec.i.xv.w must share theirs."""
     H, V = int(conf["hidden"]), int(conf["vocab"])
     n_enc, n_dec = int(conf["n_enc"]), int(conf["n_dec"])
-    if not int(conf.get("pre_ln", 1)):
-        raise ValueError("post-LN encoder-decoder models are not supported")
     emb_u = _quant_engine(t["emb"], amax["emb"])  # [V, H]
     pos = np.asarray(t["pos"], F32)
     src = (_enc_bytes(1, emb_u.tobytes()) + _enc_floats(2, pos) + _enc_floats(3, t["enc.ln.g"]) + _enc_floats(4, t["enc.ln.b"]) +
@@ -310,7 +306,7 @@ def write_quant_transformer(path: str, conf, amax, t) -> None:
     mc = (_enc_int(1, conf["heads"]) + _enc_int(2, conf["beam"]) + _enc_int(3, conf["extra_decode_length"]) +
           _enc_float(4, conf["length_penalty"]) + _enc_int(5, conf["pad_id"]) + _enc_int(6, conf["start_id"]) +
           _tag(8, 2) + _varint(len(method)) + method + _enc_float(9, conf.get("topp", 0.0)) + _enc_int(10, int(conf.get("topk", 1))) +
-          _enc_int(11, conf["end_id"]) + _enc_int(13, 1 if conf.get("no_scale_embedding") else 0) +
+          _enc_int(11, conf["end_id"]) + _enc_int(12, 0 if int(conf.get("pre_ln", 1)) else 1) + _enc_int(13, 1 if conf.get("no_scale_embedding") else 0) +
           _enc_int(14, 1 if conf.get("act_gelu") else 0))
     out = bytearray()
     out += _tag(1, 2) + _varint(len(src)) + src

@@ -160,7 +160,8 @@ SAMPLING_METHODS = ("beam_search", "topk", "topp", "topk_greedy")  # the code st
 
 def calibrate_transformer(w: Dict[str, np.ndarray], src: np.ndarray, *, heads: int, n_enc: int, n_dec: int,
                           act: str = "relu", pad_id: int = 1, seed: int = 99, k: float = 4.0,
-                          ln_offsets: Optional[Dict[str, float]] = None, no_scale_embedding: bool = False) -> Dict[str, float]:
+                          ln_offsets: Optional[Dict[str, float]] = None, no_scale_embedding: bool = False,
+                          pre_ln: bool = True) -> Dict[str, float]:
     """Clip-max table = k x std, from one fp32 pass: encoder on ``src``; decoder teacher-forced
     on random target ids of the source lengths (causal self-attention). ``ln_offsets``, when given, receives the
     average mean/std ratio of the inputs of the encoder's final LayerNorm and of every decoder ``ln2``."""
@@ -187,16 +188,21 @@ def calibrate_transformer(w: Dict[str, np.ndarray], src: np.ndarray, *, heads: i
 
     pad = src == pad_id
     x = emb(src)
+    ln = lambda t, name: _ln(t, w[name + ".g"], w[name + ".b"])  # noqa: E731
     for l in range(n_enc):
         p = f"enc.{l}"
-        qkv = lin(p + ".qkv", _ln(x, w[p + ".ln1.g"], w[p + ".ln1.b"]))
+        qkv = lin(p + ".qkv", ln(x, p + ".ln1") if pre_ln else x)
         a = _attn(qkv[..., :H], qkv[..., H:2 * H], qkv[..., 2 * H:], heads, pad[:, None, None, :])
         x = x + lin(p + ".out", a)
-        h = _act(lin(p + ".fc1", _ln(x, w[p + ".ln2.g"], w[p + ".ln2.b"])), act)
+        if not pre_ln:
+            x = ln(x, p + ".ln1")
+        h = _act(lin(p + ".fc1", ln(x, p + ".ln2") if pre_ln else x), act)
         x = x + lin(p + ".fc2", h)
+        if not pre_ln:
+            x = ln(x, p + ".ln2")
     if ln_offsets is not None:
         ln_offsets["enc.ln"] = _ln_offset(x, ~pad)
-    enc = _ln(x, w["enc.ln.g"], w["enc.ln.b"])
+    enc = _ln(x, w["enc.ln.g"], w["enc.ln.b"]) if pre_ln else x
 
     lens = (~pad).sum(1)
     tgt = np.full((B, S), pad_id, dtype=np.int64)
@@ -207,20 +213,35 @@ def calibrate_transformer(w: Dict[str, np.ndarray], src: np.ndarray, *, heads: i
     x = emb(tgt)
     for l in range(n_dec):
         p = f"dec.{l}"
-        qkv = lin(p + ".qkv", _ln(x, w[p + ".ln1.g"], w[p + ".ln1.b"]))
+        qkv = lin(p + ".qkv", ln(x, p + ".ln1") if pre_ln else x)
         st.see(p + ".kv", qkv)
         a = _attn(qkv[..., :H], qkv[..., H:2 * H], qkv[..., 2 * H:], heads,
                   causal[None, None] | tpad[:, None, None, :])
         x = x + lin(p + ".out", a)
+        if not pre_ln:
+            x = ln(x, p + ".ln1")
         if ln_offsets is not None:
             ln_offsets[p + ".ln2"] = _ln_offset(x, ~tpad)
-        q = lin(p + ".xq", _ln(x, w[p + ".ln2.g"], w[p + ".ln2.b"]))
+        q = lin(p + ".xq", ln(x, p + ".ln2") if pre_ln else x)
         kx = lin(p + ".xk", enc, False, False)
         vx = lin(p + ".xv", enc, False, False)
         a = _attn(q, kx, vx, heads, pad[:, None, None, :])
         x = x + lin(p + ".xout", a)
-        h = _act(lin(p + ".fc1", _ln(x, w[p + ".ln3.g"], w[p + ".ln3.b"])), act)
+        if not pre_ln:
+            x = ln(x, p + ".ln2")
+        h = _act(lin(p + ".fc1", ln(x, p + ".ln3") if pre_ln else x), act)
         x = x + lin(p + ".fc2", h)
+        if not pre_ln:
+            x = ln(x, p + ".ln3")
+    if not pre_ln:
+        st.see("logits.in", x)
+        st.see("logits.out", x[:, : min(S, 8)] @ w["emb"].T)
+        amax = st.amax(k)
+        for name, t in w.items():
+            if name.endswith(".w") and t.ndim == 2:
+                amax[name] = float(F32(k * t.std()))
+        amax["emb"] = float(F32(k * w["emb"].std()))
+        return amax
     x = _ln(x, w["dec.ln.g"], w["dec.ln.b"])
     st.see("logits.in", x)
     st.see("logits.out", x[:, : min(S, 8)] @ w["emb"].T)
@@ -236,7 +257,7 @@ def make_transformer(path: Optional[str] = None, *, hidden=512, heads=8, ffn=204
                      act="relu", beam=4, length_penalty=0.6, extra_decode_length=50, max_step=256, pad_id=1,
                      start_id=3, end_id=2, seed=1234, calib_src: Optional[np.ndarray] = None,
                      sampling_method: str = "beam_search", topk: int = 1, topp: float = 0.0, output_topk: bool = False,
-                     no_scale_embedding: bool = False, rng_seed: int = 0
+                     no_scale_embedding: bool = False, rng_seed: int = 0, pre_ln: bool = True
                      ) -> Tuple[Dict[str, float], Dict[str, float], Dict[str, np.ndarray]]:
     """Builds (conf, amax, tensors) of a seeded synthetic QuantTransformer and optionally writes ``path``. The
     generator options are those of the reference's model configuration (sampling_method, topk, topp; every beam in
@@ -245,9 +266,9 @@ def make_transformer(path: Optional[str] = None, *, hidden=512, heads=8, ffn=204
     if calib_src is None:
         calib_src = transformer_inputs(batch=8, min_len=8, max_len=24, vocab=vocab, pad_id=pad_id, seed=seed + 1)
     amax = calibrate_transformer(w, calib_src, heads=heads, n_enc=n_enc, n_dec=n_dec, act=act, pad_id=pad_id,
-                                 no_scale_embedding=no_scale_embedding)
+                                 no_scale_embedding=no_scale_embedding, pre_ln=pre_ln)
     conf = dict(hidden=hidden, heads=heads, ffn=ffn, n_enc=n_enc, n_dec=n_dec, vocab=vocab,
-                act_gelu=float(act == "gelu"), pre_ln=1.0, beam=beam, length_penalty=length_penalty,
+                act_gelu=float(act == "gelu"), pre_ln=float(pre_ln), beam=beam, length_penalty=length_penalty,
                 extra_decode_length=extra_decode_length, max_step=max_step, pad_id=pad_id, start_id=start_id,
                 end_id=end_id, sampling_method=float(SAMPLING_METHODS.index(sampling_method)), topk=float(topk),
                 topp=float(topp), output_topk=float(output_topk), no_scale_embedding=float(no_scale_embedding),

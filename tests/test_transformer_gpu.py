@@ -27,7 +27,8 @@ def _build(tmp_path, **kw):
                     start_id=int(conf["start_id"]), end_id=int(conf["end_id"]),
                     sampling_method=synth.SAMPLING_METHODS[int(conf["sampling_method"])], topk=int(conf["topk"]),
                     topp=float(conf["topp"]), output_topk=bool(conf["output_topk"]),
-                    no_scale_embedding=bool(conf["no_scale_embedding"]), seed_lo=int(conf["rng_seed"]))
+                    no_scale_embedding=bool(conf["no_scale_embedding"]), seed_lo=int(conf["rng_seed"]),
+                    pre_ln=bool(conf["pre_ln"]))
     return path, cfg, om.State(w=w, amax=amax)
 
 
@@ -428,3 +429,25 @@ def test_beam_result_writer_modes():
                 per = score[b] / (lens + np.float32(1e-12))
                 j = int(np.argmax(per))
                 assert np.array_equal(t[b], alive[b, j, 1:n + 1]) and s[b] == per[j]
+
+
+def test_post_ln_encoder_decoder_matches_oracle(tmp_path):
+    """is_post_ln (quant_transformer.proto:147): LayerNorm after every residual sum, as the torch layers compute it with
+    normalize_before false (torch_transformer_layers.py:630-679, 844-965); no final LayerNorms."""
+    import lightseq_b200.inference as lsi
+
+    path, cfg, st = _build(tmp_path, pre_ln=False, **SMALL)
+    _boost_eos(path, cfg, st)
+    src = synth.transformer_inputs(batch=6, min_len=3, max_len=10, vocab=cfg.vocab, pad_id=cfg.pad_id, seed=8)
+    ref_tok, ref_score, n_ref = om.Seq2Seq(cfg, st).generate(src)
+    model = lsi.QuantTransformer(path, 6)
+    tok, score = model.infer(src)
+    assert tok.shape == (6, 1, n_ref), (tok.shape, n_ref)
+    same = (tok[:, 0] == ref_tok).all(axis=1)
+    print("post-LN identical sequences", int(same.sum()), "of 6")
+    assert same.all()
+    np.testing.assert_allclose(score[:, 0], ref_score, rtol=1e-4, atol=1e-4)
+    enc_ref, pad = om.Seq2Seq(cfg, st).encode(src)
+    enc = _from_device(_encoder_tap(model), enc_ref.shape, torch.float32)
+    d = np.abs(enc - enc_ref)[~pad]
+    assert d.max() < 2e-2 and d.mean() < 1e-3
