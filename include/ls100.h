@@ -333,6 +333,8 @@ typedef struct {
   const float* seq_score;   /* [batch, beam] */
   float* cand_score;        /* out [batch*beam, beam] */
   int32_t* cand_token;      /* out [batch*beam, beam] */
+  float diverse_lambda;     /* diverse beam search: the r-th best candidate of a row competes with score - lambda * (r + 1)
+                               (ker_diverse_beam_search, lightseq/inference/kernels/transformerKernels.cc.cu:312-333); 0 = off */
 } ls100_beam_topk_args;
 int ls100_beam_topk(ls100_ctx* ctx, const ls100_beam_topk_args* args, ls100_stream_t stream);
 
@@ -350,6 +352,8 @@ typedef struct {
   int32_t* ticket;     /* [max_step] zeroed by the caller before the first step */
   int32_t* stop_step;  /* device int, -1 until every beam is finished */
   int32_t* stop_host;  /* optional mapped host int mirroring *stop_step */
+  float diverse_lambda; /* the penalty ls100_beam_topk subtracted is added back before scores and prefixes are stored
+                           (ker_refresh_result, lightseq/inference/kernels/transformerKernels.cc.cu:1430-1458) */
 } ls100_beam_update_args;
 int ls100_beam_update(ls100_ctx* ctx, const ls100_beam_update_args* args, ls100_stream_t stream);
 

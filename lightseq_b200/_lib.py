@@ -111,7 +111,7 @@ class BeamTopkArgs(C.Structure):
                 ("beam", C.c_int32), ("vocab", C.c_int32), ("max_step", C.c_int32), ("end_id", C.c_int32),
                 ("step_ptr", C.c_void_p), ("length_norm", C.c_void_p), ("alive", C.c_void_p),
                 ("seq_probs", C.c_void_p), ("seq_score", C.c_void_p), ("cand_score", C.c_void_p),
-                ("cand_token", C.c_void_p)]
+                ("cand_token", C.c_void_p), ("diverse_lambda", C.c_float)]
 
 
 class BeamUpdateArgs(C.Structure):
@@ -119,7 +119,7 @@ class BeamUpdateArgs(C.Structure):
                 ("max_step", C.c_int32), ("end_id", C.c_int32), ("step_ptr", C.c_void_p),
                 ("length_norm", C.c_void_p), ("alive", C.c_void_p), ("anc", C.c_void_p), ("seq_probs", C.c_void_p),
                 ("seq_score", C.c_void_p), ("fin_count", C.c_void_p), ("ticket", C.c_void_p),
-                ("stop_step", C.c_void_p), ("stop_host", C.c_void_p)]
+                ("stop_step", C.c_void_p), ("stop_host", C.c_void_p), ("diverse_lambda", C.c_float)]
 
 
 class SampleTopkArgs(C.Structure):

@@ -49,7 +49,7 @@ class QuantTransformer : public EngineModel {
     output_topk_ = wf.conf_or("output_topk", 0.0) != 0.0 || sampling_ != 0;
     no_scale_embedding_ = wf.conf_or("no_scale_embedding", 0.0) != 0.0;
     if (sampling_ < 0 || sampling_ > 3) throw std::runtime_error("QuantTransformer: unknown sampling_method");
-    if (wf.conf_or("diverse_lambda", 0.0) != 0.0) throw std::runtime_error("QuantTransformer: diverse beam search is not supported");
+    diverse_lambda_ = sampling_ == 0 ? (float)wf.conf_or("diverse_lambda", 0.0) : 0.f;  // topk_greedy_search zeroes it
     if (sampling_ == 1 && (topk_ < 1 || topk_ > 32)) throw std::runtime_error("QuantTransformer: topk must be in [1, 32]");
     if (sampling_ == 2 && !(topp_ > 0.f && topp_ <= 1.f)) throw std::runtime_error("QuantTransformer: topp must be in (0, 1]");
     if (sampling_ == 1 || sampling_ == 2) beam_ = 1;  // one sampled sequence per sentence (pywrapper/quant_transformer.cc:35-37)
@@ -412,6 +412,7 @@ class QuantTransformer : public EngineModel {
     t.seq_score = seq_score_;
     t.cand_score = cand_score_;
     t.cand_token = cand_token_;
+    t.diverse_lambda = diverse_lambda_;
     LS_RC(ls100_beam_topk(k, &t, st));
     ls100_beam_update_args u;
     memset(&u, 0, sizeof(u));
@@ -431,6 +432,7 @@ class QuantTransformer : public EngineModel {
     u.ticket = ticket_ptr_;
     u.stop_step = stop_ptr_;
     u.stop_host = stop_host_dev_;
+    u.diverse_lambda = diverse_lambda_;
     LS_RC(ls100_beam_update(k, &u, st));
   }
 
@@ -524,7 +526,7 @@ class QuantTransformer : public EngineModel {
   int32_t *step_ptr_ = nullptr, *stop_ptr_ = nullptr, *fin_ptr_ = nullptr, *ticket_ptr_ = nullptr;
   int32_t *stop_host_ = nullptr, *stop_host_dev_ = nullptr, *sample_ticket_ = nullptr, *sample_ended_ = nullptr;
   int sampling_ = 0, topk_ = 1;
-  float topp_ = 0.f;
+  float topp_ = 0.f, diverse_lambda_ = 0.f;
   uint32_t seed_lo_ = 0;
   bool output_topk_ = false, no_scale_embedding_ = false, pre_ln_ = true;
   std::vector<int32_t> h_anc_;

@@ -114,8 +114,8 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
   float* cs = a.cand_score + (long long)row * K;
   int32_t* ct = a.cand_token + (long long)row * K;
   if (step != 0 && a.alive[(long long)row * a.max_step + step] == a.end_id) {  // uniform over the CTA
-    if (threadIdx.x < K) {
-      cs[threadIdx.x] = (threadIdx.x == 0) ? a.seq_score[row] : -FLT_MAX;
+    if (threadIdx.x < K) {  // a finished beam: one candidate, EOS, its frozen score (rank 0 of its row)
+      cs[threadIdx.x] = (threadIdx.x == 0) ? __fsub_rn(a.seq_score[row], a.diverse_lambda) : -FLT_MAX;
       ct[threadIdx.x] = a.end_id;
     }
     return;
@@ -230,7 +230,8 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
       const unsigned key = buf[lane];
       const int val = (int)(key >> 22) - 128;
       const float lg = __fmul_rn((float)val, a.s_logits);
-      cs[lane] = fmaxf(__fmul_rn(__fadd_rn(lg, base), ln), MIN_LOG_PROB + 1.f);
+      cs[lane] = __fsub_rn(fmaxf(__fmul_rn(__fadd_rn(lg, base), ln), MIN_LOG_PROB + 1.f),
+                           __fmul_rn(a.diverse_lambda, (float)(lane + 1)));  // lane = rank of the candidate in its row
       ct[lane] = 0x3fffff - (int)(key & 0x3fffff);
     }
   }
@@ -281,7 +282,8 @@ __global__ void __launch_bounds__(128) beam_update_kernel(const ls100_beam_updat
       if (t == 0) {
         s_parent[j] = bc / K;
         s_token[j] = tok;
-        s_score[j] = best;
+        // candidates competed with the diversity penalty of their rank in their row; what is stored is the score itself
+        s_score[j] = __fadd_rn(best, __fmul_rn(a.diverse_lambda, (float)(bc % K + 1)));
       }
     }
   }

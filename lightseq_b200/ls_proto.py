@@ -237,8 +237,6 @@ def read_quant_transformer(path: str):
     if _int(mc, 15) != 0:
         raise ValueError("multilingual models are not supported by the engine")
     # fields that change the reference's output and that the engine does not implement are refused, not dropped
-    if _float(mc, 7) != 0.0:
-        raise ValueError("diverse_lambda != 0 (diverse beam search) is not supported by the engine")
     bias = _floats(trg, 7)
     if bias.size and np.any(bias != 0):
         raise ValueError("a non-zero shared_bias (logit bias) is not supported by the engine")
@@ -257,7 +255,7 @@ def read_quant_transformer(path: str):
                 act_gelu=float(_int(mc, 14)), pre_ln=float(not _int(mc, 12)), beam=_int(mc, 2), length_penalty=_float(mc, 4),
                 extra_decode_length=_int(mc, 3), max_step=max_step, pad_id=_int(mc, 5), start_id=_int(mc, 6), end_id=_int(mc, 11),
                 sampling_method=float(methods.index(method)), topk=float(max(_int(mc, 10), 1)), topp=_float(mc, 9),
-                output_topk=1.0, no_scale_embedding=float(_int(mc, 13)))
+                output_topk=1.0, no_scale_embedding=float(_int(mc, 13)), diverse_lambda=_float(mc, 7))
     return conf, amax, t
 
 
@@ -305,7 +303,7 @@ def write_quant_transformer(path: str, conf, amax, t) -> None:
     method = ("beam_search", "topk", "topp", "topk_greedy")[int(conf.get("sampling_method", 0))].encode()
     mc = (_enc_int(1, conf["heads"]) + _enc_int(2, conf["beam"]) + _enc_int(3, conf["extra_decode_length"]) +
           _enc_float(4, conf["length_penalty"]) + _enc_int(5, conf["pad_id"]) + _enc_int(6, conf["start_id"]) +
-          _tag(8, 2) + _varint(len(method)) + method + _enc_float(9, conf.get("topp", 0.0)) + _enc_int(10, int(conf.get("topk", 1))) +
+          _enc_float(7, conf.get("diverse_lambda", 0.0)) + _tag(8, 2) + _varint(len(method)) + method + _enc_float(9, conf.get("topp", 0.0)) + _enc_int(10, int(conf.get("topk", 1))) +
           _enc_int(11, conf["end_id"]) + _enc_int(12, 0 if int(conf.get("pre_ln", 1)) else 1) + _enc_int(13, 1 if conf.get("no_scale_embedding") else 0) +
           _enc_int(14, 1 if conf.get("act_gelu") else 0))
     out = bytearray()

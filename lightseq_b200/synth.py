@@ -257,7 +257,7 @@ def make_transformer(path: Optional[str] = None, *, hidden=512, heads=8, ffn=204
                      act="relu", beam=4, length_penalty=0.6, extra_decode_length=50, max_step=256, pad_id=1,
                      start_id=3, end_id=2, seed=1234, calib_src: Optional[np.ndarray] = None,
                      sampling_method: str = "beam_search", topk: int = 1, topp: float = 0.0, output_topk: bool = False,
-                     no_scale_embedding: bool = False, rng_seed: int = 0, pre_ln: bool = True
+                     no_scale_embedding: bool = False, rng_seed: int = 0, pre_ln: bool = True, diverse_lambda: float = 0.0
                      ) -> Tuple[Dict[str, float], Dict[str, float], Dict[str, np.ndarray]]:
     """Builds (conf, amax, tensors) of a seeded synthetic QuantTransformer and optionally writes ``path``. The
     generator options are those of the reference's model configuration (sampling_method, topk, topp; every beam in
@@ -272,7 +272,7 @@ def make_transformer(path: Optional[str] = None, *, hidden=512, heads=8, ffn=204
                 extra_decode_length=extra_decode_length, max_step=max_step, pad_id=pad_id, start_id=start_id,
                 end_id=end_id, sampling_method=float(SAMPLING_METHODS.index(sampling_method)), topk=float(topk),
                 topp=float(topp), output_topk=float(output_topk), no_scale_embedding=float(no_scale_embedding),
-                rng_seed=float(rng_seed))
+                rng_seed=float(rng_seed), diverse_lambda=float(diverse_lambda))
     w["pos"] = sinusoid_table(max_step, hidden)
     if path is not None:
         from . import weights

@@ -62,9 +62,13 @@ def candidate_score(lq_row: np.ndarray, s_l, prob, ln, token: int) -> np.float32
 
 
 def beam_step(lq: np.ndarray, s_l, alive: np.ndarray, probs: np.ndarray, score: np.ndarray, cur_step: int,
-              ln, end_id: int):
+              ln, end_id: int, diverse_lambda: float = 0.0):
     """lq int8 [B,K,V]; alive int32 [B,K,max_step]; probs/score fp32 [B,K].
-    Returns (new_alive, new_probs, new_score, parent [B,K], n_finished)."""
+    Returns (new_alive, new_probs, new_score, parent [B,K], n_finished).
+    ``diverse_lambda`` (diverse beam search, ker_diverse_beam_search, lightseq/inference/kernels/
+    transformerKernels.cc.cu:312-333): the r-th best candidate of a beam competes with its score minus
+    lambda * (r + 1); the stored score and prefix are the unpenalised ones (ker_refresh_result :1430-1458)."""
+    lam = F32(diverse_lambda)
     B, K, V = lq.shape
     s_l = F32(s_l)
     ln = F32(ln)
@@ -77,20 +81,21 @@ def beam_step(lq: np.ndarray, s_l, alive: np.ndarray, probs: np.ndarray, score: 
         cands = []  # (score, beam, token)
         for k in range(K):
             if cur_step != 0 and alive[b, k, cur_step] == end_id:
-                cands.append((F32(score[b, k]), k, end_id))
+                cands.append((F32(F32(score[b, k]) - lam), k, end_id, 0))
                 continue
             row = lq[b, k]
             mx, lse = row_logsumexp_base(row, s_l)
             base = F32(F32(probs[b, k] - lse) - mx)
             # exact top-K of the row: larger int8 value first, then lower token id
             order = np.lexsort((np.arange(V), -row.astype(np.int32)))[:K]
-            for v in order:
+            for rank, v in enumerate(order):
                 lg = F32(row[v]) * s_l
                 sc = max(F32(F32(lg + base) * ln), F32(MIN_LOG_PROB + F32(1.0)))
-                cands.append((F32(sc), k, int(v)))
+                cands.append((F32(sc - F32(lam * F32(rank + 1))), k, int(v), rank))
         cands.sort(key=lambda c: (-float(c[0]), c[1], c[2]))
         for j in range(K):
-            sc, k, v = cands[j]
+            sc, k, v, rank = cands[j]
+            sc = F32(sc + F32(lam * F32(rank + 1)))
             parent[b, j] = k
             new_alive[b, j, :cur_step + 1] = alive[b, k, :cur_step + 1]
             new_alive[b, j, cur_step + 1] = v

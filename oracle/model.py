@@ -65,6 +65,7 @@ class Config:
     topp: float = 0.0
     output_topk: bool = False              # every beam in the result, last position forced to EOS
     no_scale_embedding: bool = False
+    diverse_lambda: float = 0.0
     seed_lo: int = 0
     seed_hi: int = 0
 
@@ -406,7 +407,8 @@ class Seq2Seq:
             if method == "beam_search" or (method == "topk_greedy" and cur == 0):
                 ln = length_norm(cur + 1, cfg.length_penalty)
                 alive, probs, score, parent, n_fin = beam_step(
-                    lq.reshape(B, K, -1), s_l, alive, probs, score, cur, ln, cfg.end_id)
+                    lq.reshape(B, K, -1), s_l, alive, probs, score, cur, ln, cfg.end_id,
+                    cfg.diverse_lambda if method == "beam_search" else 0.0)
                 if early_stop and n_fin == B * K:
                     break
                 flat = (parent + np.arange(B)[:, None] * K).reshape(-1)

@@ -28,7 +28,7 @@ def _build(tmp_path, **kw):
                     sampling_method=synth.SAMPLING_METHODS[int(conf["sampling_method"])], topk=int(conf["topk"]),
                     topp=float(conf["topp"]), output_topk=bool(conf["output_topk"]),
                     no_scale_embedding=bool(conf["no_scale_embedding"]), seed_lo=int(conf["rng_seed"]),
-                    pre_ln=bool(conf["pre_ln"]))
+                    pre_ln=bool(conf["pre_ln"]), diverse_lambda=float(conf["diverse_lambda"]))
     return path, cfg, om.State(w=w, amax=amax)
 
 
@@ -451,3 +451,22 @@ def test_post_ln_encoder_decoder_matches_oracle(tmp_path):
     enc = _from_device(_encoder_tap(model), enc_ref.shape, torch.float32)
     d = np.abs(enc - enc_ref)[~pad]
     assert d.max() < 2e-2 and d.mean() < 1e-3
+
+
+def test_diverse_beam_search_matches_oracle(tmp_path):
+    """diverse_lambda: sibling candidates of one beam are penalised by their rank, which spreads the survivors over
+    the beams (ker_diverse_beam_search, lightseq/inference/kernels/transformerKernels.cc.cu:312-333)."""
+    import lightseq_b200.inference as lsi
+
+    path, cfg, st = _build(tmp_path, diverse_lambda=0.4, output_topk=True, **SMALL)
+    _boost_eos(path, cfg, st, 0.2)
+    src = synth.transformer_inputs(batch=6, min_len=3, max_len=10, vocab=cfg.vocab, pad_id=cfg.pad_id, seed=11)
+    ref_tok, ref_score, n_ref = om.Seq2Seq(cfg, st).generate(src)
+    tok, score = lsi.QuantTransformer(path, 6).infer(src)
+    assert tok.shape == (6, cfg.beam, n_ref)
+    assert np.array_equal(tok, ref_tok)
+    np.testing.assert_allclose(score, ref_score, rtol=1e-4, atol=1e-4)
+    plain_path, plain_cfg, plain_st = _build(tmp_path, output_topk=True, **SMALL)
+    _boost_eos(plain_path, plain_cfg, plain_st, 0.2)
+    plain, _ = lsi.QuantTransformer(plain_path, 6).infer(src)
+    assert plain.shape[2] != tok.shape[2] or not np.array_equal(plain, tok)  # the penalty changes what survives
