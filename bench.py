@@ -349,6 +349,21 @@ def kernel_cases(torch, L, conf, B, S, step):
         L.call("ls100_gemm_i8", CTX[0], a, st)
 
     cases["gemm_logits"] = (gemm_logits, T * H + V * H + T * V, "hbm", f"gemm_i8_persist_kernel, {T}x{V}x{H}, int8 out")
+    # the same GEMM keeping the per-group statistics, and the beam selection that reads them
+    G = (V + 63) // 64
+    nrb = (T + 127) // 128
+    smax = [torch.zeros((nrb, G, 128), dtype=torch.int8, device=dev) for _ in range(2)]
+    ssum = [torch.zeros((nrb, G, 128), dtype=torch.float32, device=dev) for _ in range(2)]
+
+    def gemm_logits_stats(i, st):
+        j = i % 8
+        a = L.GemmI8Args(a=a_s[j].data_ptr(), lda=H, w=wl[j].data_ptr(), ldw=H, m=T, n=V, k=H, s_acc=1e-4, s_outq=0.02,
+                         out_kind=L.OUT_OUTQ_I8, out=lo[j].data_ptr(), ldo=ldv, stat_max=smax[i % 2].data_ptr(),
+                         stat_sum=ssum[i % 2].data_ptr())
+        L.call("ls100_gemm_i8", CTX[0], a, st)
+
+    cases["gemm_logits_stats"] = (gemm_logits_stats, T * H + V * H + T * V, "hbm",
+                                  f"gemm_i8_persist_kernel, {T}x{V}x{H}, int8 out + per-group max / sum of exponentials")
     # tensor-bound GEMMs: the encoder's QKV projection over all source tokens of the batch, and a square problem
     Te = B * S
     ae, we = [i8(Te, H) for _ in range(4)], [i8(3 * H, H) for _ in range(4)]
@@ -449,6 +464,16 @@ def kernel_cases(torch, L, conf, B, S, step):
         L.call("ls100_beam_topk", CTX[0], a, st)
 
     cases["beam_topk"] = (beam_topk, T * V, "hbm", f"beam_topk_kernel, {T} rows x {V}")
+
+    def beam_select(i, st):
+        if i == 0:  # consistent statistics for logits set 0
+            gemm_logits_stats(0, st)
+        t = L.BeamTopkArgs(logits=lo[0].data_ptr(), ld_logits=ldv, s_logits=0.02, batch=B, beam=K, vocab=V, max_step=ms,
+                           end_id=2, step_ptr=dstep.data_ptr(), length_norm=lnt.data_ptr(), alive=alive.data_ptr(),
+                           seq_probs=pr.data_ptr(), seq_score=sc.data_ptr(), cand_score=cs.data_ptr(), cand_token=ct.data_ptr())
+        L.call("ls100_beam_select", CTX[0], L.BeamSelectArgs(topk=t, stat_max=smax[0].data_ptr(), stat_sum=ssum[0].data_ptr(), n_groups=G), st)
+
+    cases["beam_select"] = (beam_select, T * G * 5, "hbm", f"beam_select_kernel, {T} rows, {G} groups of 64 logits")
     g1, b1 = torch.ones(H, device=dev), torch.zeros(H, device=dev)
 
     def ln_quant(i, st):

@@ -106,6 +106,14 @@ typedef struct {
   float ln_amax;
   int8_t* ln_out;
   int64_t ln_ldq; /* elements */
+  /* Optional per-row statistics of an OUTQ_I8 output (the logits of a beam-search step), taken from the registers of
+   * the epilogue so that the selection that follows need not read the [M,N] matrix again: for every row and every
+   * group of 64 consecutive columns, the largest int8 value of the group (-128 for a group beyond N) and
+   * sum_j exp((q_j - 127) * s_outq). Layout of both arrays: [ceil(M/128)][ceil(N/64)][128] (the 128 rows of a row
+   * block contiguous). Replaces the log-sum-exp pass of select_beam_rough_topk_i8I
+   * (lightseq/inference/kernels/transformerKernels_int8.cc.cu:1718-1760). Both or neither. */
+  int8_t* stat_max;
+  float* stat_sum;
 } ls100_gemm_i8_args;
 
 int ls100_gemm_i8(ls100_ctx* ctx, const ls100_gemm_i8_args* args, ls100_stream_t stream);
@@ -337,6 +345,19 @@ typedef struct {
                                (ker_diverse_beam_search, lightseq/inference/kernels/transformerKernels.cc.cu:312-333); 0 = off */
 } ls100_beam_topk_args;
 int ls100_beam_topk(ls100_ctx* ctx, const ls100_beam_topk_args* args, ls100_stream_t stream);
+
+/* Step 1 from the statistics ls100_gemm_i8 kept while it wrote the logits (stat_max / stat_sum of its arguments,
+ * n_groups = ceil(vocab / 64)): the same candidates as ls100_beam_topk without reading the [rows, vocab] matrix
+ * again - the log-sum-exp comes from the group sums, and only the few 64-column groups whose largest value reaches
+ * the row's K-th largest group maximum are read. Scores agree with ls100_beam_topk to float rounding (the
+ * exponentials are summed in a different order), tokens exactly. */
+typedef struct {
+  ls100_beam_topk_args topk;
+  const int8_t* stat_max; /* [ceil(rows/128)][n_groups][128] */
+  const float* stat_sum;  /* same layout */
+  int32_t n_groups;
+} ls100_beam_select_args;
+int ls100_beam_select(ls100_ctx* ctx, const ls100_beam_select_args* args, ls100_stream_t stream);
 
 typedef struct {
   const float* cand_score;

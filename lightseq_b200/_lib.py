@@ -54,6 +54,7 @@ class GemmI8Args(C.Structure):
         ("out", C.c_void_p), ("ldo", C.c_int64),
         ("ln_gamma", C.c_void_p), ("ln_beta", C.c_void_p), ("ln_amax", C.c_float), ("ln_out", C.c_void_p),
         ("ln_ldq", C.c_int64),
+        ("stat_max", C.c_void_p), ("stat_sum", C.c_void_p),
     ]
 
 
@@ -114,6 +115,10 @@ class BeamTopkArgs(C.Structure):
                 ("cand_token", C.c_void_p), ("diverse_lambda", C.c_float)]
 
 
+class BeamSelectArgs(C.Structure):
+    _fields_ = [("topk", BeamTopkArgs), ("stat_max", C.c_void_p), ("stat_sum", C.c_void_p), ("n_groups", C.c_int32)]
+
+
 class BeamUpdateArgs(C.Structure):
     _fields_ = [("cand_score", C.c_void_p), ("cand_token", C.c_void_p), ("batch", C.c_int32), ("beam", C.c_int32),
                 ("max_step", C.c_int32), ("end_id", C.c_int32), ("step_ptr", C.c_void_p),
@@ -167,7 +172,7 @@ for _name, _cls in (("ls100_ln_quant", LnQuantArgs), ("ls100_embed", EmbedArgs),
                     ("ls100_beam_update", BeamUpdateArgs), ("ls100_beam_update_noalloc", BeamUpdateArgs), ("ls100_sample_topk", SampleTopkArgs),
                     ("ls100_sample_topp", SampleToppArgs),
                     ("ls100_proj_tc", ProjTcArgs), ("ls100_patch_embed", PatchEmbedArgs),
-                    ("ls100_beam_write_result", BeamResultArgs)):
+                    ("ls100_beam_write_result", BeamResultArgs), ("ls100_beam_select", BeamSelectArgs)):
     _fn = getattr(lib, _name)
     _fn.restype = C.c_int
     _fn.argtypes = [C.c_void_p, C.POINTER(_cls), C.c_void_p]

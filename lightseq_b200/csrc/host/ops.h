@@ -97,6 +97,11 @@ class QuantLinearOp : public Operator {
     rows_ = rows;
     ldo_ = ldo ? ldo : p_->n;
   }
+  // per-row group statistics of an int8 output (see ls100_gemm_i8_args::stat_max): the logits of a beam-search step
+  void keep_statistics(int8_t* stat_max, float* stat_sum) {
+    stat_max_ = stat_max;
+    stat_sum_ = stat_sum;
+  }
   void forward() override {
     ls100_gemm_i8_args a;
     memset(&a, 0, sizeof(a));
@@ -125,6 +130,8 @@ class QuantLinearOp : public Operator {
       a.ln_out = ln_out_->value<int8_t>();
       a.ln_ldq = p_->n;
     }
+    a.stat_max = stat_max_;
+    a.stat_sum = stat_sum_;
     LS_RC(ls100_gemm_i8(ctx_->kernels(), &a, ctx_->get_stream()));
   }
 
@@ -137,6 +144,8 @@ class QuantLinearOp : public Operator {
   Variable *in_ = nullptr, *out_ = nullptr, *resid_ = nullptr, *ln_out_ = nullptr;
   const float *ln_g_ = nullptr, *ln_b_ = nullptr;
   float ln_amax_ = 0.f;
+  int8_t* stat_max_ = nullptr;
+  float* stat_sum_ = nullptr;
   int rows_ = 0;
   int64_t ldo_ = 0;
 };

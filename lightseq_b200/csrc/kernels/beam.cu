@@ -237,6 +237,256 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
   }
 }
 
+// The same candidates as beam_topk_kernel, from the statistics the logits GEMM kept per (row, 64-column group) -
+// the group's largest value and its sum of exponentials - so that the [rows, vocab] matrix is not read again:
+//   1. lane = row: every warp walks a share of the row's groups (coalesced: the 128 rows of a row block are
+//      contiguous), adds the sums and keeps the K largest group maxima; the eight warps' partial results meet in
+//      shared memory. The K-th largest group maximum T of a row is a lower bound of its K-th best logit: at least K
+//      groups hold a value >= T.
+//   2. lane = row again: the groups whose maximum reaches T (a handful) are listed per row.
+//   3. warp = row: only those groups' 64 bytes are read; values >= the running bound enter the candidate buffer of
+//      beam_topk_kernel and the same selection picks the exact top K by (value desc, token asc).
+// A CTA serves 32 rows. The scores are formed exactly as in beam_topk_kernel.
+constexpr int SEL_ROWS = 32;
+constexpr int SEL_WARPS = 8;
+constexpr int SEL_LIST = 32;   // candidate groups listed per row (one per lane); a row with more reads every group, serially
+constexpr int SEL_HITS = 128;  // candidate values buffered per row on the lane-parallel path
+
+__global__ void __launch_bounds__(32 * SEL_WARPS) beam_select_kernel(const ls100_beam_select_args s) {
+  const ls100_beam_topk_args& a = s.topk;
+  __shared__ double s_sum[SEL_WARPS][SEL_ROWS];
+  __shared__ signed char s_top[SEL_WARPS][SEL_ROWS][MAX_BEAM];
+  __shared__ double s_total[SEL_ROWS];
+  __shared__ int s_T[SEL_ROWS];
+  __shared__ int s_cnt[SEL_ROWS];
+  __shared__ unsigned short s_list[SEL_ROWS][SEL_LIST];
+  __shared__ unsigned s_hits[SEL_ROWS][SEL_HITS];
+  __shared__ int s_nhit[SEL_ROWS];
+  __shared__ unsigned s_buf[SEL_WARPS][TOPK_BUF];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int rows = a.batch * a.beam;
+  const int K = a.beam;
+  const int G = s.n_groups;
+  const int step = *a.step_ptr;
+  const int row0 = blockIdx.x * SEL_ROWS;
+  const int row = row0 + lane;
+  const bool row_ok = row < rows;
+  // statistics of row r live at ((r / 128) * G + g) * 128 + r % 128
+  const long long base = row_ok ? ((long long)(row >> 7) * G) * 128 + (row & 127) : 0;
+  {
+    double sum = 0.0;
+    int top[MAX_BEAM];
+#pragma unroll
+    for (int j = 0; j < MAX_BEAM; ++j) top[j] = -128;
+    if (row_ok) {
+      // eight groups per round, their loads issued together (one after the other they would each cost an L2 round trip)
+      for (int g0 = warp; g0 < G; g0 += 8 * SEL_WARPS) {
+        float sm[8];
+        int mx[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int g = g0 + u * SEL_WARPS;
+          const long long o = base + (long long)(g < G ? g : g0) * 128;
+          sm[u] = s.stat_sum[o];
+          mx[u] = (int)s.stat_max[o];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (g0 + u * SEL_WARPS >= G) break;
+          sum += (double)sm[u];
+          int v = mx[u];
+#pragma unroll
+          for (int j = 0; j < MAX_BEAM; ++j) {  // sorted insertion, largest first
+            const int hi = max(top[j], v);
+            v = min(top[j], v);
+            top[j] = hi;
+          }
+        }
+      }
+    }
+    s_sum[warp][lane] = sum;
+#pragma unroll
+    for (int j = 0; j < MAX_BEAM; ++j) s_top[warp][lane][j] = (signed char)top[j];
+    if (warp == 0) {
+      s_cnt[lane] = 0;
+      s_nhit[lane] = 0;
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    double tot = 0.0;
+    int top[MAX_BEAM];
+#pragma unroll
+    for (int j = 0; j < MAX_BEAM; ++j) top[j] = -128;
+    for (int w = 0; w < SEL_WARPS; ++w) {
+      tot += s_sum[w][lane];
+      for (int i = 0; i < MAX_BEAM; ++i) {
+        int v = (int)s_top[w][lane][i];
+#pragma unroll
+        for (int j = 0; j < MAX_BEAM; ++j) {
+          const int hi = max(top[j], v);
+          v = min(top[j], v);
+          top[j] = hi;
+        }
+      }
+    }
+    s_total[lane] = tot;
+    int T = -128;  // fewer than K groups: every group is a candidate
+#pragma unroll
+    for (int j = 0; j < MAX_BEAM; ++j)
+      if (j == K - 1 && G >= K) T = top[j];
+    s_T[lane] = T;
+  }
+  __syncthreads();
+  if (row_ok) {
+    const int T = s_T[lane];
+    for (int g0 = warp; g0 < G; g0 += 8 * SEL_WARPS) {
+      int mx[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int g = g0 + u * SEL_WARPS;
+        mx[u] = g < G ? (int)s.stat_max[base + (long long)g * 128] : -129;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (mx[u] >= T) {
+          const int pos = atomicAdd(&s_cnt[lane], 1);
+          if (pos < SEL_LIST) s_list[lane][pos] = (unsigned short)(g0 + u * SEL_WARPS);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  unsigned* buf = s_buf[warp];
+  for (int rl = warp; rl < SEL_ROWS; rl += SEL_WARPS) {
+    const int r = row0 + rl;
+    if (r >= rows) break;
+    float* cs = a.cand_score + (long long)r * K;
+    int32_t* ct = a.cand_token + (long long)r * K;
+    if (step != 0 && a.alive[(long long)r * a.max_step + step] == a.end_id) {  // a finished beam: EOS, its frozen score
+      if (lane < K) {
+        cs[lane] = (lane == 0) ? __fsub_rn(a.seq_score[r], a.diverse_lambda) : -FLT_MAX;
+        ct[lane] = a.end_id;
+      }
+      continue;
+    }
+    const int8_t* lp = a.logits + (long long)r * a.ld_logits;
+    const int n_list = s_cnt[rl];
+    int thr = s_T[rl];  // values >= thr are candidates (ties included: the selection orders them by token)
+    int n_buf = 0;
+    bool serial = n_list > SEL_LIST;
+    if (!serial) {
+      // lane-parallel: every lane reads one candidate group (64 bytes, one round trip for the whole row) and appends its
+      // values >= thr to the row's list; a list that would overflow sends the row down the serial path instead
+      if (lane < n_list) {
+        const int g = (int)s_list[rl][lane];
+        const int off0 = g * 64;
+        unsigned w[16];
+        if (off0 + 64 <= a.vocab && ((a.ld_logits & 15) == 0)) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint4 v4 = *reinterpret_cast<const uint4*>(lp + off0 + c * 16);
+            w[c * 4] = v4.x;
+            w[c * 4 + 1] = v4.y;
+            w[c * 4 + 2] = v4.z;
+            w[c * 4 + 3] = v4.w;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            unsigned word = 0x80808080u;
+            for (int e = 0; e < 4; ++e) {
+              const int o = off0 + c * 4 + e;
+              if (o < a.vocab) word = (word & ~(0xffu << (8 * e))) | ((unsigned)(uint8_t)lp[o] << (8 * e));
+            }
+            w[c] = word;
+          }
+        }
+        const unsigned thr4 = (unsigned)(thr & 0xff) * 0x01010101u;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          unsigned ge = __vcmpges4(w[c], thr4) & 0x80808080u;
+          while (ge) {
+            const int e = (__ffs(ge) - 1) >> 3;
+            ge &= ge - 1;
+            const int o = off0 + c * 4 + e;
+            if (o < a.vocab) {
+              const int pos = atomicAdd(&s_nhit[rl], 1);
+              if (pos < SEL_HITS) s_hits[rl][pos] = topk_key((int)(int8_t)((w[c] >> (8 * e)) & 0xff), o);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      const int nh = s_nhit[rl];
+      if (nh <= SEL_HITS) {
+        for (int i = lane; i < nh; i += 32) buf[i] = s_hits[rl][i];
+        n_buf = nh;
+        __syncwarp();
+      } else {
+        serial = true;
+      }
+    }
+    if (serial) {
+      const bool all_groups = n_list > SEL_LIST;
+      const int n_scan = all_groups ? G : n_list;
+      for (int i = 0; i < n_scan; ++i) {
+        const int g = all_groups ? i : (int)s_list[rl][i];
+        const int off = g * 64 + lane * 2;
+        int q0 = -128, q1 = -128;
+        if (off + 1 < a.vocab) {
+          const short two = *reinterpret_cast<const short*>(lp + off);
+          q0 = (int)(int8_t)(two & 0xff);
+          q1 = (int)(int8_t)((two >> 8) & 0xff);
+        } else if (off < a.vocab) {
+          q0 = (int)lp[off];
+        }
+        const bool h0 = q0 >= thr && off < a.vocab, h1 = q1 >= thr && off + 1 < a.vocab;
+        const int mine = (h0 ? 1 : 0) + (h1 ? 1 : 0);
+        int pre = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int t = __shfl_up_sync(0xffffffffu, pre, o);
+          if (lane >= o) pre += t;
+        }
+        const int total = __shfl_sync(0xffffffffu, pre, 31);
+        if (total == 0) continue;
+        int pos = n_buf + pre - mine;
+        if (h0) buf[pos++] = topk_key(q0, off);
+        if (h1) buf[pos++] = topk_key(q1, off + 1);
+        n_buf += total;
+        __syncwarp();
+        if (n_buf > TOPK_BUF - 64) {  // at most 64 entries per group: the buffer never overflows
+          const int t2 = topk_flush(buf, n_buf, K, lane, &n_buf);
+          thr = max(thr, t2);
+        }
+      }
+    }
+    __syncwarp();
+    topk_flush(buf, n_buf, K, lane, &n_buf);
+    if (lane < K) {
+      const float ref = __fmul_rn(127.f, a.s_logits);
+      const float lse = __fadd_rn(logf((float)s_total[rl]), ref);
+      const float base_lp = __fsub_rn(a.seq_probs[r], lse);
+      const float ln = a.length_norm[step];
+      if (lane >= n_buf) {
+        cs[lane] = -FLT_MAX;
+        ct[lane] = a.end_id;
+      } else {
+        const unsigned key = buf[lane];
+        const int val = (int)(key >> 22) - 128;
+        const float lg = __fmul_rn((float)val, a.s_logits);
+        cs[lane] = __fsub_rn(fmaxf(__fmul_rn(__fadd_rn(lg, base_lp), ln), MIN_LOG_PROB + 1.f),
+                             __fmul_rn(a.diverse_lambda, (float)(lane + 1)));
+        ct[lane] = 0x3fffff - (int)(key & 0x3fffff);
+      }
+    }
+    __syncwarp();
+  }
+}
+
 __global__ void __launch_bounds__(128) beam_update_kernel(const ls100_beam_update_args a) {
   extern __shared__ int stage[];  // [2][K][max_step]
   __shared__ int s_parent[MAX_BEAM], s_token[MAX_BEAM];
@@ -416,6 +666,24 @@ static int beam_update_check(const ls100_ctx* ctx, const ls100_beam_update_args*
   if (a->beam > MAX_BEAM) return LS100_ERR_UNSUPPORTED;
   if ((size_t)2 * a->beam * a->max_step * sizeof(int) > 48 * 1024) return LS100_ERR_UNSUPPORTED;
   return LS100_OK;
+}
+
+extern "C" int ls100_beam_select(ls100_ctx* ctx, const ls100_beam_select_args* s, ls100_stream_t stream_) {
+  if (!ctx || !s || !s->stat_max || !s->stat_sum) return LS100_ERR_BAD_ARG;
+  const ls100_beam_topk_args* a = &s->topk;
+  if (!a->logits || !a->step_ptr || !a->length_norm || !a->alive || !a->seq_probs || !a->seq_score || !a->cand_score ||
+      !a->cand_token)
+    return LS100_ERR_BAD_ARG;
+  if (a->batch <= 0 || a->beam <= 0 || a->vocab <= 0 || a->max_step <= 0 || !(a->s_logits > 0.f)) return LS100_ERR_BAD_ARG;
+  if (a->beam > MAX_BEAM || a->vocab < a->beam || a->vocab > (1 << 22)) return LS100_ERR_UNSUPPORTED;
+  if (254.f * a->s_logits > 64.f) return LS100_ERR_UNSUPPORTED;
+  if (s->n_groups != (a->vocab + 63) / 64 || s->n_groups > 65535) return LS100_ERR_BAD_ARG;
+  if ((((uintptr_t)a->logits) & 1) || (a->ld_logits & 1)) return LS100_ERR_ALIGN;
+  const int rows = a->batch * a->beam;
+  return ls100_launch(beam_select_kernel, dim3((rows + SEL_ROWS - 1) / SEL_ROWS), dim3(32 * SEL_WARPS), 0,
+                      (cudaStream_t)stream_, *s) == cudaSuccess
+             ? LS100_OK
+             : LS100_ERR_CUDA;
 }
 
 extern "C" int ls100_beam_update(ls100_ctx* ctx, const ls100_beam_update_args* a, ls100_stream_t stream_) {

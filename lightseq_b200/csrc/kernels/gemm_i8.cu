@@ -49,6 +49,17 @@ struct GemmEpi {
   float ln_amax, ln_scale, ln_rs;
   int8_t* ln_out;
   long long ln_ldq;
+  // per (row, 64-column group) statistics of an int8 output: largest value and sum of exp((q - 127) * s_outq)
+  int8_t* st_max;
+  float* st_sum;
+  int st_groups;
+  float st_c, st_c127;  // s_outq * log2(e) and -127 times that
+};
+
+// Running statistics of one thread's row over the chunks of its column group.
+struct EpiStats {
+  float sum0, sum1;  // two chains
+  unsigned max4;     // four running maxima as packed int8
 };
 
 constexpr int BM = 128;
@@ -97,7 +108,8 @@ __device__ __forceinline__ void record_timeout(int* err) {
 template <int BN, int NC = 32>
 __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t (&r)[NC], int row, int col0,
                                                const float* s_bias, const int* s_off, const float (&rr)[NC],
-                                               bool rr_valid, double* row_sum = nullptr, double* row_sq = nullptr) {
+                                               bool rr_valid, double* row_sum = nullptr, double* row_sq = nullptr,
+                                               EpiStats* stats = nullptr) {
   const bool row_ok = row < p.m;
   const bool full = (col0 + NC <= p.n);
   int acc[NC];
@@ -298,6 +310,27 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
         if (col0 + j < p.n) op[j] = __float2half_rn(v[j]);
     }
   } else {  // int8 outputs: v[] holds the results of quant_biased
+    if (stats != nullptr) {  // this row's group statistics from the values in registers (columns beyond N do not count)
+      const float2 magic2 = f2_set(kQuantMagic), c2 = f2_set(p.st_c), o2 = f2_set(p.st_c127);
+#pragma unroll
+      for (int j = 0; j < NC; j += 2) {
+        const float2 arg = f2_fma(f2_sub(make_float2(v[j], v[j + 1]), magic2), c2, o2);  // (q - 127) * s * log2(e)
+        const float e0 = (full || col0 + j < p.n) ? ex2_approx(arg.x) : 0.f;
+        const float e1 = (full || col0 + j + 1 < p.n) ? ex2_approx(arg.y) : 0.f;
+        stats->sum0 += e0;
+        stats->sum1 += e1;
+      }
+#pragma unroll
+      for (int j = 0; j < NC; j += 4) {
+        unsigned w = pack_biased_i8x4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        if (!full) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (col0 + j + e >= p.n) w = (w & ~(0xffu << (8 * e))) | (0x80u << (8 * e));
+        }
+        stats->max4 = __vmaxs4(stats->max4, w);
+      }
+    }
     int8_t* op = reinterpret_cast<int8_t*>(p.out) + (long long)row * p.ldo + col0;
     if (full && ((p.ldo & 15) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
 #pragma unroll
@@ -741,6 +774,8 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
       }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + grp * COLS);
+      EpiStats stats = {0.f, 0.f, 0x80808080u};
+      const bool with_stats = p.st_max != nullptr && p.out_kind == LS100_OUT_OUTQ_I8;
 #pragma unroll 1
       for (int c0 = 0; c0 < COLS; c0 += 16) {
         const bool last = (c0 + 16 == COLS) || (n0 + c0 + 16 >= p.n);
@@ -753,13 +788,21 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
           }
-          epilogue_chunk<P_BN, 16>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, false);
+          epilogue_chunk<P_BN, 16>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, false, nullptr, nullptr,
+                                   with_stats ? &stats : nullptr);
         } else if (c0 == 0) {  // the whole group lies beyond N: nothing to read, release at once
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
         }
         if (last) break;
+      }
+      if (with_stats && row < p.m && n0 < p.n) {  // COLS == 64: this warp's column group is one statistics group
+        const unsigned m2 = __vmaxs4(stats.max4, stats.max4 >> 16);
+        const unsigned m1 = __vmaxs4(m2, m2 >> 8);
+        const long long slot = ((long long)(row >> 7) * p.st_groups + (n0 >> 6)) * 128 + (row & 127);
+        p.st_max[slot] = (int8_t)(m1 & 0xffu);
+        p.st_sum[slot] = stats.sum0 + stats.sum1;
       }
     }
   }
@@ -797,6 +840,11 @@ static GemmEpi make_epi(const ls100_ctx* ctx, const ls100_gemm_i8_args* a) {
   p.ln_rs = a->ln_amax > 0.f ? 1.0f / p.ln_scale : 0.f;
   p.ln_out = a->ln_out;
   p.ln_ldq = a->ln_ldq;
+  p.st_max = a->stat_max;
+  p.st_sum = a->stat_sum;
+  p.st_groups = (a->n + 63) / 64;
+  p.st_c = a->s_outq * 1.4426950408889634f;
+  p.st_c127 = -127.f * p.st_c;
   return p;
 }
 
@@ -874,6 +922,11 @@ extern "C" int ls100_gemm_i8(ls100_ctx* ctx, const ls100_gemm_i8_args* a, ls100_
   if (a->resid && a->ldr < a->n) return LS100_ERR_BAD_ARG;
   if (a->ldo < a->n) return LS100_ERR_BAD_ARG;
   cudaStream_t stream = (cudaStream_t)stream_;
+  if ((a->stat_max != nullptr) != (a->stat_sum != nullptr)) return LS100_ERR_BAD_ARG;
+  if (a->stat_max) {  // only the many-tile kernel's epilogue keeps the statistics (its warps own whole 64-column groups)
+    if (a->out_kind != LS100_OUT_OUTQ_I8 || a->ln_out || (((uintptr_t)a->stat_sum) & 3)) return LS100_ERR_BAD_ARG;
+    return launch_gemm_persist(ctx, a, stream);
+  }
   if (a->ln_out) {
     if (a->out_kind != LS100_OUT_F32 || !a->ln_gamma || !a->ln_beta || !(a->ln_amax > 0.f) || a->ln_ldq < a->n)
       return LS100_ERR_BAD_ARG;

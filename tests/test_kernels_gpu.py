@@ -702,3 +702,69 @@ def test_bounded_wait_runs_out_and_reports_once():
     out = gemm(dev(a), dev(w), s_acc=1.0, out_kind=L.OUT_I32)
     sync_check()
     assert np.array_equal(out.cpu().numpy().astype(np.int64), oq.int_matmul(a, w))
+
+
+@pytest.mark.parametrize("B,K,V,Kd,levels", [(3, 4, 37, 64, 40.0), (5, 4, 1000, 128, 40.0), (128, 4, 32000, 512, 40.0),
+                                             (9, 8, 40003, 256, 40.0), (33, 2, 32000, 128, 1.5), (4, 1, 5000, 64, 40.0)])
+def test_logits_statistics_and_beam_select_match_beam_topk(B, K, V, Kd, levels):
+    """The logits GEMM keeps, per row and 64-column group, the largest int8 value and the sum of exponentials;
+    ls100_beam_select picks the beam candidates from those statistics and the few groups that matter. The tokens
+    must be exactly those of ls100_beam_topk on the same logits, the scores equal to float rounding. `levels` = the
+    spread of the int8 logits: 1.5 leaves about seven distinct values, so that hundreds of groups tie for the maximum
+    (the path that reads every group) and the token tie-break decides."""
+    rows, ms, end_id = B * K, 16, 2
+    r = rng(41 + V)
+    a = r.integers(-127, 128, size=(rows, Kd), dtype=np.int8)
+    w = r.integers(-127, 128, size=(V, Kd), dtype=np.int8)
+    acc_std = 127 * 127 / 3.0 * np.sqrt(Kd)
+    s_out = F32(0.05)
+    s_acc = F32(float(s_out) * levels / acc_std)  # int8 logits ~ N(0, levels^2), clipped at +-127
+    ldv = (V + 15) // 16 * 16
+    G = (V + 63) // 64
+    nrb = (rows + 127) // 128
+    da, dw = dev(a), dev(w)
+    logits = torch.zeros((rows, ldv), dtype=torch.int8, device="cuda:0")
+    st_max = torch.full((nrb, G, 128), -99, dtype=torch.int8, device="cuda:0")
+    st_sum = torch.zeros((nrb, G, 128), dtype=torch.float32, device="cuda:0")
+    g = L.GemmI8Args(a=ptr(da), lda=Kd, w=ptr(dw), ldw=Kd, m=rows, n=V, k=Kd, s_acc=float(s_acc), s_outq=float(s_out),
+                     out_kind=L.OUT_OUTQ_I8, out=ptr(logits), ldo=ldv, stat_max=ptr(st_max), stat_sum=ptr(st_sum))
+    L.call("ls100_gemm_i8", ctx(), g)
+    sync_check()
+    lq = logits.cpu().numpy()[:, :V]
+    # the statistics are what numpy computes from the int8 matrix
+    pad = np.full((rows, G * 64), -128, np.int32)
+    pad[:, :V] = lq
+    want_max = pad.reshape(rows, G, 64).max(2)
+    e = np.exp((pad.astype(np.float64) - 127.0) * float(s_out))
+    e[:, V:] = 0
+    want_sum = e.reshape(rows, G, 64).sum(2)
+    got_max = st_max.cpu().numpy().transpose(0, 2, 1).reshape(nrb * 128, G)[:rows]
+    got_sum = st_sum.cpu().numpy().transpose(0, 2, 1).reshape(nrb * 128, G)[:rows]
+    assert np.array_equal(got_max, want_max)
+    np.testing.assert_allclose(got_sum, want_sum, rtol=1e-5)
+    # candidates: both kernels from the same state, step 1 with one finished beam
+    alive = np.full((B, K, ms), end_id, np.int32)
+    alive[:, :, 0] = 3
+    alive[:, :, 1] = 7
+    if K > 1:
+        alive[0, 1, 1] = end_id
+    probs = (-r.random((B, K)) * 3).astype(F32)
+    score = (-r.random((B, K)) * 3).astype(F32)
+    d_alive, d_probs, d_score = dev(alive), dev(probs), dev(score)
+    step = dev(np.ones(1, np.int32))
+    ln = dev(np.array([ob.length_norm(i + 1, 0.6) for i in range(ms)], F32))
+    outs = []
+    for fused in (False, True):
+        cs, ct = empty((rows, K), torch.float32), empty((rows, K), torch.int32)
+        t = L.BeamTopkArgs(logits=ptr(logits), ld_logits=ldv, s_logits=float(s_out), batch=B, beam=K, vocab=V, max_step=ms,
+                           end_id=end_id, step_ptr=ptr(step), length_norm=ptr(ln), alive=ptr(d_alive), seq_probs=ptr(d_probs),
+                           seq_score=ptr(d_score), cand_score=ptr(cs), cand_token=ptr(ct), diverse_lambda=0.25)
+        if fused:
+            L.call("ls100_beam_select", ctx(), L.BeamSelectArgs(topk=t, stat_max=ptr(st_max), stat_sum=ptr(st_sum), n_groups=G))
+        else:
+            L.call("ls100_beam_topk", ctx(), t)
+        sync_check()
+        outs.append((cs.cpu().numpy(), ct.cpu().numpy()))
+    assert np.array_equal(outs[0][1], outs[1][1]), "candidate tokens differ"
+    np.testing.assert_allclose(outs[1][0], outs[0][0], rtol=2e-6, atol=2e-6)
+    print("distinct logit values", len(np.unique(lq)), "rows", rows, "groups", G)

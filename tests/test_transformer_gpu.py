@@ -470,3 +470,18 @@ def test_diverse_beam_search_matches_oracle(tmp_path):
     _boost_eos(plain_path, plain_cfg, plain_st, 0.2)
     plain, _ = lsi.QuantTransformer(plain_path, 6).infer(src)
     assert plain.shape[2] != tok.shape[2] or not np.array_equal(plain, tok)  # the penalty changes what survives
+
+
+def test_beam_selection_from_logit_statistics_gives_the_same_generation(tmp_path, monkeypatch):
+    """LS100_FUSED_SELECT: the logits GEMM keeps per-group maxima and sums of exponentials and ls100_beam_select picks
+    the candidates from them instead of ls100_beam_topk reading the logits again. Same tokens, scores to rounding."""
+    import lightseq_b200.inference as lsi
+
+    path, cfg, st = _build(tmp_path, **SMALL)
+    _boost_eos(path, cfg, st)
+    src = synth.transformer_inputs(batch=6, min_len=3, max_len=10, vocab=cfg.vocab, pad_id=cfg.pad_id, seed=3)
+    tok0, score0 = lsi.QuantTransformer(path, 6).infer(src)
+    monkeypatch.setenv("LS100_FUSED_SELECT", "1")
+    tok1, score1 = lsi.QuantTransformer(path, 6).infer(src)
+    assert np.array_equal(tok0, tok1)
+    np.testing.assert_allclose(score1, score0, rtol=1e-5, atol=1e-5)
