@@ -746,7 +746,7 @@ def run_ours(args):
     # as a launch of its own only when it is not run inside the first LayerNorm
     sep_embed = 1 if os.environ.get("LS100_NO_EMBED_FUSE") is not None else 0
     split = 0 if os.environ.get("LS100_PROJ_SIMT") is not None else 1
-    per_infer = (1 + 7 * n_enc + 1) + split + 2 * n_dec + steps_per_infer * (sep_embed + 11 * n_dec + 2 + 2)
+    per_infer = (1 + 7 * n_enc + 1) + split + 2 * n_dec + steps_per_infer * (sep_embed + 11 * n_dec + 2 + 2) + 1  # + result writer
     # the decode step as a whole against the HBM roofline: the streams a step must read from HBM (activations of a
     # few MB per kernel are produced and consumed out of L2)
     H_, F_, V_, K_ = int(conf["hidden"]), int(conf["ffn"]), int(conf["vocab"]), int(conf["beam"])

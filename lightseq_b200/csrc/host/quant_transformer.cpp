@@ -50,7 +50,7 @@ class QuantTransformer : public EngineModel {
     no_scale_embedding_ = wf.conf_or("no_scale_embedding", 0.0) != 0.0;
     if (sampling_ < 0 || sampling_ > 3) throw std::runtime_error("QuantTransformer: unknown sampling_method");
     diverse_lambda_ = sampling_ == 0 ? (float)wf.conf_or("diverse_lambda", 0.0) : 0.f;  // topk_greedy_search zeroes it
-    if (sampling_ == 1 && (topk_ < 1 || topk_ > 32)) throw std::runtime_error("QuantTransformer: topk must be in [1, 32]");
+    if (sampling_ == 1 && (topk_ < 1 || topk_ > 8)) throw std::runtime_error("QuantTransformer: topk must be in [1, 8]");
     if (sampling_ == 2 && !(topp_ > 0.f && topp_ <= 1.f)) throw std::runtime_error("QuantTransformer: topp must be in (0, 1]");
     if (sampling_ == 1 || sampling_ == 2) beam_ = 1;  // one sampled sequence per sentence (pywrapper/quant_transformer.cc:35-37)
     if (H_ != heads_ * 64) throw std::runtime_error("QuantTransformer: head_dim must be 64");
