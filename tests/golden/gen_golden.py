@@ -320,6 +320,28 @@ def golden_small_gpt():
     print("small gpt: logits", tuple(logits.shape))
 
 
+@torch.no_grad()
+def golden_generation():
+    """Beam-4 generation of a small encoder-decoder assembled from the reference's own modules (oracle/ref_torch.py:
+    every layer computation is the reference's, the beam step between decoder calls is oracle/beam.py). Pins
+    oracle.model.Seq2Seq.generate end to end: tokens, scores and the number of decode steps, with early stop."""
+    from oracle import model as om
+    from oracle import ref_torch as rt
+
+    kw = dict(hidden=128, heads=2, ffn=256, n_enc=2, n_dec=2, vocab=300, max_step=32, beam=4, extra_decode_length=8, seed=5)
+    conf, amax, w = synth.make_transformer(None, **kw)
+    u = np.sign(np.random.default_rng(0).standard_normal(128)).astype(np.float32)
+    w["dec.ln.b"] = (0.15 * u).astype(np.float32)      # EOS made competitive: beams finish at different steps
+    w["emb"][int(conf["end_id"])] = (0.02 * u).astype(np.float32)
+    cfg = om.Config(hidden=128, heads=2, ffn=256, n_enc=2, n_dec=2, vocab=300, max_step=32, beam=4, extra_decode_length=8,
+                    length_penalty=float(conf["length_penalty"]), pad_id=int(conf["pad_id"]), start_id=int(conf["start_id"]),
+                    end_id=int(conf["end_id"]))
+    src = synth.transformer_inputs(batch=6, min_len=3, max_len=9, vocab=300, seed=2)
+    tok, score, n = rt.RefSeq2Seq((qz, tl), cfg, w, amax).generate(src)
+    np.savez_compressed(HERE / "small_seq2seq_generation.npz", src=src, tokens=tok, scores=score, n=np.int32(n))
+    print("generation: tokens", tok.shape, "steps", n)
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     golden_quantizer()
@@ -327,3 +349,4 @@ if __name__ == "__main__":
     golden_small_seq2seq()
     golden_small_bert()
     golden_small_gpt()
+    golden_generation()

@@ -149,3 +149,44 @@ def test_beam_step_equals_hand_worked_answer(golden_dir):
     assert n_fin == e["n_finished"]
     np.testing.assert_allclose(nsc, np.array(e["seq_score"]), rtol=0, atol=3e-6)
     np.testing.assert_allclose(npr, np.array(e["seq_probs"]), rtol=0, atol=3e-6)
+
+
+def test_generation_equals_reference_modules(golden_dir):
+    """Beam-4 generation with early stop: the oracle against the fixture made by the reference's own modules assembled
+    into the encoder-decoder (tests/golden/gen_golden.py::golden_generation)."""
+    g = np.load(golden_dir / "small_seq2seq_generation.npz")
+    kw = dict(hidden=128, heads=2, ffn=256, n_enc=2, n_dec=2, vocab=300, max_step=32, beam=4, extra_decode_length=8, seed=5)
+    conf, amax, w = synth.make_transformer(None, **kw)
+    u = np.sign(np.random.default_rng(0).standard_normal(128)).astype(np.float32)
+    w["dec.ln.b"] = (0.15 * u).astype(np.float32)
+    w["emb"][int(conf["end_id"])] = (0.02 * u).astype(np.float32)
+    cfg = om.Config(hidden=128, heads=2, ffn=256, n_enc=2, n_dec=2, vocab=300, max_step=32, beam=4, extra_decode_length=8,
+                    length_penalty=float(conf["length_penalty"]), pad_id=int(conf["pad_id"]), start_id=int(conf["start_id"]),
+                    end_id=int(conf["end_id"]))
+    assert np.array_equal(g["src"], synth.transformer_inputs(batch=6, min_len=3, max_len=9, vocab=300, seed=2))
+    tok, score, n = om.Seq2Seq(cfg, om.State(w=w, amax=amax)).generate(g["src"])
+    assert n == int(g["n"])
+    assert np.array_equal(tok, g["tokens"])
+    np.testing.assert_allclose(score, g["scores"], rtol=0, atol=1e-4)
+
+
+def test_reference_modules_tree_matches_the_oracle_when_present():
+    """Where oracle/make_ref.py has placed the reference's modules (the build does when a checkout exists), the oracle's
+    generation equals theirs on a second model; skipped elsewhere (the committed fixture above still pins it)."""
+    from oracle import make_ref
+
+    if not make_ref.available():
+        pytest.skip("oracle/_ref not made on this machine")
+    from oracle import ref_torch as rt
+
+    mods = rt.import_reference(str(make_ref.DEST))
+    kw = dict(hidden=64, heads=1, ffn=128, n_enc=1, n_dec=2, vocab=120, max_step=24, beam=2, extra_decode_length=6, seed=13)
+    conf, amax, w = synth.make_transformer(None, **kw)
+    cfg = om.Config(hidden=64, heads=1, ffn=128, n_enc=1, n_dec=2, vocab=120, max_step=24, beam=2, extra_decode_length=6,
+                    length_penalty=float(conf["length_penalty"]), pad_id=int(conf["pad_id"]), start_id=int(conf["start_id"]),
+                    end_id=int(conf["end_id"]))
+    src = synth.transformer_inputs(batch=3, min_len=3, max_len=7, vocab=120, seed=4)
+    a = om.Seq2Seq(cfg, om.State(w=w, amax=amax)).generate(src)
+    b = rt.RefSeq2Seq(mods, cfg, w, amax).generate(src)
+    assert a[2] == b[2] and np.array_equal(a[0], b[0])
+    np.testing.assert_allclose(a[1], b[1], rtol=0, atol=1e-4)
