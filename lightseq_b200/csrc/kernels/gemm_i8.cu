@@ -105,14 +105,8 @@ __device__ __forceinline__ void record_timeout(int* err) {
 // NC (32 or 16) consecutive columns of one output row. Written as a sequence of branch-free passes
 // over the 32 registers, with the (warp-uniform) mode tests between the passes: a taken
 // branch per element costs more than the arithmetic it guards.
-template <int BN, int NC = 32>
-__device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t (&r)[NC], int row, int col0,
-                                               const float* s_bias, const int* s_off, const float (&rr)[NC],
-                                               bool rr_valid, double* row_sum = nullptr, double* row_sq = nullptr,
-                                               EpiStats* stats = nullptr) {
-  const bool row_ok = row < p.m;
-  const bool full = (col0 + NC <= p.n);
-  int acc[NC];
+template <int NC>
+__device__ __forceinline__ void epilogue_acc(const GemmEpi& p, const uint32_t (&r)[NC], const int* s_off, int (&acc)[NC]) {
 #pragma unroll
   for (int j = 0; j < NC; ++j) acc[j] = (int)r[j];
   if (p.w_off != nullptr) {
@@ -125,22 +119,17 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
       acc[j + 3] += o.w;
     }
   }
-  if (p.out_kind == LS100_OUT_I32) {
-    if (!row_ok) return;
-    int* op = reinterpret_cast<int*>(p.out) + (long long)row * p.ldo + col0;
-    if (full && ((p.ldo & 3) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
-#pragma unroll
-      for (int j = 0; j < NC; j += 4) *reinterpret_cast<int4*>(op + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < NC; ++j)
-        if (col0 + j < p.n) op[j] = acc[j];
-    }
-    return;
-  }
+}
+
+// The arithmetic of QuantLinear.forward on NC accumulators of one row (every output kind but raw int32): v[] receives
+// the finished fp32 values, or for the int8 kinds the results of quant_biased.
+template <int NC>
+__device__ __forceinline__ void epilogue_arith(const GemmEpi& p, const int (&acc)[NC], int row, int col0,
+                                               const float* s_bias, const float (&rr)[NC], bool rr_valid, float (&v)[NC]) {
+  const bool row_ok = row < p.m;
+  const bool full = (col0 + NC <= p.n);
   // From here on the elements go through the arithmetic two at a time (packed fp32 pairs, every lane rounded as
   // the scalar instruction would): the epilogue is bound by instruction issue.
-  float v[NC];
   bool quantised = false;
   {
     const float2 sa = f2_set(p.s_acc);
@@ -268,6 +257,33 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
       }
     }
   }
+}
+
+// NC (32 or 16) consecutive columns of one output row: arithmetic, then the stores of this thread's own row.
+template <int BN, int NC = 32>
+__device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t (&r)[NC], int row, int col0,
+                                               const float* s_bias, const int* s_off, const float (&rr)[NC],
+                                               bool rr_valid, double* row_sum = nullptr, double* row_sq = nullptr,
+                                               EpiStats* stats = nullptr) {
+  const bool row_ok = row < p.m;
+  const bool full = (col0 + NC <= p.n);
+  int acc[NC];
+  epilogue_acc<NC>(p, r, s_off, acc);
+  if (p.out_kind == LS100_OUT_I32) {
+    if (!row_ok) return;
+    int* op = reinterpret_cast<int*>(p.out) + (long long)row * p.ldo + col0;
+    if (full && ((p.ldo & 3) == 0) && ((((uintptr_t)p.out) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < NC; j += 4) *reinterpret_cast<int4*>(op + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < NC; ++j)
+        if (col0 + j < p.n) op[j] = acc[j];
+    }
+    return;
+  }
+  float v[NC];
+  epilogue_arith<NC>(p, acc, row, col0, s_bias, rr, rr_valid, v);
   if (row_sum != nullptr) {  // statistics of the finished fp32 values for the fused LayerNorm
     double s[4] = {0.0, 0.0, 0.0, 0.0}, q[4] = {0.0, 0.0, 0.0, 0.0};  // four chains: fp64 latency, not rate, is the cost
 #pragma unroll
@@ -614,8 +630,16 @@ __global__ void __launch_bounds__(320) gemm_i8_tc_kernel(const __grid_constant__
 //   warp 1     TMEM allocator + MMA issuer
 //   warps 2-17 epilogue
 // No barrier couples the epilogue warps to each other: each stages its own bias / offset slice.
+// fp32 outputs (and their fp32 residual) go through shared memory: a thread owns one ROW of the accumulator, so its
+// own loads and stores touch 32 different lines per instruction, 16 bytes of each, and the L2 sees half-filled
+// sectors; instead every warp passes its 32 x 16 piece through a private staging block and moves it with
+// instructions that cover eight rows x 64 contiguous bytes (the residual arrives by cp.async, so no register waits
+// for it). The staging blocks take the place of the ring's fourth stage (plus a 16 KB tail), so such launches run a
+// three-stage ring. Inside a block the four 16-byte pieces of a row are permuted by (row / 2) % 4: both access
+// orders, a lane's own row and eight rows x four pieces, are then free of bank conflicts without padding.
 constexpr int P_BN = 256;
 constexpr int P_STAGES = 4;
+constexpr int P_STG_BYTES = 32 * 16 * 4;  // one 32 x 16 fp32 block; every epilogue warp has one for each direction
 constexpr int P_EPI_WARPS = 16;
 constexpr int P_THREADS = 64 + 32 * P_EPI_WARPS;
 
@@ -627,9 +651,11 @@ struct PersistSmem {
   static constexpr int VEC_OFFSET = BAR_OFFSET + 256;
   static constexpr int P_COLS = P_BN / (P_EPI_WARPS / 4);  // columns of a tile per epilogue warp: 64
   static constexpr int VEC_PER_WARP = P_COLS * 8;          // 64 fp32 bias + 64 int32 offsets
-  static constexpr int TOTAL = VEC_OFFSET + P_EPI_WARPS * VEC_PER_WARP + 1024;
+  static constexpr int STG_TAIL_OFFSET = VEC_OFFSET + P_EPI_WARPS * VEC_PER_WARP;  // outgoing blocks of warps 8..15
+  static constexpr int TOTAL = STG_TAIL_OFFSET + (P_EPI_WARPS / 2) * 2048 + 1024;
 };
 
+template <bool STAGED>
 __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                                         const __grid_constant__ CUtensorMap tma_b,
                                                                         const GemmEpi p, int tiles_n, int num_tiles) {
@@ -645,6 +671,8 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.k + BK - 1) / BK;
+  constexpr bool staged = STAGED;  // whole-line movement of fp32 outputs (the launcher checks the alignment it needs)
+  constexpr int stages = STAGED ? P_STAGES - 1 : P_STAGES;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
@@ -693,7 +721,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
           mbar_expect_tx(&full_bar[s], SM::STAGE_BYTES);
           tma_load_2d(sa, &tma_a, &full_bar[s], kb * BK, m0);
           tma_load_2d(sa + SM::A_BYTES, &tma_b, &full_bar[s], kb * BK, n0);
-          if (++s == P_STAGES) {
+          if (++s == stages) {
             s = 0;
             phase ^= 1;
           }
@@ -731,7 +759,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
                       (kb > 0 || kk > 0) ? 1u : 0u);
           }
           tc_commit(&empty_bar[s]);
-          if (++s == P_STAGES) {
+          if (++s == stages) {
             s = 0;
             phase ^= 1;
           }
@@ -749,13 +777,21 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
     float rr[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) rr[j] = 0.f;
+    // staged mode: this warp's incoming (residual) and outgoing 32 x 16 blocks, and the (row, 16-byte piece) this
+    // lane moves in each of the four instructions that cover a block: rows 8i + lane / 4, piece lane % 4
+    uint8_t* stg_in = smem + (P_STAGES - 1) * SM::STAGE_BYTES + ew * P_STG_BYTES;
+    uint8_t* stg_out = ew < 8 ? smem + (P_STAGES - 1) * SM::STAGE_BYTES + (P_EPI_WARPS + ew) * P_STG_BYTES
+                              : smem + SM::STG_TAIL_OFFSET + (ew - 8) * P_STG_BYTES;
+    const int mv_row = lane >> 2, mv_piece = lane & 3;
+    auto stg_at = [](int r, int piece) { return r * 64 + ((piece ^ ((r >> 1) & 3)) << 4); };  // byte offset in a block
     pdl_wait();  // the residual (and everything written below) belongs to the chain of kernels before this one
     int local = 0;
     bool dead = false;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const int buf = local & 1;
       const int n0 = (tile % tiles_n) * P_BN + grp * COLS;
-      const int row = (tile / tiles_n) * BM + quarter * 32 + lane;
+      const int row0 = (tile / tiles_n) * BM + quarter * 32;
+      const int row = row0 + lane;
       __syncwarp();
 #pragma unroll
       for (int i = lane; i < COLS; i += 32) {
@@ -765,6 +801,19 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
       }
       __syncwarp();
       if (dead) continue;
+      // the residual of this warp's first piece is requested before the accumulator is waited for
+      auto fetch_resid = [&](int c0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int br = 8 * i + mv_row;
+          if (row0 + br < p.m)
+            cp_async_16(stg_in + stg_at(br, mv_piece), p.resid + (long long)(row0 + br) * p.ldr + n0 + c0 + mv_piece * 4);
+        }
+        cp_async_commit();
+      };
+      if constexpr (staged) {
+        if (p.resid != nullptr && n0 + 16 <= p.n) fetch_resid(0);
+      }
       bool ok = mbar_wait(&tmem_full_bar[buf], (uint32_t)(local >> 1) & 1u);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -788,8 +837,43 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
           }
-          epilogue_chunk<P_BN, 16>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, false, nullptr, nullptr,
-                                   with_stats ? &stats : nullptr);
+          if (staged && n0 + c0 + 16 <= p.n) {
+            const bool with_resid = p.resid != nullptr;
+            if (with_resid) {  // the piece requested one step ago has landed in row order
+              cp_async_wait_all();
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float4 t = *reinterpret_cast<const float4*>(stg_in + stg_at(lane, j));
+                rr[4 * j] = t.x;
+                rr[4 * j + 1] = t.y;
+                rr[4 * j + 2] = t.z;
+                rr[4 * j + 3] = t.w;
+              }
+              __syncwarp();
+              if (!last && n0 + c0 + 32 <= p.n) fetch_resid(c0 + 16);  // in flight during this piece's arithmetic
+            }
+            int acc[16];
+            float v[16];
+            epilogue_acc<16>(p, r, s_off + c0, acc);
+            epilogue_arith<16>(p, acc, row, n0 + c0, s_bias + c0, rr, with_resid, v);
+            // own row in, eight rows x 64 bytes out per instruction
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<float4*>(stg_out + stg_at(lane, j)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            __syncwarp();
+            float* op = reinterpret_cast<float*>(p.out);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int br = 8 * i + mv_row;
+              const float4 t = *reinterpret_cast<const float4*>(stg_out + stg_at(br, mv_piece));
+              if (row0 + br < p.m) *reinterpret_cast<float4*>(op + (long long)(row0 + br) * p.ldo + n0 + c0 + mv_piece * 4) = t;
+            }
+            __syncwarp();  // the block is rewritten in the other order by the next piece
+          } else {
+            epilogue_chunk<P_BN, 16>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, false, nullptr, nullptr,
+                                     with_stats ? &stats : nullptr);
+          }
         } else if (c0 == 0) {  // the whole group lies beyond N: nothing to read, release at once
           tc_fence_before();
           __syncwarp();
@@ -859,10 +943,15 @@ static int launch_gemm_persist(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cuda
   const long long tiles = (long long)tiles_n * ((a->m + BM - 1) / BM);
   if (tiles > 0x7fffffffLL) return LS100_ERR_BAD_ARG;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
-  return ls100_launch(gemm_i8_persist_kernel, dim3(grid), dim3(P_THREADS), PersistSmem::TOTAL, stream, ta, tb, p,
-                      tiles_n, (int)tiles) == cudaSuccess
-             ? LS100_OK
-             : LS100_ERR_CUDA;
+  // fp32 outputs move through shared memory in whole lines when the rows on both sides are 16-byte aligned
+  const bool staged = a->out_kind == LS100_OUT_F32 && (a->ldo & 3) == 0 && (((uintptr_t)a->out) & 15) == 0 &&
+                      (a->resid == nullptr || ((a->ldr & 3) == 0 && (((uintptr_t)a->resid) & 15) == 0));
+  const cudaError_t e =
+      staged ? ls100_launch(gemm_i8_persist_kernel<true>, dim3(grid), dim3(P_THREADS), PersistSmem::TOTAL, stream, ta, tb, p,
+                            tiles_n, (int)tiles)
+             : ls100_launch(gemm_i8_persist_kernel<false>, dim3(grid), dim3(P_THREADS), PersistSmem::TOTAL, stream, ta, tb, p,
+                            tiles_n, (int)tiles);
+  return e == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
 
 template <int BN, int STAGES, bool LNF = false>
@@ -903,8 +992,10 @@ int ls100_gemm_i8_init_device() {
   if (!rc) rc = set_smem_attr<32, 4, true>();
   if (!rc) rc = set_smem_attr<64, 4, true>();
   if (!rc) rc = set_smem_attr<128, 3, true>();
-  if (!rc && cudaFuncSetAttribute(gemm_i8_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  PersistSmem::TOTAL) != cudaSuccess)
+  if (!rc && (cudaFuncSetAttribute(gemm_i8_persist_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   PersistSmem::TOTAL) != cudaSuccess ||
+              cudaFuncSetAttribute(gemm_i8_persist_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   PersistSmem::TOTAL) != cudaSuccess))
     rc = LS100_ERR_CUDA;
   return rc;
 }
