@@ -114,9 +114,19 @@ typedef struct {
    * (lightseq/inference/kernels/transformerKernels_int8.cc.cu:1718-1760). Both or neither. */
   int8_t* stat_max;
   float* stat_sum;
+  /* Optional table of everything after the output quantiser, for REQ_S8 / REQ_U8 outputs with the output quantiser on
+   * and no residual: the quantised output takes 255 values, so bias, activation and requantisation are a function
+   * of (column, value) that ls100_gemm_i8_build_table evaluates once per weight matrix. The many-tile kernel then
+   * reads it from shared memory instead of computing it per element (about a third of the epilogue's instructions
+   * for bias + requantise, a fifth with the erf GELU); the one-tile kernels ignore it. Results are identical either
+   * way. 16-byte aligned, ls100_gemm_i8_table_bytes(n) bytes, built with the same s_outq, bias, act, out_kind, s_req. */
+  const uint8_t* req_table;
 } ls100_gemm_i8_args;
 
 int ls100_gemm_i8(ls100_ctx* ctx, const ls100_gemm_i8_args* args, ls100_stream_t stream);
+/* Fills `table` for the given n, s_outq, bias, act, out_kind and s_req (the other members are not read). */
+size_t ls100_gemm_i8_table_bytes(int64_t n);
+int ls100_gemm_i8_build_table(ls100_ctx* ctx, const ls100_gemm_i8_args* args, uint8_t* table, ls100_stream_t stream);
 
 
 /* ----------------------------------------------------------------- embedding ---

@@ -55,6 +55,7 @@ class GemmI8Args(C.Structure):
         ("ln_gamma", C.c_void_p), ("ln_beta", C.c_void_p), ("ln_amax", C.c_float), ("ln_out", C.c_void_p),
         ("ln_ldq", C.c_int64),
         ("stat_max", C.c_void_p), ("stat_sum", C.c_void_p),
+        ("req_table", C.c_void_p),
     ]
 
 
@@ -164,6 +165,10 @@ lib.ls100_sm_count.restype = C.c_int
 lib.ls100_sm_count.argtypes = [C.c_void_p]
 lib.ls100_gemm_i8.restype = C.c_int
 lib.ls100_gemm_i8.argtypes = [C.c_void_p, C.POINTER(GemmI8Args), C.c_void_p]
+lib.ls100_gemm_i8_table_bytes.restype = C.c_size_t
+lib.ls100_gemm_i8_table_bytes.argtypes = [C.c_int64]
+lib.ls100_gemm_i8_build_table.restype = C.c_int
+lib.ls100_gemm_i8_build_table.argtypes = [C.c_void_p, C.POINTER(GemmI8Args), C.c_void_p, C.c_void_p]
 
 
 for _name, _cls in (("ls100_ln_quant", LnQuantArgs), ("ls100_embed", EmbedArgs), ("ls100_attn_self", AttnSelfArgs),

@@ -26,6 +26,9 @@
 #include "common.cuh"
 #include "ctx.h"
 
+#ifndef LS100_PTRACE
+#define LS100_PTRACE(id)
+#endif
 #ifndef LS100_TRACE
 #define LS100_TRACE(slot)
 #endif
@@ -50,6 +53,7 @@ struct GemmEpi {
   int8_t* ln_out;
   long long ln_ldq;
   // per (row, 64-column group) statistics of an int8 output: largest value and sum of exp((q - 127) * s_outq)
+  const uint8_t* table;  // [ceil(n / 256) * 256][256] requantisation table, or null
   int8_t* st_max;
   float* st_sum;
   int st_groups;
@@ -123,9 +127,13 @@ __device__ __forceinline__ void epilogue_acc(const GemmEpi& p, const uint32_t (&
 
 // The arithmetic of QuantLinear.forward on NC accumulators of one row (every output kind but raw int32): v[] receives
 // the finished fp32 values, or for the int8 kinds the results of quant_biased.
+// With `table` (this chunk's first column of a [column][256] table in shared memory, see ls100_gemm_i8_build_table)
+// everything after the output quantiser is read instead of computed: the quantised output has 255 values, so bias,
+// activation and requantisation are a function of (column, value).
 template <int NC>
 __device__ __forceinline__ void epilogue_arith(const GemmEpi& p, const int (&acc)[NC], int row, int col0,
-                                               const float* s_bias, const float (&rr)[NC], bool rr_valid, float (&v)[NC]) {
+                                               const float* s_bias, const float (&rr)[NC], bool rr_valid, float (&v)[NC],
+                                               const uint8_t* table = nullptr) {
   const bool row_ok = row < p.m;
   const bool full = (col0 + NC <= p.n);
   // From here on the elements go through the arithmetic two at a time (packed fp32 pairs, every lane rounded as
@@ -142,12 +150,25 @@ __device__ __forceinline__ void epilogue_arith(const GemmEpi& p, const int (&acc
   }
   if (p.s_outq > 0.f) {
     const float2 so = f2_set(p.s_outq), rso = f2_set(p.rs_outq);
-    if (p.out_kind == LS100_OUT_OUTQ_I8) {
+    if (p.out_kind == LS100_OUT_OUTQ_I8 || table != nullptr) {
 #pragma unroll
       for (int j = 0; j < NC; j += 2) {
         const float2 t = f2_quant_biased(f2_div_rn(make_float2(v[j], v[j + 1]), so, rso));
         v[j] = t.x;
         v[j + 1] = t.y;
+      }
+      if (table != nullptr) {
+        // the low byte of a biased result is the value as a two's-complement int8; a column's 256 entries start on
+        // a 256-byte boundary, so "or" joins base and index
+        const uint32_t base = smem_u32(table);
+#pragma unroll
+        for (int j = 0; j < NC; ++j) {
+          const uint32_t addr = (__float_as_uint(v[j]) & 0xffu) | base;
+          uint32_t e;
+          asm volatile("ld.shared.u8 %0, [%1];" : "=r"(e) : "r"(addr + (uint32_t)(j * 256)));
+          v[j] = __uint_as_float(e);
+        }
+        return;
       }
     } else {
 #pragma unroll
@@ -264,7 +285,7 @@ template <int BN, int NC = 32>
 __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t (&r)[NC], int row, int col0,
                                                const float* s_bias, const int* s_off, const float (&rr)[NC],
                                                bool rr_valid, double* row_sum = nullptr, double* row_sq = nullptr,
-                                               EpiStats* stats = nullptr) {
+                                               EpiStats* stats = nullptr, const uint8_t* table = nullptr) {
   const bool row_ok = row < p.m;
   const bool full = (col0 + NC <= p.n);
   int acc[NC];
@@ -283,7 +304,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
     return;
   }
   float v[NC];
-  epilogue_arith<NC>(p, acc, row, col0, s_bias, rr, rr_valid, v);
+  epilogue_arith<NC>(p, acc, row, col0, s_bias, rr, rr_valid, v, table);
   if (row_sum != nullptr) {  // statistics of the finished fp32 values for the fused LayerNorm
     double s[4] = {0.0, 0.0, 0.0, 0.0}, q[4] = {0.0, 0.0, 0.0, 0.0};  // four chains: fp64 latency, not rate, is the cost
 #pragma unroll
@@ -647,15 +668,43 @@ struct PersistSmem {
   static constexpr int A_BYTES = BM * BK;
   static constexpr int B_BYTES = P_BN * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = P_STAGES * STAGE_BYTES;
+  // the fourth stage and a 16 KB tail behind it are one 64 KB area for the modes that run a three-stage ring
+  static constexpr int AUX_OFFSET = (P_STAGES - 1) * STAGE_BYTES;
+  static constexpr int AUX_BYTES = 65536;
+  static constexpr int BAR_OFFSET = AUX_OFFSET + AUX_BYTES;
   static constexpr int VEC_OFFSET = BAR_OFFSET + 256;
   static constexpr int P_COLS = P_BN / (P_EPI_WARPS / 4);  // columns of a tile per epilogue warp: 64
   static constexpr int VEC_PER_WARP = P_COLS * 8;          // 64 fp32 bias + 64 int32 offsets
-  static constexpr int STG_TAIL_OFFSET = VEC_OFFSET + P_EPI_WARPS * VEC_PER_WARP;  // outgoing blocks of warps 8..15
-  static constexpr int TOTAL = STG_TAIL_OFFSET + (P_EPI_WARPS / 2) * 2048 + 1024;
+  static constexpr int TOTAL = VEC_OFFSET + P_EPI_WARPS * VEC_PER_WARP + 1024;
+};
+static_assert(PersistSmem::AUX_OFFSET + PersistSmem::AUX_BYTES >= P_STAGES * PersistSmem::STAGE_BYTES, "ring inside");
+static_assert(PersistSmem::TOTAL <= 232448, "shared memory of one SM");
+
+constexpr int P_PLAIN = 0, P_STAGED = 1, P_TABLE = 2;
+
+// The tiles of one CTA. Strided over the row-major tile list by default; with a requantisation table, a contiguous
+// run of the column-major list, so that the 256-column slice of the table in shared memory changes once or twice
+// per CTA instead of with every tile.
+struct TileWalk {
+  int first, step, count, tiles_m, tiles_n;
+  bool by_column;
+  __device__ __forceinline__ TileWalk(bool by_column_, int tiles_n_, int num_tiles) : tiles_n(tiles_n_), by_column(by_column_) {
+    tiles_m = num_tiles / tiles_n_;
+    if (by_column) {
+      first = (int)((long long)blockIdx.x * num_tiles / gridDim.x);
+      count = (int)((long long)(blockIdx.x + 1) * num_tiles / gridDim.x) - first;
+      step = 1;
+    } else {
+      first = blockIdx.x;
+      step = gridDim.x;
+      count = ((int)blockIdx.x < num_tiles) ? (num_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    }
+  }
+  __device__ __forceinline__ int n_tile(int i) const { const int t = first + i * step; return by_column ? t / tiles_m : t % tiles_n; }
+  __device__ __forceinline__ int m_tile(int i) const { const int t = first + i * step; return by_column ? t % tiles_m : t / tiles_n; }
 };
 
-template <bool STAGED>
+template <int MODE>
 __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                                         const __grid_constant__ CUtensorMap tma_b,
                                                                         const GemmEpi p, int tiles_n, int num_tiles) {
@@ -671,8 +720,10 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.k + BK - 1) / BK;
-  constexpr bool staged = STAGED;  // whole-line movement of fp32 outputs (the launcher checks the alignment it needs)
-  constexpr int stages = STAGED ? P_STAGES - 1 : P_STAGES;
+  constexpr bool staged = MODE == P_STAGED;  // whole-line movement of fp32 outputs (the launcher checks the alignment)
+  constexpr bool tabled = MODE == P_TABLE;    // requantisation table slice in shared memory
+  constexpr int stages = MODE == P_PLAIN ? P_STAGES : P_STAGES - 1;
+  const TileWalk walk(tabled, tiles_n, num_tiles);
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
@@ -707,9 +758,9 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
       uint32_t phase = 0;
       int s = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int n0 = (tile % tiles_n) * P_BN;
-        const int m0 = (tile / tiles_n) * BM;
+      for (int it = 0; it < walk.count && ok; ++it) {
+        const int n0 = walk.n_tile(it) * P_BN;
+        const int m0 = walk.m_tile(it) * BM;
         for (int kb = 0; kb < num_kb; ++kb) {
           // a stage that has never been filled reads as released (parity of the phase before the first)
           if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
@@ -735,13 +786,14 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
       int s = 0;
       int local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      for (; local < walk.count && ok; ++local) {
         const int buf = local & 1;
         if (!mbar_wait(&tmem_empty_bar[buf], ((uint32_t)(local >> 1) & 1u) ^ 1u)) {  // drained by the epilogue
           record_timeout(p.err);
           break;
         }
         tc_fence_after();
+        LS100_PTRACE(24);
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P_BN);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&full_bar[s], phase)) {
@@ -765,6 +817,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
           }
         }
         if (ok) tc_commit(&tmem_full_bar[buf]);
+        LS100_PTRACE(25);
       }
     }
   } else {
@@ -779,28 +832,47 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
     for (int j = 0; j < 16; ++j) rr[j] = 0.f;
     // staged mode: this warp's incoming (residual) and outgoing 32 x 16 blocks, and the (row, 16-byte piece) this
     // lane moves in each of the four instructions that cover a block: rows 8i + lane / 4, piece lane % 4
-    uint8_t* stg_in = smem + (P_STAGES - 1) * SM::STAGE_BYTES + ew * P_STG_BYTES;
-    uint8_t* stg_out = ew < 8 ? smem + (P_STAGES - 1) * SM::STAGE_BYTES + (P_EPI_WARPS + ew) * P_STG_BYTES
-                              : smem + SM::STG_TAIL_OFFSET + (ew - 8) * P_STG_BYTES;
+    uint8_t* stg_in = smem + SM::AUX_OFFSET + ew * P_STG_BYTES;
+    uint8_t* stg_out = smem + SM::AUX_OFFSET + (P_EPI_WARPS + ew) * P_STG_BYTES;
     const int mv_row = lane >> 2, mv_piece = lane & 3;
     auto stg_at = [](int r, int piece) { return r * 64 + ((piece ^ ((r >> 1) & 3)) << 4); };  // byte offset in a block
     pdl_wait();  // the residual (and everything written below) belongs to the chain of kernels before this one
     int local = 0;
     bool dead = false;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+    int table_tile = -1;  // the column tile whose table slice is in shared memory
+    const uint8_t* table_c = nullptr;
+    for (; local < walk.count; ++local) {
       const int buf = local & 1;
-      const int n0 = (tile % tiles_n) * P_BN + grp * COLS;
-      const int row0 = (tile / tiles_n) * BM + quarter * 32;
+      const int n0 = walk.n_tile(local) * P_BN + grp * COLS;
+      const int row0 = walk.m_tile(local) * BM + quarter * 32;
       const int row = row0 + lane;
-      __syncwarp();
-#pragma unroll
-      for (int i = lane; i < COLS; i += 32) {
-        const int n = n0 + i;
-        s_bias[i] = (p.bias != nullptr && n < p.n) ? __ldg(p.bias + n) : 0.f;
-        s_off[i] = (p.w_off != nullptr && n < p.n) ? __ldg(p.w_off + n) : 0;
+      if constexpr (tabled) {
+        // All sixteen epilogue warps walk the same tiles, so they meet here together (also the ones that gave up on
+        // a wait: a warp that stayed away would leave the others at the barrier for good).
+        if (walk.n_tile(local) != table_tile) {
+          table_tile = walk.n_tile(local);
+          asm volatile("bar.sync 1, %0;" ::"n"(32 * P_EPI_WARPS) : "memory");  // the old slice is no longer read
+          const uint8_t* src = p.table + (long long)table_tile * SM::AUX_BYTES;
+          for (int i = threadIdx.x - 64; i < SM::AUX_BYTES / 16; i += 32 * P_EPI_WARPS)
+            cp_async_16(smem + SM::AUX_OFFSET + i * 16, src + i * 16);
+          cp_async_commit();
+          cp_async_wait_all();
+          asm volatile("bar.sync 1, %0;" ::"n"(32 * P_EPI_WARPS) : "memory");
+        }
+        table_c = smem + SM::AUX_OFFSET + grp * COLS * 256;
       }
-      __syncwarp();
+      if (!tabled || p.w_off != nullptr) {  // with a table the bias is inside it
+        __syncwarp();
+#pragma unroll
+        for (int i = lane; i < COLS; i += 32) {
+          const int n = n0 + i;
+          s_bias[i] = (p.bias != nullptr && n < p.n) ? __ldg(p.bias + n) : 0.f;
+          s_off[i] = (p.w_off != nullptr && n < p.n) ? __ldg(p.w_off + n) : 0;
+        }
+        __syncwarp();
+      }
       if (dead) continue;
+      LS100_PTRACE(20);
       // the residual of this warp's first piece is requested before the accumulator is waited for
       auto fetch_resid = [&](int c0) {
 #pragma unroll
@@ -822,64 +894,70 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
         continue;
       }
       tc_fence_after();
+      LS100_PTRACE(21);
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P_BN + grp * COLS);
       EpiStats stats = {0.f, 0.f, 0x80808080u};
       const bool with_stats = p.st_max != nullptr && p.out_kind == LS100_OUT_OUTQ_I8;
+      auto present = [&](int c0) { return c0 < COLS && n0 + c0 < p.n; };
+      if (!present(0)) {  // the whole group lies beyond N: nothing to read, release at once
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+      }
+      // (Reading the next piece from TMEM during this piece's arithmetic, with a second register set, was measured
+      // 40 % slower: 96 registers per thread do not hold both.)
 #pragma unroll 1
-      for (int c0 = 0; c0 < COLS; c0 += 16) {
-        const bool last = (c0 + 16 == COLS) || (n0 + c0 + 16 >= p.n);
-        if (n0 + c0 < p.n) {
-          uint32_t r[16];
-          tmem_ld16(t_addr + (uint32_t)c0, r);
-          tmem_ld_wait();
-          if (last) {  // this warp's part of the buffer is in registers: hand it back to the MMA warp
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
-          }
-          if (staged && n0 + c0 + 16 <= p.n) {
-            const bool with_resid = p.resid != nullptr;
-            if (with_resid) {  // the piece requested one step ago has landed in row order
-              cp_async_wait_all();
-              __syncwarp();
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float4 t = *reinterpret_cast<const float4*>(stg_in + stg_at(lane, j));
-                rr[4 * j] = t.x;
-                rr[4 * j + 1] = t.y;
-                rr[4 * j + 2] = t.z;
-                rr[4 * j + 3] = t.w;
-              }
-              __syncwarp();
-              if (!last && n0 + c0 + 32 <= p.n) fetch_resid(c0 + 16);  // in flight during this piece's arithmetic
-            }
-            int acc[16];
-            float v[16];
-            epilogue_acc<16>(p, r, s_off + c0, acc);
-            epilogue_arith<16>(p, acc, row, n0 + c0, s_bias + c0, rr, with_resid, v);
-            // own row in, eight rows x 64 bytes out per instruction
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              *reinterpret_cast<float4*>(stg_out + stg_at(lane, j)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            __syncwarp();
-            float* op = reinterpret_cast<float*>(p.out);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int br = 8 * i + mv_row;
-              const float4 t = *reinterpret_cast<const float4*>(stg_out + stg_at(br, mv_piece));
-              if (row0 + br < p.m) *reinterpret_cast<float4*>(op + (long long)(row0 + br) * p.ldo + n0 + c0 + mv_piece * 4) = t;
-            }
-            __syncwarp();  // the block is rewritten in the other order by the next piece
-          } else {
-            epilogue_chunk<P_BN, 16>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, false, nullptr, nullptr,
-                                     with_stats ? &stats : nullptr);
-          }
-        } else if (c0 == 0) {  // the whole group lies beyond N: nothing to read, release at once
+      for (int c0 = 0; present(c0); c0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(t_addr + (uint32_t)c0, r);
+        tmem_ld_wait();
+        // `last`: the accumulator buffer goes back to the MMA warp (this warp's last read of it has completed)
+        const bool last = !present(c0 + 16);
+        LS100_PTRACE(22);
+        if (last) {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
         }
-        if (last) break;
+        if (staged && n0 + c0 + 16 <= p.n) {
+          const bool with_resid = p.resid != nullptr;
+          if (with_resid) {  // the piece requested one step ago has landed in row order
+            cp_async_wait_all();
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float4 t = *reinterpret_cast<const float4*>(stg_in + stg_at(lane, j));
+              rr[4 * j] = t.x;
+              rr[4 * j + 1] = t.y;
+              rr[4 * j + 2] = t.z;
+              rr[4 * j + 3] = t.w;
+            }
+            __syncwarp();
+            if (!last && n0 + c0 + 32 <= p.n) fetch_resid(c0 + 16);  // in flight during this piece's arithmetic
+          }
+          int acc[16];
+          float v[16];
+          epilogue_acc<16>(p, r, s_off + c0, acc);
+          epilogue_arith<16>(p, acc, row, n0 + c0, s_bias + c0, rr, with_resid, v);
+          // own row in, eight rows x 64 bytes out per instruction
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<float4*>(stg_out + stg_at(lane, j)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          __syncwarp();
+          float* op = reinterpret_cast<float*>(p.out);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int br = 8 * i + mv_row;
+            const float4 t = *reinterpret_cast<const float4*>(stg_out + stg_at(br, mv_piece));
+            if (row0 + br < p.m) *reinterpret_cast<float4*>(op + (long long)(row0 + br) * p.ldo + n0 + c0 + mv_piece * 4) = t;
+          }
+          __syncwarp();  // the block is rewritten in the other order by the next piece
+        } else {
+          epilogue_chunk<P_BN, 16>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, false, nullptr, nullptr,
+                                   with_stats ? &stats : nullptr, tabled ? table_c + c0 * 256 : nullptr);
+        }
+        LS100_PTRACE(23);
+      
       }
       if (with_stats && row < p.m && n0 < p.n) {  // COLS == 64: this warp's column group is one statistics group
         const unsigned m2 = __vmaxs4(stats.max4, stats.max4 >> 16);
@@ -896,6 +974,29 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * P_BN);
   }
+}
+
+// One thread per (column, value): what the epilogue computes after the output quantiser, with the scalar forms of the
+// same roundings (and the float64-erf GELU the fast path falls back to), so that reading the table and computing
+// agree in every bit. Value 0x80 (-128) never leaves the quantiser; it repeats the entry of -127.
+__global__ void requant_table_kernel(GemmEpi p, uint8_t* table, int cols_padded) {
+  const int col = blockIdx.x;
+  const int i = threadIdx.x;
+  if (col >= cols_padded) return;
+  uint8_t out = 0;
+  if (col < p.n) {
+    int q = (int)(int8_t)i;
+    if (q == -128) q = -127;
+    float v = __fmul_rn((float)q, p.s_outq);
+    if (p.bias != nullptr) v = __fadd_rn(v, p.bias[col]);
+    if (p.act == LS100_ACT_RELU)
+      v = fmaxf(v, 0.f);
+    else if (p.act == LS100_ACT_GELU)
+      v = gelu_erf_exact(v);
+    const float sub = (p.out_kind == LS100_OUT_REQ_U8) ? 127.f : 0.f;
+    out = (uint8_t)(__float_as_uint(quant_biased(__fsub_rn(div_rn(v, p.s_req, p.rs_req), sub))) & 0xffu);
+  }
+  table[(long long)col * 256 + i] = out;
 }
 
 static GemmEpi make_epi(const ls100_ctx* ctx, const ls100_gemm_i8_args* a) {
@@ -924,6 +1025,7 @@ static GemmEpi make_epi(const ls100_ctx* ctx, const ls100_gemm_i8_args* a) {
   p.ln_rs = a->ln_amax > 0.f ? 1.0f / p.ln_scale : 0.f;
   p.ln_out = a->ln_out;
   p.ln_ldq = a->ln_ldq;
+  p.table = a->req_table;
   p.st_max = a->stat_max;
   p.st_sum = a->stat_sum;
   p.st_groups = (a->n + 63) / 64;
@@ -943,14 +1045,13 @@ static int launch_gemm_persist(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cuda
   const long long tiles = (long long)tiles_n * ((a->m + BM - 1) / BM);
   if (tiles > 0x7fffffffLL) return LS100_ERR_BAD_ARG;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
-  // fp32 outputs move through shared memory in whole lines when the rows on both sides are 16-byte aligned
+  // fp32 outputs move through shared memory in whole lines when the rows on both sides are 16-byte aligned; int8
+  // outputs whose bias / activation / requantisation the caller tabulated read the table
   const bool staged = a->out_kind == LS100_OUT_F32 && (a->ldo & 3) == 0 && (((uintptr_t)a->out) & 15) == 0 &&
                       (a->resid == nullptr || ((a->ldr & 3) == 0 && (((uintptr_t)a->resid) & 15) == 0));
-  const cudaError_t e =
-      staged ? ls100_launch(gemm_i8_persist_kernel<true>, dim3(grid), dim3(P_THREADS), PersistSmem::TOTAL, stream, ta, tb, p,
-                            tiles_n, (int)tiles)
-             : ls100_launch(gemm_i8_persist_kernel<false>, dim3(grid), dim3(P_THREADS), PersistSmem::TOTAL, stream, ta, tb, p,
-                            tiles_n, (int)tiles);
+  const bool tabled = a->req_table != nullptr;  // validated by the caller: int8 requantised kind, output quantiser, no residual
+  auto kern = staged ? gemm_i8_persist_kernel<P_STAGED> : tabled ? gemm_i8_persist_kernel<P_TABLE> : gemm_i8_persist_kernel<P_PLAIN>;
+  const cudaError_t e = ls100_launch(kern, dim3(grid), dim3(P_THREADS), PersistSmem::TOTAL, stream, ta, tb, p, tiles_n, (int)tiles);
   return e == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
 
@@ -992,9 +1093,11 @@ int ls100_gemm_i8_init_device() {
   if (!rc) rc = set_smem_attr<32, 4, true>();
   if (!rc) rc = set_smem_attr<64, 4, true>();
   if (!rc) rc = set_smem_attr<128, 3, true>();
-  if (!rc && (cudaFuncSetAttribute(gemm_i8_persist_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (!rc && (cudaFuncSetAttribute(gemm_i8_persist_kernel<P_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    PersistSmem::TOTAL) != cudaSuccess ||
-              cudaFuncSetAttribute(gemm_i8_persist_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+              cudaFuncSetAttribute(gemm_i8_persist_kernel<P_STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   PersistSmem::TOTAL) != cudaSuccess ||
+              cudaFuncSetAttribute(gemm_i8_persist_kernel<P_TABLE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    PersistSmem::TOTAL) != cudaSuccess))
     rc = LS100_ERR_CUDA;
   return rc;
@@ -1013,6 +1116,9 @@ extern "C" int ls100_gemm_i8(ls100_ctx* ctx, const ls100_gemm_i8_args* a, ls100_
   if (a->resid && a->ldr < a->n) return LS100_ERR_BAD_ARG;
   if (a->ldo < a->n) return LS100_ERR_BAD_ARG;
   cudaStream_t stream = (cudaStream_t)stream_;
+  if (a->req_table && ((a->out_kind != LS100_OUT_REQ_S8 && a->out_kind != LS100_OUT_REQ_U8) || !(a->s_outq > 0.f) ||
+                       a->resid || a->ln_out || a->stat_max || (((uintptr_t)a->req_table) & 15)))
+    return LS100_ERR_BAD_ARG;
   if ((a->stat_max != nullptr) != (a->stat_sum != nullptr)) return LS100_ERR_BAD_ARG;
   if (a->stat_max) {  // only the many-tile kernel's epilogue keeps the statistics (its warps own whole 64-column groups)
     if (a->out_kind != LS100_OUT_OUTQ_I8 || a->ln_out || (((uintptr_t)a->stat_sum) & 3)) return LS100_ERR_BAD_ARG;
@@ -1059,4 +1165,19 @@ extern "C" int ls100_gemm_i8(ls100_ctx* ctx, const ls100_gemm_i8_args* a, ls100_
   // per launch, so those keep four stages.
   if (mt == 1 && a->k > 4 * BK && ctas(32) <= sms) return launch_gemm<32, 8>(ctx, a, stream);
   return launch_gemm<32, 4>(ctx, a, stream);
+}
+
+extern "C" size_t ls100_gemm_i8_table_bytes(int64_t n) { return n > 0 ? (size_t)((n + 255) / 256) * 65536 : 0; }
+
+extern "C" int ls100_gemm_i8_build_table(ls100_ctx* ctx, const ls100_gemm_i8_args* a, uint8_t* table, ls100_stream_t stream_) {
+  using namespace ls100;
+  if (!ctx || !a || !table || a->n <= 0) return LS100_ERR_BAD_ARG;
+  if ((a->out_kind != LS100_OUT_REQ_S8 && a->out_kind != LS100_OUT_REQ_U8) || !(a->s_outq > 0.f) || !(a->s_req > 0.f) ||
+      a->resid || a->act < LS100_ACT_NONE || a->act > LS100_ACT_GELU)
+    return LS100_ERR_BAD_ARG;
+  if (((uintptr_t)table) & 15) return LS100_ERR_ALIGN;
+  const GemmEpi p = make_epi(ctx, a);
+  const int cols = (int)((a->n + 255) / 256 * 256);
+  requant_table_kernel<<<cols, 256, 0, (cudaStream_t)stream_>>>(p, table, cols);
+  return cudaGetLastError() == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }

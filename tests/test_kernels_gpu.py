@@ -206,6 +206,32 @@ def test_gemm_gelu_requant_bit_exact(m, n, k):
     assert np.array_equal(out.cpu().numpy(), ref)
 
 
+@pytest.mark.parametrize("m,n,k,act,unsigned_out", [(4096, 3072, 256, "gelu", False), (5000, 2440, 208, "relu", True),
+                                                    (9000, 2100, 128, "none", False), (16384, 2304, 768, "none", False),
+                                                    (300, 512, 256, "gelu", False)])
+def test_gemm_requantisation_table_gives_the_computed_bytes(m, n, k, act, unsigned_out):
+    """Bias, activation and requantisation read from the per-column table (built on the device with the scalar forms
+    of the same roundings) instead of computed per element: the many-tile kernel walks its tiles column by column
+    and keeps one 256-column slice of the table in shared memory. The result must equal the oracle AND the bytes of
+    the computing path; N ending inside a 64-column group and a 256-column tile, ragged M, K ending inside a
+    k-block, and a problem small enough for the one-tile kernel (which ignores the table)."""
+    st, x, w, b = _qlinear_case(41, m, n, k)
+    pre = om.qlinear(st, x, "l")
+    post = {"gelu": oq.gelu, "relu": lambda t: np.maximum(t, 0), "none": lambda t: t}[act](pre)
+    amax2 = float(F32(4 * post.std()))
+    ref, s2 = oq.quantize(post, amax2, unsigned=unsigned_out)
+    xq, s_x = oq.quantize(x, st.amax["l.in"])
+    wq, s_w = oq.quantize(w, st.amax["l.w"])
+    kw = dict(s_acc=float(F32(s_x * s_w)), out_kind=L.OUT_REQ_U8 if unsigned_out else L.OUT_REQ_S8,
+              s_outq=float(oq.scale_of(st.amax["l.out"])), bias=dev(b),
+              act={"gelu": L.ACT_GELU, "relu": L.ACT_RELU, "none": L.ACT_NONE}[act], s_req=float(s2))
+    computed = gemm(dev(xq), dev(wq), **kw)
+    tabled = gemm(dev(xq), dev(wq), table=True, **kw)
+    sync_check()
+    assert np.array_equal(computed.cpu().numpy(), ref)
+    assert np.array_equal(tabled.cpu().numpy(), ref)
+
+
 def test_gemm_rejects_bad_arguments():
     a = dev(np.zeros((16, 64), np.int8))
     out = empty((16, 16), torch.int32)
