@@ -404,6 +404,33 @@ def kernel_cases(torch, L, conf, B, S, step):
                          bias=ebz.data_ptr(), resid=ex[j].data_ptr(), ldr=768, out_kind=L.OUT_F32, out=ex[j].data_ptr(), ldo=768)
         L.call("ls100_gemm_i8", CTX[0], a, st)
 
+    # first FFN of the same layer: bias + erf-GELU + requantise to int8, computed per element and read from the
+    # per-column requantisation table (ls100_gemm_i8_build_table)
+    ew3 = i8(3072, 768)
+    eb3 = torch.zeros(3072, device=dev)
+    ffn1_out = [torch.empty(er, 3072, dtype=torch.int8, device=dev) for _ in range(3)]
+
+    def ffn1_args(i):
+        j = i % 3
+        return L.GemmI8Args(a=ea[j].data_ptr(), lda=3072, w=ew3.data_ptr(), ldw=768, m=er, n=3072, k=768, s_acc=1e-4, s_outq=0.47,
+                            bias=eb3.data_ptr(), act=L.ACT_GELU, out_kind=L.OUT_REQ_S8, s_req=0.47, out=ffn1_out[j].data_ptr(), ldo=3072)
+
+    tab = torch.empty(L.lib.ls100_gemm_i8_table_bytes(3072), dtype=torch.uint8, device=dev)
+    L.check(L.lib.ls100_gemm_i8_build_table(CTX[0].handle, L.C.byref(ffn1_args(0)), L.C.c_void_p(tab.data_ptr()), None),
+            "ls100_gemm_i8_build_table")
+
+    def gemm_enc_ffn1_computed(i, st):
+        L.call("ls100_gemm_i8", CTX[0], ffn1_args(i), st)
+
+    def gemm_enc_ffn1(i, st):
+        a = ffn1_args(i)
+        a.req_table = tab.data_ptr()
+        L.call("ls100_gemm_i8", CTX[0], a, st)
+
+    cases["gemm_enc_ffn1"] = (gemm_enc_ffn1, 2 * er * 3072 * 768, "tensor",
+                              f"gemm_i8_persist_kernel<table>, {er}x3072x768, bias+GELU+requantise read from the per-column table")
+    cases["gemm_enc_ffn1_computed"] = (gemm_enc_ffn1_computed, 2 * er * 3072 * 768, "tensor",
+                                       f"gemm_i8_persist_kernel, {er}x3072x768, bias+GELU+requantise computed per element")
     cases["gemm_enc_out"] = (gemm_enc_out, er * 768 + 768 * 768 + 2 * er * 768 * 4, "hbm",
                              f"gemm_i8_persist_kernel, {er}x768x768, fake-quant+bias+residual, fp32 out")
     cases["gemm_enc_ffn2"] = (gemm_enc_ffn2, er * 3072 + 768 * 3072 + 2 * er * 768 * 4, "hbm",
@@ -1040,7 +1067,7 @@ def main():
     ap.add_argument("--decode-steps", type=int, default=-1,
                     help="cap the number of decode steps per generation (profiling aid; the result is not a bench value)")
     ap.add_argument("--kernel", default=None,
-                    help="run one kernel family alone (gemm_dec, gemm_dec_ln, gemm_logits, gemm_enc_qkv, gemm_enc_out, gemm_enc_ffn2, gemm_square, attn_self, attn_dec, attn_cross, beam_topk, ln_quant), or a measurement: i8_peak, phase_floor")
+                    help="run one kernel family alone (gemm_dec, gemm_dec_ln, gemm_logits, gemm_enc_qkv, gemm_enc_out, gemm_enc_ffn1, gemm_enc_ffn1_computed, gemm_enc_ffn2, gemm_square, attn_self, attn_dec, attn_cross, beam_topk, ln_quant), or a measurement: i8_peak, phase_floor")
     ap.add_argument("--workload", default=None, choices=["bert", "vit", "gpt", "big", "eos"],
                     help="run another BASELINE configuration (BERT-base, GPT-2 medium, Transformer-big) on one GPU, or the "
                          "benchmark model with a boosted EOS (early-stop bookkeeping)")

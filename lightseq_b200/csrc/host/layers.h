@@ -46,6 +46,8 @@ class QuantTransformerEncoderLayer : public Layer {
     fc2_.load(*ctx, wf, prefix + ".fc2", relu, true, true, "", "", true, true);  // the encoder-only file formats hold no fc2.out
     ln1_.load(*ctx, wf, prefix + ".ln1", hidden);
     ln2_.load(*ctx, wf, prefix + ".ln2", hidden);
+    // what follows fc1's output quantiser is a function of (column, value): tabulated once for the many-tile GEMM
+    fc1_.build_table(*ctx, relu ? LS100_OUT_REQ_U8 : LS100_OUT_REQ_S8, (int)act_, true, fc2_.s_in);
   }
   // (inp, pad_mask) -> out, in place on the residual stream
   Variable* operator()(StackBuffers* bufs, Variable* pad_mask) {
@@ -379,6 +381,7 @@ class QuantGptLayer : public Layer {
     ln1_.load(*ctx, wf, prefix + ".ln1", hidden);
     ln2_.load(*ctx, wf, prefix + ".ln2", hidden);
     s_kv_ = wf.amax(prefix + ".kv") / 127.0f;
+    fc1_.build_table(*ctx, LS100_OUT_REQ_S8, (int)Act::Gelu, true, fc2_.s_in);  // used by the prompt pass's many-tile GEMM
     const size_t cache = (size_t)max_batch_size * max_seq_len * hidden;
     k_cache_ = ctx->alloc_n<int8_t>(cache);
     v_cache_ = ctx->alloc_n<int8_t>(cache);

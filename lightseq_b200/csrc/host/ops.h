@@ -24,6 +24,37 @@ struct QLinearParams {
   float amax_in = 0, amax_w = 0, amax_out = 0;
   float s_in = 0, s_w = 0, s_out = 0, s_acc = 0;
   bool unsigned_in = false;
+  // Optional table of bias + activation + requantisation per (column, quantised output value), see
+  // ls100_gemm_i8_args::req_table, and the epilogue it was built for
+  uint8_t* req_table = nullptr;
+  int tab_out_kind = -1, tab_act = -1;
+  bool tab_bias = false;
+  float tab_s_req = 0.f;
+
+  void build_table(Context& ctx, int out_kind, int act, bool add_bias, float s_req) {
+    if (!(s_out > 0.f) || !(s_req > 0.f)) return;
+    ls100_gemm_i8_args a;
+    memset(&a, 0, sizeof(a));
+    a.n = n;
+    a.s_outq = s_out;
+    a.bias = add_bias ? bias : nullptr;
+    a.act = act;
+    a.out_kind = out_kind;
+    a.s_req = s_req;
+    req_table = ctx.alloc_n<uint8_t>(ls100_gemm_i8_table_bytes(n));
+    LS_RC(ls100_gemm_i8_build_table(ctx.kernels(), &a, req_table, ctx.get_stream()));
+    LS_CUDA(cudaStreamSynchronize(ctx.get_stream()));
+    tab_out_kind = out_kind;
+    tab_act = act;
+    tab_bias = add_bias;
+    tab_s_req = s_req;
+  }
+  const uint8_t* table_for(int out_kind, int act, bool out_quant, bool add_bias, float s_req, bool has_resid) const {
+    return (req_table && out_quant && !has_resid && out_kind == tab_out_kind && act == tab_act && add_bias == tab_bias &&
+            s_req == tab_s_req)
+               ? req_table
+               : nullptr;
+  }
 
   // Uploads W (fp32), quantises it on the device (ls100_quantize_weight) and frees the staging copy.
   void load(Context& ctx, const WeightsFile& wf, const std::string& name, bool unsigned_in_, bool has_in = true,
@@ -132,6 +163,7 @@ class QuantLinearOp : public Operator {
     }
     a.stat_max = stat_max_;
     a.stat_sum = stat_sum_;
+    if (!ln_out_ && !stat_max_) a.req_table = p_->table_for(out_kind_, (int)act_, out_quant_, add_bias_, s_req_, resid_ != nullptr);
     LS_RC(ls100_gemm_i8(ctx_->kernels(), &a, ctx_->get_stream()));
   }
 
