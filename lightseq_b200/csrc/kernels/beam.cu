@@ -61,8 +61,8 @@ __device__ __forceinline__ unsigned topk_key(int val, int idx) {
 
 // Re-selects the K best keys of buf[0 .. n) into buf[0 .. min(K, n)), best first. Returns the new
 // threshold: the value of the K-th best, or -128 while fewer than K candidates exist.
-__device__ __forceinline__ int topk_flush(unsigned* buf, int n, int K, int lane, int* n_kept) {
-  constexpr int PER = (TOPK_BUF + 31) / 32;
+template <int PER>
+__device__ __forceinline__ int topk_flush_n(unsigned* buf, int n, int K, int lane, int* n_kept) {
   unsigned keys[PER];
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
@@ -91,6 +91,12 @@ __device__ __forceinline__ int topk_flush(unsigned* buf, int n, int K, int lane,
   __syncwarp();
   *n_kept = min(n, K);
   return thr;
+}
+// Almost every re-selection holds a few dozen keys (the current best K and the handful that passed the threshold
+// since): two keys per lane then, the full buffer only after a chunk that arrived before any threshold existed.
+__device__ __forceinline__ int topk_flush(unsigned* buf, int n, int K, int lane, int* n_kept) {
+  if (n <= 64) return topk_flush_n<2>(buf, n, K, lane, n_kept);
+  return topk_flush_n<(TOPK_BUF + 31) / 32>(buf, n, K, lane, n_kept);
 }
 
 __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_beam_topk_args a) {
@@ -139,6 +145,26 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
     v2 = none;
     if (off + 2 * TOPK_WARPS * 512 < a.vocab) v2 = load_row16(lp, off + 2 * TOPK_WARPS * 512, a.vocab);
     const unsigned w4[4] = {(unsigned)v.x, (unsigned)v.y, (unsigned)v.z, (unsigned)v.w};
+    if (ch == warp) {
+      // First chunk of this warp: without a threshold all of its 512 bytes would go through the candidate buffer.
+      // The K-th largest of the 32 lanes' own maxima is a value that at least K bytes of the chunk reach, so
+      // nothing below it can be among the row's K best (ties at it are kept: the test below is "strictly above").
+      unsigned m = __vmaxs4(__vmaxs4(w4[0], w4[1]), __vmaxs4(w4[2], w4[3]));
+      m = __vmaxs4(m, m >> 16);
+      m = __vmaxs4(m, m >> 8);
+      int cur = (int)(int8_t)(m & 0xffu), kth = -128;
+      for (int r = 0; r < K; ++r) {
+        kth = cur;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) kth = max(kth, __shfl_xor_sync(0xffffffffu, kth, o));
+        const unsigned who = __ballot_sync(0xffffffffu, cur == kth);
+        if (lane == __ffs(who) - 1) cur = -128;  // one instance leaves per round
+      }
+      if (kth - 1 > thr) {
+        thr = kth - 1;
+        add7 = 0x01010101u * (unsigned)(127 - max(thr, 0));
+      }
+    }
     {  // the other warps of the row raise the bar too: nothing below any warp's k-th best can be in the row's top k
       const int shared_thr = *((volatile int*)&s_thr);
       if (shared_thr > thr) {
