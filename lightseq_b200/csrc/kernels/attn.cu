@@ -221,18 +221,30 @@ __global__ void __launch_bounds__(128, 7) attn_dec_kernel(const ls100_attn_dec_a
   if (wid >= a.rows * a.heads) return;
   const int r = wid / a.heads, h = wid % a.heads;
   const int hidden = a.heads * DH;
-  const int step = *a.step_ptr;
-  const int L = step + 1;
   int* slot_s = slot_all + warp * a.max_step;
   const int g = lane >> 2, c = lane & 3;
-  {
-    const int32_t* anc = a.anc ? a.anc + (long long)r * a.max_step : nullptr;
-    for (int p = lane; p < L; p += 32) slot_s[p] = (anc && p < step) ? anc[p] : r;
-  }
+  // Everything the first cache reads wait for is requested in one go: this row's q / k / v, the step counter, and the
+  // ancestry slots of the first 128 positions (read whatever the step is: the table row has max_step entries), so that
+  // one round trip to the L2 stands before the cache loads instead of three.
   const int8_t* row = a.qkv + (long long)r * a.ld_qkv + h * DH + c * 16;
   const int4 q4 = *reinterpret_cast<const int4*>(row);
   const int4 knew = *reinterpret_cast<const int4*>(row + hidden);
   const int4 vnew = *reinterpret_cast<const int4*>(row + 2 * hidden);
+  const int32_t* anc = a.anc ? a.anc + (long long)r * a.max_step : nullptr;
+  int anc_pre[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int p = lane + 32 * i;
+    anc_pre[i] = (anc && p < a.max_step) ? anc[p] : r;
+  }
+  const int step = *a.step_ptr;
+  const int L = step + 1;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int p = lane + 32 * i;
+    if (p < L) slot_s[p] = (p < step) ? anc_pre[i] : r;
+  }
+  for (int p = lane + 128; p < L; p += 32) slot_s[p] = (anc && p < step) ? anc[p] : r;
   const long long own = (((long long)r * a.heads + h) * a.max_step + step) * DH + c * 16;
   if (g == 0) *reinterpret_cast<int4*>(a.k_cache + own) = knew;
   if (g == 1) *reinterpret_cast<int4*>(a.v_cache + own) = vnew;
