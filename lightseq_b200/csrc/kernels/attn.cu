@@ -390,6 +390,15 @@ attn_cross_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     fence_barrier_init();
     if (a.kv_static) xattn_issue(xs, bar, &tm_k, &tm_v, item, 0, tm_heads, S);
   }
+  // what does not come from the preceding kernel is read ahead of the wait as well: the padding flag of this lane's
+  // key in the first tile (static with the keys) and the query bias
+  int pad_first = -1;
+  if (a.kv_static) {
+    const int kpos0 = warp * 16 + key;
+    pad_first = (a.pad_mask && kpos0 < S) ? (int)a.pad_mask[(long long)b * S + kpos0] : (kpos0 < S ? 0 : 1);
+  }
+  float2 qb_pre = make_float2(0.f, 0.f);
+  if (a.bias) qb_pre = __ldg(reinterpret_cast<const float2*>(a.bias + h * DH + lane * 2));
   LS100_TRACE(0);
   pdl_wait();
   LS100_TRACE(1);
@@ -402,8 +411,7 @@ attn_cross_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
       float q0 = 0.f, q1 = 0.f;
       if (bm < a.beam) {
         const short qraw = *reinterpret_cast<const short*>(a.q + (long long)(b * a.beam + bm) * a.ld_q + h * DH + lane * 2);
-        float2 qb = make_float2(0.f, 0.f);
-        if (a.bias) qb = __ldg(reinterpret_cast<const float2*>(a.bias + h * DH + lane * 2));
+        const float2 qb = qb_pre;
         q0 = __fadd_rn(__fmul_rn((float)(int8_t)(qraw & 0xff), a.s_q), qb.x);
         q1 = __fadd_rn(__fmul_rn((float)(int8_t)((qraw >> 8) & 0xff), a.s_q), qb.y);
       }
@@ -427,7 +435,8 @@ attn_cross_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     const int t0 = t * XT + warp * 16;       // first key of this warp in the tile
     const int ns = max(0, min(16, S - t0));  // its keys that exist
     const int kpos = t0 + key;
-    const int pad_now = (a.pad_mask && kpos < S) ? (int)a.pad_mask[(long long)b * S + kpos] : (kpos < S ? 0 : 1);
+    const int pad_now = (t == 0 && pad_first >= 0) ? pad_first
+                        : ((a.pad_mask && kpos < S) ? (int)a.pad_mask[(long long)b * S + kpos] : (kpos < S ? 0 : 1));
     LS100_TRACE(2);
     if (!dead) {
       const bool ok = mbar_wait(bar, (uint32_t)t & 1u);

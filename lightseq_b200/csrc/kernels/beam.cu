@@ -115,6 +115,13 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
   pdl_wait();
   __syncthreads();
   const int row = blockIdx.x;
+  // this warp's first two chunks are requested before the step counter and the row's last token are known (a finished
+  // row will not use them): the three reads then share one round trip instead of queueing behind each other
+  const int8_t* lp = a.logits + (long long)row * a.ld_logits;
+  const int4 none = make_int4((int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080);
+  int4 v1 = none, v2 = none;
+  if (warp * 512 + lane * 16 < a.vocab) v1 = load_row16(lp, warp * 512 + lane * 16, a.vocab);
+  if ((warp + TOPK_WARPS) * 512 + lane * 16 < a.vocab) v2 = load_row16(lp, (warp + TOPK_WARPS) * 512 + lane * 16, a.vocab);
   const int step = *a.step_ptr;
   const int K = a.beam;
   float* cs = a.cand_score + (long long)row * K;
@@ -126,18 +133,13 @@ __global__ void __launch_bounds__(32 * TOPK_WARPS) beam_topk_kernel(const ls100_
     }
     return;
   }
-  const int8_t* lp = a.logits + (long long)row * a.ld_logits;
   unsigned* buf = s_buf[warp];
   int n_buf = 0;   // entries in buf (the first ones are the current best list)
   int thr = -128;  // bytes strictly above thr are candidates
   unsigned add7 = 0x01010101u * 127u;
   float2 ps01 = make_float2(0.f, 0.f), ps23 = make_float2(0.f, 0.f);  // four running sums, added as two packed pairs
   const int n_chunks = (a.vocab + 511) / 512;
-  const int4 none = make_int4((int)0x80808080, (int)0x80808080, (int)0x80808080, (int)0x80808080);
   // this warp's chunks: warp, warp + 8, ...; the next two are always in flight
-  int4 v1 = none, v2 = none;
-  if (warp * 512 + lane * 16 < a.vocab) v1 = load_row16(lp, warp * 512 + lane * 16, a.vocab);
-  if ((warp + TOPK_WARPS) * 512 + lane * 16 < a.vocab) v2 = load_row16(lp, (warp + TOPK_WARPS) * 512 + lane * 16, a.vocab);
   for (int ch = warp; ch < n_chunks; ch += TOPK_WARPS) {
     const int off = ch * 512 + lane * 16;
     const int4 v = v1;
