@@ -811,7 +811,7 @@ def run_ours(args):
                    "global_batch": B * world, "src_len_padded": S, "decode_steps": steps_per_infer,
                    "tokens_per_sentence": n_out, "parallelism": f"replicas x{world} (batch sharding, no collective)",
                    "l2": "256 MB buffer written between timed iterations; per-step working set (KV caches, logits) > L2"},
-        "clocks": clocks, "gpu_launches": per_infer * args.steps,
+        "clocks": clocks, "gpu_launches": per_infer * args.steps * world, "gpu_launches_per_rank": per_infer * args.steps,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": int(src.nbytes), "d2h_bytes_per_step": int(d2h)},
         "roofline": roofline, "roofline_other_kernels": {k: v for k, v in per_kernel.items() if k != "gemm_dec"},
         "cpu_baseline": cpu,
