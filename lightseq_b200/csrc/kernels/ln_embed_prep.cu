@@ -17,7 +17,7 @@ __device__ __forceinline__ double warp_sum_d(double v) {
 constexpr int LN_MAXV = 32;  // float4 per lane -> hidden <= 32*32*4 = 4096
 
 template <int NV>
-__global__ void __launch_bounds__(256) ln_quant_kernel(const ls100_ln_quant_args a, const float scale, const float rs) {
+__global__ void __launch_bounds__(256, NV <= 6 ? 3 : 1) ln_quant_kernel(const ls100_ln_quant_args a, const float scale, const float rs) {
   pdl_launch_dependents();
   pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -61,9 +61,10 @@ __global__ void __launch_bounds__(256) ln_quant_kernel(const ls100_ln_quant_args
       y.w = __fadd_rn(__fmul_rn((float)(((double)v[i].w - mean) * rstd), g.w), b.w);
       if (a.out_f) *reinterpret_cast<float4*>(a.out_f + (long long)warp * a.ldf + c) = y;
       if (a.out_q) {
-        const uint32_t p = pack_i8x4(quant_s(clipf(y.x, a.amax), scale, rs), quant_s(clipf(y.y, a.amax), scale, rs),
-                                     quant_s(clipf(y.z, a.amax), scale, rs), quant_s(clipf(y.w, a.amax), scale, rs));
-        *reinterpret_cast<uint32_t*>(a.out_q + (long long)warp * a.ldq + c) = p;
+        // (clamping to +-amax first, as the learned-amax quantiser does, cannot change the result: amax / scale is 127)
+        const float2 q01 = f2_quant_biased(f2_div_rn(make_float2(y.x, y.y), f2_set(scale), f2_set(rs)));
+        const float2 q23 = f2_quant_biased(f2_div_rn(make_float2(y.z, y.w), f2_set(scale), f2_set(rs)));
+        *reinterpret_cast<uint32_t*>(a.out_q + (long long)warp * a.ldq + c) = pack_biased_i8x4(q01.x, q01.y, q23.x, q23.y);
       }
     }
   }
@@ -163,9 +164,10 @@ __global__ void __launch_bounds__(LN_ROW_THREADS) ln_quant_row_kernel(const ls10
       y.w = __fadd_rn(__fmul_rn((float)(((double)v[i].w - mean) * rstd), g[i].w), b[i].w);
       if (a.out_f) *reinterpret_cast<float4*>(a.out_f + (long long)row * a.ldf + c) = y;
       if (a.out_q) {
-        const uint32_t p = pack_i8x4(quant_s(clipf(y.x, a.amax), scale, rs), quant_s(clipf(y.y, a.amax), scale, rs),
-                                     quant_s(clipf(y.z, a.amax), scale, rs), quant_s(clipf(y.w, a.amax), scale, rs));
-        *reinterpret_cast<uint32_t*>(a.out_q + (long long)row * a.ldq + c) = p;
+        // (clamping to +-amax first, as the learned-amax quantiser does, cannot change the result: amax / scale is 127)
+        const float2 q01 = f2_quant_biased(f2_div_rn(make_float2(y.x, y.y), f2_set(scale), f2_set(rs)));
+        const float2 q23 = f2_quant_biased(f2_div_rn(make_float2(y.z, y.w), f2_set(scale), f2_set(rs)));
+        *reinterpret_cast<uint32_t*>(a.out_q + (long long)row * a.ldq + c) = pack_biased_i8x4(q01.x, q01.y, q23.x, q23.y);
       }
     }
   }
@@ -326,7 +328,7 @@ extern "C" int ls100_ln_quant(ls100_ctx* ctx, const ls100_ln_quant_args* a, ls10
   const int nv = (a->hidden + 127) / 128;
   const float rs = 1.0f / scale;
   cudaError_t e;
-  if (a->rows <= 2048) {  // decode-step sizes: a CTA per row
+  if (a->rows <= 2048) {  // decode-step sizes: a CTA per row (at 16384 rows it times the same as a warp per row)
     const int nvr = (a->hidden + 4 * LN_ROW_THREADS - 1) / (4 * LN_ROW_THREADS);
     if (nvr <= 1) e = ls100_launch(ln_quant_row_kernel<1>, dim3(a->rows), dim3(LN_ROW_THREADS), 0, stream, *a, scale, rs);
     else if (nvr <= 2) e = ls100_launch(ln_quant_row_kernel<2>, dim3(a->rows), dim3(LN_ROW_THREADS), 0, stream, *a, scale, rs);
@@ -335,6 +337,7 @@ extern "C" int ls100_ln_quant(ls100_ctx* ctx, const ls100_ln_quant_args* a, ls10
     return e == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
   }
   if (nv <= 4) e = ls100_launch(ln_quant_kernel<4>, dim3(blocks), dim3(256), 0, stream, *a, scale, rs);
+  else if (nv <= 6) e = ls100_launch(ln_quant_kernel<6>, dim3(blocks), dim3(256), 0, stream, *a, scale, rs);
   else if (nv <= 8) e = ls100_launch(ln_quant_kernel<8>, dim3(blocks), dim3(256), 0, stream, *a, scale, rs);
   else if (nv <= 16) e = ls100_launch(ln_quant_kernel<16>, dim3(blocks), dim3(256), 0, stream, *a, scale, rs);
   else e = ls100_launch(ln_quant_kernel<32>, dim3(blocks), dim3(256), 0, stream, *a, scale, rs);
