@@ -102,6 +102,11 @@ __device__ __forceinline__ constexpr uint32_t make_idesc_i8() {
          | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
+// Byte offset of 16-byte piece `piece` of row `r` in a 32-row x 64-byte staging block: the four pieces of a row are
+// permuted by (r / 2) % 4, which makes both access orders of the epilogues (a lane's own row; eight rows x four
+// pieces per instruction) free of bank conflicts without padding.
+__device__ __forceinline__ int stage_off(int r, int piece) { return r * 64 + ((piece ^ ((r >> 1) & 3)) << 4); }
+
 __device__ __forceinline__ void record_timeout(int* err) {
   if (err) atomicExch(err, (int)LS100_ERR_TIMEOUT);
 }
@@ -538,6 +543,7 @@ __global__ void __launch_bounds__(320) gemm_i8_tc_kernel(const __grid_constant__
 #pragma unroll
       for (int j = 0; j < 16; ++j) rr[j] = 0.f;
     }
+    const bool staged_out = p.out_kind == LS100_OUT_F32 && (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
     asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight epilogue warps only
     bool ok = mbar_wait(tmem_full_bar, 0);
     ok = __all_sync(0xffffffffu, ok);
@@ -554,8 +560,31 @@ __global__ void __launch_bounds__(320) gemm_i8_tc_kernel(const __grid_constant__
         tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
         tmem_ld_wait();
         if (c0 == c_first) { LS100_TRACE(7); }
-        epilogue_chunk<BN, 16>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, rr_ok && c0 == c_first,
-                               LNF ? &ln_s : nullptr, LNF ? &ln_q : nullptr);
+        if (!LNF && staged_out && n0 + c0 + 16 <= p.n) {
+          // fp32 rows leave through a 2 KB block of the (now idle) operand ring: own row in, eight rows x 64 bytes out
+          // per instruction, instead of 32 rows x 16 bytes
+          int acc[16];
+          float v[16];
+          epilogue_acc<16>(p, r, s_off + c0, acc);
+          epilogue_arith<16>(p, acc, row, n0 + c0, s_bias + c0, rr, rr_ok && c0 == c_first, v);
+          uint8_t* stg = smem + (warp - 2) * 2048;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<float4*>(stg + stage_off(lane, j)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          __syncwarp();
+          float* op = reinterpret_cast<float*>(p.out);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int br = 8 * i + (lane >> 2), piece = lane & 3;
+            const float4 t = *reinterpret_cast<const float4*>(stg + stage_off(br, piece));
+            const int gr = m0 + quarter * 32 + br;
+            if (gr < p.m) *reinterpret_cast<float4*>(op + (long long)gr * p.ldo + n0 + c0 + piece * 4) = t;
+          }
+          __syncwarp();
+        } else {
+          epilogue_chunk<BN, 16>(p, r, row, n0 + c0, s_bias + c0, s_off + c0, rr, rr_ok && c0 == c_first,
+                                 LNF ? &ln_s : nullptr, LNF ? &ln_q : nullptr);
+        }
         LS100_TRACE(8 + c0 / 32);
       }
     }
@@ -835,7 +864,6 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
     uint8_t* stg_in = smem + SM::AUX_OFFSET + ew * P_STG_BYTES;
     uint8_t* stg_out = smem + SM::AUX_OFFSET + (P_EPI_WARPS + ew) * P_STG_BYTES;
     const int mv_row = lane >> 2, mv_piece = lane & 3;
-    auto stg_at = [](int r, int piece) { return r * 64 + ((piece ^ ((r >> 1) & 3)) << 4); };  // byte offset in a block
     pdl_wait();  // the residual (and everything written below) belongs to the chain of kernels before this one
     int local = 0;
     bool dead = false;
@@ -879,7 +907,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
         for (int i = 0; i < 4; ++i) {
           const int br = 8 * i + mv_row;
           if (row0 + br < p.m)
-            cp_async_16(stg_in + stg_at(br, mv_piece), p.resid + (long long)(row0 + br) * p.ldr + n0 + c0 + mv_piece * 4);
+            cp_async_16(stg_in + stage_off(br, mv_piece), p.resid + (long long)(row0 + br) * p.ldr + n0 + c0 + mv_piece * 4);
         }
         cp_async_commit();
       };
@@ -926,7 +954,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
             __syncwarp();
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const float4 t = *reinterpret_cast<const float4*>(stg_in + stg_at(lane, j));
+              const float4 t = *reinterpret_cast<const float4*>(stg_in + stage_off(lane, j));
               rr[4 * j] = t.x;
               rr[4 * j + 1] = t.y;
               rr[4 * j + 2] = t.z;
@@ -942,13 +970,13 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
           // own row in, eight rows x 64 bytes out per instruction
 #pragma unroll
           for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<float4*>(stg_out + stg_at(lane, j)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            *reinterpret_cast<float4*>(stg_out + stage_off(lane, j)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
           __syncwarp();
           float* op = reinterpret_cast<float*>(p.out);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int br = 8 * i + mv_row;
-            const float4 t = *reinterpret_cast<const float4*>(stg_out + stg_at(br, mv_piece));
+            const float4 t = *reinterpret_cast<const float4*>(stg_out + stage_off(br, mv_piece));
             if (row0 + br < p.m) *reinterpret_cast<float4*>(op + (long long)(row0 + br) * p.ldo + n0 + c0 + mv_piece * 4) = t;
           }
           __syncwarp();  // the block is rewritten in the other order by the next piece
