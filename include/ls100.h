@@ -78,7 +78,10 @@ enum { LS100_ACT_NONE = 0, LS100_ACT_RELU = 1, LS100_ACT_GELU = 2 };
 typedef struct {
   const int8_t* a; /* [M,K], K contiguous */
   int64_t lda;     /* bytes between rows, multiple of 16 */
-  const int8_t* w; /* [N,K], K contiguous (torch Linear layout) */
+  const int8_t* w; /* [N,K], K contiguous (torch Linear layout). A weight: it, w_off, bias and req_table must be complete
+                      before a full stream dependency that precedes this launch (they are what load-time preparation
+                      wrote); the kernels fetch their first tiles of w ahead of the grid dependency on the preceding
+                      kernel, which orders only a, resid and the outputs. */
   int64_t ldw;
   int32_t m, n, k;
   float s_acc;          /* s_in * s_w */

@@ -783,14 +783,24 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
 
   if (warp == 0) {
     if (elect_one()) {
+      // First ring fill: the weight tiles of the first tile do not depend on the previous kernel, so they are
+      // requested before the grid-dependency wait (in a chain of launches this hides their trip from HBM); the
+      // activation tiles of the same stages follow the wait.
+      const int n_pre = walk.count > 0 ? (num_kb < stages ? num_kb : stages) : 0;
+      for (int kb = 0; kb < n_pre; ++kb) {
+        mbar_expect_tx(&full_bar[kb], SM::STAGE_BYTES);
+        tma_load_2d(smem + kb * SM::STAGE_BYTES + SM::A_BYTES, &tma_b, &full_bar[kb], kb * BK, walk.n_tile(0) * P_BN);
+      }
       pdl_wait();
-      uint32_t phase = 0;
-      int s = 0;
+      for (int kb = 0; kb < n_pre; ++kb)
+        tma_load_2d(smem + kb * SM::STAGE_BYTES, &tma_a, &full_bar[kb], kb * BK, walk.m_tile(0) * BM);
+      uint32_t phase = (n_pre == stages) ? 1 : 0;
+      int s = (n_pre == stages) ? 0 : n_pre;
       bool ok = true;
       for (int it = 0; it < walk.count && ok; ++it) {
         const int n0 = walk.n_tile(it) * P_BN;
         const int m0 = walk.m_tile(it) * BM;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = (it == 0 ? n_pre : 0); kb < num_kb; ++kb) {
           // a stage that has never been filled reads as released (parity of the phase before the first)
           if (!mbar_wait(&empty_bar[s], phase ^ 1)) {
             record_timeout(p.err);
