@@ -709,7 +709,7 @@ struct PersistSmem {
 static_assert(PersistSmem::AUX_OFFSET + PersistSmem::AUX_BYTES >= P_STAGES * PersistSmem::STAGE_BYTES, "ring inside");
 static_assert(PersistSmem::TOTAL <= 232448, "shared memory of one SM");
 
-constexpr int P_PLAIN = 0, P_STAGED = 1, P_TABLE = 2;
+constexpr int P_PLAIN = 0, P_STAGED = 1, P_TABLE = 2, P_OUTQ = 3;
 
 // The tiles of one CTA. Strided over the row-major tile list by default; with a requantisation table, a contiguous
 // run of the column-major list, so that the 256-column slice of the table in shared memory changes once or twice
@@ -751,7 +751,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
   const int num_kb = (p.k + BK - 1) / BK;
   constexpr bool staged = MODE == P_STAGED;  // whole-line movement of fp32 outputs (the launcher checks the alignment)
   constexpr bool tabled = MODE == P_TABLE;    // requantisation table slice in shared memory
-  constexpr int stages = MODE == P_PLAIN ? P_STAGES : P_STAGES - 1;
+  constexpr int stages = (MODE == P_PLAIN || MODE == P_OUTQ) ? P_STAGES : P_STAGES - 1;
   const TileWalk walk(tabled, tiles_n, num_tiles);
 
   if (threadIdx.x == 0) {
@@ -942,8 +942,48 @@ __global__ void __launch_bounds__(P_THREADS, 1) gemm_i8_persist_kernel(const __g
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
       }
-      // (Reading the next piece from TMEM during this piece's arithmetic, with a second register set, was measured
-      // 40 % slower: 96 registers per thread do not hold both.)
+      if constexpr (MODE == P_OUTQ) {
+        // Output-quantised int8 only (logits, QKV): the epilogue is short enough for a second register set, so the
+        // TMEM read of the next piece is in flight during the arithmetic of this one (a read takes ~0.3 us from
+        // issue to data, a third of a piece's time). In the general kernel the same loop spilled and lost 40 %.
+        GemmEpi q = p;  // the fields this mode fixes, spelled out for the compiler
+        q.out_kind = LS100_OUT_OUTQ_I8;
+        q.bias = nullptr;
+        q.resid = nullptr;
+        q.act = LS100_ACT_NONE;
+        q.table = nullptr;
+        q.st_max = nullptr;
+        if (present(0)) {
+          uint32_t ra[16], rb[16];
+          tmem_ld16(t_addr, ra);
+#pragma unroll 1
+          for (int c0 = 0; c0 < COLS; c0 += 32) {
+            tmem_ld_wait();
+            const bool more_b = present(c0 + 16);
+            if (more_b) {
+              tmem_ld16(t_addr + (uint32_t)(c0 + 16), rb);
+            } else {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+            }
+            epilogue_chunk<P_BN, 16>(q, ra, row, n0 + c0, s_bias + c0, s_off + c0, rr, false);
+            if (!more_b) break;
+            tmem_ld_wait();
+            const bool more_a = present(c0 + 32);
+            if (more_a) {
+              tmem_ld16(t_addr + (uint32_t)(c0 + 32), ra);
+            } else {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+            }
+            epilogue_chunk<P_BN, 16>(q, rb, row, n0 + c0 + 16, s_bias + c0 + 16, s_off + c0 + 16, rr, false);
+            if (!more_a) break;
+          }
+        }
+        continue;
+      }
 #pragma unroll 1
       for (int c0 = 0; present(c0); c0 += 16) {
         uint32_t r[16];
@@ -1088,7 +1128,11 @@ static int launch_gemm_persist(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cuda
   const bool staged = a->out_kind == LS100_OUT_F32 && (a->ldo & 3) == 0 && (((uintptr_t)a->out) & 15) == 0 &&
                       (a->resid == nullptr || ((a->ldr & 3) == 0 && (((uintptr_t)a->resid) & 15) == 0));
   const bool tabled = a->req_table != nullptr;  // validated by the caller: int8 requantised kind, output quantiser, no residual
-  auto kern = staged ? gemm_i8_persist_kernel<P_STAGED> : tabled ? gemm_i8_persist_kernel<P_TABLE> : gemm_i8_persist_kernel<P_PLAIN>;
+  const bool outq = a->out_kind == LS100_OUT_OUTQ_I8 && !a->stat_max && !a->bias && !a->resid && a->act == LS100_ACT_NONE && !tabled;
+  auto kern = staged ? gemm_i8_persist_kernel<P_STAGED>
+              : tabled ? gemm_i8_persist_kernel<P_TABLE>
+              : outq   ? gemm_i8_persist_kernel<P_OUTQ>
+                       : gemm_i8_persist_kernel<P_PLAIN>;
   const cudaError_t e = ls100_launch(kern, dim3(grid), dim3(P_THREADS), PersistSmem::TOTAL, stream, ta, tb, p, tiles_n, (int)tiles);
   return e == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
@@ -1136,6 +1180,8 @@ int ls100_gemm_i8_init_device() {
               cudaFuncSetAttribute(gemm_i8_persist_kernel<P_STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    PersistSmem::TOTAL) != cudaSuccess ||
               cudaFuncSetAttribute(gemm_i8_persist_kernel<P_TABLE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   PersistSmem::TOTAL) != cudaSuccess ||
+              cudaFuncSetAttribute(gemm_i8_persist_kernel<P_OUTQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    PersistSmem::TOTAL) != cudaSuccess))
     rc = LS100_ERR_CUDA;
   return rc;
