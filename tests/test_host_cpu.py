@@ -45,6 +45,51 @@ def test_library_exports_every_declared_symbol():
     assert _lib.lib.ls100_strerror(-5).decode().startswith("a bounded device-side wait")
 
 
+def test_ctypes_structures_have_the_layout_of_the_header(tmp_path):
+    """The argument structs cross the C ABI by pointer: the ctypes mirror of every one must have the size the C
+    compiler gives the declaration in include/ls100.h, and its last member must sit at the same offset (a member
+    appended in the header but not in the mirror would leave it unset and go unnoticed otherwise)."""
+    import shutil
+    import subprocess
+
+    from lightseq_b200 import _lib as L
+
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    pairs = {"ls100_gemm_i8_args": L.GemmI8Args, "ls100_embed_args": L.EmbedArgs, "ls100_ln_quant_args": L.LnQuantArgs,
+             "ls100_patch_embed_args": L.PatchEmbedArgs, "ls100_attn_self_args": L.AttnSelfArgs,
+             "ls100_attn_dec_args": L.AttnDecArgs, "ls100_attn_cross_args": L.AttnCrossArgs, "ls100_proj_f32_args": L.ProjF32Args,
+             "ls100_proj_tc_args": L.ProjTcArgs, "ls100_beam_topk_args": L.BeamTopkArgs, "ls100_beam_select_args": L.BeamSelectArgs,
+             "ls100_beam_update_args": L.BeamUpdateArgs, "ls100_beam_result_args": L.BeamResultArgs,
+             "ls100_sample_topk_args": L.SampleTopkArgs, "ls100_sample_topp_args": L.SampleToppArgs}
+    header = (ROOT / "include" / "ls100.h").read_text()
+    last = {}
+    for name in pairs:  # last member of the C declaration
+        body = header[:header.index("} " + name + ";")]
+        body = body[body.rindex("typedef struct {"):]
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        decl = [d.strip() for d in body.split(";") if d.strip()][-1]
+        last[name] = re.findall(r"([A-Za-z_][A-Za-z0-9_]*)\s*(?:\[[^\]]*\])?$", decl.split(",")[-1].strip())[0]
+    src = ["#include <stdio.h>", "#include <stddef.h>", '#include "ls100.h"', "int main(void) {"]
+    for name in pairs:
+        src.append(f'  printf("{name} %zu %zu\\n", sizeof({name}), offsetof({name}, {last[name]}));')
+    src += ["  return 0;", "}"]
+    c = tmp_path / "layout.c"
+    c.write_text("\n".join(src))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", str(ROOT / "include"), str(c), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    seen = 0
+    for line in out.splitlines():
+        name, size, off = line.split()
+        cls = pairs[name]
+        assert C.sizeof(cls) == int(size), f"{name}: header {size} bytes, ctypes {C.sizeof(cls)}"
+        assert getattr(cls, cls._fields_[-1][0]).offset == int(off), f"{name}: last member at {off} in the header"
+        assert cls._fields_[-1][0] == last[name], f"{name}: last member {last[name]} in the header, {cls._fields_[-1][0]} in ctypes"
+        seen += 1
+    assert seen == len(pairs)
+
+
 def test_null_arguments_are_rejected_without_a_gpu():
     from lightseq_b200 import _lib as L
 
