@@ -70,9 +70,9 @@ constexpr int BM = 128;
 constexpr int BK = 128;  // bytes == int8 elements per k-block (one 128B swizzle row)
 constexpr int UMMA_K = 32;
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int BMT = 128>
 struct GemmSmem {
-  static constexpr int A_BYTES = BM * BK;
+  static constexpr int A_BYTES = BMT * BK;
   static constexpr int B_BYTES = BN * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
@@ -92,14 +92,14 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   return d;
 }
 
-template <int BN>
+template <int BN, int BMT = 128>
 __device__ __forceinline__ constexpr uint32_t make_idesc_i8() {
   return (2u << 4)      // D format: s32
          | (1u << 7)    // A: signed 8-bit
          | (1u << 10)   // B: signed 8-bit
          | (0u << 15)   // A K-major
          | (0u << 16)   // B K-major
-         | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+         | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BMT >> 4) << 24);
 }
 
 // Byte offset of 16-byte piece `piece` of row `r` in a 32-row x 64-byte staging block: the four pieces of a row are
@@ -397,11 +397,17 @@ __device__ __forceinline__ void epilogue_chunk(const GemmEpi& p, const uint32_t 
 // distributed shared memory, every CTA adds them in rank order (so all agree to the bit), then each thread
 // normalises and quantises its own columns. EVERY thread of the cluster meets both cluster barriers on every
 // path, including the time-out paths.
-template <int BN, int STAGES, bool LNF = false>
+// BMT = 64: tiles of 64 rows (an M = 64 MMA: row r of the tile lives in TMEM lane 32 * (r / 16) + r % 16, so every
+// lane quarter and every epilogue warp keeps 16 active lanes). Half the activation bytes per CTA and twice the CTAs:
+// for the decode-step GEMMs whose grid is otherwise 64 CTAs, what a CTA waits for after the grid dependency is its
+// activation tile arriving at the per-SM L2 rate.
+template <int BN, int STAGES, bool LNF = false, int BMT = 128>
 __global__ void __launch_bounds__(320) gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                          const __grid_constant__ CUtensorMap tma_b,
                                                          const GemmEpi p) {
-  using SM = GemmSmem<BN, STAGES>;
+  static_assert(BMT == 128 || (BMT == 64 && !LNF), "tile heights");
+  using SM = GemmSmem<BN, STAGES, BMT>;
+  constexpr int ROWS_Q = BMT / 4;  // rows per TMEM lane quarter
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFFSET);
@@ -415,7 +421,7 @@ __global__ void __launch_bounds__(320) gemm_i8_tc_kernel(const __grid_constant__
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN;
-  const int m0 = blockIdx.y * BM;
+  const int m0 = blockIdx.y * BMT;
   const int num_kb = (p.k + BK - 1) / BK;
 
   LS100_TRACE(0);
@@ -476,7 +482,7 @@ __global__ void __launch_bounds__(320) gemm_i8_tc_kernel(const __grid_constant__
     }
   } else if (warp == 1) {
     if (elect_one()) {
-      constexpr uint32_t idesc = make_idesc_i8<BN>();
+      constexpr uint32_t idesc = make_idesc_i8<BN, BMT>();
       uint32_t phase = 0;
       int s = 0;
       bool ok = true;
@@ -512,7 +518,9 @@ __global__ void __launch_bounds__(320) gemm_i8_tc_kernel(const __grid_constant__
     // hide each other's issue latency.
     const int quarter = warp & 3;
     const int grp = (warp - 2) >> 2;
-    const int row = m0 + quarter * 32 + lane;
+    // lanes beyond the tile's rows of this quarter (BMT = 64: lanes 16..31) get a row no problem has: they compute on
+    // zeros and store nothing
+    const int row = lane < ROWS_Q ? m0 + quarter * ROWS_Q + lane : 0x7fffffff;
     // While the main loop runs: stage this tile's bias / weight offsets in shared memory and
     // prefetch the residual values of this thread's first piece, so that no global-load latency
     // is left between "accumulator ready" and the stores.
@@ -577,8 +585,8 @@ __global__ void __launch_bounds__(320) gemm_i8_tc_kernel(const __grid_constant__
           for (int i = 0; i < 4; ++i) {
             const int br = 8 * i + (lane >> 2), piece = lane & 3;
             const float4 t = *reinterpret_cast<const float4*>(stg + stage_off(br, piece));
-            const int gr = m0 + quarter * 32 + br;
-            if (gr < p.m) *reinterpret_cast<float4*>(op + (long long)gr * p.ldo + n0 + c0 + piece * 4) = t;
+            const int gr = m0 + quarter * ROWS_Q + br;
+            if (br < ROWS_Q && gr < p.m) *reinterpret_cast<float4*>(op + (long long)gr * p.ldo + n0 + c0 + piece * 4) = t;
           }
           __syncwarp();
         } else {
@@ -1137,27 +1145,27 @@ static int launch_gemm_persist(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cuda
   return e == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
 
-template <int BN, int STAGES, bool LNF = false>
+template <int BN, int STAGES, bool LNF = false, int BMT = 128>
 static int launch_gemm(ls100_ctx* ctx, const ls100_gemm_i8_args* a, cudaStream_t stream) {
-  using SM = GemmSmem<BN, STAGES>;
-  auto kern = gemm_i8_tc_kernel<BN, STAGES, LNF>;
+  using SM = GemmSmem<BN, STAGES, BMT>;
+  auto kern = gemm_i8_tc_kernel<BN, STAGES, LNF, BMT>;
   CUtensorMap ta, tb;
-  int rc = ls100_get_tmap_u8(ctx, a->a, (uint64_t)a->m, (uint64_t)a->k, (uint64_t)a->lda, BM, BK, &ta);
+  int rc = ls100_get_tmap_u8(ctx, a->a, (uint64_t)a->m, (uint64_t)a->k, (uint64_t)a->lda, BMT, BK, &ta);
   if (rc) return rc;
   rc = ls100_get_tmap_u8(ctx, a->w, (uint64_t)a->n, (uint64_t)a->k, (uint64_t)a->ldw, BN, BK, &tb);
   if (rc) return rc;
   const GemmEpi p = make_epi(ctx, a);
-  dim3 grid((a->n + BN - 1) / BN, (a->m + BM - 1) / BM);
+  dim3 grid((a->n + BN - 1) / BN, (a->m + BMT - 1) / BMT);
   if (LNF)  // one cluster per 128-row block
     return ls100_launch_cluster(kern, grid, dim3(320), SM::TOTAL, stream, grid.x, ta, tb, p) == cudaSuccess ? LS100_OK
                                                                                                              : LS100_ERR_CUDA;
   return ls100_launch(kern, grid, dim3(320), SM::TOTAL, stream, ta, tb, p) == cudaSuccess ? LS100_OK : LS100_ERR_CUDA;
 }
 
-template <int BN, int STAGES, bool LNF = false>
+template <int BN, int STAGES, bool LNF = false, int BMT = 128>
 static int set_smem_attr() {
-  return cudaFuncSetAttribute(gemm_i8_tc_kernel<BN, STAGES, LNF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              GemmSmem<BN, STAGES>::TOTAL) == cudaSuccess
+  return cudaFuncSetAttribute(gemm_i8_tc_kernel<BN, STAGES, LNF, BMT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              GemmSmem<BN, STAGES, BMT>::TOTAL) == cudaSuccess
              ? LS100_OK
              : LS100_ERR_CUDA;
 }
@@ -1172,6 +1180,7 @@ int ls100_gemm_i8_init_device() {
   if (!rc) rc = set_smem_attr<64, 4>();
   if (!rc) rc = set_smem_attr<32, 4>();
   if (!rc) rc = set_smem_attr<32, 8>();
+  if (!rc) rc = set_smem_attr<32, 4, false, 64>();
   if (!rc) rc = set_smem_attr<32, 4, true>();
   if (!rc) rc = set_smem_attr<64, 4, true>();
   if (!rc) rc = set_smem_attr<128, 3, true>();
@@ -1248,6 +1257,10 @@ extern "C" int ls100_gemm_i8(ls100_ctx* ctx, const ls100_gemm_i8_args* a, ls100_
   // steps 17 % faster; with several row blocks (Transformer-base FFN2, 512 rows) the deeper ring was 1.8 us SLOWER
   // per launch, so those keep four stages.
   if (mt == 1 && a->k > 4 * BK && ctas(32) <= sms) return launch_gemm<32, 8>(ctx, a, stream);
+  // several row blocks and at most half a wave of 128-row tiles: 64-row tiles halve the activation bytes a CTA waits
+  // for and still fit one CTA per SM
+  const long long ctas64 = ((a->m + 63) / 64) * ((a->n + 31) / 32);
+  if (mt >= 2 && ctas64 <= sms) return launch_gemm<32, 4, false, 64>(ctx, a, stream);
   return launch_gemm<32, 4>(ctx, a, stream);
 }
 

@@ -131,6 +131,37 @@ def test_gemm_outq_int8_and_bias_residual_bit_exact():
     assert np.array_equal(out.cpu().numpy(), resid + y)
 
 
+@pytest.mark.parametrize("m,n,k", [(512, 512, 512), (190, 100, 384), (130, 512, 2048), (448, 288, 640)])
+def test_gemm_64_row_tiles_every_epilogue_bit_exact(m, n, k):
+    """Problems of several row blocks and at most one CTA per SM run 64-row tiles (an M = 64 MMA, 16 active lanes per
+    TMEM lane quarter): the out-projection / FFN2 shapes of a decode step, ragged M (last tile of 62 and of 2 rows),
+    N ending inside a 32-column tile, K ending inside a k-block; int32, int8 of the output quantiser, fp32 + bias +
+    residual in place, and bias + GELU + requantise."""
+    st, x, w, b = _qlinear_case(51, m, n, k)
+    st.trace = {}
+    y = om.qlinear(st, x, "l")
+    xq, s_x = oq.quantize(x, st.amax["l.in"])
+    wq, s_w = oq.quantize(w, st.amax["l.w"])
+    s_o = oq.scale_of(st.amax["l.out"])
+    s_acc = float(F32(s_x * s_w))
+    out = gemm(dev(xq), dev(wq), s_acc=1.0, out_kind=L.OUT_I32)
+    sync_check()
+    assert np.array_equal(out.cpu().numpy().astype(np.int64), oq.int_matmul(xq, wq))
+    out = gemm(dev(xq), dev(wq), s_acc=s_acc, out_kind=L.OUT_OUTQ_I8, s_outq=float(s_o))
+    sync_check()
+    assert np.array_equal(out.cpu().numpy(), st.trace["l.out_q"])
+    resid = rng(52).standard_normal((m, n)).astype(F32)
+    out = gemm(dev(xq), dev(wq), s_acc=s_acc, out_kind=L.OUT_F32, s_outq=float(s_o), bias=dev(b), resid=dev(resid), in_place=True)
+    sync_check()
+    assert np.array_equal(out.cpu().numpy(), resid + y)
+    act = oq.gelu(y)
+    amax2 = float(F32(4 * act.std()))
+    ref, s2 = oq.quantize(act, amax2)
+    out = gemm(dev(xq), dev(wq), s_acc=s_acc, out_kind=L.OUT_REQ_S8, s_outq=float(s_o), bias=dev(b), act=L.ACT_GELU, s_req=float(s2))
+    sync_check()
+    assert np.array_equal(out.cpu().numpy(), ref)
+
+
 @pytest.mark.parametrize("m,n,k", [(512, 512, 512), (300, 512, 2048), (512, 1024, 1024), (130, 256, 128), (260, 768, 768),
                                    (200, 2048, 256), (64, 1024, 4096)])
 def test_gemm_fused_layernorm_bit_exact(m, n, k):
