@@ -190,3 +190,17 @@ def test_reference_modules_tree_matches_the_oracle_when_present():
     b = rt.RefSeq2Seq(mods, cfg, w, amax).generate(src)
     assert a[2] == b[2] and np.array_equal(a[0], b[0])
     np.testing.assert_allclose(a[1], b[1], rtol=0, atol=1e-4)
+
+
+def test_philox_counter_stream_matches_the_published_known_answers():
+    """The sampling oracle draws from Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as
+    1, 2, 3", SC'11). Its first output word for the three known-answer inputs published with the generator (all-zero
+    counter and key; all-ones; the digits of pi) pins the restatement to the published algorithm; the device kernels
+    are in turn compared with this function draw for draw in the GPU tests."""
+    from oracle.beam import philox4x32_10_first as philox
+
+    assert philox(0, 0, 0, 0, 0, 0) == 0x6627E8D5
+    m = 0xFFFFFFFF
+    assert philox(m, m, m, m, m, m) == 0x408F276D
+    assert philox(0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344, 0xA4093822, 0x299F31D0) == 0xD16CFE09
+
