@@ -204,3 +204,28 @@ def test_philox_counter_stream_matches_the_published_known_answers():
     assert philox(m, m, m, m, m, m) == 0x408F276D
     assert philox(0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344, 0xA4093822, 0x299F31D0) == 0xD16CFE09
 
+
+def test_sampling_equals_hand_worked_answer(golden_dir):
+    """oracle/beam.py's top-k and top-p sampling against two rows worked by hand (closed forms in the fixture): the
+    uniform draw is fixed by the generator's published known answer, the kept tokens, their cumulative masses and the
+    drawn token follow by inspection (a four-way tie at the largest logit; a row whose first token holds 45 %)."""
+    import json
+
+    from oracle import beam as ob
+
+    fx = json.loads((golden_dir / "sampling_hand_worked.json").read_text())
+    u = ((ob.philox4x32_10_first(0, 0, 0, 0, 0, 0) >> 8) + 1) * 2.0 ** -24
+    assert abs(u - fx["u"]) < 1e-12
+    for name, row in fx["rows"].items():
+        lq = np.array(row["logits_q"], np.int8)
+        assert ob.sample_topk_row(lq, fx["s_logits"], row["topk"]["k"], 0, 0, 0, 0) == row["topk"]["token"], name
+        assert ob.sample_topp_row(lq, fx["s_logits"], row["topp"]["p"], 0, 0, 0, 0) == row["topp"]["token"], name
+        # the cumulative masses of the fixture, recomputed from the logits in the stated order
+        kept = row["topk"]["kept_in_order"]
+        w = np.exp((lq[kept].astype(np.float64) - lq[kept[0]]) * fx["s_logits"])
+        np.testing.assert_allclose(np.cumsum(w / w.sum()), row["topk"]["cumulative"], atol=1e-6)
+        nuc = row["topp"]["nucleus"]
+        wn = np.exp((lq[nuc].astype(np.float64) - lq.max()) * fx["s_logits"])
+        assert abs(wn.sum() - row["topp"]["nucleus_mass"]) < 1e-4
+        assert abs(np.exp((lq.astype(np.float64) - lq.max()) * fx["s_logits"]).sum() - row["topp"]["total_mass"]) < 1e-4
+
