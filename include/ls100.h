@@ -251,6 +251,11 @@ typedef struct {
   float amax_out;
   int8_t* out;
   int64_t ld_out;
+  /* Nonzero: *step_ptr, anc and the cache positions below *step_ptr were complete before a full stream dependency
+   * that precedes this launch (the decode step runs as one graph launch and they were written by earlier ones), so
+   * the kernel may read them before its grid dependency on the preceding kernel resolves; only qkv then waits for
+   * that kernel. Zero is always safe. */
+  int32_t history_static;
 } ls100_attn_dec_args;
 int ls100_attn_dec(ls100_ctx* ctx, const ls100_attn_dec_args* args, ls100_stream_t stream);
 

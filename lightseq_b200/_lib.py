@@ -91,7 +91,7 @@ class AttnDecArgs(C.Structure):
     _fields_ = [("qkv", C.c_void_p), ("ld_qkv", C.c_int64), ("s_kv", C.c_float), ("k_cache", C.c_void_p),
                 ("v_cache", C.c_void_p), ("anc", C.c_void_p), ("step_ptr", C.c_void_p), ("rows", C.c_int32),
                 ("heads", C.c_int32), ("max_step", C.c_int32), ("amax_out", C.c_float), ("out", C.c_void_p),
-                ("ld_out", C.c_int64)]
+                ("ld_out", C.c_int64), ("history_static", C.c_int32)]
 
 
 class AttnCrossArgs(C.Structure):

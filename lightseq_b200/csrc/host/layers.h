@@ -252,6 +252,9 @@ class QuantTransformerDecoderLayer : public Layer {
   // (the next layer's QKV projection, or the output projection after the last layer).
   void set_next_input_amax(float amax) { next_amax_ = amax; }
   float qkv_input_amax() const { return qkv_.amax_in; }
+  // The decode step is replayed as one graph launch: the step counter, the ancestry table and the cache history were
+  // written by earlier launches, so the self-attention kernel may read them ahead of its grid dependency.
+  void set_history_static(bool on) { history_static_ = on; }
 
   void forward() override {
     const int rows = batch_ * beam_;
@@ -277,6 +280,7 @@ class QuantTransformerDecoderLayer : public Layer {
       a.amax_out = out_.amax_in;
       a.out = b_->attn_q->value<int8_t>();
       a.ld_out = hidden_;
+      a.history_static = history_static_ ? 1 : 0;
       LS_RC(ls100_attn_dec(ctx_->kernels(), &a, ctx_->get_stream()));
     }
     gemm(b_->attn_q, out_, rows, LS100_OUT_F32, b_->x, Act::None, b_->x, 0.f);
@@ -341,6 +345,7 @@ class QuantTransformerDecoderLayer : public Layer {
     op.before_forward(rows);
     op.forward();
   }
+  bool history_static_ = false;
   int hidden_, heads_, ffn_;
   Act act_;
   int max_rows_, max_step_, max_enc_tokens_;
@@ -388,6 +393,7 @@ class QuantGptLayer : public Layer {
     LS_CUDA(cudaMemset(k_cache_, 0, cache));
     LS_CUDA(cudaMemset(v_cache_, 0, cache));
   }
+  void set_history_static(bool on) { history_static_ = on; }  // see QuantTransformerDecoderLayer
   void operator()(StackBuffers* bufs, const int32_t* step_ptr) {
     b_ = bufs;
     step_ptr_ = step_ptr;
@@ -436,6 +442,7 @@ class QuantGptLayer : public Layer {
       a.amax_out = out_.amax_in;
       a.out = b_->attn_q->value<int8_t>();
       a.ld_out = hidden_;
+      a.history_static = history_static_ ? 1 : 0;
       LS_RC(ls100_attn_dec(ctx_->kernels(), &a, ctx_->get_stream()));
     }
     gemm(b_->attn_q, out_, rows, LS100_OUT_F32, b_->x, Act::None, b_->x, 0.f);
@@ -466,6 +473,7 @@ class QuantGptLayer : public Layer {
     op.before_forward(rows);
     op.forward();
   }
+  bool history_static_ = false;
   int hidden_, heads_, ffn_, max_tokens_, max_bs_, max_step_;
   QLinearParams qkv_, out_, fc1_, fc2_;
   LayerNormParams ln1_, ln2_;

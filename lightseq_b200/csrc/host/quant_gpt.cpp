@@ -62,6 +62,7 @@ class QuantGpt : public EngineModel {
     LS_CUDA(cudaHostRegister(h_seq_.data(), h_seq_.size() * 4, cudaHostRegisterDefault));
     for (auto& e : ring_) LS_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     use_graph_ = getenv("LS100_NO_GRAPH") == nullptr;
+    for (auto& l : layers_) l->set_history_static(use_graph_);  // a decode step is then one graph launch
   }
   ~QuantGpt() override {
     cudaSetDevice(ctx_->device());

@@ -161,6 +161,7 @@ class QuantTransformer : public EngineModel {
     LS_CUDA(cudaHostRegister(h_counters_.data(), h_counters_.size() * 4, cudaHostRegisterDefault));
     for (auto& e : ring_) LS_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     use_graph_ = getenv("LS100_NO_GRAPH") == nullptr;
+    for (auto& l : dec_layers_) l->set_history_static(use_graph_);  // a decode step is then one graph launch
   }
 
   ~QuantTransformer() override {

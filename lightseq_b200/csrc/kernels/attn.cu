@@ -215,14 +215,35 @@ __global__ void __launch_bounds__(128, 7) attn_dec_kernel(const ls100_attn_dec_a
                                                         const float rs_out, const float score_scale) {
   extern __shared__ int slot_all[];
   pdl_launch_dependents();
-  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wid = blockIdx.x * 4 + warp;
-  if (wid >= a.rows * a.heads) return;
-  const int r = wid / a.heads, h = wid % a.heads;
+  const bool live = wid < a.rows * a.heads;
+  const int r = live ? wid / a.heads : 0, h = live ? wid % a.heads : 0;
   const int hidden = a.heads * DH;
   int* slot_s = slot_all + warp * a.max_step;
   const int g = lane >> 2, c = lane & 3;
+  // With a static history the keys and values of the first 32 positions are copied into this warp's shared-memory
+  // block while the preceding kernel is still running (cp.async: no register waits for them).
+  uint8_t* kv_s = reinterpret_cast<uint8_t*>(slot_all + 4 * a.max_step) + warp * 4096;
+  const bool pre = a.history_static != 0 && live;
+  if (pre) {
+    const int step0 = *a.step_ptr;
+    const int32_t* anc0 = a.anc ? a.anc + (long long)r * a.max_step : nullptr;
+    const int mine = (anc0 && lane < step0 && lane < a.max_step) ? anc0[lane] : r;  // slot of position `lane`
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int p = u * 8 + g;
+      const int slot = __shfl_sync(0xffffffffu, mine, p);
+      if (p < step0) {
+        const long long o = (long long)slot * a.heads * a.max_step * DH + (long long)h * a.max_step * DH + (long long)p * DH + c * 16;
+        cp_async_16(kv_s + p * 64 + c * 16, a.k_cache + o);
+        cp_async_16(kv_s + 2048 + p * 64 + c * 16, a.v_cache + o);
+      }
+    }
+    cp_async_commit();
+  }
+  pdl_wait();
+  if (!live) return;
   // Everything the first cache reads wait for is requested in one go: this row's q / k / v, the step counter, and the
   // ancestry slots of the first 128 positions (read whatever the step is: the table row has max_step entries), so that
   // one round trip to the L2 stands before the cache loads instead of three.
@@ -256,6 +277,7 @@ __global__ void __launch_bounds__(128, 7) attn_dec_kernel(const ls100_attn_dec_a
   float acc[16];
 #pragma unroll
   for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+  if (pre) cp_async_wait_all();
   for (int p0 = 0; p0 < L; p0 += 32) {
     int4 k4[4], v4[4];
 #pragma unroll
@@ -264,9 +286,14 @@ __global__ void __launch_bounds__(128, 7) attn_dec_kernel(const ls100_attn_dec_a
       k4[u] = make_int4(0, 0, 0, 0);
       v4[u] = make_int4(0, 0, 0, 0);
       if (p < step) {
-        const long long o = slot_s[p] * slot_stride + head_off + (long long)p * DH;
-        k4[u] = __ldcs(reinterpret_cast<const int4*>(a.k_cache + o));  // streamed once per step: evict first
-        v4[u] = __ldcs(reinterpret_cast<const int4*>(a.v_cache + o));
+        if (pre && p0 == 0) {  // copied ahead of the grid dependency (this lane reads back the pieces it copied)
+          k4[u] = *reinterpret_cast<const int4*>(kv_s + p * 64 + c * 16);
+          v4[u] = *reinterpret_cast<const int4*>(kv_s + 2048 + p * 64 + c * 16);
+        } else {
+          const long long o = slot_s[p] * slot_stride + head_off + (long long)p * DH;
+          k4[u] = __ldcs(reinterpret_cast<const int4*>(a.k_cache + o));  // streamed once per step: evict first
+          v4[u] = __ldcs(reinterpret_cast<const int4*>(a.v_cache + o));
+        }
       } else if (p == step) {
         k4[u] = knew;
         v4[u] = vnew;
@@ -628,11 +655,12 @@ extern "C" int ls100_attn_dec(ls100_ctx* ctx, const ls100_attn_dec_args* a, ls10
   if ((((uintptr_t)a->qkv) & 15) || (a->ld_qkv & 15) || (((uintptr_t)a->out) & 15) || (a->ld_out & 15) ||
       (((uintptr_t)a->k_cache) & 15) || (((uintptr_t)a->v_cache) & 15))
     return LS100_ERR_ALIGN;
-  if (a->max_step > 2048) return LS100_ERR_UNSUPPORTED;  // 4 * max_step * 4 bytes of shared memory per CTA
+  if (a->max_step > 2048) return LS100_ERR_UNSUPPORTED;  // 4 * max_step * 4 + 16384 bytes of shared memory per CTA (48 KB at most)
   const long long warps = (long long)a->rows * a->heads;
   const float score_scale = (a->s_kv * a->s_kv) * 0.125f;
   const float so = a->amax_out / 127.0f;
-  return ls100_launch(attn_dec_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 4 * a->max_step * sizeof(int),
+  // ancestry slots of the four warps + a 4 KB key/value block per warp
+  return ls100_launch(attn_dec_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 4 * a->max_step * sizeof(int) + 4 * 4096,
                       (cudaStream_t)stream_, *a, so, 1.0f / so, score_scale) == cudaSuccess
              ? LS100_OK
              : LS100_ERR_CUDA;
