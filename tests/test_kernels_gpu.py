@@ -441,7 +441,7 @@ def test_attn_dec_int8_cache_with_beam_ancestry():
     ok_k = np.zeros((T, 0, H), np.int8)
     ok_v = np.zeros((T, 0, H), np.int8)
     worst = 0.0
-    for step in range(5):
+    for step in range(n_steps):
         qkv = r.integers(-127, 128, size=(T, 3 * H), dtype=np.int8)
         ok_k = np.concatenate([ok_k, qkv[:, None, H:2 * H]], 1)
         ok_v = np.concatenate([ok_v, qkv[:, None, 2 * H:]], 1)
@@ -454,7 +454,8 @@ def test_attn_dec_int8_cache_with_beam_ancestry():
         danc.copy_(torch.from_numpy(anc))
         out = empty((T, H), torch.int8)
         args = L.AttnDecArgs(qkv=ptr(dq), ld_qkv=3 * H, s_kv=float(s_kv), k_cache=ptr(kc), v_cache=ptr(vc), anc=ptr(danc),
-                             step_ptr=ptr(dstep), rows=T, heads=heads, max_step=ms, amax_out=amax, out=ptr(out), ld_out=H)
+                             step_ptr=ptr(dstep), rows=T, heads=heads, max_step=ms, amax_out=amax, out=ptr(out), ld_out=H,
+                             history_static=history_static)
         L.call("ls100_attn_dec", ctx(), args)
         sync_check()
         worst = max(worst, _int8_close(out.cpu().numpy(), ref, 5e-3))
