@@ -425,10 +425,13 @@ def test_attn_self_causal_prompt_fills_the_kv_cache(B, S, heads, ms):
     assert (kc.cpu().numpy()[:, :, S:] == 77).all() and (vc.cpu().numpy()[:, :, S:] == 77).all()  # nothing past the prompt
 
 
-def test_attn_dec_int8_cache_with_beam_ancestry():
-    """Five decode steps with a random beam reshuffle after each; the oracle permutes its
-    cache physically, the kernel only follows the ancestry table."""
-    B, K, heads, ms = 3, 4, 4, 16
+@pytest.mark.parametrize("history_static,ms,n_steps", [(0, 16, 5), (1, 16, 5), (1, 48, 40)])
+def test_attn_dec_int8_cache_with_beam_ancestry(history_static, ms, n_steps):
+    """Decode steps with a random beam reshuffle after each; the oracle permutes its cache physically, the kernel only
+    follows the ancestry table. history_static: the step counter, the ancestry table and the cache history are read
+    ahead of the grid dependency (every launch here follows a synchronisation, so they are static); 40 steps take the
+    history past the 32 positions that are copied early."""
+    B, K, heads = 3, 4, 4
     H, T = heads * 64, 3 * 4
     r = rng(17)
     s_kv = F32(0.03)
